@@ -1,0 +1,343 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-matmul hot path: Q4_K / Q6_K decode GEMV at 9B shapes, batch 1.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
+
+Workload ("ffn9b_b1"): the feed-forward projections of a 9B-shaped decoder, per layer
+  ffn_gate Q4_K 12288x4096, ffn_up Q4_K 12288x4096, ffn_down Q6_K 4096x12288, batch 1,
+on seeded synthetic GGUF superblocks (cogni_ml_b200.synth) that stand in for the model file the
+reference measures on.  One step = one pass over L layers (3L GEMV launches); the L layers are
+distinct device buffers totalling far more than L2, so every launch streams its weights from HBM.
+
+Printed JSON (one line, rank 0):
+  value     weight GB/s with inputs resident in HBM (CUDA events on the launching stream)
+  e2e       the same pass through the resident runner with HOST activations: pinned H2D of the
+            step's inputs, the GEMVs, D2H of the step's result, every step
+  roofline  the dominant kernel (Q4_K GEMV) against the measured copy bandwidth
+  cpu_baseline  the CPU restatement of the reference's QuantMatmul timed on this host
+
+N > 1: each rank holds the row shard [rank*N_out/G, (rank+1)*N_out/G) of every matrix of a model
+G times wider per GPU (weak scaling: per-GPU bytes fixed), followed by the all-gather of the
+row-sharded outputs over NCCL, as the multi-GPU split of the path prescribes.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+HIDDEN, FFN = 4096, 12288
+Q4_K, Q6_K = 12, 14
+Q4K_BYTES = FFN * (HIDDEN // 256) * 144      # 28,311,552
+Q6K_BYTES = HIDDEN * (FFN // 256) * 210      # 41,287,680
+
+
+def algorithmic_bytes(weight_bytes: int, in_dim: int, out_dim: int, batch: int) -> int:
+    """Weights once + activations in + outputs out, per GEMV launch."""
+    return weight_bytes + batch * in_dim * 4 + batch * out_dim * 4
+
+
+def measured_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.25)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_baseline(seconds: float, threads: int):
+    """Times the C restatement of QuantMatmul.matmul_add on one layer's three projections."""
+    from cogni_ml_b200 import synth
+    from oracle import loader as oracle
+    gate = synth.make_weight(Q4_K, FFN, HIDDEN, seed=0, tensor_id=1)
+    down = synth.make_weight(Q6_K, HIDDEN, FFN, seed=0, tensor_id=3)
+    xh = synth.make_activation(1, HIDDEN, seed=0, tensor_id=10)
+    xf = synth.make_activation(1, FFN, seed=0, tensor_id=11)
+    zf, zh = np.zeros(FFN, np.float32), np.zeros(HIDDEN, np.float32)
+    oracle.matmul_add(xh, 1, HIDDEN, gate, Q4_K, FFN, zf, threads=threads)  # warm
+    t0, passes = time.perf_counter(), 0
+    while True:
+        oracle.matmul_add(xh, 1, HIDDEN, gate, Q4_K, FFN, zf, threads=threads)   # ffn_gate
+        oracle.matmul_add(xh, 1, HIDDEN, gate, Q4_K, FFN, zf, threads=threads)   # ffn_up
+        oracle.matmul_add(xf, 1, FFN, down, Q6_K, HIDDEN, zh, threads=threads)   # ffn_down
+        passes += 1
+        dt = time.perf_counter() - t0
+        if dt >= seconds:
+            break
+    layer_bytes = 2 * Q4K_BYTES + Q6K_BYTES
+    return {"value": passes * layer_bytes / dt / 1e9, "unit": "GB/s", "cores": threads,
+            "kind": "port",
+            "sample": f"{passes} passes of one layer (ffn_gate+ffn_up Q4_K 12288x4096, ffn_down "
+                      f"Q6_K 4096x12288, batch 1) in {dt:.1f} s; C restatement of "
+                      "QuantMatmul.matmul_add, f64 accumulate, OpenMP over output rows"}
+
+
+def run_reference(args):
+    """--impl reference: the reference's CPU QuantMatmul for the same workload.  The reference is
+    Crystal and cannot be compiled in this image, so its line-for-line C restatement (oracle/) is
+    what runs, on all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import loader as oracle
+    threads = oracle.max_threads()
+    per_step = max(1.0, min(8.0, 120.0 / max(1, args.steps + args.warmup)))
+    for _ in range(args.warmup):
+        cpu_baseline(per_step / 4, threads)
+    vals = [cpu_baseline(per_step, threads) for _ in range(args.steps)]
+    value = float(np.mean([v["value"] for v in vals]))
+    layer_bytes = 2 * Q4K_BYTES + Q6K_BYTES
+    base = dict(vals[-1], value=value)
+    print(json.dumps({
+        "impl": "reference", "metric": "q4k_q6k_gemv_weight_gbs", "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": layer_bytes / value / 1e6, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": "ffn9b_b1", "batch": 1, "sample": "one layer per pass, bounded time",
+                   "note": "reference CPU QuantMatmul restated in C (Crystal toolchain absent)"},
+        "cpu_baseline": base,
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from cogni_ml_b200 import DeviceQuantWeight, QuantWeight, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    L, B = args.layers, args.batch
+    # One layer's bytes are generated on the host (rank-keyed seed), then replicated into L distinct
+    # device buffers: timing depends on addresses, not on contents.
+    gate_h = synth.make_weight(Q4_K, FFN, HIDDEN, seed=rank, tensor_id=1)
+    up_h = synth.make_weight(Q4_K, FFN, HIDDEN, seed=rank, tensor_id=2)
+    down_h = synth.make_weight(Q6_K, HIDDEN, FFN, seed=rank, tensor_id=3)
+
+    def ring(raw, qtype, out_dim, in_dim):
+        first = DeviceQuantWeight.upload(QuantWeight(raw, qtype, out_dim, in_dim), dev)
+        return [first] + [DeviceQuantWeight(first.raw.clone(), qtype, out_dim, in_dim)
+                          for _ in range(L - 1)]
+
+    gates, ups, downs = (ring(gate_h, Q4_K, FFN, HIDDEN), ring(up_h, Q4_K, FFN, HIDDEN),
+                         ring(down_h, Q6_K, HIDDEN, FFN))
+    xh_host = torch.from_numpy(synth.make_activation(B, HIDDEN, seed=0, tensor_id=10)).pin_memory()
+    xf_host = torch.from_numpy(synth.make_activation(B, FFN, seed=0, tensor_id=11)).pin_memory()
+    xh, xf = xh_host.to(dev), xf_host.to(dev)
+    # shard outputs land in slot `rank` of a [world, B, rows] gather buffer
+    y_gate = torch.empty(world, B, FFN, dtype=torch.float32, device=dev)
+    y_up = torch.empty(world, B, FFN, dtype=torch.float32, device=dev)
+    y_down = torch.empty(world, B, HIDDEN, dtype=torch.float32, device=dev)
+    out_host = [torch.empty(B, n, dtype=torch.float32).pin_memory() for n in (FFN, FFN, HIDDEN)]
+
+    def gather(buf):
+        if world > 1:
+            dist.all_gather_into_tensor(buf.view(-1), buf[rank].reshape(-1))
+
+    def step(marks=None):
+        for l in range(L):
+            gates[l].gemv(xh, out=y_gate[rank])
+            ups[l].gemv(xh, out=y_up[rank])
+        if marks is not None:
+            marks[1].record()
+        for l in range(L):
+            downs[l].gemv(xf, out=y_down[rank])
+        if marks is not None:
+            marks[2].record()
+        gather(y_gate)
+        gather(y_up)
+        gather(y_down)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    sync_all()
+    marks = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    with ClockSampler(local_rank) as clocks:
+        for k in range(args.steps):
+            marks[k][0].record()
+            step(marks[k])
+            marks[k][3].record()
+        sync_all()
+    total_ms = marks[0][0].elapsed_time(marks[-1][3])
+    q4_ms = sum(m[0].elapsed_time(m[1]) for m in marks)
+    q6_ms = sum(m[1].elapsed_time(m[2]) for m in marks)
+    if world > 1:
+        t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    step_bytes = L * (2 * Q4K_BYTES + Q6K_BYTES)
+    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # end to end through the resident path with host activations
+    def e2e_step():
+        xh.copy_(xh_host, non_blocking=True)
+        xf.copy_(xf_host, non_blocking=True)
+        step()
+        out_host[0].copy_(y_gate[rank], non_blocking=True)
+        out_host[1].copy_(y_up[rank], non_blocking=True)
+        out_host[2].copy_(y_down[rank], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(args.warmup):
+        e2e_step()
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    sync_all()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = world * step_bytes / (e2e_ms / args.steps * 1e-3) / 1e9
+
+    if rank == 0:
+        peak, peak_src = measured_peak()
+        q4_launch_ms = q4_ms / (args.steps * 2 * L)
+        q6_launch_ms = q6_ms / (args.steps * L)
+        q4_alg = algorithmic_bytes(Q4K_BYTES, HIDDEN, FFN, B)
+        q6_alg = algorithmic_bytes(Q6K_BYTES, FFN, HIDDEN, B)
+        q4_ach = q4_alg / (q4_launch_ms * 1e-3) / 1e9
+        q6_ach = q6_alg / (q6_launch_ms * 1e-3) / 1e9
+        line = {
+            "metric": "q4k_q6k_gemv_weight_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": "ffn9b_b1", "layers": L, "batch": B,
+                       "per_layer": "ffn_gate+ffn_up Q4_K 12288x4096, ffn_down Q6_K 4096x12288",
+                       "weight_bytes_per_step_per_gpu": step_bytes,
+                       "l2": f"{L} distinct weight sets ({step_bytes / 1e9:.2f} GB) >> 126 MB L2",
+                       "parallelism": "single GPU" if world == 1 else
+                       f"row-sharded x{world}, weak (per-GPU rows fixed), all-gather of outputs"},
+            "e2e": {"value": e2e_value, "unit": "GB/s",
+                    "h2d_bytes_per_step": B * (HIDDEN + FFN) * 4,
+                    "d2h_bytes_per_step": B * (2 * FFN + HIDDEN) * 4},
+            "gpu_launches": args.steps * 3 * L,
+            "roofline": {"bound": "hbm", "kernel": "Q4_K GEMV 12288x4096 b1", "achieved": q4_ach,
+                         "peak": peak, "unit": "GB/s", "frac": q4_ach / peak, "traffic": None,
+                         "peak_source": f"of {peak_src}", "us_per_launch": q4_launch_ms * 1e3,
+                         "algorithmic_bytes": q4_alg, "frac_of_nominal_8tbs": q4_ach / 8000.0},
+            "roofline_q6k": {"bound": "hbm", "kernel": "Q6_K GEMV 4096x12288 b1",
+                             "achieved": q6_ach, "peak": peak, "unit": "GB/s",
+                             "frac": q6_ach / peak, "us_per_launch": q6_launch_ms * 1e3,
+                             "algorithmic_bytes": q6_alg, "frac_of_nominal_8tbs": q6_ach / 8000.0},
+            "clocks": clocks.summary(),
+        }
+        if world == 1 and not args.no_cpu:
+            from oracle import loader as oracle
+            line["cpu_baseline"] = cpu_baseline(args.cpu_seconds, oracle.max_threads())
+            line["cpu_baseline_1thread"] = cpu_baseline(min(args.cpu_seconds, 5.0), 1)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

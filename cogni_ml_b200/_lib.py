@@ -1,0 +1,59 @@
+"""ctypes binding of libcogni_qmm.so — one Python function per symbol in include/cogni_qmm.h.
+
+There is no fallback: if the shared library is missing or a symbol cannot be resolved the
+import fails, and every compute call needs a CUDA device.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libcogni_qmm.so"
+
+_vp, _i, _i64, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_size_t
+
+# symbol -> (restype, argtypes); kept in the order of include/cogni_qmm.h
+SIGNATURES = {
+    "cogni_qmm_abi_version": (_i, []),
+    "cogni_qmm_status_string": (C.c_char_p, [_i]),
+    "cogni_qmm_block_bytes": (_i, [_i]),
+    "cogni_qmm_block_elements": (_i, [_i]),
+    "cogni_qmm_row_bytes": (_i64, [_i, _i]),
+    "cogni_qmm_tensor_bytes": (_i64, [_i, _i, _i]),
+    "cogni_qmm_dequantize": (_i, [_i, _vp, _i64, _vp, _vp]),
+    "cogni_qmm_gemv": (_i, [_i, _vp, _vp, _vp, _i64, _vp, _i, _i, _i, _vp]),
+    "cogni_qmm_gemv_top1_scratch_bytes": (_sz, [_i, _i]),
+    "cogni_qmm_gemv_top1": (_i, [_i, _vp, _vp, _i, _i, _i, C.c_int32, _vp, _sz, _vp, _vp, _vp, _vp]),
+    "cogni_qmm_top1_unpack_keys": (_i, [_vp, _i, _vp, _vp, _vp]),
+    "cogni_qmm_gemm_bf16": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "cogni_qmm_matmul_add_host": (_i, [_vp, _i, _i, _vp, _i64, _i, _i, _vp, _vp]),
+}
+
+
+class CogniQmmError(RuntimeError):
+    """Raised for any non-zero status, like ML::CUDA.check! in the reference's driver binding."""
+
+    def __init__(self, what: str, status: int, text: str):
+        super().__init__(f"{what} failed with status {status} ({text})")
+        self.status = status
+
+
+def load() -> C.CDLL:
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m cogni_ml_b200.build` "
+            "(there is no CPU or PyTorch fallback for this engine)")
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here means the header and the library disagree
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = load()
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        raise CogniQmmError(what, status, lib.cogni_qmm_status_string(status).decode())

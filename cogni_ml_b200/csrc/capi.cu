@@ -1,0 +1,156 @@
+// extern "C" entry points of libcogni_qmm.so: argument checks, kernel selection, and the
+// one-shot host-buffer form.  Declarations and per-function contracts: include/cogni_qmm.h.
+#include <cstdio>
+#include <cstring>
+
+#include "qmm_common.cuh"
+
+using namespace cogni;
+
+namespace {
+
+bool supported(int type) { return block_bytes(type) > 0; }
+
+int check_gemv_args(int type, const void *w, const void *x, const void *y, int in_dim, int out_dim,
+                    int batch) {
+  if (!supported(type)) return COGNI_QMM_ERR_TYPE;
+  if (!w || !x || !y || in_dim <= 0 || out_dim <= 0 || batch <= 0) return COGNI_QMM_ERR_ARG;
+  if (in_dim % block_elems(type) != 0) return COGNI_QMM_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x) & 3) ||
+      (reinterpret_cast<uintptr_t>(y) & 3))
+    return COGNI_QMM_ERR_ALIGN;
+  return COGNI_QMM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int cogni_qmm_abi_version(void) { return COGNI_QMM_ABI_VERSION; }
+
+const char *cogni_qmm_status_string(int status) {
+  switch (status) {
+    case COGNI_QMM_OK: return "ok";
+    case COGNI_QMM_ERR_TYPE: return "unsupported tensor type";
+    case COGNI_QMM_ERR_ARG: return "invalid argument";
+    case COGNI_QMM_ERR_ALIGN: return "misaligned device pointer";
+    case COGNI_QMM_ERR_SCRATCH: return "scratch buffer too small";
+    case COGNI_QMM_ERR_DEVICE: return "device is not compute capability 10.x";
+    case COGNI_QMM_ERR_LIMIT: return "size beyond the entry point's fixed maximum";
+    default: break;
+  }
+  if (status > 0 && status < 1000) return cudaGetErrorString(static_cast<cudaError_t>(status));
+  return "unknown status";
+}
+
+int cogni_qmm_block_bytes(int type) { return block_bytes(type); }
+int cogni_qmm_block_elements(int type) { return block_elems(type); }
+
+int64_t cogni_qmm_row_bytes(int type, int in_dim) {
+  int be = block_elems(type);
+  if (be < 0 || in_dim <= 0 || in_dim % be != 0) return -1;
+  return (int64_t)(in_dim / be) * block_bytes(type);
+}
+
+int64_t cogni_qmm_tensor_bytes(int type, int out_dim, int in_dim) {
+  int64_t rb = cogni_qmm_row_bytes(type, in_dim);
+  if (rb < 0 || out_dim <= 0) return -1;
+  return rb * out_dim;
+}
+
+int cogni_qmm_dequantize(int type, const void *d_w, int64_t n_elements, float *d_out,
+                         void *stream) {
+  if (!supported(type)) return COGNI_QMM_ERR_TYPE;
+  if (!d_w || !d_out || n_elements < 0 || n_elements % block_elems(type) != 0)
+    return COGNI_QMM_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(d_w) & 1) || (reinterpret_cast<uintptr_t>(d_out) & 3))
+    return COGNI_QMM_ERR_ALIGN;
+  return launch_dequantize(type, d_w, n_elements, d_out, static_cast<cudaStream_t>(stream));
+}
+
+int cogni_qmm_gemv(int type, const void *d_w, const float *d_x, const float *d_addend,
+                   int64_t addend_stride, float *d_y, int in_dim, int out_dim, int batch,
+                   void *stream) {
+  int st = check_gemv_args(type, d_w, d_x, d_y, in_dim, out_dim, batch);
+  if (st) return st;
+  if (d_addend && addend_stride != 0 && addend_stride != out_dim) return COGNI_QMM_ERR_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  for (int b0 = 0; b0 < batch; b0 += 16) {
+    int nb = batch - b0 < 16 ? batch - b0 : 16;
+    const float *add = d_addend ? d_addend + (int64_t)b0 * addend_stride : nullptr;
+    st = launch_gemv(type, d_w, d_x + (int64_t)b0 * in_dim, add, addend_stride,
+                     d_y + (int64_t)b0 * out_dim, in_dim, out_dim, nb, s);
+    if (st) return st;
+  }
+  return COGNI_QMM_OK;
+}
+
+size_t cogni_qmm_gemv_top1_scratch_bytes(int out_dim, int batch) {
+  if (out_dim <= 0 || batch <= 0) return 0;
+  return top1_scratch_bytes(out_dim, batch);
+}
+
+int cogni_qmm_gemv_top1(int type, const void *d_w, const float *d_x, int in_dim, int out_dim,
+                        int batch, int32_t index_base, void *d_scratch, size_t scratch_bytes,
+                        int32_t *d_top_index, float *d_top_value, int64_t *d_top_key,
+                        void *stream) {
+  int st = check_gemv_args(type, d_w, d_x, d_top_value, in_dim, out_dim, batch);
+  if (st) return st;
+  if (!d_top_index || !d_scratch || index_base < 0) return COGNI_QMM_ERR_ARG;
+  if (reinterpret_cast<uintptr_t>(d_scratch) & 7) return COGNI_QMM_ERR_ALIGN;
+  if (scratch_bytes < top1_scratch_bytes(out_dim, batch)) return COGNI_QMM_ERR_SCRATCH;
+  return launch_gemv_top1(type, d_w, d_x, in_dim, out_dim, batch, index_base, d_scratch,
+                          d_top_index, d_top_value, reinterpret_cast<long long *>(d_top_key),
+                          static_cast<cudaStream_t>(stream));
+}
+
+int cogni_qmm_top1_unpack_keys(const int64_t *d_keys, int batch, int32_t *d_top_index,
+                               float *d_top_value, void *stream) {
+  if (!d_keys || !d_top_index || !d_top_value || batch <= 0) return COGNI_QMM_ERR_ARG;
+  return launch_top1_unpack(reinterpret_cast<const long long *>(d_keys), batch, d_top_index,
+                            d_top_value, static_cast<cudaStream_t>(stream));
+}
+
+int cogni_qmm_gemm_bf16(int type, const void *d_w, const void *d_x_bf16, void *d_y, int out_type,
+                        int m_rows, int n_out, int k_in, void *stream) {
+  if (type != kQ4_K && type != kQ5_K && type != kQ6_K) return COGNI_QMM_ERR_TYPE;
+  if (!d_w || !d_x_bf16 || !d_y || m_rows <= 0 || n_out <= 0 || k_in <= 0 || k_in % 256 != 0)
+    return COGNI_QMM_ERR_ARG;
+  if (out_type != COGNI_QMM_OUT_F32 && out_type != COGNI_QMM_OUT_BF16) return COGNI_QMM_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(d_w) & 15) || (reinterpret_cast<uintptr_t>(d_x_bf16) & 15) ||
+      (reinterpret_cast<uintptr_t>(d_y) & 15))
+    return COGNI_QMM_ERR_ALIGN;
+  return launch_gemm_prefill(type, d_w, d_x_bf16, d_y, out_type, m_rows, n_out, k_in,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int cogni_qmm_matmul_add_host(const float *x, int rows, int in_dim, const void *w_raw,
+                              int64_t w_bytes, int type, int out_dim, const float *bias, float *y) {
+  if (!supported(type)) return COGNI_QMM_ERR_TYPE;
+  if (!x || !w_raw || !y || rows <= 0 || in_dim <= 0 || out_dim <= 0) return COGNI_QMM_ERR_ARG;
+  int64_t need = cogni_qmm_tensor_bytes(type, out_dim, in_dim);
+  if (need < 0 || w_bytes < need) return COGNI_QMM_ERR_ARG;
+  void *d_w = nullptr;
+  float *d_x = nullptr, *d_b = nullptr, *d_y = nullptr;
+  size_t xb = (size_t)rows * in_dim * 4, yb = (size_t)rows * out_dim * 4;
+  int st = COGNI_QMM_OK;
+  auto step = [&](cudaError_t e) {
+    if (st == COGNI_QMM_OK && e != cudaSuccess) st = (int)e;
+    return st == COGNI_QMM_OK;
+  };
+  if (step(cudaMalloc(&d_w, (size_t)need)) && step(cudaMalloc(&d_x, xb)) &&
+      step(cudaMalloc(&d_y, yb)) && (!bias || step(cudaMalloc(&d_b, (size_t)out_dim * 4))) &&
+      step(cudaMemcpy(d_w, w_raw, (size_t)need, cudaMemcpyHostToDevice)) &&
+      step(cudaMemcpy(d_x, x, xb, cudaMemcpyHostToDevice)) &&
+      (!bias || step(cudaMemcpy(d_b, bias, (size_t)out_dim * 4, cudaMemcpyHostToDevice)))) {
+    st = cogni_qmm_gemv(type, d_w, d_x, d_b, 0, d_y, in_dim, out_dim, rows, nullptr);
+    if (st == COGNI_QMM_OK) step(cudaMemcpy(y, d_y, yb, cudaMemcpyDeviceToHost));
+  }
+  cudaFree(d_w);
+  cudaFree(d_x);
+  cudaFree(d_y);
+  cudaFree(d_b);
+  return st;
+}
+
+}  // extern "C"

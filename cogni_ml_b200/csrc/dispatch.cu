@@ -1,0 +1,41 @@
+// Kernel selection for the C-ABI entry points.
+#include "qmm_common.cuh"
+
+namespace cogni {
+
+namespace {
+__global__ void top1_unpack_kernel(const long long *keys, int batch, int32_t *idx, float *val) {
+  int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= batch) return;
+  float v;
+  uint32_t i;
+  top1_unkey(keys[b], v, i);
+  idx[b] = (int32_t)i;
+  val[b] = v;
+}
+}  // namespace
+
+int launch_gemv(int type, const void *d_w, const float *d_x, const float *d_addend,
+                int64_t addend_stride, float *d_y, int in_dim, int out_dim, int batch,
+                cudaStream_t s) {
+  return launch_gemv_rowwarp(type, d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, s);
+}
+
+int launch_gemv_top1(int type, const void *d_w, const float *d_x, int in_dim, int out_dim,
+                     int batch, int32_t index_base, void *d_scratch, int32_t *d_idx, float *d_val,
+                     long long *d_key, cudaStream_t s) {
+  return launch_gemv_top1_rowwarp(type, d_w, d_x, in_dim, out_dim, batch, index_base, d_scratch,
+                                  d_idx, d_val, d_key, s);
+}
+
+int launch_top1_unpack(const long long *d_keys, int batch, int32_t *d_idx, float *d_val,
+                       cudaStream_t s) {
+  top1_unpack_kernel<<<(batch + 127) / 128, 128, 0, s>>>(d_keys, batch, d_idx, d_val);
+  return (int)cudaGetLastError();
+}
+
+int launch_gemm_prefill(int, const void *, const void *, void *, int, int, int, int, cudaStream_t) {
+  return COGNI_QMM_ERR_TYPE;
+}
+
+}  // namespace cogni

@@ -1,0 +1,153 @@
+/*
+ * cogni_qmm — C ABI of the B200 (sm_100a) quantized-matmul engine for GGUF weights.
+ *
+ * This is the boundary a host runtime binds through its FFI.  Every entry point takes
+ * plain pointers and sizes; device pointers are ordinary CUDA device addresses (the same
+ * 64-bit value the Driver API calls CUdeviceptr), `stream` is a CUstream / cudaStream_t
+ * (NULL = the default stream).  Calls run in whatever CUDA context is current on the
+ * calling thread (a context made with cuCtxCreate or the primary context both work).
+ *
+ * Return value: 0 on success.  Values 1..999 are CUDA error codes (cudaError_t, numerically
+ * equal to the Driver API's CUresult for the errors a launch can raise), values >= 1000 are
+ * the COGNI_QMM_ERR_* codes below.  cogni_qmm_status_string() names either kind.
+ * The reference's convention is "every driver call returns Int32, non-zero raises"
+ * (src/ml/cuda/driver.cr:57-59); a binding wraps each call in the same check!.
+ *
+ * Weights are always the raw GGUF block bytes, row-major [out_dim rows][in_dim/block
+ * blocks], exactly as GGUFFile#read_tensor_raw returns them (src/ml/gguf/reader.cr:169-194);
+ * nothing is repacked on the host.
+ */
+#ifndef COGNI_QMM_H
+#define COGNI_QMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define COGNI_QMM_ABI_VERSION 1
+
+/* ggml tensor type ids, identical to ML::GGUF::TensorType (src/ml/gguf/reader.cr:36-50). */
+#define COGNI_QMM_TYPE_Q8_0 8
+#define COGNI_QMM_TYPE_Q4_K 12
+#define COGNI_QMM_TYPE_Q5_K 13
+#define COGNI_QMM_TYPE_Q6_K 14
+
+#define COGNI_QMM_OK 0
+#define COGNI_QMM_ERR_TYPE 1001      /* tensor type not supported by this engine           */
+#define COGNI_QMM_ERR_ARG 1002       /* null pointer, non-positive size, in_dim not a block multiple */
+#define COGNI_QMM_ERR_ALIGN 1003     /* a device pointer is not aligned as documented      */
+#define COGNI_QMM_ERR_SCRATCH 1004   /* scratch buffer too small                           */
+#define COGNI_QMM_ERR_DEVICE 1005    /* device is not compute capability 10.x             */
+#define COGNI_QMM_ERR_LIMIT 1006     /* size beyond a documented fixed maximum             */
+
+/* Output element types of the prefill GEMM. */
+#define COGNI_QMM_OUT_F32 0
+#define COGNI_QMM_OUT_BF16 1
+
+/* ABI version of the loaded library (== COGNI_QMM_ABI_VERSION it was built with). */
+int cogni_qmm_abi_version(void);
+
+/* Human-readable name of a status returned by any entry point. Never NULL. */
+const char *cogni_qmm_status_string(int status);
+
+/* Block geometry: TensorType#block_bytes / #block_elements (reader.cr:53-80).
+ * Return -1 for a type this engine does not handle. */
+int cogni_qmm_block_bytes(int type);
+int cogni_qmm_block_elements(int type);
+
+/* Bytes of one weight row / of a whole [out_dim, in_dim] tensor: the row_bytes the
+ * reference computes in every matmul_add_* (quant_matmul.cr:46-48) and
+ * TensorInfo#data_bytes (reader.cr:119-127). -1 on a bad type or in_dim. */
+int64_t cogni_qmm_row_bytes(int type, int in_dim);
+int64_t cogni_qmm_tensor_bytes(int type, int out_dim, int in_dim);
+
+/*
+ * Bulk dequantisation on the device: replaces Dequant.dequantize for Q8_0 / Q4_K / Q5_K /
+ * Q6_K (src/ml/gguf/dequant.cr:20-32, 53-71, 106-142, 146-193, 197-236).  All arithmetic
+ * is f32 in the reference's operation order, so the result is bit-identical to the CPU
+ * dequantiser.  d_w: raw blocks (2-byte aligned is enough), d_out: n_elements floats.
+ * n_elements must be a multiple of the block size.
+ */
+int cogni_qmm_dequantize(int type, const void *d_w, int64_t n_elements, float *d_out,
+                         void *stream);
+
+/*
+ * Decode GEMV, batch 1..16 rows of x against one quantized weight matrix:
+ *     y[b, o] = addend[b*addend_stride + o] + sum_j x[b, j] * dequant(W[o, j])
+ * Replaces QuantMatmul.matmul_add on the device (src/ml/gguf/quant_matmul.cr:20-36, with
+ * bias as the accumulator start) and the reference's GEMV kernels
+ * q4_k_gemv_warp4_f32 / _add_ / _batched / _tbatch4 and their Q5_K / Q6_K / Q8_0 twins
+ * (src/ml/cuda/kernels/q4k_gemv_probe.ptx:219,437,1362,1584; q5k_gemv_probe.ptx:5,237,589;
+ * q6k_gemv_probe.ptx:193,398,609,977,1582; bin/cuda_q8_gemv_probe.cr:126).
+ *   d_w       raw GGUF blocks, [out_dim][in_dim], 16-byte aligned base
+ *   d_x       f32 [batch, in_dim] row-major
+ *   d_addend  NULL, or f32: addend_stride == 0 -> a bias of out_dim entries added to every
+ *             batch row (matmul_add's bias); addend_stride == out_dim -> a residual
+ *             [batch, out_dim] (the *_gemv_add_* kernels). May alias d_y.
+ *   d_y       f32 [batch, out_dim]
+ * The weight bytes are streamed from HBM once per call whatever the batch.  Accumulation is
+ * fp32.  batch > 16 is processed in groups of 16.
+ */
+int cogni_qmm_gemv(int type, const void *d_w, const float *d_x, const float *d_addend,
+                   int64_t addend_stride, float *d_y, int in_dim, int out_dim, int batch,
+                   void *stream);
+
+/*
+ * Fused lm_head: GEMV over `out_dim` vocabulary rows plus top-1 per batch row, without
+ * writing the logits.  Replaces q6_k_gemv_top1_partial_f32 + output_top1_values_reduce_probe
+ * (q6k_gemv_probe.ptx:1331; src/ml/cuda/qwen_output_head_runner.cr:530-624, 884-947).
+ * Tie rule: highest value, lowest index (src/ml/gguf/qwen35_cpu.cr:2052-2055).
+ *   index_base   added to the local row number: a vocab shard passes its first row here
+ *   d_scratch    device scratch of at least cogni_qmm_gemv_top1_scratch_bytes() bytes,
+ *                8-byte aligned, zero-filled once by the caller before its first use; the
+ *                kernel leaves it ready for the next call.  Calls that share one scratch
+ *                buffer must be ordered on the device (same stream).
+ *   d_top_index  int32 [batch]   global index of the maximum
+ *   d_top_value  f32   [batch]   its value
+ *   d_top_key    NULL or int64 [batch]: (orderable(value) << 32) | (0xFFFFFFFF - index);
+ *                a signed 64-bit MAX over shards' keys yields the global winner under the
+ *                same tie rule (used for the cross-GPU reduction).
+ */
+size_t cogni_qmm_gemv_top1_scratch_bytes(int out_dim, int batch);
+int cogni_qmm_gemv_top1(int type, const void *d_w, const float *d_x, int in_dim, int out_dim,
+                        int batch, int32_t index_base, void *d_scratch, size_t scratch_bytes,
+                        int32_t *d_top_index, float *d_top_value, int64_t *d_top_key,
+                        void *stream);
+
+/* Decode keys produced by cogni_qmm_gemv_top1 (after a MAX reduction across shards):
+ * d_keys int64 [batch] -> d_top_index int32 [batch], d_top_value f32 [batch]. */
+int cogni_qmm_top1_unpack_keys(const int64_t *d_keys, int batch, int32_t *d_top_index,
+                               float *d_top_value, void *stream);
+
+/*
+ * Chunked-prefill GEMM with dequantisation fused into the tile loop:
+ *     y[m, n] = sum_k bf16(x[m, k]) * bf16(dequant(W[n, k]))      (fp32 accumulation)
+ * The tensor-core replacement for the reference's batched matmul route
+ * (Qwen35Metal.matmul with batch > GEMM_BATCH_THRESHOLD, src/ml/gguf/qwen35_metal.cr:75,
+ * 10597-10636, 11404-11449; operands rounded to 16-bit, src/ml/gguf/kernels/gemm_q4k.metal:773-776).
+ *   d_w      raw GGUF blocks [n_out][k_in], 16-byte aligned
+ *   d_x      bf16 [m_rows, k_in] row-major, 16-byte aligned
+ *   d_y      [m_rows, n_out] row-major, f32 or bf16 per out_type
+ * k_in must be a multiple of 256.
+ */
+int cogni_qmm_gemm_bf16(int type, const void *d_w, const void *d_x_bf16, void *d_y,
+                        int out_type, int m_rows, int n_out, int k_in, void *stream);
+
+/*
+ * One-shot host-buffer form with the exact call surface of
+ * ML::GGUF::QuantMatmul.matmul_add(x, rows, in_dim, w_raw, w_type, out_dim, bias)
+ * (src/ml/gguf/quant_matmul.cr:20-24): uploads, runs the device GEMV, reads back.
+ * All pointers are HOST pointers; y receives rows*out_dim floats.  Intended for parity
+ * checks and ad-hoc tensors; resident weights use the device entry points above.
+ */
+int cogni_qmm_matmul_add_host(const float *x, int rows, int in_dim, const void *w_raw,
+                              int64_t w_bytes, int type, int out_dim, const float *bias,
+                              float *y);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* COGNI_QMM_H */
