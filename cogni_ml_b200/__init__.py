@@ -2,7 +2,7 @@
 
 The product is the C-ABI shared library built from csrc/ (see include/cogni_qmm.h); this package
 is the host-side mirror of the reference's call surface over that ABI.  Importing it loads the
-library and fails if it has not been built (`python -m cogni_ml_b200.build`).
+library and fails if it has not been built (`python cogni_ml_b200/build.py`).
 """
 from . import synth  # noqa: F401  (numpy only)
 from ._lib import CogniQmmError, lib  # noqa: F401

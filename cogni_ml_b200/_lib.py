@@ -41,7 +41,7 @@ class CogniQmmError(RuntimeError):
 def load() -> C.CDLL:
     if not LIB_PATH.exists():
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m cogni_ml_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python cogni_ml_b200/build.py` "
             "(there is no CPU or PyTorch fallback for this engine)")
     lib = C.CDLL(str(LIB_PATH))
     for name, (res, args) in SIGNATURES.items():

@@ -1,7 +1,7 @@
 """Builds libcogni_qmm.so (CUDA kernels + C ABI) in-tree with nvcc for sm_100a.
 
-    python -m cogni_ml_b200.build          # build if sources are newer than the library
-    python -m cogni_ml_b200.build --force
+    python cogni_ml_b200/build.py          # build if sources are newer than the library
+    python cogni_ml_b200/build.py --force
 
 nvcc cross-compiles without a GPU, so this runs on a CPU-only build machine; the resulting
 shared library sits beside this file and is what `cogni_ml_b200._lib` loads.
