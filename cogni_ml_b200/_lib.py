@@ -24,6 +24,8 @@ SIGNATURES = {
     "cogni_qmm_gemv": (_i, [_i, _vp, _vp, _vp, _i64, _vp, _i, _i, _i, _vp]),
     "cogni_qmm_gemv_top1_scratch_bytes": (_sz, [_i, _i]),
     "cogni_qmm_gemv_top1": (_i, [_i, _vp, _vp, _i, _i, _i, C.c_int32, _vp, _sz, _vp, _vp, _vp, _vp]),
+    "cogni_qmm_gemv_top1_noalloc_max_scratch": (_sz, []),
+    "cogni_qmm_gemv_top1_noalloc": (_i, [_i, _vp, _vp, _i, _i, _i, C.c_int32, _vp, _vp, _vp, _vp]),
     "cogni_qmm_top1_unpack_keys": (_i, [_vp, _i, _vp, _vp, _vp]),
     "cogni_qmm_gemm_bf16": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "cogni_qmm_matmul_add_host": (_i, [_vp, _i, _i, _vp, _i64, _i, _i, _vp, _vp]),

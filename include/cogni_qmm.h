@@ -117,6 +117,32 @@ int cogni_qmm_gemv_top1(int type, const void *d_w, const float *d_x, int in_dim,
                         int32_t *d_top_index, float *d_top_value, int64_t *d_top_key,
                         void *stream);
 
+/*
+ * cogni_qmm_gemv_top1 for callers that cannot allocate device memory.  (No counterpart in the
+ * reference: its output-head runner allocates its own partial buffers with cuMemAlloc.)
+ *
+ * A host that gave all of HBM to its own arena at start-up, a plugin whose host only lends it
+ * input and output buffers, or a binding that cannot create memory handles at this point has no
+ * scratch buffer to pass to cogni_qmm_gemv_top1.  This entry point computes exactly the same
+ * result with the scratch kept in a fixed array inside the library; it calls no cudaMalloc,
+ * cudaFree or any other allocating routine.  The caller still passes the weights, x and the
+ * outputs, with the same meaning and alignment as for cogni_qmm_gemv_top1.
+ *
+ *   - The array is cogni_qmm_gemv_top1_noalloc_max_scratch() bytes (1 MiB) and every GPU that
+ *     loads the library holds it until the process exits, used or not.
+ *   - Shapes whose scratch need (cogni_qmm_gemv_top1_scratch_bytes) exceeds that size are
+ *     rejected with COGNI_QMM_ERR_LIMIT; a 262144-row vocabulary at batch 16 fits.
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current).  Make that first call outside any stream capture.
+ *   - All calls on a device share the one array: calls that can overlap on the GPU (different
+ *     streams without an ordering between them) race and give wrong answers.  Keep them on one
+ *     stream or order them with events.
+ */
+size_t cogni_qmm_gemv_top1_noalloc_max_scratch(void);
+int cogni_qmm_gemv_top1_noalloc(int type, const void *d_w, const float *d_x, int in_dim,
+                                int out_dim, int batch, int32_t index_base, int32_t *d_top_index,
+                                float *d_top_value, int64_t *d_top_key, void *stream);
+
 /* Decode keys produced by cogni_qmm_gemv_top1 (after a MAX reduction across shards):
  * d_keys int64 [batch] -> d_top_index int32 [batch], d_top_value f32 [batch]. */
 int cogni_qmm_top1_unpack_keys(const int64_t *d_keys, int batch, int32_t *d_top_index,
