@@ -16,6 +16,8 @@ _vp, _i, _i64, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_size_t
 SIGNATURES = {
     "cogni_qmm_abi_version": (_i, []),
     "cogni_qmm_status_string": (C.c_char_p, [_i]),
+    "cogni_qmm_set_kernel_choice": (_i, [_i]),
+    "cogni_qmm_wait_timeouts": (C.c_uint, []),
     "cogni_qmm_block_bytes": (_i, [_i]),
     "cogni_qmm_block_elements": (_i, [_i]),
     "cogni_qmm_row_bytes": (_i64, [_i, _i]),

@@ -7,6 +7,8 @@
 
 using namespace cogni;
 
+namespace cogni { extern int g_force_rowwarp; }
+
 namespace {
 
 bool supported(int type) { return block_bytes(type) > 0; }
@@ -42,6 +44,14 @@ const char *cogni_qmm_status_string(int status) {
   if (status > 0 && status < 1000) return cudaGetErrorString(static_cast<cudaError_t>(status));
   return "unknown status";
 }
+
+int cogni_qmm_set_kernel_choice(int choice) {
+  if (choice != 0 && choice != 1) return COGNI_QMM_ERR_ARG;
+  g_force_rowwarp = choice;
+  return COGNI_QMM_OK;
+}
+
+unsigned cogni_qmm_wait_timeouts(void) { return gemv_mma_timeouts(); }
 
 int cogni_qmm_block_bytes(int type) { return block_bytes(type); }
 int cogni_qmm_block_elements(int type) { return block_elems(type); }

@@ -3,6 +3,9 @@
 
 namespace cogni {
 
+// 1 = route every GEMV to the general row-per-warp kernel (testing and A/B timing)
+int g_force_rowwarp = 0;
+
 namespace {
 __global__ void top1_unpack_kernel(const long long *keys, int batch, int32_t *idx, float *val) {
   int b = blockIdx.x * blockDim.x + threadIdx.x;
@@ -18,12 +21,17 @@ __global__ void top1_unpack_kernel(const long long *keys, int batch, int32_t *id
 int launch_gemv(int type, const void *d_w, const float *d_x, const float *d_addend,
                 int64_t addend_stride, float *d_y, int in_dim, int out_dim, int batch,
                 cudaStream_t s) {
+  if (g_force_rowwarp == 0 && gemv_mma_supports(type, d_w, d_x, in_dim))
+    return launch_gemv_mma(type, d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, s);
   return launch_gemv_rowwarp(type, d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, s);
 }
 
 int launch_gemv_top1(int type, const void *d_w, const float *d_x, int in_dim, int out_dim,
                      int batch, int32_t index_base, void *d_scratch, int32_t *d_idx, float *d_val,
                      long long *d_key, cudaStream_t s) {
+  if (g_force_rowwarp == 0 && gemv_mma_supports(type, d_w, d_x, in_dim))
+    return launch_gemv_top1_mma(type, d_w, d_x, in_dim, out_dim, batch, index_base, d_scratch,
+                                d_idx, d_val, d_key, s);
   return launch_gemv_top1_rowwarp(type, d_w, d_x, in_dim, out_dim, batch, index_base, d_scratch,
                                   d_idx, d_val, d_key, s);
 }

@@ -248,7 +248,9 @@ int run_top1(const void *d_w, const float *d_x, int in_dim, int out_dim, int bat
 }  // namespace
 
 size_t top1_scratch_bytes(int out_dim, int batch) {
+  // one slot per 64 rows, and never fewer than 256 so a one-CTA-per-SM kernel always has a slot
   size_t nparts = ((size_t)out_dim + kTop1RowsPerPart - 1) / kTop1RowsPerPart;
+  if (nparts < 256) nparts = 256;
   return (((size_t)batch * 4 + 7) & ~(size_t)7) + (size_t)batch * nparts * 8;
 }
 

@@ -104,6 +104,16 @@ int launch_gemv_top1_rowwarp(int type, const void *d_w, const float *d_x, int in
                              int32_t *d_idx, float *d_val, long long *d_key, cudaStream_t s);
 size_t top1_scratch_bytes(int out_dim, int batch);
 
+// Tiled tensor-core GEMV (gemv_mma.cu): Q4_K / Q5_K / Q6_K, 16-byte aligned w and x.
+bool gemv_mma_supports(int type, const void *d_w, const float *d_x, int in_dim);
+int launch_gemv_mma(int type, const void *d_w, const float *d_x, const float *d_addend,
+                    int64_t addend_stride, float *d_y, int in_dim, int out_dim, int batch,
+                    cudaStream_t s);
+int launch_gemv_top1_mma(int type, const void *d_w, const float *d_x, int in_dim, int out_dim,
+                         int batch, int32_t index_base, void *d_scratch, int32_t *d_idx,
+                         float *d_val, long long *d_key, cudaStream_t s);
+unsigned gemv_mma_timeouts();
+
 // Kernel selection (dispatch.cu): picks the tiled kernel when the shape allows it, else the
 // general row-per-warp kernel.
 int launch_gemv(int type, const void *d_w, const float *d_x, const float *d_addend,

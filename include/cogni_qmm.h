@@ -53,6 +53,15 @@ int cogni_qmm_abi_version(void);
 /* Human-readable name of a status returned by any entry point. Never NULL. */
 const char *cogni_qmm_status_string(int status);
 
+/* Diagnostics (no counterpart in the reference).
+ * cogni_qmm_set_kernel_choice: 0 = automatic (tiled tensor-core GEMV where the shape allows it,
+ * the default), 1 = always the general row-per-warp GEMV; process-wide, for A/B checks.
+ * cogni_qmm_wait_timeouts: how many bounded device-side waits have expired since the library
+ * was loaded (0 in a healthy process; a non-zero value means the results of some launch are
+ * invalid).  Synchronises the device. */
+int cogni_qmm_set_kernel_choice(int choice);
+unsigned cogni_qmm_wait_timeouts(void);
+
 /* Block geometry: TensorType#block_bytes / #block_elements (reader.cr:53-80).
  * Return -1 for a type this engine does not handle. */
 int cogni_qmm_block_bytes(int type);

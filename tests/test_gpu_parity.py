@@ -21,6 +21,16 @@ ALL_TYPES = [Q8_0, Q4_K, Q5_K, Q6_K]
 REL_TOL = 1e-3
 
 
+@pytest.fixture(autouse=True, params=["auto", "rowwarp"])
+def kernel_choice(request, engine):
+    """Every case runs twice: automatic kernel selection (the tiled tensor-core GEMV where the
+    shape allows it) and the general row-per-warp kernel forced."""
+    engine.lib.cogni_qmm_set_kernel_choice(1 if request.param == "rowwarp" else 0)
+    yield request.param
+    engine.lib.cogni_qmm_set_kernel_choice(0)
+    assert engine.lib.cogni_qmm_wait_timeouts() == 0, "a bounded device-side wait expired"
+
+
 def cosine(a, b):
     a = a.astype(np.float64).ravel()
     b = b.astype(np.float64).ravel()
