@@ -186,6 +186,9 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
+    if args.kernel_choice:
+        from cogni_ml_b200 import lib
+        lib.cogni_qmm_set_kernel_choice(args.kernel_choice)
     L, B = args.layers, args.batch
     # One layer's bytes are generated on the host (rank-keyed seed), then replicated into L distinct
     # device buffers: timing depends on addresses, not on contents.
@@ -213,14 +216,36 @@ def run_ours(args):
         if world > 1:
             dist.all_gather_into_tensor(buf.view(-1), buf[rank].reshape(-1))
 
-    def step(marks=None):
+    def launch_q4():
         for l in range(L):
             gates[l].gemv(xh, out=y_gate[rank])
             ups[l].gemv(xh, out=y_up[rank])
-        if marks is not None:
-            marks[1].record()
+
+    def launch_q6():
         for l in range(L):
             downs[l].gemv(xf, out=y_down[rank])
+
+    if args.no_graph:
+        run_q4, run_q6 = launch_q4, launch_q6
+    else:
+        # The 3L launches of a step are captured once into two CUDA graphs (one per kernel kind,
+        # so an event can sit between them) and replayed: the host cost of 96 Python->C calls per
+        # step would otherwise bound a step made of 4-7 us kernels.
+        launch_q4()
+        launch_q6()
+        torch.cuda.synchronize()
+        g4, g6 = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g4):
+            launch_q4()
+        with torch.cuda.graph(g6):
+            launch_q6()
+        run_q4, run_q6 = g4.replay, g6.replay
+
+    def step(marks=None):
+        run_q4()
+        if marks is not None:
+            marks[1].record()
+        run_q6()
         if marks is not None:
             marks[2].record()
         gather(y_gate)
@@ -294,6 +319,7 @@ def run_ours(args):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
             "config": {"workload": "ffn9b_b1", "layers": L, "batch": B,
+                       "launch": "eager" if args.no_graph else "cuda graph replay",
                        "per_layer": "ffn_gate+ffn_up Q4_K 12288x4096, ffn_down Q6_K 4096x12288",
                        "weight_bytes_per_step_per_gpu": step_bytes,
                        "l2": f"{L} distinct weight sets ({step_bytes / 1e9:.2f} GB) >> 126 MB L2",
@@ -332,6 +358,9 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--kernel-choice", type=int, default=0,
+                    help="diagnostics: passed to cogni_qmm_set_kernel_choice before the run")
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of graph replay")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

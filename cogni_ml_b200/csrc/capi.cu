@@ -46,6 +46,10 @@ const char *cogni_qmm_status_string(int status) {
 }
 
 int cogni_qmm_set_kernel_choice(int choice) {
+  if (choice >= 16 && choice <= 18) {  // timing diagnostics of the tiled kernel (results invalid)
+    gemv_mma_set_debug(choice - 16);
+    return COGNI_QMM_OK;
+  }
   if (choice != 0 && choice != 1) return COGNI_QMM_ERR_ARG;
   g_force_rowwarp = choice;
   return COGNI_QMM_OK;

@@ -113,6 +113,7 @@ int launch_gemv_top1_mma(int type, const void *d_w, const float *d_x, int in_dim
                          int batch, int32_t index_base, void *d_scratch, int32_t *d_idx,
                          float *d_val, long long *d_key, cudaStream_t s);
 unsigned gemv_mma_timeouts();
+void gemv_mma_set_debug(int mode);
 
 // Kernel selection (dispatch.cu): picks the tiled kernel when the shape allows it, else the
 // general row-per-warp kernel.
