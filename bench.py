@@ -198,8 +198,12 @@ def run_ours(args):
 
     def ring(raw, qtype, out_dim, in_dim):
         first = DeviceQuantWeight.upload(QuantWeight(raw, qtype, out_dim, in_dim), dev)
-        return [first] + [DeviceQuantWeight(first.raw.clone(), qtype, out_dim, in_dim)
-                          for _ in range(L - 1)]
+        copies = [first] + [DeviceQuantWeight(first.raw.clone(), qtype, out_dim, in_dim)
+                            for _ in range(L - 1)]
+        torch.cuda.synchronize()
+        for w in copies:
+            w.resident = True   # bytes complete before any GEMV is enqueued
+        return copies
 
     gates, ups, downs = (ring(gate_h, Q4_K, FFN, HIDDEN), ring(up_h, Q4_K, FFN, HIDDEN),
                          ring(down_h, Q6_K, HIDDEN, FFN))

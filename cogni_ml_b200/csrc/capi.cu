@@ -48,6 +48,7 @@ const char *cogni_qmm_status_string(int status) {
 int cogni_qmm_set_kernel_choice(int choice) {
   if (choice >= 16 && choice <= 18) {  // timing diagnostics of the tiled kernel (results invalid)
     gemv_mma_set_debug(choice - 16);
+    gemv_imma_set_debug(choice - 16);
     return COGNI_QMM_OK;
   }
   if (choice != 0 && choice != 1) return COGNI_QMM_ERR_ARG;
@@ -55,7 +56,7 @@ int cogni_qmm_set_kernel_choice(int choice) {
   return COGNI_QMM_OK;
 }
 
-unsigned cogni_qmm_wait_timeouts(void) { return gemv_mma_timeouts(); }
+unsigned cogni_qmm_wait_timeouts(void) { return gemv_mma_timeouts() + gemv_imma_timeouts(); }
 
 int cogni_qmm_block_bytes(int type) { return block_bytes(type); }
 int cogni_qmm_block_elements(int type) { return block_elems(type); }
@@ -82,9 +83,9 @@ int cogni_qmm_dequantize(int type, const void *d_w, int64_t n_elements, float *d
   return launch_dequantize(type, d_w, n_elements, d_out, static_cast<cudaStream_t>(stream));
 }
 
-int cogni_qmm_gemv(int type, const void *d_w, const float *d_x, const float *d_addend,
-                   int64_t addend_stride, float *d_y, int in_dim, int out_dim, int batch,
-                   void *stream) {
+static int gemv_common(int type, const void *d_w, const float *d_x, const float *d_addend,
+                       int64_t addend_stride, float *d_y, int in_dim, int out_dim, int batch,
+                       int resident, void *stream) {
   int st = check_gemv_args(type, d_w, d_x, d_y, in_dim, out_dim, batch);
   if (st) return st;
   if (d_addend && addend_stride != 0 && addend_stride != out_dim) return COGNI_QMM_ERR_ARG;
@@ -93,10 +94,22 @@ int cogni_qmm_gemv(int type, const void *d_w, const float *d_x, const float *d_a
     int nb = batch - b0 < 16 ? batch - b0 : 16;
     const float *add = d_addend ? d_addend + (int64_t)b0 * addend_stride : nullptr;
     st = launch_gemv(type, d_w, d_x + (int64_t)b0 * in_dim, add, addend_stride,
-                     d_y + (int64_t)b0 * out_dim, in_dim, out_dim, nb, s);
+                     d_y + (int64_t)b0 * out_dim, in_dim, out_dim, nb, resident, s);
     if (st) return st;
   }
   return COGNI_QMM_OK;
+}
+
+int cogni_qmm_gemv(int type, const void *d_w, const float *d_x, const float *d_addend,
+                   int64_t addend_stride, float *d_y, int in_dim, int out_dim, int batch,
+                   void *stream) {
+  return gemv_common(type, d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, 0, stream);
+}
+
+int cogni_qmm_gemv_resident(int type, const void *d_w, const float *d_x, const float *d_addend,
+                            int64_t addend_stride, float *d_y, int in_dim, int out_dim, int batch,
+                            void *stream) {
+  return gemv_common(type, d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, 1, stream);
 }
 
 size_t cogni_qmm_gemv_top1_scratch_bytes(int out_dim, int batch) {

@@ -20,7 +20,10 @@ __global__ void top1_unpack_kernel(const long long *keys, int batch, int32_t *id
 
 int launch_gemv(int type, const void *d_w, const float *d_x, const float *d_addend,
                 int64_t addend_stride, float *d_y, int in_dim, int out_dim, int batch,
-                cudaStream_t s) {
+                int resident, cudaStream_t s) {
+  if (g_force_rowwarp == 0 && gemv_imma_supports(type, d_w, d_x, in_dim, batch))
+    return launch_gemv_imma(type, d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch,
+                            resident, s);
   if (g_force_rowwarp == 0 && gemv_mma_supports(type, d_w, d_x, in_dim))
     return launch_gemv_mma(type, d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, s);
   return launch_gemv_rowwarp(type, d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, s);
@@ -29,6 +32,9 @@ int launch_gemv(int type, const void *d_w, const float *d_x, const float *d_adde
 int launch_gemv_top1(int type, const void *d_w, const float *d_x, int in_dim, int out_dim,
                      int batch, int32_t index_base, void *d_scratch, int32_t *d_idx, float *d_val,
                      long long *d_key, cudaStream_t s) {
+  if (g_force_rowwarp == 0 && gemv_imma_supports(type, d_w, d_x, in_dim, batch))
+    return launch_gemv_top1_imma(type, d_w, d_x, in_dim, out_dim, batch, index_base, d_scratch,
+                                 d_idx, d_val, d_key, 0, s);
   if (g_force_rowwarp == 0 && gemv_mma_supports(type, d_w, d_x, in_dim))
     return launch_gemv_top1_mma(type, d_w, d_x, in_dim, out_dim, batch, index_base, d_scratch,
                                 d_idx, d_val, d_key, s);

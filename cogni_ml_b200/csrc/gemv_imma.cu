@@ -1,0 +1,617 @@
+// Decode GEMV for batch 1-2, Q4_K / Q5_K / Q6_K straight from the raw GGUF superblocks (sm_100a):
+// bulk-async staging + integer tensor-core MMAs on the raw quants.
+//
+// The kernel is HBM-bound; at 6.5 TB/s an SM has about three issue slots per weight, and the
+// integer (ALU) pipe runs at half rate, so the design removes every per-weight instruction it can:
+//
+//  * A persistent CTA per SM walks row tiles of 16 output rows.  One producer warp streams the
+//    tile's rows with 1-D bulk async copies (cp.async.bulk, completion on an mbarrier) into a ring
+//    of shared-memory stages, KB superblocks of every row per stage; 16 consumer warps split the
+//    stage (Q4_K/Q5_K: one superblock per warp, Q6_K: half a superblock per warp).  Rows that are
+//    only 2/8-byte aligned (Q6_K) are fetched from the 16-byte boundary below their start.
+//  * Activations are quantised once per CTA to 15-bit block floating point: per scale group
+//    (32 elements for Q4_K/Q5_K, 16 for Q6_K) x = sx * n with |n| <= 16256, n = 128*hi + lo, hi
+//    and lo int8.  The rounding step is 2^-14 of the group maximum, i.e. ~4e-5 relative rms.
+//  * The quants feed mma.sync.m16n8k32 (u8 x s8 -> s32) as they are: Q4_K nibbles need one AND /
+//    shift-AND per four weights and no widening.  One MMA covers two scale groups at once: the hi
+//    and lo planes of group A occupy columns 0-1 with zeros in group B's k-slots, group B's planes
+//    columns 2-3 with zeros in A's slots, so each lane ends up with the exact integer dot product
+//    of one (row, group) pair.  It is combined (128*hi + lo), converted once and multiplied by
+//    d*sc*sx in fp32; accumulation across groups is fp32.
+//  * Terms that do not depend on the quants (Q4_K/Q5_K -dmin*m, Q6_K's -32) are folded into one
+//    correction per (row, superblock) from the per-group sums of the quantised activations.
+//  * Per tile the warps' partial sums are added in a fixed order through shared memory, the addend
+//    (bias or residual) is added and y is stored.  Results are deterministic.
+//
+// The kernel is launched with programmatic stream serialisation: it lets its successor start
+// launching at once and itself waits for its predecessor only before it touches x or y.  With
+// `resident` weights the producer starts fetching weights before that wait.
+#include <climits>
+
+#include "qmm_common.cuh"
+#include "tma_pipe.cuh"
+
+namespace cogni {
+namespace {
+
+constexpr int kNW = 16;                      // consumer warps
+constexpr int kThreads = (kNW + 1) * 32;     // + 1 producer warp
+constexpr int kR = 16;                       // rows per tile
+constexpr size_t kDynSmemMax = 227 * 1024 - 1024;
+constexpr int kNMax = 16256;                 // |n| bound: 127 * 128
+
+constexpr int stage_row_stride(int bb, int kb, bool unaligned_rows) {
+  int rs = (bb * kb + (unaligned_rows ? 16 : 0) + 15) / 16 * 16;
+  for (;; rs += 16) {
+    const int m = rs % 128;
+    if (unaligned_rows ? ((m / 16) % 2 == 1) : (m == 32 || m == 96)) return rs;
+  }
+}
+
+template <int TYPE> struct Cfg;
+template <> struct Cfg<kQ4_K> {
+  static constexpr int BB = 144, KB = 16, HV = 1, GROUP = 32;
+  static constexpr int RS = stage_row_stride(BB, KB, false);
+  static constexpr bool HAS_MIN = true;
+};
+template <> struct Cfg<kQ5_K> {
+  static constexpr int BB = 176, KB = 16, HV = 1, GROUP = 32;
+  static constexpr int RS = stage_row_stride(BB, KB, false);
+  static constexpr bool HAS_MIN = true;
+};
+template <> struct Cfg<kQ6_K> {
+  static constexpr int BB = 210, KB = 8, HV = 2, GROUP = 16;
+  static constexpr int RS = stage_row_stride(BB, KB, true);
+  static constexpr bool HAS_MIN = false;
+};
+
+struct Params {
+  const uint8_t *w;
+  const float *x;
+  const float *addend;
+  long long addend_stride;
+  float *y;
+  int in_dim, out_dim;
+  int nblk, nchunks, ntiles, stages;
+  long long row_bytes;
+  int off_red, off_area, off_sx, off_xx, off_xq, off_stage, stage_bytes;
+  int resident;  // weights were complete before the preceding kernel started
+  int debug;     // diagnostics: 1 = stream only, 2 = stream + decode
+  long long *part_keys;  // fused top-1 (nullptr: plain GEMV)
+  unsigned *counter;
+  int32_t *top_idx;
+  float *top_val;
+  long long *top_key;
+  int index_base;
+};
+
+__device__ __forceinline__ void consumer_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kNW * 32) : "memory");
+}
+__device__ __forceinline__ void imma_zero(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                          uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%10,%10,%10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+__device__ __forceinline__ void imma_acc(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// byte i of v as a float, exactly: 0x4B0000bb is 2^23 + b
+__device__ __forceinline__ float byte_to_float(uint32_t v, int i) {
+  return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7650 + i)) - 8388608.f;
+}
+
+// Shared-memory layout of the quantised activations, in MMA B-fragment order.  A "unit" is 64
+// consecutive-in-layout elements that one warp turns into two MMAs:
+//   Q4_K/Q5_K  unit = (superblock, pair g4): elements 64*g4 .. 64*g4+63 (sub-blocks 2g4, 2g4+1)
+//   Q6_K       unit = (superblock, half n, h): elements 128n + 32k + 16h + (0..15), k = 0..3
+// Per unit: NCX = 4*NB columns (batch b, group slot sub, plane pl -> column 4b + 2sub + pl), per
+// column 4 lanes t, per lane 16 bytes = (MMA0.b0, MMA0.b1, MMA1.b0, MMA1.b1).  A column of group
+// slot `sub` only fills the b`sub` words; the other words stay zero.
+template <int TYPE>
+__device__ __forceinline__ int xq_word_offset(int e_in /*element within superblock*/, int ncx,
+                                              int col_base /*4b + plane*/, int &sub) {
+  int unit, t, m;
+  if (TYPE == kQ6_K) {
+    const int n = e_in >> 7, k = (e_in & 127) >> 5, h = (e_in & 31) >> 4;
+    unit = 2 * n + h;
+    m = k >> 1;
+    sub = k & 1;
+    t = (e_in & 15) >> 2;
+  } else {
+    const int g4 = e_in >> 6;
+    unit = g4;
+    sub = (e_in >> 5) & 1;
+    t = (e_in & 31) >> 3;
+    m = (e_in & 7) >> 2;
+  }
+  return ((unit * ncx + col_base + 2 * sub) * 4 + t) * 16 + m * 8 + sub * 4;
+}
+
+// ---------------------------------------------------------------------------- per-warp decode
+// Area of one warp: dscx[NB][8][16] floats (d*sc*sx of the warp's 8 scale groups, 16 rows, per
+// batch row) followed by corr[NB][16].
+template <int TYPE, int NB>
+__device__ __forceinline__ void decode_scales(const uint8_t *blk_row, int lane, int hv, int kblk,
+                                              const float *SX, const float *XX, float *area) {
+  using C = Cfg<TYPE>;
+  const int r = lane & 15, half = lane >> 4;
+  float dsc[4], kk[4];
+  int grp0;  // first of this lane's four groups in the tables
+  if constexpr (C::HAS_MIN) {
+    const uint4 h = *reinterpret_cast<const uint4 *>(blk_row);
+    const __half2 dd = *reinterpret_cast<const __half2 *>(&h.x);
+    const float d = __low2float(dd), dmin = __high2float(dd);
+    const uint32_t u0 = h.y, u1 = h.z, u2 = h.w;
+    // four 6-bit scales / mins of this half as bytes (dequant.cr:240-249, four at a time)
+    const uint32_t scw = half ? ((u2 & 0x0f0f0f0fu) | ((u0 >> 2) & 0x30303030u)) : (u0 & 0x3f3f3f3fu);
+    const uint32_t mnw = half ? (((u2 >> 4) & 0x0f0f0f0fu) | ((u1 >> 2) & 0x30303030u)) : (u1 & 0x3f3f3f3fu);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      dsc[i] = d * byte_to_float(scw, i);
+      kk[i] = -(dmin * byte_to_float(mnw, i));
+    }
+    grp0 = kblk * 8 + 4 * half;
+  } else {
+    const float d = load_half_as_float(blk_row + 208);
+    const int8_t *sc = reinterpret_cast<const int8_t *>(blk_row + 192 + 8 * hv + 4 * half);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      dsc[i] = d * (float)sc[i];
+      kk[i] = -32.f * dsc[i];
+    }
+    grp0 = kblk * 16 + 8 * hv + 4 * half;
+  }
+#pragma unroll
+  for (int b = 0; b < NB; b++) {
+    float corr = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      area[(b * 8 + 4 * half + i) * 16 + r] = dsc[i] * SX[(grp0 + i) * NB + b];
+      corr = fmaf(kk[i], XX[(grp0 + i) * NB + b], corr);
+    }
+    corr += __shfl_xor_sync(0xffffffffu, corr, 16);
+    if (half == 0) area[NB * 128 + b * 16 + r] = corr;
+  }
+}
+
+// ---------------------------------------------------------------------------- the kernel
+template <int TYPE, int NB>
+__global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) {
+  using C = Cfg<TYPE>;
+  constexpr int NCX = 4 * NB;                    // columns of the quantised-x layout
+  constexpr int UNIT_BYTES = NCX * 64;
+  constexpr int AREA_FLOATS = NB * 128 + NB * 16;
+  static_assert(C::KB * C::HV == kNW, "one warp per (superblock, half)");
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem);  // full[S], empty[S]
+  const int S = p.stages;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; s++) {
+      mbar_init(smem_u32(&bars[s]), 1);
+      mbar_init(smem_u32(&bars[S + s]), kNW);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  pdl_launch_dependents();
+
+  uint8_t *stages = smem + p.off_stage;
+
+  if (warp == kNW) {
+    // ------------------------------------------------------------------ producer warp
+    if (!p.resident) pdl_wait_prior_grid();
+    int it = 0;
+    for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
+      const int row = tile * kR + lane;
+      const bool rvalid = lane < kR && row < p.out_dim;
+      const uint8_t *rsrc = p.w + (long long)row * p.row_bytes;
+      for (int c = 0; c < p.nchunks; c++, it++) {
+        const int s = it % S;
+        mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1);
+        const int nb = min(C::KB, p.nblk - c * C::KB);
+        const uint8_t *src = rsrc + (long long)c * C::KB * C::BB;
+        const uint32_t padb = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15);
+        const uint32_t bytes = rvalid ? ((padb + nb * C::BB + 15u) & ~15u) : 0u;
+        const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
+        const uint32_t full = smem_u32(&bars[s]);
+        if (lane == 0) mbar_arrive_expect_tx(full, total);
+        __syncwarp();
+        if (rvalid)
+          bulk_g2s(smem_u32(stages + (size_t)s * p.stage_bytes + lane * C::RS), src - padb, bytes,
+                   full);
+      }
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------------- consumer warps
+  const int ctid = threadIdx.x;  // 0 .. 511
+  uint8_t *xq = smem + p.off_xq;
+  float *SX = reinterpret_cast<float *>(smem + p.off_sx);
+  float *XX = reinterpret_cast<float *>(smem + p.off_xx);
+  const int K = p.in_dim;
+
+  {  // zero the fragment-ordered activation area (half of its words are structural zeros)
+    const int n16 = (K >> 6) * UNIT_BYTES / 16;
+    for (int i = ctid; i < n16; i += kNW * 32) reinterpret_cast<uint4 *>(xq)[i] = make_uint4(0, 0, 0, 0);
+  }
+  consumer_sync();
+  pdl_wait_prior_grid();  // x (and y / the addend) may be produced by the preceding kernel
+  {  // quantise x: per group sx = max|x| / 16256, n = rint(x / sx) = 128*hi + lo
+    const int k8n = K >> 3, items = NB * k8n;
+    constexpr int LPG = C::GROUP / 8;  // lanes per scale group
+    for (int i = ctid; i < items; i += kNW * 32) {
+      const int b = i / k8n, k = (i - b * k8n) * 8;
+      const float4 v0 = __ldg(reinterpret_cast<const float4 *>(p.x + (long long)b * K + k));
+      const float4 v1 = __ldg(reinterpret_cast<const float4 *>(p.x + (long long)b * K + k + 4));
+      const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+      float mx = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; e++) mx = fmaxf(mx, fabsf(v[e]));
+#pragma unroll
+      for (int off = 1; off < LPG; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      const float sx = mx > 0.f ? mx * (1.f / kNMax) : 1.f;
+      const float inv = mx > 0.f ? (float)kNMax / mx : 0.f;
+      uint32_t hw[2] = {0, 0}, lw[2] = {0, 0};
+      int nsum = 0;
+#pragma unroll
+      for (int e = 0; e < 8; e++) {
+        int n = __float2int_rn(v[e] * inv);
+        n = max(-kNMax, min(kNMax, n));
+        const int hi = (n + 64) >> 7, lo = n - (hi << 7);
+        nsum += n;
+        hw[e >> 2] |= (uint32_t)(hi & 0xff) << (8 * (e & 3));
+        lw[e >> 2] |= (uint32_t)(lo & 0xff) << (8 * (e & 3));
+      }
+#pragma unroll
+      for (int off = 1; off < LPG; off <<= 1) nsum += __shfl_xor_sync(0xffffffffu, nsum, off);
+      if ((lane & (LPG - 1)) == 0) {
+        const int grp = k / C::GROUP;
+        SX[grp * NB + b] = sx;
+        XX[grp * NB + b] = sx * (float)nsum;
+      }
+      uint8_t *blk_base = xq + (size_t)(k >> 8) * 4 * UNIT_BYTES;
+      const int e_in = k & 255;
+#pragma unroll
+      for (int w4 = 0; w4 < 2; w4++) {  // the two 4-element words of this thread's 8 elements
+        int sub;
+        const int off = xq_word_offset<TYPE>(e_in + 4 * w4, NCX, 4 * b, sub);
+        *reinterpret_cast<uint32_t *>(blk_base + off) = hw[w4];       // hi plane: column + 0
+        *reinterpret_cast<uint32_t *>(blk_base + off + 64) = lw[w4];  // lo plane: column + 1
+      }
+    }
+  }
+  consumer_sync();
+
+  const int g = lane >> 2, t = lane & 3;
+  const int sub = t & 1, bt = (t >> 1) & (NB - 1);  // this lane's group slot and batch row
+  const int wkb = warp / C::HV, whv = warp % C::HV;
+  float *area = reinterpret_cast<float *>(smem + p.off_area) + warp * AREA_FLOATS;
+  const float *dscx = area + bt * 128;
+  float2 *red = reinterpret_cast<float2 *>(smem + p.off_red);
+  // this lane's 16 bytes of a unit's B fragments
+  const uint8_t *xlane = xq + ((g & (NCX - 1)) * 4 + t) * 16;
+
+  long long best = LLONG_MIN;  // fused top-1: this thread's running maximum
+
+  int it = 0, tcount = 0;
+  for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, tcount++) {
+    float acc0 = 0.f, acc1 = 0.f;  // rows g and g+8 of (group slot sub, batch row bt)
+    const uintptr_t wbase = reinterpret_cast<uintptr_t>(p.w);
+    const int pad_a = (int)((wbase + ((long long)tile * kR + g) * p.row_bytes) & 15);
+    const int pad_b = (int)((wbase + ((long long)tile * kR + g + 8) * p.row_bytes) & 15);
+    const int pad_d = (int)((wbase + ((long long)tile * kR + (lane & 15)) * p.row_bytes) & 15);
+
+    for (int c = 0; c < p.nchunks; c++, it++) {
+      const int s = it % S;
+      mbar_wait(smem_u32(&bars[s]), (it / S) & 1);
+      const int kblk = c * C::KB + wkb;
+      if (kblk < p.nblk && p.debug != 1) {
+        const uint8_t *stage = stages + (size_t)s * p.stage_bytes + wkb * C::BB;
+        decode_scales<TYPE, NB>(stage + (lane & 15) * C::RS + pad_d, lane, whv, kblk, SX, XX, area);
+        __syncwarp();
+        if (p.debug != 2) {
+          const uint8_t *xu = xlane + (size_t)kblk * 4 * UNIT_BYTES;
+          if constexpr (C::HAS_MIN) {
+            constexpr bool Q5 = TYPE == kQ5_K;
+            constexpr int QOFF = Q5 ? 48 : 16;
+            constexpr uint32_t M4 = 0x0f0f0f0fu, M1 = 0x10101010u;
+            const uint8_t *ra = stage + g * C::RS + pad_a + 8 * t, *rb = stage + (g + 8) * C::RS + pad_b + 8 * t;
+            uint2 qha = make_uint2(0, 0), qhb = make_uint2(0, 0);
+            if constexpr (Q5) {
+              qha = *reinterpret_cast<const uint2 *>(ra + 16);
+              qhb = *reinterpret_cast<const uint2 *>(rb + 16);
+            }
+#pragma unroll
+            for (int g4 = 0; g4 < 4; g4++) {
+              const uint4 bv = *reinterpret_cast<const uint4 *>(xu + g4 * UNIT_BYTES);
+              const uint2 qa = *reinterpret_cast<const uint2 *>(ra + QOFF + 32 * g4);
+              const uint2 qb = *reinterpret_cast<const uint2 *>(rb + QOFF + 32 * g4);
+              uint32_t la0 = qa.x & M4, la1 = qa.y & M4, lb0 = qb.x & M4, lb1 = qb.y & M4;
+              uint32_t ha0 = (qa.x >> 4) & M4, ha1 = (qa.y >> 4) & M4;
+              uint32_t hb0 = (qb.x >> 4) & M4, hb1 = (qb.y >> 4) & M4;
+              if constexpr (Q5) {
+                auto bit = [&](uint32_t q, int b) { return b <= 4 ? ((q << (4 - b)) & M1) : ((q >> (b - 4)) & M1); };
+                la0 |= bit(qha.x, 2 * g4);     la1 |= bit(qha.y, 2 * g4);
+                lb0 |= bit(qhb.x, 2 * g4);     lb1 |= bit(qhb.y, 2 * g4);
+                ha0 |= bit(qha.x, 2 * g4 + 1); ha1 |= bit(qha.y, 2 * g4 + 1);
+                hb0 |= bit(qhb.x, 2 * g4 + 1); hb1 |= bit(qhb.y, 2 * g4 + 1);
+              }
+              int cc[4];
+              // k-slots 0..15: sub-block 2*g4 (low nibbles), 16..31: sub-block 2*g4+1 (high)
+              imma_zero(cc, la0, lb0, ha0, hb0, bv.x, bv.y);
+              imma_acc(cc, la1, lb1, ha1, hb1, bv.z, bv.w);
+              const float sa = dscx[(2 * g4 + sub) * 16 + g], sb = dscx[(2 * g4 + sub) * 16 + g + 8];
+              acc0 = fmaf(sa, (float)(cc[0] * 128 + cc[1]), acc0);
+              acc1 = fmaf(sb, (float)(cc[2] * 128 + cc[3]), acc1);
+            }
+          } else {
+            constexpr uint32_t M4 = 0x0f0f0f0fu, M2 = 0x30303030u;
+            const uintptr_t aa = reinterpret_cast<uintptr_t>(stage + g * C::RS + pad_a + 64 * whv + 4 * t);
+            const uintptr_t ab = reinterpret_cast<uintptr_t>(stage + (g + 8) * C::RS + pad_b + 64 * whv + 4 * t);
+            const uint8_t *base[2] = {reinterpret_cast<const uint8_t *>(aa & ~(uintptr_t)3),
+                                      reinterpret_cast<const uint8_t *>(ab & ~(uintptr_t)3)};
+            const uint32_t sh[2] = {(uint32_t)(aa & 2) * 8, (uint32_t)(ab & 2) * 8};
+            const int qh_off = 128 - 32 * whv;  // qh[32*hv + ..] relative to ql[64*hv + ..]
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+              const uint4 bv = *reinterpret_cast<const uint4 *>(xu + (2 * whv + h) * UNIT_BYTES);
+              uint32_t q[2][4];
+#pragma unroll
+              for (int r = 0; r < 2; r++) {
+                auto ld = [&](int off) {
+                  const uint32_t *w32 = reinterpret_cast<const uint32_t *>(base[r] + off);
+                  return __funnelshift_r(w32[0], w32[1], sh[r]);
+                };
+                const uint32_t ql0 = ld(16 * h), ql1 = ld(32 + 16 * h), qhw = ld(qh_off + 16 * h);
+                q[r][0] = (ql0 & M4) | ((qhw << 4) & M2);
+                q[r][1] = (ql1 & M4) | ((qhw << 2) & M2);
+                q[r][2] = ((ql0 >> 4) & M4) | (qhw & M2);
+                q[r][3] = ((ql1 >> 4) & M4) | ((qhw >> 2) & M2);
+              }
+#pragma unroll
+              for (int m = 0; m < 2; m++) {
+                int cc[4];
+                // k-slots 0..15: group k = 2m, 16..31: group k = 2m+1 (scale group h + 2k)
+                imma_zero(cc, q[0][2 * m], q[1][2 * m], q[0][2 * m + 1], q[1][2 * m + 1],
+                          m ? bv.z : bv.x, m ? bv.w : bv.y);
+                const int j8 = h + 2 * (2 * m + sub);
+                const float sa = dscx[j8 * 16 + g], sb = dscx[j8 * 16 + g + 8];
+                acc0 = fmaf(sa, (float)(cc[0] * 128 + cc[1]), acc0);
+                acc1 = fmaf(sb, (float)(cc[2] * 128 + cc[3]), acc1);
+              }
+            }
+          }
+        }
+        if (sub == 0) {
+          const float *corr = area + NB * 128 + bt * 16;
+          acc0 += corr[g];
+          acc1 += corr[g + 8];
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars[S + s]));
+    }
+
+    // fixed-order sum of the warps' partial tiles
+    float2 *rbuf = red + (size_t)(tcount & 1) * (kNW * 32);
+    rbuf[warp * 32 + lane] = make_float2(acc0, acc1);
+    consumer_sync();
+    if (ctid < 16 * NB) {
+      const int r16 = ctid & 15, b = ctid >> 4;
+      const int gg = r16 & 7, upper = r16 >> 3;
+      float v = 0.f;
+#pragma unroll
+      for (int ww = 0; ww < kNW; ww++) {
+        const float2 pa = rbuf[ww * 32 + gg * 4 + 2 * b], pb = rbuf[ww * 32 + gg * 4 + 2 * b + 1];
+        v += upper ? (pa.y + pb.y) : (pa.x + pb.x);
+      }
+      const int row = tile * kR + r16;
+      if (row < p.out_dim) {
+        if (p.part_keys) {
+          const long long key = top1_key(v, (uint32_t)(p.index_base + row));
+          best = key > best ? key : best;
+        } else {
+          const float a = p.addend ? p.addend[(long long)b * p.addend_stride + row] : 0.f;
+          p.y[(long long)b * p.out_dim + row] = a + v;
+        }
+      }
+    }
+  }
+
+  if (p.part_keys == nullptr) return;
+
+  // ------------------------------------------------------------ fused top-1 epilogue
+  // per-CTA maximum per batch row -> scratch slot; the CTA with the last ticket folds all slots
+  __shared__ long long s_best[2];
+  __shared__ bool s_last;
+  if (ctid < 2) s_best[ctid] = LLONG_MIN;
+  consumer_sync();
+  if (ctid < 16 * NB) atomicMax(&s_best[ctid >> 4], best);
+  consumer_sync();
+  const int nparts = gridDim.x;
+  if (ctid < NB) p.part_keys[(long long)ctid * nparts + blockIdx.x] = s_best[ctid];
+  __threadfence();
+  consumer_sync();
+  if (ctid == 0) {
+    const unsigned ticket = atomicAdd(p.counter, 1u);
+    s_last = ticket == (unsigned)nparts - 1u;
+  }
+  consumer_sync();
+  if (!s_last) return;
+  __threadfence();
+  if (warp < NB) {
+    const int b = warp;
+    long long m = LLONG_MIN;
+    for (int i = lane; i < nparts; i += 32) {
+      const long long k = __ldcg(&p.part_keys[(long long)b * nparts + i]);
+      m = k > m ? k : m;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const long long o = __shfl_xor_sync(0xffffffffu, m, off);
+      m = o > m ? o : m;
+    }
+    if (lane == 0) {
+      float v;
+      uint32_t idx;
+      top1_unkey(m, v, idx);
+      p.top_idx[b] = (int32_t)idx;
+      p.top_val[b] = v;
+      if (p.top_key) p.top_key[b] = m;
+    }
+  }
+  if (ctid == 0) *p.counter = 0u;  // ready for the next call on this scratch buffer
+}
+
+// ---------------------------------------------------------------------------- host side
+int g_imma_debug = 0;
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return 148;
+  if (!cached[dev]) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
+  return cached[dev] > 0 ? cached[dev] : 148;
+}
+
+template <int TYPE>
+bool make_plan(int in_dim, int out_dim, int nb, Params &p, size_t &smem) {
+  using C = Cfg<TYPE>;
+  const int nblk = in_dim / 256;
+  const int ngroups = in_dim / C::GROUP;
+  auto al = [](size_t v) { return (v + 127) & ~(size_t)127; };
+  size_t off = 128;
+  const size_t off_red = off;    off = al(off + 2ull * kNW * 32 * 8);
+  const size_t off_area = off;   off = al(off + (size_t)kNW * (nb * 128 + nb * 16) * 4);
+  const size_t off_sx = off;     off = al(off + (size_t)ngroups * nb * 4);
+  const size_t off_xx = off;     off = al(off + (size_t)ngroups * nb * 4);
+  const size_t off_xq = off;     off = al(off + (size_t)(in_dim / 64) * (4 * nb) * 64);
+  const size_t off_stage = off;
+  const size_t stage_bytes = al((size_t)kR * C::RS);
+  if (off_stage + 3 * stage_bytes > kDynSmemMax) return false;
+  int stages = (int)((kDynSmemMax - off_stage) / stage_bytes);
+  if (stages > 8) stages = 8;
+  p.in_dim = in_dim; p.out_dim = out_dim;
+  p.nblk = nblk; p.nchunks = (nblk + C::KB - 1) / C::KB; p.ntiles = (out_dim + kR - 1) / kR;
+  p.stages = stages; p.row_bytes = (long long)nblk * C::BB;
+  p.off_red = (int)off_red; p.off_area = (int)off_area; p.off_sx = (int)off_sx;
+  p.off_xx = (int)off_xx; p.off_xq = (int)off_xq; p.off_stage = (int)off_stage;
+  p.stage_bytes = (int)stage_bytes;
+  smem = off_stage + (size_t)stages * stage_bytes;
+  return true;
+}
+
+template <int TYPE, int NB>
+int launch_instance(const Params &p, size_t smem, int grid, cudaStream_t s) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemv_imma_kernel<TYPE, NB>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kDynSmemMax);
+    if (e != cudaSuccess) return (int)e;
+    configured[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, gemv_imma_kernel<TYPE, NB>, p);
+}
+
+template <int TYPE>
+int gemv_typed(const void *d_w, const float *d_x, const float *d_addend, int64_t addend_stride,
+               float *d_y, int in_dim, int out_dim, int batch, int resident, const Params *top1,
+               cudaStream_t s) {
+  Params p{};
+  size_t smem = 0;
+  if (!make_plan<TYPE>(in_dim, out_dim, batch, p, smem)) return COGNI_QMM_ERR_LIMIT;
+  p.w = static_cast<const uint8_t *>(d_w);
+  p.x = d_x;
+  p.addend = d_addend;
+  p.addend_stride = addend_stride;
+  p.y = d_y;
+  p.resident = resident;
+  p.debug = g_imma_debug;
+  const int sms = sm_count();
+  const int grid = p.ntiles < sms ? p.ntiles : sms;
+  if (top1) {
+    p.part_keys = top1->part_keys;
+    p.counter = top1->counter;
+    p.top_idx = top1->top_idx;
+    p.top_val = top1->top_val;
+    p.top_key = top1->top_key;
+    p.index_base = top1->index_base;
+  }
+  return batch == 1 ? launch_instance<TYPE, 1>(p, smem, grid, s)
+                    : launch_instance<TYPE, 2>(p, smem, grid, s);
+}
+
+}  // namespace
+
+void gemv_imma_set_debug(int mode) { g_imma_debug = mode; }
+
+bool gemv_imma_supports(int type, const void *d_w, const float *d_x, int in_dim, int batch) {
+  if (type != kQ4_K && type != kQ5_K && type != kQ6_K) return false;
+  if (batch < 1 || batch > 2) return false;
+  if ((reinterpret_cast<uintptr_t>(d_w) & 15) || (reinterpret_cast<uintptr_t>(d_x) & 15)) return false;
+  return in_dim % 256 == 0 && in_dim <= 16384;
+}
+
+int launch_gemv_imma(int type, const void *d_w, const float *d_x, const float *d_addend,
+                     int64_t addend_stride, float *d_y, int in_dim, int out_dim, int batch,
+                     int resident, cudaStream_t s) {
+  switch (type) {
+    case kQ4_K: return gemv_typed<kQ4_K>(d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, resident, nullptr, s);
+    case kQ5_K: return gemv_typed<kQ5_K>(d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, resident, nullptr, s);
+    case kQ6_K: return gemv_typed<kQ6_K>(d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, resident, nullptr, s);
+    default: return COGNI_QMM_ERR_TYPE;
+  }
+}
+
+int launch_gemv_top1_imma(int type, const void *d_w, const float *d_x, int in_dim, int out_dim,
+                          int batch, int32_t index_base, void *d_scratch, int32_t *d_idx,
+                          float *d_val, long long *d_key, int resident, cudaStream_t s) {
+  Params t{};
+  t.counter = static_cast<unsigned *>(d_scratch);
+  t.part_keys = reinterpret_cast<long long *>(static_cast<char *>(d_scratch) +
+                                              (((size_t)batch * 4 + 7) & ~(size_t)7));
+  t.top_idx = d_idx;
+  t.top_val = d_val;
+  t.top_key = d_key;
+  t.index_base = index_base;
+  switch (type) {
+    case kQ4_K: return gemv_typed<kQ4_K>(d_w, d_x, nullptr, 0, nullptr, in_dim, out_dim, batch, resident, &t, s);
+    case kQ5_K: return gemv_typed<kQ5_K>(d_w, d_x, nullptr, 0, nullptr, in_dim, out_dim, batch, resident, &t, s);
+    case kQ6_K: return gemv_typed<kQ6_K>(d_w, d_x, nullptr, 0, nullptr, in_dim, out_dim, batch, resident, &t, s);
+    default: return COGNI_QMM_ERR_TYPE;
+  }
+}
+
+unsigned gemv_imma_timeouts() {
+  unsigned v = 0;
+  cudaMemcpyFromSymbol(&v, g_pipe_wait_timeouts, sizeof(v));
+  return v;
+}
+
+}  // namespace cogni

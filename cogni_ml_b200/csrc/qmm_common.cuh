@@ -115,11 +115,22 @@ int launch_gemv_top1_mma(int type, const void *d_w, const float *d_x, int in_dim
 unsigned gemv_mma_timeouts();
 void gemv_mma_set_debug(int mode);
 
+// Integer tensor-core GEMV for batch 1-2 (gemv_imma.cu): Q4_K / Q5_K / Q6_K.
+bool gemv_imma_supports(int type, const void *d_w, const float *d_x, int in_dim, int batch);
+int launch_gemv_imma(int type, const void *d_w, const float *d_x, const float *d_addend,
+                     int64_t addend_stride, float *d_y, int in_dim, int out_dim, int batch,
+                     int resident, cudaStream_t s);
+int launch_gemv_top1_imma(int type, const void *d_w, const float *d_x, int in_dim, int out_dim,
+                          int batch, int32_t index_base, void *d_scratch, int32_t *d_idx,
+                          float *d_val, long long *d_key, int resident, cudaStream_t s);
+unsigned gemv_imma_timeouts();
+void gemv_imma_set_debug(int mode);
+
 // Kernel selection (dispatch.cu): picks the tiled kernel when the shape allows it, else the
 // general row-per-warp kernel.
 int launch_gemv(int type, const void *d_w, const float *d_x, const float *d_addend,
                 int64_t addend_stride, float *d_y, int in_dim, int out_dim, int batch,
-                cudaStream_t s);
+                int resident, cudaStream_t s);
 int launch_gemv_top1(int type, const void *d_w, const float *d_x, int in_dim, int out_dim,
                      int batch, int32_t index_base, void *d_scratch, int32_t *d_idx, float *d_val,
                      long long *d_key, cudaStream_t s);

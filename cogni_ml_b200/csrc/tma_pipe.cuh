@@ -1,0 +1,82 @@
+// mbarrier / bulk-async-copy / programmatic-dependent-launch helpers shared by the tiled kernels.
+//
+// Every wait on an mbarrier is bounded by a wall-clock limit: on expiry the waiter records the
+// event in a device counter, treats the wait as satisfied and carries on, so a kernel always runs
+// to completion (its results are then invalid; cogni::pipe_wait_timeouts() reports it).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace cogni {
+
+constexpr unsigned long long kPipeWaitLimitNs = 2000000000ull;
+
+// one counter per translation unit that includes this header; summed by the host accessor
+static __device__ unsigned int g_pipe_wait_timeouts;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Waits for the phase with the given parity; gives up after kPipeWaitLimitNs.
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return;
+  const unsigned long long t0 = global_ns();
+  for (unsigned spin = 1;; spin++) {
+    if (mbar_try_wait(bar, parity)) return;
+    if ((spin & 63u) == 0 && global_ns() - t0 > kPipeWaitLimitNs) {
+      atomicAdd(&g_pipe_wait_timeouts, 1u);
+      return;
+    }
+  }
+}
+// 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier.
+// src, dst 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes,
+                                         uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+// Programmatic dependent launch: let the next kernel of the stream start launching / wait until
+// the previous kernel of the stream has completed and its writes are visible.  Both are no-ops
+// for a kernel that was not launched with the programmatic-serialization attribute.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait_prior_grid() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+}  // namespace cogni

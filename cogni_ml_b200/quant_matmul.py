@@ -109,6 +109,9 @@ class DeviceQuantWeight:
         self.out_dim = out_dim      # rows held by THIS buffer
         self.in_dim = in_dim
         self.row_begin = row_begin  # global index of the first row (vocab/row sharding)
+        # True once the bytes are known to be complete on the device: gemv may then overlap its
+        # weight fetch with the tail of the preceding kernel (cogni_qmm_gemv_resident)
+        self.resident = False
         self._top1_scratch: Optional[torch.Tensor] = None
 
     @classmethod
@@ -121,7 +124,10 @@ class DeviceQuantWeight:
         host = torch.from_numpy(qw.raw[row_begin * rb:row_end * rb])
         dev = torch.empty(host.numel(), dtype=torch.uint8, device=device)
         dev.copy_(host)
-        return cls(dev, qw.type, row_end - row_begin, qw.in_dim, row_begin)
+        torch.cuda.current_stream(dev.device).synchronize()
+        out = cls(dev, qw.type, row_end - row_begin, qw.in_dim, row_begin)
+        out.resident = True
+        return out
 
     @property
     def nbytes(self) -> int:
@@ -146,10 +152,11 @@ class DeviceQuantWeight:
         if bias is not None and residual is not None:
             raise ValueError("pass bias or residual, not both")
         addend, stride = (bias, 0) if bias is not None else (residual, self.out_dim)
-        check(lib.cogni_qmm_gemv(self.type, self.raw.data_ptr(), x.data_ptr(),
-                                 addend.data_ptr() if addend is not None else None, stride,
-                                 out.data_ptr(), self.in_dim, self.out_dim, batch,
-                                 _stream_ptr(stream)), "cogni_qmm_gemv")
+        fn = lib.cogni_qmm_gemv_resident if self.resident else lib.cogni_qmm_gemv
+        check(fn(self.type, self.raw.data_ptr(), x.data_ptr(),
+                 addend.data_ptr() if addend is not None else None, stride,
+                 out.data_ptr(), self.in_dim, self.out_dim, batch, _stream_ptr(stream)),
+              "cogni_qmm_gemv")
         return out
 
     def top1_scratch(self, batch: int) -> torch.Tensor:

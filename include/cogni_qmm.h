@@ -105,6 +105,19 @@ int cogni_qmm_gemv(int type, const void *d_w, const float *d_x, const float *d_a
                    void *stream);
 
 /*
+ * cogni_qmm_gemv for weights that are resident: identical arguments and result, with one extra
+ * promise from the caller — the weight bytes at d_w were complete before the kernel that precedes
+ * this call in `stream` was launched.  That is the reference's runner lifecycle (upload_weights
+ * once, then run_sequence many times; src/ml/cuda/qwen_recurrent_layer_runner.cr:570-587,
+ * 1158-1266).  The kernel may then start fetching weights while the preceding kernel of the
+ * stream is still draining (programmatic dependent launch); x, the addend and y are still only
+ * touched after the preceding kernel has completed.
+ */
+int cogni_qmm_gemv_resident(int type, const void *d_w, const float *d_x, const float *d_addend,
+                            int64_t addend_stride, float *d_y, int in_dim, int out_dim, int batch,
+                            void *stream);
+
+/*
  * Fused lm_head: GEMV over `out_dim` vocabulary rows plus top-1 per batch row, without
  * writing the logits.  Replaces q6_k_gemv_top1_partial_f32 + output_top1_values_reduce_probe
  * (q6k_gemv_probe.ptx:1331; src/ml/cuda/qwen_output_head_runner.cr:530-624, 884-947).
