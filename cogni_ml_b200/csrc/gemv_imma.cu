@@ -85,12 +85,26 @@ struct Params {
   int index_base;
 };
 
+#ifdef COGNI_TRACE
+__device__ long long g_trace[1 << 16];
+__device__ __forceinline__ void trace(int warp, int lane, int &n, int ev) {
+  if (blockIdx.x == 0 && lane == 0 && n < 1000) {
+    g_trace[(warp * 1024 + n) * 2] = ev;
+    g_trace[(warp * 1024 + n) * 2 + 1] = clock64();
+    n++;
+  }
+}
+#define TRACE(ev) trace(warp, lane, tr_n, ev)
+#else
+#define TRACE(ev)
+#endif
+
 __device__ __forceinline__ void consumer_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(kNW * 32) : "memory");
 }
 __device__ __forceinline__ void imma_zero(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                           uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%10,%10,%10,%10};"
       : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
@@ -98,15 +112,16 @@ __device__ __forceinline__ void imma_zero(int (&d)[4], uint32_t a0, uint32_t a1,
 }
 __device__ __forceinline__ void imma_acc(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};"
       : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-// byte i of v as a float, exactly: 0x4B0000bb is 2^23 + b
-__device__ __forceinline__ float byte_to_float(uint32_t v, int i) {
-  return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7650 + i)) - 8388608.f;
+// scale * (byte i of v), exactly rounded once: 0x4B0000bb is the float 2^23 + b, and
+// fma(2^23 + b, scale, -2^23 * scale) = b * scale (the product 2^23 * scale is exact).
+__device__ __forceinline__ float byte_times(uint32_t v, int i, float scale, float scale_2p23) {
+  return fmaf(__uint_as_float(__byte_perm(v, 0x4B000000u, 0x7650 + i)), scale, -scale_2p23);
 }
 
 // Shared-memory layout of the quantised activations, in MMA B-fragment order.  A "unit" is 64
@@ -154,10 +169,11 @@ __device__ __forceinline__ void decode_scales(const uint8_t *blk_row, int lane, 
     // four 6-bit scales / mins of this half as bytes (dequant.cr:240-249, four at a time)
     const uint32_t scw = half ? ((u2 & 0x0f0f0f0fu) | ((u0 >> 2) & 0x30303030u)) : (u0 & 0x3f3f3f3fu);
     const uint32_t mnw = half ? (((u2 >> 4) & 0x0f0f0f0fu) | ((u1 >> 2) & 0x30303030u)) : (u1 & 0x3f3f3f3fu);
+    const float d23 = d * 8388608.f, ndmin = -dmin, ndmin23 = ndmin * 8388608.f;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-      dsc[i] = d * byte_to_float(scw, i);
-      kk[i] = -(dmin * byte_to_float(mnw, i));
+      dsc[i] = byte_times(scw, i, d, d23);
+      kk[i] = byte_times(mnw, i, ndmin, ndmin23);
     }
     grp0 = kblk * 8 + 4 * half;
   } else {
@@ -195,16 +211,23 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem);  // full[S], empty[S]
   const int S = p.stages;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef COGNI_TRACE
+  int tr_n = 0;
+#endif
+  TRACE(1);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; s++) {
       mbar_init(smem_u32(&bars[s]), 1);
       mbar_init(smem_u32(&bars[S + s]), kNW);
     }
+    mbar_init(smem_u32(&bars[2 * S]), kNW);      // partial sums of an even tile are complete
+    mbar_init(smem_u32(&bars[2 * S + 1]), kNW);  // ... of an odd tile
     mbar_fence_init();
   }
   __syncthreads();
   pdl_launch_dependents();
+  TRACE(2);
 
   uint8_t *stages = smem + p.off_stage;
 
@@ -218,7 +241,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
       const uint8_t *rsrc = p.w + (long long)row * p.row_bytes;
       for (int c = 0; c < p.nchunks; c++, it++) {
         const int s = it % S;
+        TRACE(100 + it);
         mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1);
+        TRACE(200 + it);
         const int nb = min(C::KB, p.nblk - c * C::KB);
         const uint8_t *src = rsrc + (long long)c * C::KB * C::BB;
         const uint32_t padb = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15);
@@ -247,7 +272,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
     for (int i = ctid; i < n16; i += kNW * 32) reinterpret_cast<uint4 *>(xq)[i] = make_uint4(0, 0, 0, 0);
   }
   consumer_sync();
+  TRACE(3);
   pdl_wait_prior_grid();  // x (and y / the addend) may be produced by the preceding kernel
+  TRACE(4);
   {  // quantise x: per group sx = max|x| / 16256, n = rint(x / sx) = 128*hi + lo
     const int k8n = K >> 3, items = NB * k8n;
     constexpr int LPG = C::GROUP / 8;  // lanes per scale group
@@ -293,6 +320,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
     }
   }
   consumer_sync();
+  TRACE(5);
 
   const int g = lane >> 2, t = lane & 3;
   const int sub = t & 1, bt = (t >> 1) & (NB - 1);  // this lane's group slot and batch row
@@ -303,19 +331,54 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
   // this lane's 16 bytes of a unit's B fragments
   const uint8_t *xlane = xq + ((g & (NCX - 1)) * 4 + t) * 16;
 
-  long long best = LLONG_MIN;  // fused top-1: this thread's running maximum
+  long long best[NB];  // fused top-1: running maximum of row `warp` of every tile (lane 0)
+#pragma unroll
+  for (int b = 0; b < NB; b++) best[b] = LLONG_MIN;
 
-  int it = 0, tcount = 0;
+  // Sum of the 16 warps' partial results of tile number `tn` (row tile index `tl`): warp w folds
+  // row w.  The 32 partials of a (row, batch row) pair sit one per lane and are added by a
+  // fixed butterfly, so the result does not depend on timing.  A tile is folded one tile late
+  // (after the next tile's MMAs), when all partials have long been written: nobody waits.
+  auto fold_tile = [&](int tl, int tn) {
+    mbar_wait(smem_u32(&bars[2 * S + (tn & 1)]), (tn >> 1) & 1);
+    const float2 *rb = red + (size_t)(tn & 1) * (kNW * 32);
+    const int gg = warp & 7, upper = warp >> 3;
+    const int row = tl * kR + warp;
+#pragma unroll
+    for (int b = 0; b < NB; b++) {
+      const float2 pv = rb[(lane >> 1) * 32 + gg * 4 + 2 * b + (lane & 1)];
+      float v = upper ? pv.y : pv.x;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+      if (lane == 0 && row < p.out_dim) {
+        if (p.part_keys) {
+          const long long key = top1_key(v, (uint32_t)(p.index_base + row));
+          best[b] = key > best[b] ? key : best[b];
+        } else {
+          const float a = p.addend ? p.addend[(long long)b * p.addend_stride + row] : 0.f;
+          p.y[(long long)b * p.out_dim + row] = a + v;
+        }
+      }
+    }
+  };
+
+  const uintptr_t wbase = reinterpret_cast<uintptr_t>(p.w);
+  int it = 0, tcount = 0, prev_tile = 0;
   for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, tcount++) {
     float acc0 = 0.f, acc1 = 0.f;  // rows g and g+8 of (group slot sub, batch row bt)
-    const uintptr_t wbase = reinterpret_cast<uintptr_t>(p.w);
-    const int pad_a = (int)((wbase + ((long long)tile * kR + g) * p.row_bytes) & 15);
-    const int pad_b = (int)((wbase + ((long long)tile * kR + g + 8) * p.row_bytes) & 15);
-    const int pad_d = (int)((wbase + ((long long)tile * kR + (lane & 15)) * p.row_bytes) & 15);
+    // byte offset of a row's data inside its stage slot; only Q6_K rows can be unaligned
+    int pad_a = 0, pad_b = 0, pad_d = 0;
+    if (TYPE == kQ6_K) {
+      pad_a = (int)((wbase + ((long long)tile * kR + g) * p.row_bytes) & 15);
+      pad_b = (int)((wbase + ((long long)tile * kR + g + 8) * p.row_bytes) & 15);
+      pad_d = (int)((wbase + ((long long)tile * kR + (lane & 15)) * p.row_bytes) & 15);
+    }
 
     for (int c = 0; c < p.nchunks; c++, it++) {
       const int s = it % S;
+      TRACE(300 + it);
       mbar_wait(smem_u32(&bars[s]), (it / S) & 1);
+      TRACE(400 + it);
       const int kblk = c * C::KB + wkb;
       if (kblk < p.nblk && p.debug != 1) {
         const uint8_t *stage = stages + (size_t)s * p.stage_bytes + wkb * C::BB;
@@ -402,33 +465,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars[S + s]));
+      TRACE(500 + it);
     }
 
-    // fixed-order sum of the warps' partial tiles
-    float2 *rbuf = red + (size_t)(tcount & 1) * (kNW * 32);
-    rbuf[warp * 32 + lane] = make_float2(acc0, acc1);
-    consumer_sync();
-    if (ctid < 16 * NB) {
-      const int r16 = ctid & 15, b = ctid >> 4;
-      const int gg = r16 & 7, upper = r16 >> 3;
-      float v = 0.f;
-#pragma unroll
-      for (int ww = 0; ww < kNW; ww++) {
-        const float2 pa = rbuf[ww * 32 + gg * 4 + 2 * b], pb = rbuf[ww * 32 + gg * 4 + 2 * b + 1];
-        v += upper ? (pa.y + pb.y) : (pa.x + pb.x);
-      }
-      const int row = tile * kR + r16;
-      if (row < p.out_dim) {
-        if (p.part_keys) {
-          const long long key = top1_key(v, (uint32_t)(p.index_base + row));
-          best = key > best ? key : best;
-        } else {
-          const float a = p.addend ? p.addend[(long long)b * p.addend_stride + row] : 0.f;
-          p.y[(long long)b * p.out_dim + row] = a + v;
-        }
-      }
-    }
+    // hand this tile's partial sums over; fold the previous tile while they trickle in
+    if (tcount > 0) fold_tile(prev_tile, tcount - 1);
+    red[(size_t)(tcount & 1) * (kNW * 32) + warp * 32 + lane] = make_float2(acc0, acc1);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&bars[2 * S + (tcount & 1)]));
+    TRACE(600 + tcount);
+    prev_tile = tile;
   }
+  if (tcount > 0) fold_tile(prev_tile, tcount - 1);
 
   if (p.part_keys == nullptr) return;
 
@@ -438,7 +486,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
   __shared__ bool s_last;
   if (ctid < 2) s_best[ctid] = LLONG_MIN;
   consumer_sync();
-  if (ctid < 16 * NB) atomicMax(&s_best[ctid >> 4], best);
+  if (lane == 0) {
+#pragma unroll
+    for (int b = 0; b < NB; b++) atomicMax(&s_best[b], best[b]);
+  }
   consumer_sync();
   const int nparts = gridDim.x;
   if (ctid < NB) p.part_keys[(long long)ctid * nparts + blockIdx.x] = s_best[ctid];
@@ -503,7 +554,7 @@ bool make_plan(int in_dim, int out_dim, int nb, Params &p, size_t &smem) {
   const size_t stage_bytes = al((size_t)kR * C::RS);
   if (off_stage + 3 * stage_bytes > kDynSmemMax) return false;
   int stages = (int)((kDynSmemMax - off_stage) / stage_bytes);
-  if (stages > 8) stages = 8;
+  if (stages > 7) stages = 7;  // 2*stages + 2 mbarriers live in the first 128 bytes
   p.in_dim = in_dim; p.out_dim = out_dim;
   p.nblk = nblk; p.nchunks = (nblk + C::KB - 1) / C::KB; p.ntiles = (out_dim + kR - 1) / kR;
   p.stages = stages; p.row_bytes = (long long)nblk * C::BB;
@@ -607,6 +658,14 @@ int launch_gemv_top1_imma(int type, const void *d_w, const float *d_x, int in_di
     default: return COGNI_QMM_ERR_TYPE;
   }
 }
+
+#ifdef COGNI_TRACE
+}  // namespace cogni
+extern "C" int cogni_qmm_debug_trace(long long *out, int n) {
+  return (int)cudaMemcpyFromSymbol(out, cogni::g_trace, (size_t)n * 8);
+}
+namespace cogni {
+#endif
 
 unsigned gemv_imma_timeouts() {
   unsigned v = 0;
