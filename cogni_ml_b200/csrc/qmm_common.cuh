@@ -86,6 +86,7 @@ __host__ __device__ __forceinline__ float float_from_orderable(int32_t o) {
 // key = (orderable(value) << 32) | (0xFFFFFFFF - index): a signed MAX picks the highest
 // value and, among equal values, the lowest index.
 __host__ __device__ __forceinline__ long long top1_key(float v, uint32_t index) {
+  v += 0.f;  // -0.0 -> +0.0: the CPU reference compares them equal
   return (long long)(((unsigned long long)(uint32_t)orderable_from_float(v) << 32) |
                      (unsigned long long)(0xFFFFFFFFu - index));
 }

@@ -1,0 +1,124 @@
+"""Row / vocabulary sharding of the quantized matmul over the GPUs of one box.
+
+Output rows are independent (y[o] reads only row o of W and all of x), and rows are stored back to
+back in the GGUF tensor, so rank g of G owns the contiguous row range shard_rows(N, g, G) — a
+contiguous byte range of the raw tensor — and x is replicated.  There is exactly one exchange
+step per matmul:
+
+  * ShardedQuantWeight.gemv: each rank writes its [batch, rows] result into slot `rank` of a
+    [G, batch, rows] buffer, one all-gather fills the other slots (NCCL over NVLink on GPUs);
+  * ShardedLmHead.top1: each rank's fused GEMV + top-1 yields one int64 key per batch row,
+    key = (orderable(value) << 32) | (0xFFFFFFFF - global_index); a MAX all-reduce of the keys
+    picks the highest value and, among equal values, the lowest index — the reference's tie rule
+    (src/ml/gguf/qwen35_cpu.cr:2052-2055).
+
+One process per GPU, torch.distributed for the plumbing.  The local compute is a
+DeviceQuantWeight; `local_factory` lets the host logic run under gloo on CPU in tests with a
+stand-in for the device kernels.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from .quant_matmul import QuantWeight, row_bytes
+
+
+def shard_rows(out_dim: int, rank: int, world: int) -> Tuple[int, int]:
+    """Contiguous row range of `rank`: sizes differ by at most one row, earlier ranks get the extra."""
+    if not 0 <= rank < world:
+        raise ValueError("rank must be in [0, world)")
+    base, extra = divmod(out_dim, world)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def shard_bytes(qw: QuantWeight, rank: int, world: int) -> np.ndarray:
+    """The raw GGUF bytes of this rank's rows: a slice, never a repack."""
+    r0, r1 = shard_rows(qw.out_dim, rank, world)
+    rb = row_bytes(qw.type, qw.in_dim)
+    return qw.raw[r0 * rb:r1 * rb]
+
+
+def pack_top1_key(value: np.ndarray, index: np.ndarray) -> np.ndarray:
+    """Host restatement of the device key: int64 (orderable(value) << 32) | (0xFFFFFFFF - index)."""
+    value = np.asarray(value, dtype=np.float32) + np.float32(0.0)   # -0.0 -> +0.0
+    bits = value.view(np.int32).astype(np.int64)
+    ordv = np.where(bits >= 0, bits, bits ^ 0x7FFFFFFF)          # signed order == float order
+    low = (0xFFFFFFFF - np.asarray(index, dtype=np.int64)) & 0xFFFFFFFF
+    return (ordv << 32) | low
+
+
+def unpack_top1_key(key: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
+    key = np.asarray(key, dtype=np.int64)
+    ordv = (key >> 32).astype(np.int32)
+    bits = np.where(ordv >= 0, ordv, ordv ^ 0x7FFFFFFF).astype(np.int32)
+    index = (0xFFFFFFFF - (key & 0xFFFFFFFF)).astype(np.int64)
+    return index.astype(np.int32), bits.view(np.float32)
+
+
+def _default_factory(qw: QuantWeight, r0: int, r1: int, device):
+    from .quant_matmul import DeviceQuantWeight
+    return DeviceQuantWeight.upload(qw, device, r0, r1)
+
+
+class ShardedQuantWeight:
+    """This rank's row shard of a quantized weight plus the all-gather of the outputs."""
+
+    def __init__(self, qw: QuantWeight, device, group: Optional[dist.ProcessGroup] = None,
+                 local_factory: Callable = _default_factory):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.out_dim, self.in_dim = qw.out_dim, qw.in_dim
+        if qw.out_dim % self.world:
+            raise ValueError("out_dim must divide evenly over the ranks for the gathered layout")
+        self.rows = qw.out_dim // self.world
+        self.r0, self.r1 = shard_rows(qw.out_dim, self.rank, self.world)
+        self.device = torch.device(device)
+        self.local = local_factory(qw, self.r0, self.r1, self.device)
+        self._gather: Optional[torch.Tensor] = None
+
+    def gather_buffer(self, batch: int) -> torch.Tensor:
+        if self._gather is None or self._gather.shape[1] != batch:
+            self._gather = torch.empty(self.world, batch, self.rows, dtype=torch.float32,
+                                       device=self.device)
+        return self._gather
+
+    def gemv(self, x: torch.Tensor) -> torch.Tensor:
+        """x f32 [batch, in_dim] (replicated) -> y f32 [batch, out_dim] on every rank."""
+        batch = x.numel() // self.in_dim
+        buf = self.gather_buffer(batch)
+        self.local.gemv(x, out=buf[self.rank])
+        if self.world > 1:
+            dist.all_gather_into_tensor(buf.view(-1), buf[self.rank].reshape(-1), group=self.group)
+        # [G, batch, rows] -> [batch, G*rows]: rank g's rows are columns [g*rows, (g+1)*rows)
+        return buf.permute(1, 0, 2).reshape(batch, self.out_dim)
+
+
+class ShardedLmHead:
+    """Vocabulary-sharded fused lm_head: per-shard top-1, one MAX all-reduce of int64 keys."""
+
+    def __init__(self, qw: QuantWeight, device, group: Optional[dist.ProcessGroup] = None,
+                 local_factory: Callable = _default_factory):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.r0, self.r1 = shard_rows(qw.out_dim, self.rank, self.world)
+        self.device = torch.device(device)
+        self.in_dim = qw.in_dim
+        self.local = local_factory(qw, self.r0, self.r1, self.device)
+
+    def top1(self, x: torch.Tensor):
+        """(index int32 [batch], value f32 [batch]) of the global maximum, identical on all ranks."""
+        _idx, _val, key = self.local.gemv_top1(x, want_keys=True)
+        if self.world > 1:
+            dist.all_reduce(key, op=dist.ReduceOp.MAX, group=self.group)
+        if key.is_cuda:
+            from .quant_matmul import unpack_top1_keys
+            return unpack_top1_keys(key)
+        idx, val = unpack_top1_key(key.numpy())
+        return torch.from_numpy(idx.copy()), torch.from_numpy(val.copy())
