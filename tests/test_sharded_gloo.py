@@ -109,7 +109,7 @@ def test_top1_key_order_and_round_trip():
     # once +inf is removed
     assert list(vals[order][:2]) == [-np.inf, -3.5]
     assert keys[6] > keys[5]                   # equal values: lower index has the larger key
-    assert keys[2] > keys[3]                   # -0.0 == +0.0 as values: the lower index wins
+    assert keys[3] > keys[2]                   # -0.0 == +0.0 as values: index 6 beats index 7
     i2, v2 = unpack_top1_key(keys)
     assert np.array_equal(i2, idx.astype(np.int32))
     assert np.array_equal(v2, vals)
