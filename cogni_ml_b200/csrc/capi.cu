@@ -56,7 +56,7 @@ int cogni_qmm_set_kernel_choice(int choice) {
   return COGNI_QMM_OK;
 }
 
-unsigned cogni_qmm_wait_timeouts(void) { return gemv_mma_timeouts() + gemv_imma_timeouts(); }
+unsigned cogni_qmm_wait_timeouts(void) { return gemv_mma_timeouts() + gemv_imma_timeouts() + gemm_prefill_timeouts(); }
 
 int cogni_qmm_block_bytes(int type) { return block_bytes(type); }
 int cogni_qmm_block_elements(int type) { return block_elems(type); }

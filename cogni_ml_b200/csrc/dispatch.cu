@@ -48,8 +48,5 @@ int launch_top1_unpack(const long long *d_keys, int batch, int32_t *d_idx, float
   return (int)cudaGetLastError();
 }
 
-int launch_gemm_prefill(int, const void *, const void *, void *, int, int, int, int, cudaStream_t) {
-  return COGNI_QMM_ERR_TYPE;
-}
 
 }  // namespace cogni

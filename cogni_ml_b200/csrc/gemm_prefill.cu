@@ -1,0 +1,453 @@
+// Chunked-prefill GEMM with dequantisation fused into the tile loop (sm_100a, tcgen05 + TMEM).
+//
+//     y[m, n] = sum_k bf16(x[m, k]) * bf16(dequant(W[n, k]))        fp32 accumulation in TMEM
+//
+// One CTA computes a 128 (weight rows n) x BN (tokens m) tile of y^T:
+//   * A operand = weights.  Four dequant warps read the raw GGUF superblocks of their 128 rows
+//     straight from global memory (L2-resident across the token tiles), rebuild the f32 weight
+//     with the reference's operation order (src/ml/gguf/dequant.cr), round it to bf16 and write
+//     a 128 x 64 K-major tile into shared memory in the 128-byte-swizzled canonical layout.
+//   * B operand = activations.  One thread issues a TMA tile load (bf16 [BN x 64], 128-byte
+//     swizzle) per k-step.
+//   * One thread issues tcgen05.mma (kind::f16, M = 128, N = BN, K = 16) four times per k-step,
+//     accumulating in BN columns of tensor memory, and tcgen05.commit releases the stage.
+//   * After the last k-step the same four warps read the accumulator back with tcgen05.ld
+//     (each warp owns 32 TMEM lanes = 32 weight rows) and store y[m, n]: for a fixed token the
+//     warp's 32 lanes write 32 consecutive n, one 128-byte segment.
+// A 4-stage mbarrier ring decouples the three roles.  Every wait is bounded (tma_pipe.cuh).
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "qmm_common.cuh"
+#include "tma_pipe.cuh"
+
+namespace cogni {
+namespace {
+
+constexpr int kBM = 128;      // weight rows per tile (UMMA M)
+constexpr int kBK = 64;       // k elements per stage: 128 bytes of bf16 = one swizzle row
+constexpr int kStages = 4;
+constexpr int kThreads = 192; // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: dequant + epilogue
+constexpr int kATile = kBM * kBK * 2;  // 16 KB
+
+struct GemmParams {
+  const uint8_t *w;
+  void *y;
+  int m_rows, n_out, k_in, out_bf16;
+  long long row_bytes;
+};
+
+// ---------------------------------------------------------------------------- tcgen05 wrappers
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
+      "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// 2-D TMA tile load (no multicast), completion in bytes on an mbarrier.  c0 (the innermost
+// coordinate) times the element size must be a multiple of 16 bytes: here c0 = 64 * k-step.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tmap, int c0, int c1,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], "
+      "[%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(tmap), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, rows of 128 bytes, SWIZZLE_128B, 8-row groups
+// 1024 bytes apart (start >> 4 | LBO 1 | SBO 64 | version 1 | layout type 2).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr & 0x3FFFF) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+// Instruction descriptor: D = f32, A = B = bf16, both K-major, M x N.
+__host__ __device__ constexpr uint32_t idesc_bf16(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+// byte i of v as an exact float
+__device__ __forceinline__ float byte_f(uint32_t v, int i) {
+  return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7650 + i)) - 8388608.f;
+}
+// Stores chunk c (8 consecutive k elements = 16 bytes) of tile row r at its swizzled position.
+__device__ __forceinline__ void store_chunk(uint8_t *tile, int r, int c, uint4 v) {
+  *reinterpret_cast<uint4 *>(tile + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+}
+
+// ---------------------------------------------------------------------------- raw block fetch
+// N 32-bit words starting at a 2-byte aligned global address (aligned loads + funnel shift).
+template <int N>
+__device__ __forceinline__ void ldg_words_unaligned(const uint8_t *p, uint32_t (&out)[N]) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  const uint32_t *q = reinterpret_cast<const uint32_t *>(a & ~(uintptr_t)3);
+  const uint32_t sh = (uint32_t)(a & 2) * 8;
+  uint32_t prev = __ldg(q);
+#pragma unroll
+  for (int i = 0; i < N; i++) {
+    const uint32_t next = __ldg(q + i + 1);
+    out[i] = __funnelshift_r(prev, next, sh);
+    prev = next;
+  }
+}
+
+// The raw bytes one thread needs to rebuild 64 consecutive weights (one k-step) of its row.
+template <int TYPE> struct Raw;
+template <> struct Raw<kQ4_K> { uint4 hdr, q0, q1; };
+template <> struct Raw<kQ5_K> { uint4 hdr, h0, h1, q0, q1; };
+template <> struct Raw<kQ6_K> { uint32_t ql[16], qh[8], sc[2]; uint32_t d; };
+
+template <int TYPE>
+__device__ __forceinline__ void fetch_raw(const uint8_t *row, int ks, Raw<TYPE> &r) {
+  const uint8_t *blk = row + (size_t)(ks >> 2) * BlockGeom<TYPE>::bytes;
+  const int j = ks & 3;
+  if constexpr (TYPE == kQ4_K) {
+    r.hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
+    r.q0 = __ldg(reinterpret_cast<const uint4 *>(blk + 16 + 32 * j));
+    r.q1 = __ldg(reinterpret_cast<const uint4 *>(blk + 32 + 32 * j));
+  } else if constexpr (TYPE == kQ5_K) {
+    r.hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
+    r.h0 = __ldg(reinterpret_cast<const uint4 *>(blk + 16));
+    r.h1 = __ldg(reinterpret_cast<const uint4 *>(blk + 32));
+    r.q0 = __ldg(reinterpret_cast<const uint4 *>(blk + 48 + 32 * j));
+    r.q1 = __ldg(reinterpret_cast<const uint4 *>(blk + 64 + 32 * j));
+  } else {
+    const int n = j >> 1;
+    ldg_words_unaligned<16>(blk + 64 * n, r.ql);
+    ldg_words_unaligned<8>(blk + 128 + 32 * n, r.qh);
+    ldg_words_unaligned<2>(blk + 192 + 8 * n, r.sc);
+    r.d = __ldg(reinterpret_cast<const unsigned short *>(blk + 208));
+  }
+}
+
+// 6-bit (scale, min) pair s of a Q4_K / Q5_K header held in registers (dequant.cr:240-249)
+__device__ __forceinline__ void scale_min_regs(const uint4 &h, int s, float &sc, float &mn) {
+  const uint32_t u0 = h.y, u1 = h.z, u2 = h.w;
+  uint32_t a, b;
+  if (s < 4) {
+    a = (u0 >> (8 * s)) & 63;
+    b = (u1 >> (8 * s)) & 63;
+  } else {
+    const int t = 8 * (s - 4);
+    a = ((u2 >> t) & 0xF) | (((u0 >> (t + 6)) & 3) << 4);
+    b = ((u2 >> (t + 4)) & 0xF) | (((u1 >> (t + 6)) & 3) << 4);
+  }
+  sc = (float)a;
+  mn = (float)b;
+}
+
+// Rebuilds the 64 weights of k-step ks of tile row r as bf16 and stores them swizzled.
+template <int TYPE>
+__device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, uint8_t *tile, int r,
+                                             bool valid) {
+  if (!valid) {
+#pragma unroll
+    for (int c = 0; c < 8; c++) store_chunk(tile, r, c, make_uint4(0, 0, 0, 0));
+    return;
+  }
+  const int j = ks & 3;
+  if constexpr (TYPE == kQ4_K || TYPE == kQ5_K) {
+    const __half2 dd = *reinterpret_cast<const __half2 *>(&raw.hdr.x);
+    const float d = __low2float(dd), dmin = __high2float(dd);
+    const uint32_t qw[8] = {raw.q0.x, raw.q0.y, raw.q0.z, raw.q0.w,
+                            raw.q1.x, raw.q1.y, raw.q1.z, raw.q1.w};
+    uint32_t hw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if constexpr (TYPE == kQ5_K) {
+      hw[0] = raw.h0.x; hw[1] = raw.h0.y; hw[2] = raw.h0.z; hw[3] = raw.h0.w;
+      hw[4] = raw.h1.x; hw[5] = raw.h1.y; hw[6] = raw.h1.z; hw[7] = raw.h1.w;
+    }
+#pragma unroll
+    for (int half = 0; half < 2; half++) {       // low nibbles: sub-block 2j, high: 2j+1
+      float sc, mn;
+      scale_min_regs(raw.hdr, 2 * j + half, sc, mn);
+      const float d1 = __fmul_rn(d, sc), m1 = __fmul_rn(dmin, mn);
+#pragma unroll
+      for (int c4 = 0; c4 < 4; c4++) {           // 8 elements: bytes 8*c4 .. 8*c4+7
+        uint32_t out[4];
+#pragma unroll
+        for (int w2 = 0; w2 < 2; w2++) {
+          uint32_t q = (qw[2 * c4 + w2] >> (4 * half)) & 0x0f0f0f0fu;
+          if constexpr (TYPE == kQ5_K)
+            q |= ((hw[2 * c4 + w2] >> (2 * j + half)) & 0x01010101u) << 4;
+          const float w0 = __fmaf_rn(d1, byte_f(q, 0), -m1), w1 = __fmaf_rn(d1, byte_f(q, 1), -m1);
+          const float w2f = __fmaf_rn(d1, byte_f(q, 2), -m1), w3 = __fmaf_rn(d1, byte_f(q, 3), -m1);
+          out[2 * w2] = pack_bf16(w0, w1);
+          out[2 * w2 + 1] = pack_bf16(w2f, w3);
+        }
+        store_chunk(tile, r, 4 * half + c4, make_uint4(out[0], out[1], out[2], out[3]));
+      }
+    }
+  } else {
+    const float d = __half2float(__ushort_as_half((unsigned short)raw.d));
+    const int hi = j & 1;
+#pragma unroll
+    for (int c = 0; c < 8; c++) {
+      const int kk = 2 * hi + (c >> 2);          // which of the four 32-element runs of the half
+      const int sidx = ((c & 3) >> 1) + 2 * kk;  // scale within the half: l/16 + 2*kk
+      // sidx >> 2 == hi for every chunk, sidx & 3 is a compile-time constant per chunk
+      const uint32_t scw = hi ? raw.sc[1] : raw.sc[0];
+      const int scb = (int)(int8_t)((scw >> (8 * ((((c & 3) >> 1) + 2 * (c >> 2)) & 3))) & 0xff);
+      (void)sidx;
+      const float dsc = __fmul_rn(d, (float)scb);
+      uint32_t out[4];
+#pragma unroll
+      for (int w2 = 0; w2 < 2; w2++) {
+        const uint32_t qlw = raw.ql[8 * (c >> 2) + 2 * (c & 3) + w2];
+        const uint32_t qhw = raw.qh[2 * (c & 3) + w2];
+        const uint32_t q = ((qlw >> (4 * hi)) & 0x0f0f0f0fu) | (((qhw >> (2 * kk)) & 0x03030303u) << 4);
+        const float w0 = __fmul_rn(dsc, byte_f(q, 0) - 32.f), w1 = __fmul_rn(dsc, byte_f(q, 1) - 32.f);
+        const float w2f = __fmul_rn(dsc, byte_f(q, 2) - 32.f), w3 = __fmul_rn(dsc, byte_f(q, 3) - 32.f);
+        out[2 * w2] = pack_bf16(w0, w1);
+        out[2 * w2 + 1] = pack_bf16(w2f, w3);
+      }
+      store_chunk(tile, r, c, make_uint4(out[0], out[1], out[2], out[3]));
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------- the kernel
+template <int TYPE, int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+  constexpr int kBTile = BN * kBK * 2;
+  constexpr int kStageBytes = kATile + kBTile;
+  extern __shared__ uint8_t smem_raw[];
+  // stage tiles must sit on 1024-byte boundaries (the swizzle pattern repeats every 1024 bytes)
+  uint8_t *smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kStages * kStageBytes);
+  // bars: full_a[S] | full_b[S] | empty[S] | acc_full ; then the TMEM base address slot
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * kStages + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * kBM, m0 = blockIdx.y * BN;
+  const int nks = p.k_in / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; s++) {
+      mbar_init(smem_u32(&bars[s]), 4);                    // full_a: one arrive per dequant warp
+      mbar_init(smem_u32(&bars[kStages + s]), 1);          // full_b: the TMA thread
+      mbar_init(smem_u32(&bars[2 * kStages + s]), 1);      // empty: tcgen05.commit
+    }
+    mbar_init(smem_u32(&bars[3 * kStages]), 1);            // accumulator complete
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- activations via TMA
+    if (lane == 0) {
+      for (int ks = 0; ks < nks; ks++) {
+        const int s = ks % kStages;
+        mbar_wait(smem_u32(&bars[2 * kStages + s]), ((ks / kStages) & 1) ^ 1);
+        const uint32_t full = smem_u32(&bars[kStages + s]);
+        mbar_arrive_expect_tx(full, kBTile);
+        tma_load_2d(smem_u32(smem + s * kStageBytes + kATile), &tmap_x, ks * kBK, m0, full);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issue
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_bf16(kBM, BN);
+      for (int ks = 0; ks < nks; ks++) {
+        const int s = ks % kStages;
+        const uint32_t ph = (ks / kStages) & 1;
+        mbar_wait(smem_u32(&bars[s]), ph);
+        mbar_wait(smem_u32(&bars[kStages + s]), ph);
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
+        const uint32_t b_addr = a_addr + kATile;
+#pragma unroll
+        for (int k = 0; k < kBK / 16; k++)   // 16 bf16 = 32 bytes further along the swizzled row
+          umma_bf16(tmem_base, smem_desc_sw128(a_addr + 32 * k), smem_desc_sw128(b_addr + 32 * k),
+                    idesc, (ks | k) != 0);
+        umma_commit(smem_u32(&bars[2 * kStages + s]));     // frees the stage when the MMAs are done
+      }
+      umma_commit(smem_u32(&bars[3 * kStages]));           // accumulator ready
+    }
+  } else {
+    // ---------------------------------------------------------------- dequant producers
+    const int r = threadIdx.x - 64;                        // tile row 0..127
+    const bool valid = n0 + r < p.n_out;
+    const uint8_t *row = p.w + (long long)(valid ? n0 + r : 0) * p.row_bytes;
+    Raw<TYPE> cur, nxt;
+    fetch_raw<TYPE>(row, 0, cur);
+    for (int ks = 0; ks < nks; ks++) {
+      const int s = ks % kStages;
+      if (ks + 1 < nks) fetch_raw<TYPE>(row, ks + 1, nxt);  // in flight while this k-step expands
+      mbar_wait(smem_u32(&bars[2 * kStages + s]), ((ks / kStages) & 1) ^ 1);
+      expand_kstep<TYPE>(cur, ks, smem + s * kStageBytes, r, valid);
+      fence_async_smem();                                   // generic-proxy writes -> tensor core
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars[s]));
+      cur = nxt;
+    }
+
+    // ---------------------------------------------------------------- epilogue
+    mbar_wait(smem_u32(&bars[3 * kStages]), 0);
+    tc_fence_after();
+    const int q = warp & 3;                                // TMEM lane quarter this warp may read
+    const int n = n0 + 32 * q + lane;
+    const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16);
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+      uint32_t v[32];
+      tmem_ld32(taddr + c0, v);
+      tmem_ld_wait();
+      if (n < p.n_out) {
+#pragma unroll
+        for (int jj = 0; jj < 32; jj++) {
+          const int m = m0 + c0 + jj;
+          if (m < p.m_rows) {
+            const float f = __uint_as_float(v[jj]);
+            if (p.out_bf16)
+              reinterpret_cast<__nv_bfloat16 *>(p.y)[(long long)m * p.n_out + n] = __float2bfloat16_rn(f);
+            else
+              reinterpret_cast<float *>(p.y)[(long long)m * p.n_out + n] = f;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, BN);
+}
+
+// ---------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+template <int TYPE, int BN>
+int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows, int n_out,
+           int k_in, cudaStream_t s) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (!encode) return COGNI_QMM_ERR_DEVICE;
+  CUtensorMap tmap;
+  const cuuint64_t dims[2] = {(cuuint64_t)k_in, (cuuint64_t)m_rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)k_in * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)BN};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult cr = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(d_x), dims,
+                       strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (cr != CUDA_SUCCESS) return (int)cr;
+  constexpr int smem = kStages * (kATile + BN * kBK * 2) + 1024 /*alignment*/ + 256 /*barriers*/;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_prefill_kernel<TYPE, BN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured[dev] = true;
+  }
+  GemmParams p;
+  p.w = static_cast<const uint8_t *>(d_w);
+  p.y = d_y;
+  p.m_rows = m_rows; p.n_out = n_out; p.k_in = k_in;
+  p.out_bf16 = out_type == COGNI_QMM_OUT_BF16;
+  p.row_bytes = (long long)(k_in / 256) * BlockGeom<TYPE>::bytes;
+  dim3 grid((n_out + kBM - 1) / kBM, (m_rows + BN - 1) / BN);
+  gemm_prefill_kernel<TYPE, BN><<<grid, kThreads, smem, s>>>(tmap, p);
+  return (int)cudaGetLastError();
+}
+
+template <int TYPE>
+int launch_typed(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows, int n_out,
+                 int k_in, cudaStream_t s) {
+  // 256-token tiles halve the dequant work per flop; fall back to 128 when that would leave
+  // most SMs without a tile
+  const long long tiles256 = (long long)((n_out + kBM - 1) / kBM) * ((m_rows + 255) / 256);
+  if (m_rows > 128 && tiles256 >= 120)
+    return launch<TYPE, 256>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, s);
+  return launch<TYPE, 128>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, s);
+}
+
+}  // namespace
+
+int launch_gemm_prefill(int type, const void *d_w, const void *d_x_bf16, void *d_y, int out_type,
+                        int m_rows, int n_out, int k_in, cudaStream_t s) {
+  switch (type) {
+    case kQ4_K: return launch_typed<kQ4_K>(d_w, d_x_bf16, d_y, out_type, m_rows, n_out, k_in, s);
+    case kQ5_K: return launch_typed<kQ5_K>(d_w, d_x_bf16, d_y, out_type, m_rows, n_out, k_in, s);
+    case kQ6_K: return launch_typed<kQ6_K>(d_w, d_x_bf16, d_y, out_type, m_rows, n_out, k_in, s);
+    default: return COGNI_QMM_ERR_TYPE;
+  }
+}
+
+unsigned gemm_prefill_timeouts() {
+  unsigned v = 0;
+  cudaMemcpyFromSymbol(&v, g_pipe_wait_timeouts, sizeof(v));
+  return v;
+}
+
+}  // namespace cogni

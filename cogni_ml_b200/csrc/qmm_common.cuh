@@ -125,6 +125,7 @@ int launch_gemv_top1_imma(int type, const void *d_w, const float *d_x, int in_di
                           int batch, int32_t index_base, void *d_scratch, int32_t *d_idx,
                           float *d_val, long long *d_key, int resident, cudaStream_t s);
 unsigned gemv_imma_timeouts();
+unsigned gemm_prefill_timeouts();
 void gemv_imma_set_debug(int mode);
 
 // Kernel selection (dispatch.cu): picks the tiled kernel when the shape allows it, else the

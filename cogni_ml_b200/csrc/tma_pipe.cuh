@@ -10,7 +10,7 @@
 
 namespace cogni {
 
-constexpr unsigned long long kPipeWaitLimitNs = 2000000000ull;
+constexpr unsigned long long kPipeWaitLimitNs = 1000000000ull;
 
 // one counter per translation unit that includes this header; summed by the host accessor
 static __device__ unsigned int g_pipe_wait_timeouts;
@@ -47,15 +47,20 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Waits for the phase with the given parity; gives up after kPipeWaitLimitNs.
+// Waits for the phase with the given parity; gives up after kPipeWaitLimitNs.  Once any wait of
+// the process has expired, later waits give up at their first slow-path check, so a broken
+// pipeline costs one time limit in total rather than one per wait.
 __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return;
   const unsigned long long t0 = global_ns();
   for (unsigned spin = 1;; spin++) {
     if (mbar_try_wait(bar, parity)) return;
-    if ((spin & 63u) == 0 && global_ns() - t0 > kPipeWaitLimitNs) {
-      atomicAdd(&g_pipe_wait_timeouts, 1u);
-      return;
+    if ((spin & 63u) == 0) {
+      if (*reinterpret_cast<volatile unsigned int *>(&g_pipe_wait_timeouts) != 0u) return;
+      if (global_ns() - t0 > kPipeWaitLimitNs) {
+        atomicAdd(&g_pipe_wait_timeouts, 1u);
+        return;
+      }
     }
   }
 }

@@ -1,0 +1,58 @@
+"""Prefill GEMM (dequant-fused, bf16 operands on the tensor cores) against the CPU oracle.
+
+Two references per case:
+  * tight: the oracle's f32 dequantised weights rounded to bf16, times the bf16 activations, in
+    f64 — the kernel's exact operand set, so only fp32 accumulation order differs
+    (tolerance 1e-4 * |y|inf);
+  * the stated acceptance: the CPU QuantMatmul on the same bf16 activations without rounding the
+    weights, on a row subset, relative error <= 2e-2 * |y|inf.
+"""
+import numpy as np
+import pytest
+import torch
+
+from cogni_ml_b200 import DeviceQuantWeight, QuantWeight, synth
+
+pytestmark = pytest.mark.gpu
+Q4_K, Q5_K, Q6_K = synth.Q4_K, synth.Q5_K, synth.Q6_K
+
+
+def bf16_round(a: np.ndarray) -> np.ndarray:
+    return torch.from_numpy(np.ascontiguousarray(a, np.float32)).bfloat16().float().numpy()
+
+
+def run_case(cuda, oracle, qtype, m, n, k, seed, out_dtype=torch.float32):
+    w = synth.make_weight(qtype, n, k, seed=seed, tensor_id=qtype)
+    x = bf16_round(synth.make_activation(m, k, seed=seed))
+    dw = DeviceQuantWeight.upload(QuantWeight(w, qtype, n, k), cuda)
+    xd = torch.from_numpy(x).to(cuda).bfloat16()
+    y = dw.gemm(xd, out_dtype=out_dtype).float().cpu().numpy()
+    wq = bf16_round(oracle.dequantize(qtype, w, n * k)).reshape(n, k).astype(np.float64)
+    ref = x.astype(np.float64) @ wq.T
+    return w, x, y, ref
+
+
+@pytest.mark.parametrize("qtype", [Q4_K, Q5_K, Q6_K])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 256), (256, 256, 512), (200, 200, 768), (1, 37, 256),
+                                   (300, 1000, 1024)])
+def test_gemm_matches_bf16_operand_reference(cuda, oracle, engine, qtype, m, n, k):
+    w, x, y, ref = run_case(cuda, oracle, qtype, m, n, k, seed=3)
+    assert y.shape == (m, n) and not np.isnan(y).any()
+    assert np.abs(y - ref).max() <= 1e-4 * np.abs(ref).max()
+    assert engine.lib.cogni_qmm_wait_timeouts() == 0
+
+
+@pytest.mark.parametrize("qtype,n,k", [(Q4_K, 1024, 4096), (Q6_K, 512, 12288)])
+def test_gemm_within_stated_tolerance_of_cpu_quant_matmul(cuda, oracle, qtype, n, k):
+    m = 512
+    w, x, y, ref = run_case(cuda, oracle, qtype, m, n, k, seed=5)
+    assert np.abs(y - ref).max() <= 1e-4 * np.abs(ref).max()
+    rows = [0, 1, 255, 256, 511]                              # row subset through the CPU QuantMatmul
+    full = np.stack([oracle.matmul_add(x[r], 1, k, w, qtype, n, np.zeros(n, np.float32),
+                                       threads=oracle.max_threads()) for r in rows])
+    assert np.abs(y[rows] - full).max() <= 2e-2 * np.abs(full).max()
+
+
+def test_gemm_bf16_output(cuda, oracle):
+    w, x, y, ref = run_case(cuda, oracle, Q4_K, 256, 256, 512, seed=7, out_dtype=torch.bfloat16)
+    assert np.abs(y - ref).max() <= 1e-2 * np.abs(ref).max()    # bf16 rounding of the result
