@@ -5,10 +5,14 @@
 // integer (ALU) pipe runs at half rate, so the design removes every per-weight instruction it can:
 //
 //  * A persistent CTA per SM walks row tiles of 16 output rows.  One producer warp streams the
-//    tile's rows with 1-D bulk async copies (cp.async.bulk, completion on an mbarrier) into a ring
-//    of shared-memory stages, KB superblocks of every row per stage; 16 consumer warps split the
-//    stage (Q4_K/Q5_K: one superblock per warp, Q6_K: half a superblock per warp).  Rows that are
-//    only 2/8-byte aligned (Q6_K) are fetched from the 16-byte boundary below their start.
+//    tiles' rows with 1-D bulk async copies (cp.async.bulk, completion on an mbarrier) into a ring
+//    of shared-memory stages, KB superblocks of every row per stage.  The 16 consumer warps form
+//    four groups of four; a stage belongs to one group (stages are dealt to the groups in turn, so
+//    four tiles are in progress at once) and its four warps split the stage's superblocks.  The
+//    groups drift apart in time, so each scheduler always holds warps in different phases (waiting
+//    for data, decoding scales, issuing MMAs, folding), which is what hides the long dependent
+//    chains of this kernel.  Rows that are only 2/8-byte aligned (Q6_K) are fetched from the
+//    16-byte boundary below their start.
 //  * Activations are quantised once per CTA to 15-bit block floating point: per scale group
 //    (32 elements for Q4_K/Q5_K, 16 for Q6_K) x = sx * n with |n| <= 16256, n = 128*hi + lo, hi
 //    and lo int8.  The rounding step is 2^-14 of the group maximum, i.e. ~4e-5 relative rms.
@@ -20,8 +24,9 @@
 //    d*sc*sx in fp32; accumulation across groups is fp32.
 //  * Terms that do not depend on the quants (Q4_K/Q5_K -dmin*m, Q6_K's -32) are folded into one
 //    correction per (row, superblock) from the per-group sums of the quantised activations.
-//  * Per tile the warps' partial sums are added in a fixed order through shared memory, the addend
-//    (bias or residual) is added and y is stored.  Results are deterministic.
+//  * Per tile the four warps' partial sums are added by a fixed butterfly through shared memory,
+//    one tile late so that nobody waits; the addend (bias or residual) is added and y is stored.
+//    Results are deterministic.
 //
 // The kernel is launched with programmatic stream serialisation: it lets its successor start
 // launching at once and itself waits for its predecessor only before it touches x or y.  With
@@ -35,6 +40,7 @@ namespace cogni {
 namespace {
 
 constexpr int kNW = 16;                      // consumer warps
+constexpr int kGroups = 4, kGW = 4;          // consumer groups x warps per group
 constexpr int kThreads = (kNW + 1) * 32;     // + 1 producer warp
 constexpr int kR = 16;                       // rows per tile
 constexpr size_t kDynSmemMax = 227 * 1024 - 1024;
@@ -50,17 +56,17 @@ constexpr int stage_row_stride(int bb, int kb, bool unaligned_rows) {
 
 template <int TYPE> struct Cfg;
 template <> struct Cfg<kQ4_K> {
-  static constexpr int BB = 144, KB = 16, HV = 1, GROUP = 32;
+  static constexpr int BB = 144, KB = 16, NG = 8, GROUP = 32;
   static constexpr int RS = stage_row_stride(BB, KB, false);
   static constexpr bool HAS_MIN = true;
 };
 template <> struct Cfg<kQ5_K> {
-  static constexpr int BB = 176, KB = 16, HV = 1, GROUP = 32;
+  static constexpr int BB = 176, KB = 16, NG = 8, GROUP = 32;
   static constexpr int RS = stage_row_stride(BB, KB, false);
   static constexpr bool HAS_MIN = true;
 };
 template <> struct Cfg<kQ6_K> {
-  static constexpr int BB = 210, KB = 8, HV = 2, GROUP = 16;
+  static constexpr int BB = 210, KB = 8, NG = 16, GROUP = 16;
   static constexpr int RS = stage_row_stride(BB, KB, true);
   static constexpr bool HAS_MIN = false;
 };
@@ -84,20 +90,6 @@ struct Params {
   long long *top_key;
   int index_base;
 };
-
-#ifdef COGNI_TRACE
-__device__ long long g_trace[1 << 16];
-__device__ __forceinline__ void trace(int warp, int lane, int &n, int ev) {
-  if (blockIdx.x == 0 && lane == 0 && n < 1000) {
-    g_trace[(warp * 1024 + n) * 2] = ev;
-    g_trace[(warp * 1024 + n) * 2 + 1] = clock64();
-    n++;
-  }
-}
-#define TRACE(ev) trace(warp, lane, tr_n, ev)
-#else
-#define TRACE(ev)
-#endif
 
 __device__ __forceinline__ void consumer_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(kNW * 32) : "memory");
@@ -151,16 +143,19 @@ __device__ __forceinline__ int xq_word_offset(int e_in /*element within superblo
   return ((unit * ncx + col_base + 2 * sub) * 4 + t) * 16 + m * 8 + sub * 4;
 }
 
-// ---------------------------------------------------------------------------- per-warp decode
-// Area of one warp: dscx[NB][8][16] floats (d*sc*sx of the warp's 8 scale groups, 16 rows, per
-// batch row) followed by corr[NB][16].
+// ---------------------------------------------------------------------------- per-block work
+// Area of one warp: dscx[NB][NG][16] floats (d*sc*sx of the superblock's NG scale groups, 16
+// rows, per batch row) followed by corr[NB][16].
+
+// Lanes (r = lane & 15, half = lane >> 4) decode one half of the scale groups of row r; the two
+// halves' corrections are combined with one shuffle.
 template <int TYPE, int NB>
-__device__ __forceinline__ void decode_scales(const uint8_t *blk_row, int lane, int hv, int kblk,
+__device__ __forceinline__ void decode_scales(const uint8_t *blk_row, int lane, int kblk,
                                               const float *SX, const float *XX, float *area) {
   using C = Cfg<TYPE>;
+  constexpr int NH = C::NG / 2;  // groups per lane
   const int r = lane & 15, half = lane >> 4;
-  float dsc[4], kk[4];
-  int grp0;  // first of this lane's four groups in the tables
+  float dsc[NH], kk[NH];
   if constexpr (C::HAS_MIN) {
     const uint4 h = *reinterpret_cast<const uint4 *>(blk_row);
     const __half2 dd = *reinterpret_cast<const __half2 *>(&h.x);
@@ -175,27 +170,109 @@ __device__ __forceinline__ void decode_scales(const uint8_t *blk_row, int lane, 
       dsc[i] = byte_times(scw, i, d, d23);
       kk[i] = byte_times(mnw, i, ndmin, ndmin23);
     }
-    grp0 = kblk * 8 + 4 * half;
   } else {
     const float d = load_half_as_float(blk_row + 208);
-    const int8_t *sc = reinterpret_cast<const int8_t *>(blk_row + 192 + 8 * hv + 4 * half);
+    const int8_t *sc = reinterpret_cast<const int8_t *>(blk_row + 192 + 8 * half);
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
+    for (int i = 0; i < 8; i++) {
       dsc[i] = d * (float)sc[i];
       kk[i] = -32.f * dsc[i];
     }
-    grp0 = kblk * 16 + 8 * hv + 4 * half;
   }
+  const int grp0 = kblk * C::NG + NH * half;  // first of this lane's groups in the tables
 #pragma unroll
   for (int b = 0; b < NB; b++) {
     float corr = 0.f;
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-      area[(b * 8 + 4 * half + i) * 16 + r] = dsc[i] * SX[(grp0 + i) * NB + b];
+    for (int i = 0; i < NH; i++) {
+      area[(b * C::NG + NH * half + i) * 16 + r] = dsc[i] * SX[(grp0 + i) * NB + b];
       corr = fmaf(kk[i], XX[(grp0 + i) * NB + b], corr);
     }
     corr += __shfl_xor_sync(0xffffffffu, corr, 16);
-    if (half == 0) area[NB * 128 + b * 16 + r] = corr;
+    if (half == 0) area[NB * C::NG * 16 + b * 16 + r] = corr;
+  }
+}
+
+// MMAs of one superblock (16 rows x 256 columns) for this lane's (group slot sub, batch row).
+// blk: the superblock of row 0 of the tile inside the stage; xu: this lane's B fragments of the
+// superblock's first unit; dscx: this lane's batch row of the decoded scales.
+template <int TYPE, int UNIT_BYTES>
+__device__ __forceinline__ void mma_block(const uint8_t *blk, int pad_a, int pad_b,
+                                          const uint8_t *xu, const float *dscx, int g, int t,
+                                          int sub, float &acc0, float &acc1) {
+  using C = Cfg<TYPE>;
+  constexpr uint32_t M4 = 0x0f0f0f0fu;
+  if constexpr (C::HAS_MIN) {
+    constexpr bool Q5 = TYPE == kQ5_K;
+    constexpr int QOFF = Q5 ? 48 : 16;
+    constexpr uint32_t M1 = 0x10101010u;
+    const uint8_t *ra = blk + g * C::RS + pad_a + 8 * t, *rb = blk + (g + 8) * C::RS + pad_b + 8 * t;
+    uint2 qha = make_uint2(0, 0), qhb = make_uint2(0, 0);
+    if constexpr (Q5) {
+      qha = *reinterpret_cast<const uint2 *>(ra + 16);
+      qhb = *reinterpret_cast<const uint2 *>(rb + 16);
+    }
+#pragma unroll
+    for (int g4 = 0; g4 < 4; g4++) {
+      const uint4 bv = *reinterpret_cast<const uint4 *>(xu + g4 * UNIT_BYTES);
+      const uint2 qa = *reinterpret_cast<const uint2 *>(ra + QOFF + 32 * g4);
+      const uint2 qb = *reinterpret_cast<const uint2 *>(rb + QOFF + 32 * g4);
+      uint32_t la0 = qa.x & M4, la1 = qa.y & M4, lb0 = qb.x & M4, lb1 = qb.y & M4;
+      uint32_t ha0 = (qa.x >> 4) & M4, ha1 = (qa.y >> 4) & M4;
+      uint32_t hb0 = (qb.x >> 4) & M4, hb1 = (qb.y >> 4) & M4;
+      if constexpr (Q5) {
+        // fifth bit: bit 2*g4 of qh for the low-nibble elements, bit 2*g4+1 for the high ones
+        auto bit = [&](uint32_t q, int b) { return b <= 4 ? ((q << (4 - b)) & M1) : ((q >> (b - 4)) & M1); };
+        la0 |= bit(qha.x, 2 * g4);     la1 |= bit(qha.y, 2 * g4);
+        lb0 |= bit(qhb.x, 2 * g4);     lb1 |= bit(qhb.y, 2 * g4);
+        ha0 |= bit(qha.x, 2 * g4 + 1); ha1 |= bit(qha.y, 2 * g4 + 1);
+        hb0 |= bit(qhb.x, 2 * g4 + 1); hb1 |= bit(qhb.y, 2 * g4 + 1);
+      }
+      int cc[4];
+      // k-slots 0..15: sub-block 2*g4 (low nibbles), 16..31: sub-block 2*g4+1 (high)
+      imma_zero(cc, la0, lb0, ha0, hb0, bv.x, bv.y);
+      imma_acc(cc, la1, lb1, ha1, hb1, bv.z, bv.w);
+      const float sa = dscx[(2 * g4 + sub) * 16 + g], sb = dscx[(2 * g4 + sub) * 16 + g + 8];
+      acc0 = fmaf(sa, (float)(cc[0] * 128 + cc[1]), acc0);
+      acc1 = fmaf(sb, (float)(cc[2] * 128 + cc[3]), acc1);
+    }
+  } else {
+    constexpr uint32_t M2 = 0x30303030u;
+    const uintptr_t aa = reinterpret_cast<uintptr_t>(blk + g * C::RS + pad_a + 4 * t);
+    const uintptr_t ab = reinterpret_cast<uintptr_t>(blk + (g + 8) * C::RS + pad_b + 4 * t);
+    const uint8_t *base[2] = {reinterpret_cast<const uint8_t *>(aa & ~(uintptr_t)3),
+                              reinterpret_cast<const uint8_t *>(ab & ~(uintptr_t)3)};
+    const uint32_t sh[2] = {(uint32_t)(aa & 2) * 8, (uint32_t)(ab & 2) * 8};
+#pragma unroll
+    for (int nh = 0; nh < 4; nh++) {
+      const int n = nh >> 1, h = nh & 1;
+      const uint4 bv = *reinterpret_cast<const uint4 *>(xu + nh * UNIT_BYTES);
+      uint32_t q[2][4];
+#pragma unroll
+      for (int r = 0; r < 2; r++) {
+        auto ld = [&](int off) {
+          const uint32_t *w32 = reinterpret_cast<const uint32_t *>(base[r] + off);
+          return __funnelshift_r(w32[0], w32[1], sh[r]);
+        };
+        const uint32_t ql0 = ld(64 * n + 16 * h), ql1 = ld(64 * n + 32 + 16 * h);
+        const uint32_t qhw = ld(128 + 32 * n + 16 * h);
+        q[r][0] = (ql0 & M4) | ((qhw << 4) & M2);
+        q[r][1] = (ql1 & M4) | ((qhw << 2) & M2);
+        q[r][2] = ((ql0 >> 4) & M4) | (qhw & M2);
+        q[r][3] = ((ql1 >> 4) & M4) | ((qhw >> 2) & M2);
+      }
+#pragma unroll
+      for (int m = 0; m < 2; m++) {
+        int cc[4];
+        // k-slots 0..15: run k = 2m, 16..31: run k = 2m+1 (scale group 8n + h + 2k)
+        imma_zero(cc, q[0][2 * m], q[1][2 * m], q[0][2 * m + 1], q[1][2 * m + 1],
+                  m ? bv.z : bv.x, m ? bv.w : bv.y);
+        const int j16 = 8 * n + h + 2 * (2 * m + sub);
+        const float sa = dscx[j16 * 16 + g], sb = dscx[j16 * 16 + g + 8];
+        acc0 = fmaf(sa, (float)(cc[0] * 128 + cc[1]), acc0);
+        acc1 = fmaf(sb, (float)(cc[2] * 128 + cc[3]), acc1);
+      }
+    }
   }
 }
 
@@ -205,56 +282,58 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
   using C = Cfg<TYPE>;
   constexpr int NCX = 4 * NB;                    // columns of the quantised-x layout
   constexpr int UNIT_BYTES = NCX * 64;
-  constexpr int AREA_FLOATS = NB * 128 + NB * 16;
-  static_assert(C::KB * C::HV == kNW, "one warp per (superblock, half)");
+  constexpr int AREA_FLOATS = NB * C::NG * 16 + NB * 16;
+  constexpr int BPW = C::KB / kGW;               // superblocks per warp per stage
+  static_assert(C::KB % kGW == 0 && kGroups * kGW == kNW, "stage splits evenly over a group");
   extern __shared__ __align__(128) uint8_t smem[];
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem);  // full[S], empty[S]
+  // mbarriers: full[S] | empty[S] | fold[group][2]
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
   const int S = p.stages;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef COGNI_TRACE
-  int tr_n = 0;
-#endif
-  TRACE(1);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; s++) {
       mbar_init(smem_u32(&bars[s]), 1);
-      mbar_init(smem_u32(&bars[S + s]), kNW);
+      mbar_init(smem_u32(&bars[S + s]), kGW);
     }
-    mbar_init(smem_u32(&bars[2 * S]), kNW);      // partial sums of an even tile are complete
-    mbar_init(smem_u32(&bars[2 * S + 1]), kNW);  // ... of an odd tile
+    for (int i = 0; i < 2 * kGroups; i++) mbar_init(smem_u32(&bars[2 * S + i]), kGW);
     mbar_fence_init();
   }
   __syncthreads();
   pdl_launch_dependents();
-  TRACE(2);
 
   uint8_t *stages = smem + p.off_stage;
+  // this CTA's tiles are blockIdx.x + i * gridDim.x, i < ntl; tile i belongs to group i % 4.
+  // Stage items are dealt in the order (round, chunk, group): four tiles advance together.
+  const int ntl = (p.ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int rounds = (ntl + kGroups - 1) / kGroups;
 
   if (warp == kNW) {
     // ------------------------------------------------------------------ producer warp
     if (!p.resident) pdl_wait_prior_grid();
     int it = 0;
-    for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
-      const int row = tile * kR + lane;
-      const bool rvalid = lane < kR && row < p.out_dim;
-      const uint8_t *rsrc = p.w + (long long)row * p.row_bytes;
-      for (int c = 0; c < p.nchunks; c++, it++) {
-        const int s = it % S;
-        TRACE(100 + it);
-        mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1);
-        TRACE(200 + it);
-        const int nb = min(C::KB, p.nblk - c * C::KB);
-        const uint8_t *src = rsrc + (long long)c * C::KB * C::BB;
-        const uint32_t padb = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15);
-        const uint32_t bytes = rvalid ? ((padb + nb * C::BB + 15u) & ~15u) : 0u;
-        const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
-        const uint32_t full = smem_u32(&bars[s]);
-        if (lane == 0) mbar_arrive_expect_tx(full, total);
-        __syncwarp();
-        if (rvalid)
-          bulk_g2s(smem_u32(stages + (size_t)s * p.stage_bytes + lane * C::RS), src - padb, bytes,
-                   full);
+    for (int r = 0; r < rounds; r++) {
+      for (int c = 0; c < p.nchunks; c++) {
+        for (int j = 0; j < kGroups; j++) {
+          const int li = r * kGroups + j;
+          if (li >= ntl) continue;
+          const int row = (blockIdx.x + li * gridDim.x) * kR + lane;
+          const bool rvalid = lane < kR && row < p.out_dim;
+          const int s = it % S;
+          mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1);
+          const int nb = min(C::KB, p.nblk - c * C::KB);
+          const uint8_t *src = p.w + (long long)row * p.row_bytes + (long long)c * C::KB * C::BB;
+          const uint32_t padb = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15);
+          const uint32_t bytes = rvalid ? ((padb + nb * C::BB + 15u) & ~15u) : 0u;
+          const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
+          const uint32_t full = smem_u32(&bars[s]);
+          if (lane == 0) mbar_arrive_expect_tx(full, total);
+          __syncwarp();
+          if (rvalid)
+            bulk_g2s(smem_u32(stages + (size_t)s * p.stage_bytes + lane * C::RS), src - padb, bytes,
+                     full);
+          it++;
+        }
       }
     }
     return;
@@ -272,9 +351,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
     for (int i = ctid; i < n16; i += kNW * 32) reinterpret_cast<uint4 *>(xq)[i] = make_uint4(0, 0, 0, 0);
   }
   consumer_sync();
-  TRACE(3);
   pdl_wait_prior_grid();  // x (and y / the addend) may be produced by the preceding kernel
-  TRACE(4);
   {  // quantise x: per group sx = max|x| / 16256, n = rint(x / sx) = 128*hi + lo
     const int k8n = K >> 3, items = NB * k8n;
     constexpr int LPG = C::GROUP / 8;  // lanes per scale group
@@ -320,37 +397,40 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
     }
   }
   consumer_sync();
-  TRACE(5);
 
   const int g = lane >> 2, t = lane & 3;
   const int sub = t & 1, bt = (t >> 1) & (NB - 1);  // this lane's group slot and batch row
-  const int wkb = warp / C::HV, whv = warp % C::HV;
+  const int grp = warp / kGW, mem = warp % kGW;     // consumer group, member within the group
   float *area = reinterpret_cast<float *>(smem + p.off_area) + warp * AREA_FLOATS;
-  const float *dscx = area + bt * 128;
-  float2 *red = reinterpret_cast<float2 *>(smem + p.off_red);
+  const float *dscx = area + bt * C::NG * 16;
+  const float *corr = area + NB * C::NG * 16 + bt * 16;
+  // fold buffers: [group][tile parity][member][lane]
+  float2 *red = reinterpret_cast<float2 *>(smem + p.off_red) + (size_t)grp * 2 * kGW * 32;
+  const uint32_t fold_bar = smem_u32(&bars[2 * S + 2 * grp]);
   // this lane's 16 bytes of a unit's B fragments
   const uint8_t *xlane = xq + ((g & (NCX - 1)) * 4 + t) * 16;
 
-  long long best[NB];  // fused top-1: running maximum of row `warp` of every tile (lane 0)
+  long long best[NB];  // fused top-1: running maxima of the rows this lane folds
 #pragma unroll
   for (int b = 0; b < NB; b++) best[b] = LLONG_MIN;
 
-  // Sum of the 16 warps' partial results of tile number `tn` (row tile index `tl`): warp w folds
-  // row w.  The 32 partials of a (row, batch row) pair sit one per lane and are added by a
-  // fixed butterfly, so the result does not depend on timing.  A tile is folded one tile late
-  // (after the next tile's MMAs), when all partials have long been written: nobody waits.
+  // Sum of the group's four partial results of its tn-th tile (row tile index tl): member m folds
+  // rows 4m .. 4m+3, eight partials per (row, batch row) spread over eight lanes and added by a
+  // fixed butterfly.  Runs one tile late, when the partials have long been written.
   auto fold_tile = [&](int tl, int tn) {
-    mbar_wait(smem_u32(&bars[2 * S + (tn & 1)]), (tn >> 1) & 1);
-    const float2 *rb = red + (size_t)(tn & 1) * (kNW * 32);
-    const int gg = warp & 7, upper = warp >> 3;
-    const int row = tl * kR + warp;
+    mbar_wait(fold_bar + 8 * (tn & 1), (tn >> 1) & 1);
+    const float2 *rb = red + (size_t)(tn & 1) * (kGW * 32);
+    const int r16 = 4 * mem + (lane >> 3), pidx = lane & 7;
+    const int gg = r16 & 7, upper = r16 >> 3;
+    const int row = tl * kR + r16;
 #pragma unroll
     for (int b = 0; b < NB; b++) {
-      const float2 pv = rb[(lane >> 1) * 32 + gg * 4 + 2 * b + (lane & 1)];
+      const float2 pv = rb[(pidx >> 1) * 32 + gg * 4 + 2 * b + (pidx & 1)];
       float v = upper ? pv.y : pv.x;
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-      if (lane == 0 && row < p.out_dim) {
+      v += __shfl_xor_sync(0xffffffffu, v, 1);
+      v += __shfl_xor_sync(0xffffffffu, v, 2);
+      v += __shfl_xor_sync(0xffffffffu, v, 4);
+      if (pidx == 0 && row < p.out_dim) {
         if (p.part_keys) {
           const long long key = top1_key(v, (uint32_t)(p.index_base + row));
           best[b] = key > best[b] ? key : best[b];
@@ -363,120 +443,59 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
   };
 
   const uintptr_t wbase = reinterpret_cast<uintptr_t>(p.w);
-  int it = 0, tcount = 0, prev_tile = 0;
-  for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x, tcount++) {
-    float acc0 = 0.f, acc1 = 0.f;  // rows g and g+8 of (group slot sub, batch row bt)
-    // byte offset of a row's data inside its stage slot; only Q6_K rows can be unaligned
-    int pad_a = 0, pad_b = 0, pad_d = 0;
-    if (TYPE == kQ6_K) {
+  int it = 0, tn = 0, prev_tile = 0;
+  float acc0 = 0.f, acc1 = 0.f;  // rows g and g+8 of (group slot sub, batch row bt)
+  int pad_a = 0, pad_b = 0, pad_d = 0;
+  for (int r = 0; r < rounds; r++) {
+    const int my_li = r * kGroups + grp;
+    const int tile = blockIdx.x + my_li * gridDim.x;
+    if (my_li < ntl && TYPE == kQ6_K) {  // only Q6_K rows can start off a 16-byte boundary
       pad_a = (int)((wbase + ((long long)tile * kR + g) * p.row_bytes) & 15);
       pad_b = (int)((wbase + ((long long)tile * kR + g + 8) * p.row_bytes) & 15);
       pad_d = (int)((wbase + ((long long)tile * kR + (lane & 15)) * p.row_bytes) & 15);
     }
-
-    for (int c = 0; c < p.nchunks; c++, it++) {
-      const int s = it % S;
-      TRACE(300 + it);
-      mbar_wait(smem_u32(&bars[s]), (it / S) & 1);
-      TRACE(400 + it);
-      const int kblk = c * C::KB + wkb;
-      if (kblk < p.nblk && p.debug != 1) {
-        const uint8_t *stage = stages + (size_t)s * p.stage_bytes + wkb * C::BB;
-        decode_scales<TYPE, NB>(stage + (lane & 15) * C::RS + pad_d, lane, whv, kblk, SX, XX, area);
-        __syncwarp();
-        if (p.debug != 2) {
-          const uint8_t *xu = xlane + (size_t)kblk * 4 * UNIT_BYTES;
-          if constexpr (C::HAS_MIN) {
-            constexpr bool Q5 = TYPE == kQ5_K;
-            constexpr int QOFF = Q5 ? 48 : 16;
-            constexpr uint32_t M4 = 0x0f0f0f0fu, M1 = 0x10101010u;
-            const uint8_t *ra = stage + g * C::RS + pad_a + 8 * t, *rb = stage + (g + 8) * C::RS + pad_b + 8 * t;
-            uint2 qha = make_uint2(0, 0), qhb = make_uint2(0, 0);
-            if constexpr (Q5) {
-              qha = *reinterpret_cast<const uint2 *>(ra + 16);
-              qhb = *reinterpret_cast<const uint2 *>(rb + 16);
+    for (int c = 0; c < p.nchunks; c++) {
+      for (int j = 0; j < kGroups; j++) {
+        if (r * kGroups + j >= ntl) continue;
+        if (j != grp) { it++; continue; }
+        const int s = it % S;
+        mbar_wait(smem_u32(&bars[s]), (it / S) & 1);
+        if (p.debug != 1) {
+          const uint8_t *stage = stages + (size_t)s * p.stage_bytes;
+#pragma unroll 1
+          for (int bi = 0; bi < BPW; bi++) {
+            const int kblk = c * C::KB + mem * BPW + bi;
+            if (kblk >= p.nblk) break;
+            const uint8_t *blk = stage + (mem * BPW + bi) * C::BB;
+            decode_scales<TYPE, NB>(blk + (lane & 15) * C::RS + pad_d, lane, kblk, SX, XX, area);
+            __syncwarp();
+            if (p.debug != 2)
+              mma_block<TYPE, UNIT_BYTES>(blk, pad_a, pad_b, xlane + (size_t)kblk * 4 * UNIT_BYTES,
+                                          dscx, g, t, sub, acc0, acc1);
+            if (sub == 0) {
+              acc0 += corr[g];
+              acc1 += corr[g + 8];
             }
-#pragma unroll
-            for (int g4 = 0; g4 < 4; g4++) {
-              const uint4 bv = *reinterpret_cast<const uint4 *>(xu + g4 * UNIT_BYTES);
-              const uint2 qa = *reinterpret_cast<const uint2 *>(ra + QOFF + 32 * g4);
-              const uint2 qb = *reinterpret_cast<const uint2 *>(rb + QOFF + 32 * g4);
-              uint32_t la0 = qa.x & M4, la1 = qa.y & M4, lb0 = qb.x & M4, lb1 = qb.y & M4;
-              uint32_t ha0 = (qa.x >> 4) & M4, ha1 = (qa.y >> 4) & M4;
-              uint32_t hb0 = (qb.x >> 4) & M4, hb1 = (qb.y >> 4) & M4;
-              if constexpr (Q5) {
-                auto bit = [&](uint32_t q, int b) { return b <= 4 ? ((q << (4 - b)) & M1) : ((q >> (b - 4)) & M1); };
-                la0 |= bit(qha.x, 2 * g4);     la1 |= bit(qha.y, 2 * g4);
-                lb0 |= bit(qhb.x, 2 * g4);     lb1 |= bit(qhb.y, 2 * g4);
-                ha0 |= bit(qha.x, 2 * g4 + 1); ha1 |= bit(qha.y, 2 * g4 + 1);
-                hb0 |= bit(qhb.x, 2 * g4 + 1); hb1 |= bit(qhb.y, 2 * g4 + 1);
-              }
-              int cc[4];
-              // k-slots 0..15: sub-block 2*g4 (low nibbles), 16..31: sub-block 2*g4+1 (high)
-              imma_zero(cc, la0, lb0, ha0, hb0, bv.x, bv.y);
-              imma_acc(cc, la1, lb1, ha1, hb1, bv.z, bv.w);
-              const float sa = dscx[(2 * g4 + sub) * 16 + g], sb = dscx[(2 * g4 + sub) * 16 + g + 8];
-              acc0 = fmaf(sa, (float)(cc[0] * 128 + cc[1]), acc0);
-              acc1 = fmaf(sb, (float)(cc[2] * 128 + cc[3]), acc1);
-            }
-          } else {
-            constexpr uint32_t M4 = 0x0f0f0f0fu, M2 = 0x30303030u;
-            const uintptr_t aa = reinterpret_cast<uintptr_t>(stage + g * C::RS + pad_a + 64 * whv + 4 * t);
-            const uintptr_t ab = reinterpret_cast<uintptr_t>(stage + (g + 8) * C::RS + pad_b + 64 * whv + 4 * t);
-            const uint8_t *base[2] = {reinterpret_cast<const uint8_t *>(aa & ~(uintptr_t)3),
-                                      reinterpret_cast<const uint8_t *>(ab & ~(uintptr_t)3)};
-            const uint32_t sh[2] = {(uint32_t)(aa & 2) * 8, (uint32_t)(ab & 2) * 8};
-            const int qh_off = 128 - 32 * whv;  // qh[32*hv + ..] relative to ql[64*hv + ..]
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-              const uint4 bv = *reinterpret_cast<const uint4 *>(xu + (2 * whv + h) * UNIT_BYTES);
-              uint32_t q[2][4];
-#pragma unroll
-              for (int r = 0; r < 2; r++) {
-                auto ld = [&](int off) {
-                  const uint32_t *w32 = reinterpret_cast<const uint32_t *>(base[r] + off);
-                  return __funnelshift_r(w32[0], w32[1], sh[r]);
-                };
-                const uint32_t ql0 = ld(16 * h), ql1 = ld(32 + 16 * h), qhw = ld(qh_off + 16 * h);
-                q[r][0] = (ql0 & M4) | ((qhw << 4) & M2);
-                q[r][1] = (ql1 & M4) | ((qhw << 2) & M2);
-                q[r][2] = ((ql0 >> 4) & M4) | (qhw & M2);
-                q[r][3] = ((ql1 >> 4) & M4) | ((qhw >> 2) & M2);
-              }
-#pragma unroll
-              for (int m = 0; m < 2; m++) {
-                int cc[4];
-                // k-slots 0..15: group k = 2m, 16..31: group k = 2m+1 (scale group h + 2k)
-                imma_zero(cc, q[0][2 * m], q[1][2 * m], q[0][2 * m + 1], q[1][2 * m + 1],
-                          m ? bv.z : bv.x, m ? bv.w : bv.y);
-                const int j8 = h + 2 * (2 * m + sub);
-                const float sa = dscx[j8 * 16 + g], sb = dscx[j8 * 16 + g + 8];
-                acc0 = fmaf(sa, (float)(cc[0] * 128 + cc[1]), acc0);
-                acc1 = fmaf(sb, (float)(cc[2] * 128 + cc[3]), acc1);
-              }
-            }
+            __syncwarp();  // the area is rewritten by the next superblock's decode
           }
         }
-        if (sub == 0) {
-          const float *corr = area + NB * 128 + bt * 16;
-          acc0 += corr[g];
-          acc1 += corr[g + 8];
-        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars[S + s]));
+        it++;
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bars[S + s]));
-      TRACE(500 + it);
     }
-
-    // hand this tile's partial sums over; fold the previous tile while they trickle in
-    if (tcount > 0) fold_tile(prev_tile, tcount - 1);
-    red[(size_t)(tcount & 1) * (kNW * 32) + warp * 32 + lane] = make_float2(acc0, acc1);
-    __syncwarp();
-    if (lane == 0) mbar_arrive(smem_u32(&bars[2 * S + (tcount & 1)]));
-    TRACE(600 + tcount);
-    prev_tile = tile;
+    if (my_li < ntl) {
+      // hand this tile's partial sums over; fold the previous tile while they trickle in
+      if (tn > 0) fold_tile(prev_tile, tn - 1);
+      red[(size_t)(tn & 1) * (kGW * 32) + mem * 32 + lane] = make_float2(acc0, acc1);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(fold_bar + 8 * (tn & 1));
+      prev_tile = tile;
+      tn++;
+      acc0 = acc1 = 0.f;
+    }
   }
-  if (tcount > 0) fold_tile(prev_tile, tcount - 1);
+  if (tn > 0) fold_tile(prev_tile, tn - 1);
 
   if (p.part_keys == nullptr) return;
 
@@ -486,7 +505,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
   __shared__ bool s_last;
   if (ctid < 2) s_best[ctid] = LLONG_MIN;
   consumer_sync();
-  if (lane == 0) {
+  if ((lane & 7) == 0) {
 #pragma unroll
     for (int b = 0; b < NB; b++) atomicMax(&s_best[b], best[b]);
   }
@@ -544,9 +563,9 @@ bool make_plan(int in_dim, int out_dim, int nb, Params &p, size_t &smem) {
   const int nblk = in_dim / 256;
   const int ngroups = in_dim / C::GROUP;
   auto al = [](size_t v) { return (v + 127) & ~(size_t)127; };
-  size_t off = 128;
-  const size_t off_red = off;    off = al(off + 2ull * kNW * 32 * 8);
-  const size_t off_area = off;   off = al(off + (size_t)kNW * (nb * 128 + nb * 16) * 4);
+  size_t off = 256;  // mbarriers
+  const size_t off_red = off;    off = al(off + 2ull * kNW * 32 * 8);  // [group][2][member][lane] float2
+  const size_t off_area = off;   off = al(off + (size_t)kNW * (nb * C::NG * 16 + nb * 16) * 4);
   const size_t off_sx = off;     off = al(off + (size_t)ngroups * nb * 4);
   const size_t off_xx = off;     off = al(off + (size_t)ngroups * nb * 4);
   const size_t off_xq = off;     off = al(off + (size_t)(in_dim / 64) * (4 * nb) * 64);
@@ -554,7 +573,7 @@ bool make_plan(int in_dim, int out_dim, int nb, Params &p, size_t &smem) {
   const size_t stage_bytes = al((size_t)kR * C::RS);
   if (off_stage + 3 * stage_bytes > kDynSmemMax) return false;
   int stages = (int)((kDynSmemMax - off_stage) / stage_bytes);
-  if (stages > 7) stages = 7;  // 2*stages + 2 mbarriers live in the first 128 bytes
+  if (stages > 8) stages = 8;  // 2*stages + 8 mbarriers live in the first 256 bytes
   p.in_dim = in_dim; p.out_dim = out_dim;
   p.nblk = nblk; p.nchunks = (nblk + C::KB - 1) / C::KB; p.ntiles = (out_dim + kR - 1) / kR;
   p.stages = stages; p.row_bytes = (long long)nblk * C::BB;
@@ -658,14 +677,6 @@ int launch_gemv_top1_imma(int type, const void *d_w, const float *d_x, int in_di
     default: return COGNI_QMM_ERR_TYPE;
   }
 }
-
-#ifdef COGNI_TRACE
-}  // namespace cogni
-extern "C" int cogni_qmm_debug_trace(long long *out, int n) {
-  return (int)cudaMemcpyFromSymbol(out, cogni::g_trace, (size_t)n * 8);
-}
-namespace cogni {
-#endif
 
 unsigned gemv_imma_timeouts() {
   unsigned v = 0;
