@@ -6,13 +6,12 @@
 //
 //  * A persistent CTA per SM walks row tiles of 16 output rows.  One producer warp streams the
 //    tiles' rows with 1-D bulk async copies (cp.async.bulk, completion on an mbarrier) into a ring
-//    of shared-memory stages, KB superblocks of every row per stage.  The 16 consumer warps form
-//    four groups of four; a stage belongs to one group (stages are dealt to the groups in turn, so
-//    four tiles are in progress at once) and its four warps split the stage's superblocks.  The
-//    groups drift apart in time, so each scheduler always holds warps in different phases (waiting
-//    for data, decoding scales, issuing MMAs, folding), which is what hides the long dependent
-//    chains of this kernel.  Rows that are only 2/8-byte aligned (Q6_K) are fetched from the
-//    16-byte boundary below their start.
+//    of shared-memory stages, KB superblocks of every row per stage.  The 16 consumer warps take
+//    work items (one superblock of a 16-row tile, or the fold of a finished tile) in order from a
+//    shared counter: every warp stays busy until the CTA runs dry and the warps of a scheduler
+//    are always in different phases (waiting for data, decoding scales, issuing MMAs, folding),
+//    which is what hides the long dependent chains of this kernel.  Rows that are only 2/8-byte
+//    aligned (Q6_K) are fetched from the 16-byte boundary below their start.
 //  * Activations are quantised once per CTA to 15-bit block floating point: per scale group
 //    (32 elements for Q4_K/Q5_K, 16 for Q6_K) x = sx * n with |n| <= 16256, n = 128*hi + lo, hi
 //    and lo int8.  The rounding step is 2^-14 of the group maximum, i.e. ~4e-5 relative rms.
@@ -24,9 +23,9 @@
 //    d*sc*sx in fp32; accumulation across groups is fp32.
 //  * Terms that do not depend on the quants (Q4_K/Q5_K -dmin*m, Q6_K's -32) are folded into one
 //    correction per (row, superblock) from the per-group sums of the quantised activations.
-//  * Per tile the four warps' partial sums are added by a fixed butterfly through shared memory,
-//    one tile late so that nobody waits; the addend (bias or residual) is added and y is stored.
-//    Results are deterministic.
+//  * Each superblock's partial sums go to a per-tile buffer indexed by superblock; a later work
+//    item adds them in superblock order, adds the addend (bias or residual) and stores y.  The
+//    result does not depend on which warp computed what.
 //
 // The kernel is launched with programmatic stream serialisation: it lets its successor start
 // launching at once and itself waits for its predecessor only before it touches x or y.  With
@@ -39,8 +38,11 @@
 namespace cogni {
 namespace {
 
-constexpr int kNW = 16;                      // consumer warps
-constexpr int kGroups = 4, kGW = 4;          // consumer groups x warps per group
+#ifndef COGNI_IMMA_WARPS
+#define COGNI_IMMA_WARPS 24
+#endif
+constexpr int kNW = COGNI_IMMA_WARPS;        // consumer warps
+constexpr int kFoldBufs = 4;                 // tiles whose partial sums can be pending
 constexpr int kThreads = (kNW + 1) * 32;     // + 1 producer warp
 constexpr int kR = 16;                       // rows per tile
 constexpr size_t kDynSmemMax = 227 * 1024 - 1024;
@@ -283,10 +285,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
   constexpr int NCX = 4 * NB;                    // columns of the quantised-x layout
   constexpr int UNIT_BYTES = NCX * 64;
   constexpr int AREA_FLOATS = NB * C::NG * 16 + NB * 16;
-  constexpr int BPW = C::KB / kGW;               // superblocks per warp per stage
-  static_assert(C::KB % kGW == 0 && kGroups * kGW == kNW, "stage splits evenly over a group");
   extern __shared__ __align__(128) uint8_t smem[];
-  // mbarriers: full[S] | empty[S] | fold[group][2]
+  // mbarriers: full[S] | empty[S] | tile partials complete[kFoldBufs] | tile buffer free[kFoldBufs],
+  // then the work counter
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
   const int S = p.stages;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -294,46 +295,44 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; s++) {
       mbar_init(smem_u32(&bars[s]), 1);
-      mbar_init(smem_u32(&bars[S + s]), kGW);
+      mbar_init(smem_u32(&bars[S + s]), C::KB);
     }
-    for (int i = 0; i < 2 * kGroups; i++) mbar_init(smem_u32(&bars[2 * S + i]), kGW);
+    for (int i = 0; i < kFoldBufs; i++) {
+      mbar_init(smem_u32(&bars[2 * S + i]), p.nblk);
+      mbar_init(smem_u32(&bars[2 * S + kFoldBufs + i]), 1);
+    }
+    *reinterpret_cast<int *>(&bars[2 * S + 2 * kFoldBufs]) = 0;
     mbar_fence_init();
   }
   __syncthreads();
   pdl_launch_dependents();
 
   uint8_t *stages = smem + p.off_stage;
-  // this CTA's tiles are blockIdx.x + i * gridDim.x, i < ntl; tile i belongs to group i % 4.
-  // Stage items are dealt in the order (round, chunk, group): four tiles advance together.
+  // this CTA's tiles are blockIdx.x + i * gridDim.x, i < ntl
   const int ntl = (p.ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-  const int rounds = (ntl + kGroups - 1) / kGroups;
 
   if (warp == kNW) {
     // ------------------------------------------------------------------ producer warp
     if (!p.resident) pdl_wait_prior_grid();
     int it = 0;
-    for (int r = 0; r < rounds; r++) {
-      for (int c = 0; c < p.nchunks; c++) {
-        for (int j = 0; j < kGroups; j++) {
-          const int li = r * kGroups + j;
-          if (li >= ntl) continue;
-          const int row = (blockIdx.x + li * gridDim.x) * kR + lane;
-          const bool rvalid = lane < kR && row < p.out_dim;
-          const int s = it % S;
-          mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1);
-          const int nb = min(C::KB, p.nblk - c * C::KB);
-          const uint8_t *src = p.w + (long long)row * p.row_bytes + (long long)c * C::KB * C::BB;
-          const uint32_t padb = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15);
-          const uint32_t bytes = rvalid ? ((padb + nb * C::BB + 15u) & ~15u) : 0u;
-          const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
-          const uint32_t full = smem_u32(&bars[s]);
-          if (lane == 0) mbar_arrive_expect_tx(full, total);
-          __syncwarp();
-          if (rvalid)
-            bulk_g2s(smem_u32(stages + (size_t)s * p.stage_bytes + lane * C::RS), src - padb, bytes,
-                     full);
-          it++;
-        }
+    for (int li = 0; li < ntl; li++) {
+      const int row = (blockIdx.x + li * gridDim.x) * kR + lane;
+      const bool rvalid = lane < kR && row < p.out_dim;
+      const uint8_t *rsrc = p.w + (long long)row * p.row_bytes;
+      for (int c = 0; c < p.nchunks; c++, it++) {
+        const int s = it % S;
+        mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1);
+        const int nb = min(C::KB, p.nblk - c * C::KB);
+        const uint8_t *src = rsrc + (long long)c * C::KB * C::BB;
+        const uint32_t padb = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15);
+        const uint32_t bytes = rvalid ? ((padb + nb * C::BB + 15u) & ~15u) : 0u;
+        const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
+        const uint32_t full = smem_u32(&bars[s]);
+        if (lane == 0) mbar_arrive_expect_tx(full, total);
+        __syncwarp();
+        if (rvalid)
+          bulk_g2s(smem_u32(stages + (size_t)s * p.stage_bytes + lane * C::RS), src - padb, bytes,
+                   full);
       }
     }
     return;
@@ -400,102 +399,100 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
 
   const int g = lane >> 2, t = lane & 3;
   const int sub = t & 1, bt = (t >> 1) & (NB - 1);  // this lane's group slot and batch row
-  const int grp = warp / kGW, mem = warp % kGW;     // consumer group, member within the group
   float *area = reinterpret_cast<float *>(smem + p.off_area) + warp * AREA_FLOATS;
   const float *dscx = area + bt * C::NG * 16;
   const float *corr = area + NB * C::NG * 16 + bt * 16;
-  // fold buffers: [group][tile parity][member][lane]
-  float2 *red = reinterpret_cast<float2 *>(smem + p.off_red) + (size_t)grp * 2 * kGW * 32;
-  const uint32_t fold_bar = smem_u32(&bars[2 * S + 2 * grp]);
+  // partial sums: [tile buffer][superblock of the row][g][batch row] float2 (rows g, g+8)
+  float2 *red = reinterpret_cast<float2 *>(smem + p.off_red);
+  const int red_tile = p.nblk * 8 * NB;
   // this lane's 16 bytes of a unit's B fragments
   const uint8_t *xlane = xq + ((g & (NCX - 1)) * 4 + t) * 16;
+  int *work_ctr = reinterpret_cast<int *>(&bars[2 * S + 2 * kFoldBufs]);
 
-  long long best[NB];  // fused top-1: running maxima of the rows this lane folds
-#pragma unroll
-  for (int b = 0; b < NB; b++) best[b] = LLONG_MIN;
+  long long best = LLONG_MIN, best_b1 = LLONG_MIN;  // fused top-1: running maxima (batch row 0 / 1)
 
-  // Sum of the group's four partial results of its tn-th tile (row tile index tl): member m folds
-  // rows 4m .. 4m+3, eight partials per (row, batch row) spread over eight lanes and added by a
-  // fixed butterfly.  Runs one tile late, when the partials have long been written.
-  auto fold_tile = [&](int tl, int tn) {
-    mbar_wait(fold_bar + 8 * (tn & 1), (tn >> 1) & 1);
-    const float2 *rb = red + (size_t)(tn & 1) * (kGW * 32);
-    const int r16 = 4 * mem + (lane >> 3), pidx = lane & 7;
-    const int gg = r16 & 7, upper = r16 >> 3;
-    const int row = tl * kR + r16;
-#pragma unroll
-    for (int b = 0; b < NB; b++) {
-      const float2 pv = rb[(pidx >> 1) * 32 + gg * 4 + 2 * b + (pidx & 1)];
-      float v = upper ? pv.y : pv.x;
-      v += __shfl_xor_sync(0xffffffffu, v, 1);
-      v += __shfl_xor_sync(0xffffffffu, v, 2);
-      v += __shfl_xor_sync(0xffffffffu, v, 4);
-      if (pidx == 0 && row < p.out_dim) {
+  // Work items are handed out in order from one shared counter, so every warp is busy until the
+  // CTA runs dry and neighbouring warps are always in different phases.  Per tile: one item per
+  // superblock of the row (decode + MMAs of 16 rows x 256 columns, partial sums to the tile
+  // buffer), then one item that folds the PREVIOUS tile (its partials are complete by then).
+  const uintptr_t wbase = reinterpret_cast<uintptr_t>(p.w);
+  const int per_tile = p.nblk + 1, total = ntl * per_tile + 1;
+  for (;;) {
+    int q = 0;
+    if (lane == 0) q = atomicAdd(work_ctr, 1);
+    q = __shfl_sync(0xffffffffu, q, 0);
+    if (q >= total) break;
+    const int li = q / per_tile, e = q - li * per_tile;
+    if (e < p.nblk && li < ntl) {
+      // ------------------------------------------------ one superblock of tile li
+      const int c = e / C::KB, bi = e - c * C::KB;
+      const int cc = li * p.nchunks + c, s = cc % S;
+      const int tile = blockIdx.x + li * gridDim.x;
+      int pad_a = 0, pad_b = 0, pad_d = 0;
+      if (TYPE == kQ6_K) {  // only Q6_K rows can start off a 16-byte boundary
+        pad_a = (int)((wbase + ((long long)tile * kR + g) * p.row_bytes) & 15);
+        pad_b = (int)((wbase + ((long long)tile * kR + g + 8) * p.row_bytes) & 15);
+        pad_d = (int)((wbase + ((long long)tile * kR + (lane & 15)) * p.row_bytes) & 15);
+      }
+      float acc0 = 0.f, acc1 = 0.f;  // rows g and g+8 of (group slot sub, batch row bt)
+      mbar_wait(smem_u32(&bars[s]), (cc / S) & 1);
+      if (p.debug != 1) {
+        const uint8_t *blk = stages + (size_t)s * p.stage_bytes + bi * C::BB;
+        decode_scales<TYPE, NB>(blk + (lane & 15) * C::RS + pad_d, lane, e, SX, XX, area);
+        __syncwarp();
+        if (p.debug != 2)
+          mma_block<TYPE, UNIT_BYTES>(blk, pad_a, pad_b, xlane + (size_t)e * 4 * UNIT_BYTES, dscx,
+                                      g, t, sub, acc0, acc1);
+        if (sub == 0) {
+          acc0 += corr[g];
+          acc1 += corr[g + 8];
+        }
+        __syncwarp();  // the area is rewritten by this warp's next decode
+      }
+      // release the stage; the warp that takes the last superblock of a short final chunk also
+      // arrives for the superblocks that do not exist
+      if (lane == 0) {
+        const int nb = min(C::KB, p.nblk - c * C::KB);
+        mbar_arrive_n(smem_u32(&bars[S + s]), bi == nb - 1 ? C::KB - nb + 1 : 1);
+      }
+      // the two group slots of a batch row sit in neighbouring lanes
+      acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
+      acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+      const int tb = li % kFoldBufs;
+      mbar_wait(smem_u32(&bars[2 * S + kFoldBufs + tb]), ((li / kFoldBufs) & 1) ^ 1);  // buffer free
+      if (sub == 0 && (t >> 1) < NB)
+        red[tb * red_tile + (e * 8 + g) * NB + (t >> 1)] = make_float2(acc0, acc1);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars[2 * S + tb]));
+    } else {
+      // ------------------------------------------------ fold tile li - 1 (or the last tile)
+      const int fl = e < p.nblk ? ntl - 1 : li - 1;  // q == total - 1 has li == ntl, e == 0
+      if (fl < 0) continue;
+      const int tb = fl % kFoldBufs;
+      mbar_wait(smem_u32(&bars[2 * S + tb]), (fl / kFoldBufs) & 1);
+      // lane = (batch row, row of the tile): a fixed-order sum over the superblocks
+      const int r16 = lane & 15, b = lane >> 4;
+      const float2 *src = red + tb * red_tile + (r16 & 7) * NB + (b & (NB - 1));
+      float v = 0.f;
+      for (int k = 0; k < p.nblk; k++) {
+        const float2 pv = src[k * 8 * NB];
+        v += (r16 >> 3) ? pv.y : pv.x;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars[2 * S + kFoldBufs + tb]));
+      const int row = (blockIdx.x + fl * gridDim.x) * kR + r16;
+      if (b < NB && row < p.out_dim) {
         if (p.part_keys) {
           const long long key = top1_key(v, (uint32_t)(p.index_base + row));
-          best[b] = key > best[b] ? key : best[b];
+          if (b == 0) best = key > best ? key : best;
+          else best_b1 = key > best_b1 ? key : best_b1;
         } else {
           const float a = p.addend ? p.addend[(long long)b * p.addend_stride + row] : 0.f;
           p.y[(long long)b * p.out_dim + row] = a + v;
         }
       }
     }
-  };
-
-  const uintptr_t wbase = reinterpret_cast<uintptr_t>(p.w);
-  int it = 0, tn = 0, prev_tile = 0;
-  float acc0 = 0.f, acc1 = 0.f;  // rows g and g+8 of (group slot sub, batch row bt)
-  int pad_a = 0, pad_b = 0, pad_d = 0;
-  for (int r = 0; r < rounds; r++) {
-    const int my_li = r * kGroups + grp;
-    const int tile = blockIdx.x + my_li * gridDim.x;
-    if (my_li < ntl && TYPE == kQ6_K) {  // only Q6_K rows can start off a 16-byte boundary
-      pad_a = (int)((wbase + ((long long)tile * kR + g) * p.row_bytes) & 15);
-      pad_b = (int)((wbase + ((long long)tile * kR + g + 8) * p.row_bytes) & 15);
-      pad_d = (int)((wbase + ((long long)tile * kR + (lane & 15)) * p.row_bytes) & 15);
-    }
-    for (int c = 0; c < p.nchunks; c++) {
-      for (int j = 0; j < kGroups; j++) {
-        if (r * kGroups + j >= ntl) continue;
-        if (j != grp) { it++; continue; }
-        const int s = it % S;
-        mbar_wait(smem_u32(&bars[s]), (it / S) & 1);
-        if (p.debug != 1) {
-          const uint8_t *stage = stages + (size_t)s * p.stage_bytes;
-#pragma unroll 1
-          for (int bi = 0; bi < BPW; bi++) {
-            const int kblk = c * C::KB + mem * BPW + bi;
-            if (kblk >= p.nblk) break;
-            const uint8_t *blk = stage + (mem * BPW + bi) * C::BB;
-            decode_scales<TYPE, NB>(blk + (lane & 15) * C::RS + pad_d, lane, kblk, SX, XX, area);
-            __syncwarp();
-            if (p.debug != 2)
-              mma_block<TYPE, UNIT_BYTES>(blk, pad_a, pad_b, xlane + (size_t)kblk * 4 * UNIT_BYTES,
-                                          dscx, g, t, sub, acc0, acc1);
-            if (sub == 0) {
-              acc0 += corr[g];
-              acc1 += corr[g + 8];
-            }
-            __syncwarp();  // the area is rewritten by the next superblock's decode
-          }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bars[S + s]));
-        it++;
-      }
-    }
-    if (my_li < ntl) {
-      // hand this tile's partial sums over; fold the previous tile while they trickle in
-      if (tn > 0) fold_tile(prev_tile, tn - 1);
-      red[(size_t)(tn & 1) * (kGW * 32) + mem * 32 + lane] = make_float2(acc0, acc1);
-      __syncwarp();
-      if (lane == 0) mbar_arrive(fold_bar + 8 * (tn & 1));
-      prev_tile = tile;
-      tn++;
-      acc0 = acc1 = 0.f;
-    }
   }
-  if (tn > 0) fold_tile(prev_tile, tn - 1);
 
   if (p.part_keys == nullptr) return;
 
@@ -505,10 +502,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
   __shared__ bool s_last;
   if (ctid < 2) s_best[ctid] = LLONG_MIN;
   consumer_sync();
-  if ((lane & 7) == 0) {
-#pragma unroll
-    for (int b = 0; b < NB; b++) atomicMax(&s_best[b], best[b]);
-  }
+  atomicMax(&s_best[0], best);
+  if (NB > 1) atomicMax(&s_best[1], best_b1);
   consumer_sync();
   const int nparts = gridDim.x;
   if (ctid < NB) p.part_keys[(long long)ctid * nparts + blockIdx.x] = s_best[ctid];
@@ -564,7 +559,7 @@ bool make_plan(int in_dim, int out_dim, int nb, Params &p, size_t &smem) {
   const int ngroups = in_dim / C::GROUP;
   auto al = [](size_t v) { return (v + 127) & ~(size_t)127; };
   size_t off = 256;  // mbarriers
-  const size_t off_red = off;    off = al(off + 2ull * kNW * 32 * 8);  // [group][2][member][lane] float2
+  const size_t off_red = off;    off = al(off + (size_t)kFoldBufs * nblk * 8 * nb * 8);  // [tile buffer][superblock][g][batch] float2
   const size_t off_area = off;   off = al(off + (size_t)kNW * (nb * C::NG * 16 + nb * 16) * 4);
   const size_t off_sx = off;     off = al(off + (size_t)ngroups * nb * 4);
   const size_t off_xx = off;     off = al(off + (size_t)ngroups * nb * 4);
@@ -573,7 +568,7 @@ bool make_plan(int in_dim, int out_dim, int nb, Params &p, size_t &smem) {
   const size_t stage_bytes = al((size_t)kR * C::RS);
   if (off_stage + 3 * stage_bytes > kDynSmemMax) return false;
   int stages = (int)((kDynSmemMax - off_stage) / stage_bytes);
-  if (stages > 8) stages = 8;  // 2*stages + 8 mbarriers live in the first 256 bytes
+  if (stages > 8) stages = 8;  // 2*stages + 2*kFoldBufs mbarriers + the work counter: 200 bytes
   p.in_dim = in_dim; p.out_dim = out_dim;
   p.nblk = nblk; p.nchunks = (nblk + C::KB - 1) / C::KB; p.ntiles = (out_dim + kR - 1) / kR;
   p.stages = stages; p.row_bytes = (long long)nblk * C::BB;
