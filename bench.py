@@ -58,7 +58,7 @@ def measured_peak():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks and throttle reasons sampled every 100 ms while the timed region runs."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -73,7 +73,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "200"],
+                 "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
@@ -168,6 +168,52 @@ def run_reference(args):
         "cpu_baseline": base,
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
+
+
+def measure_extras(dev, gate_h, down_h, peaks):
+    """The path's other two kernels at their benchmark shapes (reported beside the headline):
+    prefill dequant-fused GEMM (TFLOP/s) and the fused vocab-sized lm_head GEMV + top-1 (GB/s)."""
+    import torch
+
+    from cogni_ml_b200 import DeviceQuantWeight, QuantWeight, synth
+
+    def timed(fn, reps, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    out = {"prefill": [], "lm_head": None}
+    tf_burst, tf_sust = peaks.get("bf16_tflops"), peaks.get("bf16_tflops_sustained")
+    for qtype, raw, n, k in ((Q4_K, gate_h, FFN, HIDDEN), (Q6_K, down_h, HIDDEN, FFN)):
+        dw = DeviceQuantWeight.upload(QuantWeight(raw, qtype, n, k), dev)
+        for m in (512, 4096):
+            x = torch.randn(m, k, device=dev).bfloat16()
+            y = torch.empty(m, n, dtype=torch.float32, device=dev)
+            ms = timed(lambda: dw.gemm(x, out=y), 10)
+            tf = 2.0 * m * n * k / ms / 1e9
+            out["prefill"].append({"type": "Q4_K" if qtype == Q4_K else "Q6_K", "M": m, "N": n,
+                                   "K": k, "ms": ms, "tflops": tf,
+                                   "frac_of_measured_burst": tf / tf_burst if tf_burst else None,
+                                   "frac_of_measured_sustained": tf / tf_sust if tf_sust else None})
+        del dw
+    vocab, hid = 151936, 5120
+    head = DeviceQuantWeight.upload(
+        QuantWeight(synth.make_weight(Q6_K, vocab, hid, seed=7, tensor_id=9), Q6_K, vocab, hid), dev)
+    xh = torch.from_numpy(synth.make_activation(1, hid, seed=7, tensor_id=12)).to(dev)
+    ms = timed(lambda: head.gemv_top1(xh), 20)
+    nbytes = head.nbytes + hid * 4 + 8
+    hbm = peaks.get("hbm_gbs")
+    out["lm_head"] = {"kernel": "Q6_K 151936x5120 GEMV + top-1, batch 1", "ms": ms,
+                      "achieved_gbs": nbytes / ms / 1e6, "algorithmic_bytes": nbytes,
+                      "frac_of_measured": nbytes / ms / 1e6 / hbm if hbm else None}
+    return out
 
 
 def run_ours(args):
@@ -343,6 +389,14 @@ def run_ours(args):
                              "algorithmic_bytes": q6_alg, "frac_of_nominal_8tbs": q6_ach / 8000.0},
             "clocks": clocks.summary(),
         }
+        if world == 1 and not args.no_extras:
+            try:
+                peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+            except Exception:
+                peaks = {}
+            del gates, ups, downs
+            torch.cuda.empty_cache()
+            line["extras"] = measure_extras(dev, gate_h, down_h, peaks)
         if world == 1 and not args.no_cpu:
             from oracle import loader as oracle
             line["cpu_baseline"] = cpu_baseline(args.cpu_seconds, oracle.max_threads())
@@ -355,13 +409,15 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the prefill-GEMM and lm_head side measurements")
     ap.add_argument("--kernel-choice", type=int, default=0,
                     help="diagnostics: passed to cogni_qmm_set_kernel_choice before the run")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of graph replay")
