@@ -42,6 +42,11 @@ Q4K_BYTES = FFN * (HIDDEN // 256) * 144      # 28,311,552
 Q6K_BYTES = HIDDEN * (FFN // 256) * 210      # 41,287,680
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
+# profiles/gemv_imma_q4k_q6k_ffn9b_b1.md (batch 1; traffic does not depend on the layer count)
+NCU_TRAFFIC_BYTES = {"q4k_12288x4096_b1": 28_356_608 + 65_536, "q6k_4096x12288_b1": 41_368_576 + 65_536}
+
+
 def algorithmic_bytes(weight_bytes: int, in_dim: int, out_dim: int, batch: int) -> int:
     """Weights once + activations in + outputs out, per GEMV launch."""
     return weight_bytes + batch * in_dim * 4 + batch * out_dim * 4
@@ -380,12 +385,14 @@ def run_ours(args):
                     "d2h_bytes_per_step": B * (2 * FFN + HIDDEN) * 4},
             "gpu_launches": args.steps * 3 * L,
             "roofline": {"bound": "hbm", "kernel": "Q4_K GEMV 12288x4096 b1", "achieved": q4_ach,
-                         "peak": peak, "unit": "GB/s", "frac": q4_ach / peak, "traffic": None,
+                         "peak": peak, "unit": "GB/s", "frac": q4_ach / peak,
+                         "traffic": NCU_TRAFFIC_BYTES["q4k_12288x4096_b1"] if B == 1 else None,
                          "peak_source": f"of {peak_src}", "us_per_launch": q4_launch_ms * 1e3,
                          "algorithmic_bytes": q4_alg, "frac_of_nominal_8tbs": q4_ach / 8000.0},
             "roofline_q6k": {"bound": "hbm", "kernel": "Q6_K GEMV 4096x12288 b1",
                              "achieved": q6_ach, "peak": peak, "unit": "GB/s",
                              "frac": q6_ach / peak, "us_per_launch": q6_launch_ms * 1e3,
+                             "traffic": NCU_TRAFFIC_BYTES["q6k_4096x12288_b1"] if B == 1 else None,
                              "algorithmic_bytes": q6_alg, "frac_of_nominal_8tbs": q6_ach / 8000.0},
             "clocks": clocks.summary(),
         }
