@@ -6,10 +6,10 @@ library and fails if it has not been built (`python cogni_ml_b200/build.py`).
 """
 from . import synth  # noqa: F401  (numpy only)
 from ._lib import CogniQmmError, lib  # noqa: F401
-from .quant_matmul import (DeviceQuantWeight, QuantMatmul, QuantWeight, TensorType,  # noqa: F401
-                           row_bytes, unpack_top1_keys)
+from .quant_matmul import (DeviceQuantWeight, GemvMany, QuantMatmul, QuantWeight,  # noqa: F401
+                           TensorType, gemv_many, row_bytes, unpack_top1_keys)
 from .runner import Projection, QuantProjectionRunner, ResidentSequenceRunner  # noqa: F401
 
-__all__ = ["CogniQmmError", "DeviceQuantWeight", "Projection", "QuantMatmul", "QuantProjectionRunner",
+__all__ = ["CogniQmmError", "DeviceQuantWeight", "GemvMany", "gemv_many", "Projection", "QuantMatmul", "QuantProjectionRunner",
            "QuantWeight", "ResidentSequenceRunner", "TensorType", "lib", "row_bytes", "synth",
            "unpack_top1_keys"]

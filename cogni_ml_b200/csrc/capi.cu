@@ -112,6 +112,31 @@ int cogni_qmm_gemv_resident(int type, const void *d_w, const float *d_x, const f
   return gemv_common(type, d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, 1, stream);
 }
 
+int cogni_qmm_gemv_many(int type, int n_weights, const void *const *d_w, const float *d_x,
+                        const float *const *d_addend, int64_t addend_stride, float *const *d_y,
+                        const int *out_dims, int in_dim, int batch, int resident, void *stream) {
+  if (!supported(type)) return COGNI_QMM_ERR_TYPE;
+  if (n_weights <= 0 || !d_w || !d_y || !out_dims) return COGNI_QMM_ERR_ARG;
+  bool tiled = g_force_rowwarp == 0;
+  for (int j = 0; j < n_weights; j++) {
+    int st = check_gemv_args(type, d_w[j], d_x, d_y[j], in_dim, out_dims[j], batch);
+    if (st) return st;
+    if (d_addend && d_addend[j] && addend_stride != 0 && addend_stride != out_dims[j])
+      return COGNI_QMM_ERR_ARG;
+    tiled = tiled && gemv_imma_supports(type, d_w[j], d_x, in_dim, batch);
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (tiled)
+    return launch_gemv_imma_many(type, n_weights, d_w, d_x, d_addend, addend_stride, d_y, out_dims,
+                                 in_dim, batch, resident, s);
+  for (int j = 0; j < n_weights; j++) {
+    int st = gemv_common(type, d_w[j], d_x, d_addend ? d_addend[j] : nullptr, addend_stride, d_y[j],
+                         in_dim, out_dims[j], batch, resident, stream);
+    if (st) return st;
+  }
+  return COGNI_QMM_OK;
+}
+
 size_t cogni_qmm_gemv_top1_scratch_bytes(int out_dim, int batch) {
   if (out_dim <= 0 || batch <= 0) return 0;
   return top1_scratch_bytes(out_dim, batch);

@@ -73,14 +73,23 @@ template <> struct Cfg<kQ6_K> {
   static constexpr bool HAS_MIN = false;
 };
 
-struct Params {
+constexpr int kMaxJobs = 32;  // weight matrices one launch can take (they share x)
+
+struct Job {
   const uint8_t *w;
-  const float *x;
   const float *addend;
-  long long addend_stride;
   float *y;
-  int in_dim, out_dim;
-  int nblk, nchunks, ntiles, stages;
+  int out_dim;
+};
+
+struct Params {
+  const float *x;
+  long long addend_stride;
+  int in_dim;
+  int nblk, nchunks, stages;
+  int njobs;
+  int tcum[kMaxJobs + 1];  // tcum[j] = first global tile of job j; tcum[njobs] = all tiles
+  Job jobs[kMaxJobs];
   long long row_bytes;
   int off_red, off_area, off_sx, off_xx, off_xq, off_stage, stage_bytes;
   int resident;  // weights were complete before the preceding kernel started
@@ -92,6 +101,21 @@ struct Params {
   long long *top_key;
   int index_base;
 };
+
+#ifdef COGNI_TRACE
+// timing diagnostics (never compiled into the shipped library): per-warp event log of CTA 0
+__device__ long long g_trace[1 << 16];
+__device__ __forceinline__ void trace(int warp, int lane, int &n, int ev) {
+  if (blockIdx.x == 0 && lane == 0 && n < 500) {
+    g_trace[(warp * 512 + n) * 2] = ev;
+    g_trace[(warp * 512 + n) * 2 + 1] = clock64();
+    n++;
+  }
+}
+#define TRACE(ev) trace(warp, lane, tr_n, ev)
+#else
+#define TRACE(ev)
+#endif
 
 __device__ __forceinline__ void consumer_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(kNW * 32) : "memory");
@@ -291,6 +315,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
   const int S = p.stages;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef COGNI_TRACE
+  int tr_n = 0;
+#endif
+  TRACE(1);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; s++) {
@@ -308,20 +336,29 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
   pdl_launch_dependents();
 
   uint8_t *stages = smem + p.off_stage;
-  // this CTA's tiles are blockIdx.x + i * gridDim.x, i < ntl
-  const int ntl = (p.ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  // The jobs' 16-row tiles form one global sequence (job-major); this CTA's tiles are
+  // blockIdx.x + i * gridDim.x, i < ntl.
+  const int ntl = (p.tcum[p.njobs] - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  auto locate = [&](int gt, int &j) {  // job of global tile gt, searched from the hint j
+    while (gt >= p.tcum[j + 1]) j++;
+    while (gt < p.tcum[j]) j--;
+  };
 
   if (warp == kNW) {
     // ------------------------------------------------------------------ producer warp
     if (!p.resident) pdl_wait_prior_grid();
-    int it = 0;
+    int it = 0, pj = 0;
     for (int li = 0; li < ntl; li++) {
-      const int row = (blockIdx.x + li * gridDim.x) * kR + lane;
-      const bool rvalid = lane < kR && row < p.out_dim;
-      const uint8_t *rsrc = p.w + (long long)row * p.row_bytes;
+      const int gt = blockIdx.x + li * gridDim.x;
+      locate(gt, pj);
+      const int row = (gt - p.tcum[pj]) * kR + lane;
+      const bool rvalid = lane < kR && row < p.jobs[pj].out_dim;
+      const uint8_t *rsrc = p.jobs[pj].w + (long long)row * p.row_bytes;
       for (int c = 0; c < p.nchunks; c++, it++) {
         const int s = it % S;
+        TRACE(100 + it);
         mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1);
+        TRACE(200 + it);
         const int nb = min(C::KB, p.nblk - c * C::KB);
         const uint8_t *src = rsrc + (long long)c * C::KB * C::BB;
         const uint32_t padb = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15);
@@ -350,7 +387,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
     for (int i = ctid; i < n16; i += kNW * 32) reinterpret_cast<uint4 *>(xq)[i] = make_uint4(0, 0, 0, 0);
   }
   consumer_sync();
+  TRACE(3);
   pdl_wait_prior_grid();  // x (and y / the addend) may be produced by the preceding kernel
+  TRACE(4);
   {  // quantise x: per group sx = max|x| / 16256, n = rint(x / sx) = 128*hi + lo
     const int k8n = K >> 3, items = NB * k8n;
     constexpr int LPG = C::GROUP / 8;  // lanes per scale group
@@ -396,6 +435,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
     }
   }
   consumer_sync();
+  TRACE(5);
 
   const int g = lane >> 2, t = lane & 3;
   const int sub = t & 1, bt = (t >> 1) & (NB - 1);  // this lane's group slot and batch row
@@ -415,8 +455,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
   // CTA runs dry and neighbouring warps are always in different phases.  Per tile: one item per
   // superblock of the row (decode + MMAs of 16 rows x 256 columns, partial sums to the tile
   // buffer), then one item that folds the PREVIOUS tile (its partials are complete by then).
-  const uintptr_t wbase = reinterpret_cast<uintptr_t>(p.w);
   const int per_tile = p.nblk + 1, total = ntl * per_tile + 1;
+  int cj = 0;  // job hint of this warp
   for (;;) {
     int q = 0;
     if (lane == 0) q = atomicAdd(work_ctr, 1);
@@ -427,15 +467,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
       // ------------------------------------------------ one superblock of tile li
       const int c = e / C::KB, bi = e - c * C::KB;
       const int cc = li * p.nchunks + c, s = cc % S;
-      const int tile = blockIdx.x + li * gridDim.x;
       int pad_a = 0, pad_b = 0, pad_d = 0;
       if (TYPE == kQ6_K) {  // only Q6_K rows can start off a 16-byte boundary
+        const int gt = blockIdx.x + li * gridDim.x;
+        locate(gt, cj);
+        const int tile = gt - p.tcum[cj];
+        const uintptr_t wbase = reinterpret_cast<uintptr_t>(p.jobs[cj].w);
         pad_a = (int)((wbase + ((long long)tile * kR + g) * p.row_bytes) & 15);
         pad_b = (int)((wbase + ((long long)tile * kR + g + 8) * p.row_bytes) & 15);
         pad_d = (int)((wbase + ((long long)tile * kR + (lane & 15)) * p.row_bytes) & 15);
       }
       float acc0 = 0.f, acc1 = 0.f;  // rows g and g+8 of (group slot sub, batch row bt)
+      TRACE(1000 + q);
       mbar_wait(smem_u32(&bars[s]), (cc / S) & 1);
+      TRACE(2000 + q);
       if (p.debug != 1) {
         const uint8_t *blk = stages + (size_t)s * p.stage_bytes + bi * C::BB;
         decode_scales<TYPE, NB>(blk + (lane & 15) * C::RS + pad_d, lane, e, SX, XX, area);
@@ -464,12 +509,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
         red[tb * red_tile + (e * 8 + g) * NB + (t >> 1)] = make_float2(acc0, acc1);
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars[2 * S + tb]));
+      TRACE(3000 + q);
     } else {
       // ------------------------------------------------ fold tile li - 1 (or the last tile)
       const int fl = e < p.nblk ? ntl - 1 : li - 1;  // q == total - 1 has li == ntl, e == 0
       if (fl < 0) continue;
       const int tb = fl % kFoldBufs;
+      TRACE(4000 + q);
       mbar_wait(smem_u32(&bars[2 * S + tb]), (fl / kFoldBufs) & 1);
+      TRACE(5000 + q);
       // lane = (batch row, row of the tile): a fixed-order sum over the superblocks
       const int r16 = lane & 15, b = lane >> 4;
       const float2 *src = red + tb * red_tile + (r16 & 7) * NB + (b & (NB - 1));
@@ -480,15 +528,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars[2 * S + kFoldBufs + tb]));
-      const int row = (blockIdx.x + fl * gridDim.x) * kR + r16;
-      if (b < NB && row < p.out_dim) {
+      const int gt = blockIdx.x + fl * gridDim.x;
+      locate(gt, cj);
+      const Job &job = p.jobs[cj];
+      const int row = (gt - p.tcum[cj]) * kR + r16;
+      if (b < NB && row < job.out_dim) {
         if (p.part_keys) {
           const long long key = top1_key(v, (uint32_t)(p.index_base + row));
           if (b == 0) best = key > best ? key : best;
           else best_b1 = key > best_b1 ? key : best_b1;
         } else {
-          const float a = p.addend ? p.addend[(long long)b * p.addend_stride + row] : 0.f;
-          p.y[(long long)b * p.out_dim + row] = a + v;
+          const float a = job.addend ? job.addend[(long long)b * p.addend_stride + row] : 0.f;
+          job.y[(long long)b * job.out_dim + row] = a + v;
         }
       }
     }
@@ -553,7 +604,7 @@ int sm_count() {
 }
 
 template <int TYPE>
-bool make_plan(int in_dim, int out_dim, int nb, Params &p, size_t &smem) {
+bool make_plan(int in_dim, int nb, Params &p, size_t &smem) {
   using C = Cfg<TYPE>;
   const int nblk = in_dim / 256;
   const int ngroups = in_dim / C::GROUP;
@@ -569,8 +620,8 @@ bool make_plan(int in_dim, int out_dim, int nb, Params &p, size_t &smem) {
   if (off_stage + 3 * stage_bytes > kDynSmemMax) return false;
   int stages = (int)((kDynSmemMax - off_stage) / stage_bytes);
   if (stages > 8) stages = 8;  // 2*stages + 2*kFoldBufs mbarriers + the work counter: 200 bytes
-  p.in_dim = in_dim; p.out_dim = out_dim;
-  p.nblk = nblk; p.nchunks = (nblk + C::KB - 1) / C::KB; p.ntiles = (out_dim + kR - 1) / kR;
+  p.in_dim = in_dim;
+  p.nblk = nblk; p.nchunks = (nblk + C::KB - 1) / C::KB;
   p.stages = stages; p.row_bytes = (long long)nblk * C::BB;
   p.off_red = (int)off_red; p.off_area = (int)off_area; p.off_sx = (int)off_sx;
   p.off_xx = (int)off_xx; p.off_xq = (int)off_xq; p.off_stage = (int)off_stage;
@@ -604,32 +655,44 @@ int launch_instance(const Params &p, size_t smem, int grid, cudaStream_t s) {
   return (int)cudaLaunchKernelEx(&cfg, gemv_imma_kernel<TYPE, NB>, p);
 }
 
+// njobs weight matrices (same type and in_dim), one x: the reference's qmatvec_many
+// (src/ml/gguf/qwen35_cpu.cr:1419-1490) and dual GEMV (q4k_dual_gemv_probe.ptx:5) as one launch.
 template <int TYPE>
-int gemv_typed(const void *d_w, const float *d_x, const float *d_addend, int64_t addend_stride,
-               float *d_y, int in_dim, int out_dim, int batch, int resident, const Params *top1,
-               cudaStream_t s) {
-  Params p{};
-  size_t smem = 0;
-  if (!make_plan<TYPE>(in_dim, out_dim, batch, p, smem)) return COGNI_QMM_ERR_LIMIT;
-  p.w = static_cast<const uint8_t *>(d_w);
-  p.x = d_x;
-  p.addend = d_addend;
-  p.addend_stride = addend_stride;
-  p.y = d_y;
-  p.resident = resident;
-  p.debug = g_imma_debug;
-  const int sms = sm_count();
-  const int grid = p.ntiles < sms ? p.ntiles : sms;
-  if (top1) {
-    p.part_keys = top1->part_keys;
-    p.counter = top1->counter;
-    p.top_idx = top1->top_idx;
-    p.top_val = top1->top_val;
-    p.top_key = top1->top_key;
-    p.index_base = top1->index_base;
+int gemv_typed(int njobs, const void *const *d_w, const float *d_x, const float *const *d_addend,
+               int64_t addend_stride, float *const *d_y, const int *out_dims, int in_dim, int batch,
+               int resident, const Params *top1, cudaStream_t s) {
+  for (int j0 = 0; j0 < njobs; j0 += kMaxJobs) {
+    const int nj = njobs - j0 < kMaxJobs ? njobs - j0 : kMaxJobs;
+    Params p{};
+    size_t smem = 0;
+    if (!make_plan<TYPE>(in_dim, batch, p, smem)) return COGNI_QMM_ERR_LIMIT;
+    p.x = d_x;
+    p.addend_stride = addend_stride;
+    p.resident = resident;
+    p.debug = g_imma_debug;
+    p.njobs = nj;
+    for (int j = 0; j < nj; j++) {
+      p.jobs[j].w = static_cast<const uint8_t *>(d_w[j0 + j]);
+      p.jobs[j].addend = d_addend ? d_addend[j0 + j] : nullptr;
+      p.jobs[j].y = d_y ? d_y[j0 + j] : nullptr;
+      p.jobs[j].out_dim = out_dims[j0 + j];
+      p.tcum[j + 1] = p.tcum[j] + (out_dims[j0 + j] + kR - 1) / kR;
+    }
+    const int sms = sm_count();
+    const int grid = p.tcum[nj] < sms ? p.tcum[nj] : sms;
+    if (top1) {
+      p.part_keys = top1->part_keys;
+      p.counter = top1->counter;
+      p.top_idx = top1->top_idx;
+      p.top_val = top1->top_val;
+      p.top_key = top1->top_key;
+      p.index_base = top1->index_base;
+    }
+    const int st = batch == 1 ? launch_instance<TYPE, 1>(p, smem, grid, s)
+                              : launch_instance<TYPE, 2>(p, smem, grid, s);
+    if (st) return st;
   }
-  return batch == 1 ? launch_instance<TYPE, 1>(p, smem, grid, s)
-                    : launch_instance<TYPE, 2>(p, smem, grid, s);
+  return COGNI_QMM_OK;
 }
 
 }  // namespace
@@ -643,15 +706,22 @@ bool gemv_imma_supports(int type, const void *d_w, const float *d_x, int in_dim,
   return in_dim % 256 == 0 && in_dim <= 16384;
 }
 
+int launch_gemv_imma_many(int type, int njobs, const void *const *d_w, const float *d_x,
+                          const float *const *d_addend, int64_t addend_stride, float *const *d_y,
+                          const int *out_dims, int in_dim, int batch, int resident, cudaStream_t s) {
+  switch (type) {
+    case kQ4_K: return gemv_typed<kQ4_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s);
+    case kQ5_K: return gemv_typed<kQ5_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s);
+    case kQ6_K: return gemv_typed<kQ6_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s);
+    default: return COGNI_QMM_ERR_TYPE;
+  }
+}
+
 int launch_gemv_imma(int type, const void *d_w, const float *d_x, const float *d_addend,
                      int64_t addend_stride, float *d_y, int in_dim, int out_dim, int batch,
                      int resident, cudaStream_t s) {
-  switch (type) {
-    case kQ4_K: return gemv_typed<kQ4_K>(d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, resident, nullptr, s);
-    case kQ5_K: return gemv_typed<kQ5_K>(d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, resident, nullptr, s);
-    case kQ6_K: return gemv_typed<kQ6_K>(d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, resident, nullptr, s);
-    default: return COGNI_QMM_ERR_TYPE;
-  }
+  return launch_gemv_imma_many(type, 1, &d_w, d_x, d_addend ? &d_addend : nullptr, addend_stride,
+                               &d_y, &out_dim, in_dim, batch, resident, s);
 }
 
 int launch_gemv_top1_imma(int type, const void *d_w, const float *d_x, int in_dim, int out_dim,
@@ -666,12 +736,20 @@ int launch_gemv_top1_imma(int type, const void *d_w, const float *d_x, int in_di
   t.top_key = d_key;
   t.index_base = index_base;
   switch (type) {
-    case kQ4_K: return gemv_typed<kQ4_K>(d_w, d_x, nullptr, 0, nullptr, in_dim, out_dim, batch, resident, &t, s);
-    case kQ5_K: return gemv_typed<kQ5_K>(d_w, d_x, nullptr, 0, nullptr, in_dim, out_dim, batch, resident, &t, s);
-    case kQ6_K: return gemv_typed<kQ6_K>(d_w, d_x, nullptr, 0, nullptr, in_dim, out_dim, batch, resident, &t, s);
+    case kQ4_K: return gemv_typed<kQ4_K>(1, &d_w, d_x, nullptr, 0, nullptr, &out_dim, in_dim, batch, resident, &t, s);
+    case kQ5_K: return gemv_typed<kQ5_K>(1, &d_w, d_x, nullptr, 0, nullptr, &out_dim, in_dim, batch, resident, &t, s);
+    case kQ6_K: return gemv_typed<kQ6_K>(1, &d_w, d_x, nullptr, 0, nullptr, &out_dim, in_dim, batch, resident, &t, s);
     default: return COGNI_QMM_ERR_TYPE;
   }
 }
+
+#ifdef COGNI_TRACE
+}  // namespace cogni
+extern "C" int cogni_qmm_debug_trace(long long *out, int n) {
+  return (int)cudaMemcpyFromSymbol(out, cogni::g_trace, (size_t)n * 8);
+}
+namespace cogni {
+#endif
 
 unsigned gemv_imma_timeouts() {
   unsigned v = 0;

@@ -199,6 +199,53 @@ class DeviceQuantWeight:
         return out
 
 
+class GemvMany:
+    """A prepared qmatvec_many call: several resident weights of one type and in_dim against one
+    x (src/ml/gguf/qwen35_cpu.cr:1419-1490).  The pointer tables are built once; `run` issues one
+    launch."""
+
+    def __init__(self, weights, x: torch.Tensor, outs, residuals=None):
+        import ctypes as C
+        if not weights or len({(w.type, w.in_dim) for w in weights}) != 1:
+            raise ValueError("weights must share type and in_dim")
+        self.weights, self.x, self.outs = list(weights), x, list(outs)
+        n = len(self.weights)
+        w0 = self.weights[0]
+        if x.dtype != torch.float32 or not x.is_contiguous() or x.shape[-1] != w0.in_dim:
+            raise ValueError("x must be contiguous f32 [batch, in_dim]")
+        self.batch = x.numel() // w0.in_dim
+        self._w = (C.c_void_p * n)(*[w.raw.data_ptr() for w in self.weights])
+        self._y = (C.c_void_p * n)(*[o.data_ptr() for o in self.outs])
+        self._n = (C.c_int * n)(*[w.out_dim for w in self.weights])
+        self._add = None
+        self._stride = 0
+        if residuals is not None:
+            self.residuals = list(residuals)
+            self._add = (C.c_void_p * n)(*[r.data_ptr() if r is not None else None
+                                           for r in self.residuals])
+            self._stride = -1   # per matrix: out_dim; checked below
+            if len({w.out_dim for w in self.weights}) != 1:
+                raise ValueError("residuals need equal out_dim across the weights")
+            self._stride = self.weights[0].out_dim
+        self._resident = int(all(w.resident for w in self.weights))
+
+    def run(self, stream=None):
+        w0 = self.weights[0]
+        check(lib.cogni_qmm_gemv_many(w0.type, len(self.weights), self._w, self.x.data_ptr(),
+                                      self._add, self._stride, self._y, self._n, w0.in_dim,
+                                      self.batch, self._resident, _stream_ptr(stream)),
+              "cogni_qmm_gemv_many")
+        return self.outs
+
+
+def gemv_many(weights, x: torch.Tensor, outs=None, stream=None):
+    """y_j = W_j @ x for several weights sharing x, in one launch."""
+    batch = x.numel() // weights[0].in_dim
+    if outs is None:
+        outs = [torch.empty(batch, w.out_dim, dtype=torch.float32, device=x.device) for w in weights]
+    return GemvMany(weights, x, outs).run(stream)
+
+
 def unpack_top1_keys(keys: torch.Tensor):
     """(index int32, value f32) from int64 keys, e.g. after a MAX all-reduce across vocab shards."""
     batch = keys.numel()

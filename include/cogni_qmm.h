@@ -118,6 +118,22 @@ int cogni_qmm_gemv_resident(int type, const void *d_w, const float *d_x, const f
                             void *stream);
 
 /*
+ * Several weight matrices of one type and in_dim against the SAME x in one launch:
+ *     y_j[b, o] = addend_j[b*addend_stride + o] + sum_k x[b, k] * dequant(W_j[o, k])
+ * Replaces Qwen35CPU.qmatvec_many (src/ml/gguf/qwen35_cpu.cr:1419-1490: qkv / gate / alpha / beta
+ * from one hidden state, ffn_gate + ffn_up) and the dual GEMV kernel
+ * (src/ml/cuda/kernels/q4k_dual_gemv_probe.ptx:5).  The matrices' row tiles form one work
+ * sequence, so the launch ramp and tail are paid once and the rows balance over the SMs together.
+ *   d_w, d_y, out_dims   HOST arrays of n_weights device pointers / row counts
+ *   d_addend             NULL, or a HOST array of n_weights device pointers (entries may be NULL)
+ *   resident             non-zero: the promise of cogni_qmm_gemv_resident for every matrix
+ * Other arguments as for cogni_qmm_gemv.  batch > 2 or unaligned pointers run one GEMV per matrix.
+ */
+int cogni_qmm_gemv_many(int type, int n_weights, const void *const *d_w, const float *d_x,
+                        const float *const *d_addend, int64_t addend_stride, float *const *d_y,
+                        const int *out_dims, int in_dim, int batch, int resident, void *stream);
+
+/*
  * Fused lm_head: GEMV over `out_dim` vocabulary rows plus top-1 per batch row, without
  * writing the logits.  Replaces q6_k_gemv_top1_partial_f32 + output_top1_values_reduce_probe
  * (q6k_gemv_probe.ptx:1331; src/ml/cuda/qwen_output_head_runner.cr:530-624, 884-947).

@@ -155,6 +155,24 @@ def test_matmul_add_host_surface(cuda, oracle, qtype):
     assert_close(mine, ref, f"matmul_add type {qtype}")
 
 
+@pytest.mark.parametrize("qtype", [Q4_K, Q5_K, Q6_K, Q8_0])
+@pytest.mark.parametrize("batch", [1, 2, 5])
+def test_gemv_many_shares_x_across_weights(cuda, oracle, qtype, batch):
+    """qmatvec_many: several matrices (ragged row counts, more than one launch's worth), one x."""
+    from cogni_ml_b200 import gemv_many
+    in_dim = 1024
+    out_dims = [33, 256, 16, 1000] + [48] * 31          # 35 matrices > 32 per launch
+    x = synth.make_activation(batch, in_dim, seed=43)
+    xd = torch.from_numpy(x).to(cuda)
+    raws = [synth.make_weight(qtype, n, in_dim, seed=43, tensor_id=100 + j) for j, n in enumerate(out_dims)]
+    dws = [DeviceQuantWeight.upload(QuantWeight(r, qtype, n, in_dim), cuda) for r, n in zip(raws, out_dims)]
+    outs = [torch.full((batch, n), float("nan"), device=cuda) for n in out_dims]
+    gemv_many(dws, xd, outs)
+    for j, n in enumerate(out_dims):
+        ref = oracle.matmul_add(x, batch, in_dim, raws[j], qtype, n, np.zeros(n, np.float32))
+        assert_close(outs[j].cpu().numpy().ravel(), ref, f"matrix {j}")
+
+
 def test_matmul_add_rejects_unknown_type(cuda):
     with pytest.raises(RuntimeError, match="unsupported tensor type"):
         QuantMatmul.matmul_add(np.zeros(32, np.float32), 1, 32, np.zeros(64, np.uint8), 2, 1,
