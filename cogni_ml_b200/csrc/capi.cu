@@ -46,7 +46,7 @@ const char *cogni_qmm_status_string(int status) {
 }
 
 int cogni_qmm_set_kernel_choice(int choice) {
-  if (choice >= 16 && choice <= 18) {  // timing diagnostics of the tiled kernel (results invalid)
+  if (choice >= 16 && choice <= 19) {  // timing diagnostics of the tiled kernel (results invalid)
     gemv_mma_set_debug(choice - 16);
     gemv_imma_set_debug(choice - 16);
     return COGNI_QMM_OK;

@@ -6,7 +6,7 @@
 //
 //  * A persistent CTA per SM walks row tiles of 16 output rows.  One producer warp streams the
 //    tiles' rows with 1-D bulk async copies (cp.async.bulk, completion on an mbarrier) into a ring
-//    of shared-memory stages, KB superblocks of every row per stage.  The 16 consumer warps take
+//    of shared-memory stages, KB superblocks of every row per stage.  The consumer warps take
 //    work items (one superblock of a 16-row tile, or the fold of a finished tile) in order from a
 //    shared counter: every warp stays busy until the CTA runs dry and the warps of a scheduler
 //    are always in different phases (waiting for data, decoding scales, issuing MMAs, folding),
@@ -15,12 +15,16 @@
 //  * Activations are quantised once per CTA to 15-bit block floating point: per scale group
 //    (32 elements for Q4_K/Q5_K, 16 for Q6_K) x = sx * n with |n| <= 16256, n = 128*hi + lo, hi
 //    and lo int8.  The rounding step is 2^-14 of the group maximum, i.e. ~4e-5 relative rms.
-//  * The quants feed mma.sync.m16n8k32 (u8 x s8 -> s32) as they are: Q4_K nibbles need one AND /
-//    shift-AND per four weights and no widening.  One MMA covers two scale groups at once: the hi
-//    and lo planes of group A occupy columns 0-1 with zeros in group B's k-slots, group B's planes
-//    columns 2-3 with zeros in A's slots, so each lane ends up with the exact integer dot product
-//    of one (row, group) pair.  It is combined (128*hi + lo), converted once and multiplied by
-//    d*sc*sx in fp32; accumulation across groups is fp32.
+//  * The quants feed mma.sync.m16n8k32 (u8 x s8 -> s32) as they are.  One MMA covers two scale
+//    groups at once: the hi and lo planes of group A occupy columns 0-1 with zeros in group B's
+//    k-slots, group B's planes columns 2-3 with zeros in A's slots, so each lane ends up with the
+//    exact integer dot product of one (row, group) pair.  It is combined (128*hi + lo), converted
+//    once and multiplied by d*sc*sx in fp32; accumulation across groups is fp32.
+//    Q4_K does not even separate its nibbles: a byte b = lo + 16*hi goes in whole (k-slots 0..15)
+//    next to H = b & 0xF0 (k-slots 16..31).  Group A's columns hold x in the first half and -x in
+//    the second, so the MMA yields sum((b - H) * x) = sum(lo * x); group B's columns hold x only in
+//    the second half and yield 16 * sum(hi * x), the 1/16 being folded into that group's scale.
+//    That is one AND per eight weights.
 //  * Terms that do not depend on the quants (Q4_K/Q5_K -dmin*m, Q6_K's -32) are folded into one
 //    correction per (row, superblock) from the per-group sums of the quantised activations.
 //  * Each superblock's partial sums go to a per-tile buffer indexed by superblock; a later work
@@ -42,11 +46,16 @@ namespace {
 #define COGNI_IMMA_WARPS 24
 #endif
 constexpr int kNW = COGNI_IMMA_WARPS;        // consumer warps
-constexpr int kFoldBufs = 4;                 // tiles whose partial sums can be pending
-constexpr int kThreads = (kNW + 1) * 32;     // + 1 producer warp
+constexpr int kFoldBufs = 4;                 // tiles whose partial sums can be pending (power of 2)
+// One warp issues bulk copies at roughly one per 70-90 cycles however many of its lanes take
+// part; the copy unit itself accepts several times that, so the rows of a stage are split over
+// kPW producer warps.
+constexpr int kPW = 4;                       // producer warps
+constexpr int kThreads = (kNW + kPW) * 32;
 constexpr int kR = 16;                       // rows per tile
 constexpr size_t kDynSmemMax = 227 * 1024 - 1024;
 constexpr int kNMax = 16256;                 // |n| bound: 127 * 128
+static_assert(kR == 4 * kPW, "each producer warp issues four rows of a stage");
 
 constexpr int stage_row_stride(int bb, int kb, bool unaligned_rows) {
   int rs = (bb * kb + (unaligned_rows ? 16 : 0) + 15) / 16 * 16;
@@ -93,7 +102,7 @@ struct Params {
   long long row_bytes;
   int off_red, off_area, off_sx, off_xx, off_xq, off_stage, stage_bytes;
   int resident;  // weights were complete before the preceding kernel started
-  int debug;     // diagnostics: 1 = stream only, 2 = stream + decode
+  int debug;     // diagnostics: 1 = stream only, 2 = stream + decode, 3 = compute only (no copies)
   long long *part_keys;  // fused top-1 (nullptr: plain GEMV)
   unsigned *counter;
   int32_t *top_idx;
@@ -170,8 +179,15 @@ __device__ __forceinline__ int xq_word_offset(int e_in /*element within superblo
 }
 
 // ---------------------------------------------------------------------------- per-block work
-// Area of one warp: dscx[NB][NG][16] floats (d*sc*sx of the superblock's NG scale groups, 16
-// rows, per batch row) followed by corr[NB][16].
+// Area of one warp: per batch row 16 tile rows of AREA_ROW floats.  Row r holds d*sc*sx of the
+// superblock's scale groups, ordered so that an MMA lane fetches the ones of its group slot `sub`
+// with vector loads, then the row's correction term at index NG:
+//   Q4_K/Q5_K  index 4*sub + g4                group 2*g4 + sub
+//   Q6_K       index 8*sub + 4*n + 2*h + m     group 8*n + h + 2*sub + 4*m
+template <int TYPE> struct Area {
+  static constexpr int ROW = Cfg<TYPE>::NG + 4;  // 12 / 20 floats: rows stay 16-byte aligned
+  static constexpr int BATCH = 16 * ROW;         // floats per batch row
+};
 
 // Lanes (r = lane & 15, half = lane >> 4) decode one half of the scale groups of row r; the two
 // halves' corrections are combined with one shuffle.
@@ -179,6 +195,7 @@ template <int TYPE, int NB>
 __device__ __forceinline__ void decode_scales(const uint8_t *blk_row, int lane, int kblk,
                                               const float *SX, const float *XX, float *area) {
   using C = Cfg<TYPE>;
+  using A = Area<TYPE>;
   constexpr int NH = C::NG / 2;  // groups per lane
   const int r = lane & 15, half = lane >> 4;
   float dsc[NH], kk[NH];
@@ -191,9 +208,11 @@ __device__ __forceinline__ void decode_scales(const uint8_t *blk_row, int lane, 
     const uint32_t scw = half ? ((u2 & 0x0f0f0f0fu) | ((u0 >> 2) & 0x30303030u)) : (u0 & 0x3f3f3f3fu);
     const uint32_t mnw = half ? (((u2 >> 4) & 0x0f0f0f0fu) | ((u1 >> 2) & 0x30303030u)) : (u1 & 0x3f3f3f3fu);
     const float d23 = d * 8388608.f, ndmin = -dmin, ndmin23 = ndmin * 8388608.f;
+    // Q4_K: the odd groups' integer sums arrive multiplied by 16 (see mma_block)
+    const float dodd = TYPE == kQ4_K ? d * 0.0625f : d, dodd23 = dodd * 8388608.f;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-      dsc[i] = byte_times(scw, i, d, d23);
+      dsc[i] = (i & 1) ? byte_times(scw, i, dodd, dodd23) : byte_times(scw, i, d, d23);
       kk[i] = byte_times(mnw, i, ndmin, ndmin23);
     }
   } else {
@@ -205,34 +224,59 @@ __device__ __forceinline__ void decode_scales(const uint8_t *blk_row, int lane, 
       kk[i] = -32.f * dsc[i];
     }
   }
-  const int grp0 = kblk * C::NG + NH * half;  // first of this lane's groups in the tables
+  // this lane's groups are consecutive in the tables: NH * NB floats each, 16-byte aligned
+  const int grp0 = kblk * C::NG + NH * half;
+  float sxv[NH * NB], xxv[NH * NB];
+#pragma unroll
+  for (int i = 0; i < NH * NB / 4; i++) {
+    const float4 a = reinterpret_cast<const float4 *>(SX + grp0 * NB)[i];
+    const float4 c = reinterpret_cast<const float4 *>(XX + grp0 * NB)[i];
+    sxv[4 * i] = a.x; sxv[4 * i + 1] = a.y; sxv[4 * i + 2] = a.z; sxv[4 * i + 3] = a.w;
+    xxv[4 * i] = c.x; xxv[4 * i + 1] = c.y; xxv[4 * i + 2] = c.z; xxv[4 * i + 3] = c.w;
+  }
 #pragma unroll
   for (int b = 0; b < NB; b++) {
-    float corr = 0.f;
+    float *row = area + b * A::BATCH + r * A::ROW;
+    float v[NH], corr = 0.f;
 #pragma unroll
     for (int i = 0; i < NH; i++) {
-      area[(b * C::NG + NH * half + i) * 16 + r] = dsc[i] * SX[(grp0 + i) * NB + b];
-      corr = fmaf(kk[i], XX[(grp0 + i) * NB + b], corr);
+      v[i] = dsc[i] * sxv[i * NB + b];
+      corr = fmaf(kk[i], xxv[i * NB + b], corr);
+    }
+    if constexpr (C::HAS_MIN) {  // lane's groups 4*half + i: g4 = 2*half + (i >> 1), sub = i & 1
+      *reinterpret_cast<float2 *>(row + 2 * half) = make_float2(v[0], v[2]);
+      *reinterpret_cast<float2 *>(row + 4 + 2 * half) = make_float2(v[1], v[3]);
+    } else {  // lane's groups 8*half + i: n = half, h = i & 1, sub = (i >> 1) & 1, m = i >> 2
+      *reinterpret_cast<float4 *>(row + 4 * half) = make_float4(v[0], v[4], v[1], v[5]);
+      *reinterpret_cast<float4 *>(row + 8 + 4 * half) = make_float4(v[2], v[6], v[3], v[7]);
     }
     corr += __shfl_xor_sync(0xffffffffu, corr, 16);
-    if (half == 0) area[NB * C::NG * 16 + b * 16 + r] = corr;
+    if (half == 0) row[C::NG] = corr;
   }
 }
 
 // MMAs of one superblock (16 rows x 256 columns) for this lane's (group slot sub, batch row).
 // blk: the superblock of row 0 of the tile inside the stage; xu: this lane's B fragments of the
-// superblock's first unit; dscx: this lane's batch row of the decoded scales.
+// superblock's first unit; ab: this lane's batch row of the warp's area.  Returns the partial
+// sums of rows g and g+8 (the correction included in the sub == 0 lanes).
 template <int TYPE, int UNIT_BYTES>
 __device__ __forceinline__ void mma_block(const uint8_t *blk, int pad_a, int pad_b,
-                                          const uint8_t *xu, const float *dscx, int g, int t,
+                                          const uint8_t *xu, const float *ab, int g, int t,
                                           int sub, float &acc0, float &acc1) {
   using C = Cfg<TYPE>;
+  using A = Area<TYPE>;
   constexpr uint32_t M4 = 0x0f0f0f0fu;
+  const float *rowa = ab + g * A::ROW, *rowb = ab + (g + 8) * A::ROW;
+  acc0 = sub ? 0.f : rowa[C::NG];
+  acc1 = sub ? 0.f : rowb[C::NG];
   if constexpr (C::HAS_MIN) {
     constexpr bool Q5 = TYPE == kQ5_K;
     constexpr int QOFF = Q5 ? 48 : 16;
     constexpr uint32_t M1 = 0x10101010u;
     const uint8_t *ra = blk + g * C::RS + pad_a + 8 * t, *rb = blk + (g + 8) * C::RS + pad_b + 8 * t;
+    const float4 sa4 = *reinterpret_cast<const float4 *>(rowa + 4 * sub);
+    const float4 sb4 = *reinterpret_cast<const float4 *>(rowb + 4 * sub);
+    const float sa[4] = {sa4.x, sa4.y, sa4.z, sa4.w}, sb[4] = {sb4.x, sb4.y, sb4.z, sb4.w};
     uint2 qha = make_uint2(0, 0), qhb = make_uint2(0, 0);
     if constexpr (Q5) {
       qha = *reinterpret_cast<const uint2 *>(ra + 16);
@@ -243,60 +287,66 @@ __device__ __forceinline__ void mma_block(const uint8_t *blk, int pad_a, int pad
       const uint4 bv = *reinterpret_cast<const uint4 *>(xu + g4 * UNIT_BYTES);
       const uint2 qa = *reinterpret_cast<const uint2 *>(ra + QOFF + 32 * g4);
       const uint2 qb = *reinterpret_cast<const uint2 *>(rb + QOFF + 32 * g4);
-      uint32_t la0 = qa.x & M4, la1 = qa.y & M4, lb0 = qb.x & M4, lb1 = qb.y & M4;
-      uint32_t ha0 = (qa.x >> 4) & M4, ha1 = (qa.y >> 4) & M4;
-      uint32_t hb0 = (qb.x >> 4) & M4, hb1 = (qb.y >> 4) & M4;
-      if constexpr (Q5) {
+      int cc[4];
+      if constexpr (!Q5) {
+        constexpr uint32_t MH = 0xf0f0f0f0u;
+        imma_zero(cc, qa.x, qb.x, qa.x & MH, qb.x & MH, bv.x, bv.y);
+        imma_acc(cc, qa.y, qb.y, qa.y & MH, qb.y & MH, bv.z, bv.w);
+      } else {
+        uint32_t la0 = qa.x & M4, la1 = qa.y & M4, lb0 = qb.x & M4, lb1 = qb.y & M4;
+        uint32_t ha0 = (qa.x >> 4) & M4, ha1 = (qa.y >> 4) & M4;
+        uint32_t hb0 = (qb.x >> 4) & M4, hb1 = (qb.y >> 4) & M4;
         // fifth bit: bit 2*g4 of qh for the low-nibble elements, bit 2*g4+1 for the high ones
         auto bit = [&](uint32_t q, int b) { return b <= 4 ? ((q << (4 - b)) & M1) : ((q >> (b - 4)) & M1); };
         la0 |= bit(qha.x, 2 * g4);     la1 |= bit(qha.y, 2 * g4);
         lb0 |= bit(qhb.x, 2 * g4);     lb1 |= bit(qhb.y, 2 * g4);
         ha0 |= bit(qha.x, 2 * g4 + 1); ha1 |= bit(qha.y, 2 * g4 + 1);
         hb0 |= bit(qhb.x, 2 * g4 + 1); hb1 |= bit(qhb.y, 2 * g4 + 1);
+        // k-slots 0..15: sub-block 2*g4 (low nibbles), 16..31: sub-block 2*g4+1 (high)
+        imma_zero(cc, la0, lb0, ha0, hb0, bv.x, bv.y);
+        imma_acc(cc, la1, lb1, ha1, hb1, bv.z, bv.w);
       }
-      int cc[4];
-      // k-slots 0..15: sub-block 2*g4 (low nibbles), 16..31: sub-block 2*g4+1 (high)
-      imma_zero(cc, la0, lb0, ha0, hb0, bv.x, bv.y);
-      imma_acc(cc, la1, lb1, ha1, hb1, bv.z, bv.w);
-      const float sa = dscx[(2 * g4 + sub) * 16 + g], sb = dscx[(2 * g4 + sub) * 16 + g + 8];
-      acc0 = fmaf(sa, (float)(cc[0] * 128 + cc[1]), acc0);
-      acc1 = fmaf(sb, (float)(cc[2] * 128 + cc[3]), acc1);
+      acc0 = fmaf(sa[g4], (float)(cc[0] * 128 + cc[1]), acc0);
+      acc1 = fmaf(sb[g4], (float)(cc[2] * 128 + cc[3]), acc1);
     }
   } else {
     constexpr uint32_t M2 = 0x30303030u;
     const uintptr_t aa = reinterpret_cast<uintptr_t>(blk + g * C::RS + pad_a + 4 * t);
-    const uintptr_t ab = reinterpret_cast<uintptr_t>(blk + (g + 8) * C::RS + pad_b + 4 * t);
+    const uintptr_t ab8 = reinterpret_cast<uintptr_t>(blk + (g + 8) * C::RS + pad_b + 4 * t);
     const uint8_t *base[2] = {reinterpret_cast<const uint8_t *>(aa & ~(uintptr_t)3),
-                              reinterpret_cast<const uint8_t *>(ab & ~(uintptr_t)3)};
-    const uint32_t sh[2] = {(uint32_t)(aa & 2) * 8, (uint32_t)(ab & 2) * 8};
+                              reinterpret_cast<const uint8_t *>(ab8 & ~(uintptr_t)3)};
+    const uint32_t sh[2] = {(uint32_t)(aa & 2) * 8, (uint32_t)(ab8 & 2) * 8};
 #pragma unroll
-    for (int nh = 0; nh < 4; nh++) {
-      const int n = nh >> 1, h = nh & 1;
-      const uint4 bv = *reinterpret_cast<const uint4 *>(xu + nh * UNIT_BYTES);
-      uint32_t q[2][4];
+    for (int n = 0; n < 2; n++) {
+      const float4 sa4 = *reinterpret_cast<const float4 *>(rowa + 8 * sub + 4 * n);
+      const float4 sb4 = *reinterpret_cast<const float4 *>(rowb + 8 * sub + 4 * n);
+      const float sa[4] = {sa4.x, sa4.y, sa4.z, sa4.w}, sb[4] = {sb4.x, sb4.y, sb4.z, sb4.w};
 #pragma unroll
-      for (int r = 0; r < 2; r++) {
-        auto ld = [&](int off) {
-          const uint32_t *w32 = reinterpret_cast<const uint32_t *>(base[r] + off);
-          return __funnelshift_r(w32[0], w32[1], sh[r]);
-        };
-        const uint32_t ql0 = ld(64 * n + 16 * h), ql1 = ld(64 * n + 32 + 16 * h);
-        const uint32_t qhw = ld(128 + 32 * n + 16 * h);
-        q[r][0] = (ql0 & M4) | ((qhw << 4) & M2);
-        q[r][1] = (ql1 & M4) | ((qhw << 2) & M2);
-        q[r][2] = ((ql0 >> 4) & M4) | (qhw & M2);
-        q[r][3] = ((ql1 >> 4) & M4) | ((qhw >> 2) & M2);
-      }
+      for (int h = 0; h < 2; h++) {
+        const uint4 bv = *reinterpret_cast<const uint4 *>(xu + (2 * n + h) * UNIT_BYTES);
+        uint32_t q[2][4];
 #pragma unroll
-      for (int m = 0; m < 2; m++) {
-        int cc[4];
-        // k-slots 0..15: run k = 2m, 16..31: run k = 2m+1 (scale group 8n + h + 2k)
-        imma_zero(cc, q[0][2 * m], q[1][2 * m], q[0][2 * m + 1], q[1][2 * m + 1],
-                  m ? bv.z : bv.x, m ? bv.w : bv.y);
-        const int j16 = 8 * n + h + 2 * (2 * m + sub);
-        const float sa = dscx[j16 * 16 + g], sb = dscx[j16 * 16 + g + 8];
-        acc0 = fmaf(sa, (float)(cc[0] * 128 + cc[1]), acc0);
-        acc1 = fmaf(sb, (float)(cc[2] * 128 + cc[3]), acc1);
+        for (int r = 0; r < 2; r++) {
+          auto ld = [&](int off) {
+            const uint32_t *w32 = reinterpret_cast<const uint32_t *>(base[r] + off);
+            return __funnelshift_r(w32[0], w32[1], sh[r]);
+          };
+          const uint32_t ql0 = ld(64 * n + 16 * h), ql1 = ld(64 * n + 32 + 16 * h);
+          const uint32_t qhw = ld(128 + 32 * n + 16 * h);
+          q[r][0] = (ql0 & M4) | ((qhw << 4) & M2);
+          q[r][1] = (ql1 & M4) | ((qhw << 2) & M2);
+          q[r][2] = ((ql0 >> 4) & M4) | (qhw & M2);
+          q[r][3] = ((ql1 >> 4) & M4) | ((qhw >> 2) & M2);
+        }
+#pragma unroll
+        for (int m = 0; m < 2; m++) {
+          int cc[4];
+          // k-slots 0..15: run k = 2m, 16..31: run k = 2m+1 (scale group 8n + h + 2k)
+          imma_zero(cc, q[0][2 * m], q[1][2 * m], q[0][2 * m + 1], q[1][2 * m + 1],
+                    m ? bv.z : bv.x, m ? bv.w : bv.y);
+          acc0 = fmaf(sa[2 * h + m], (float)(cc[0] * 128 + cc[1]), acc0);
+          acc1 = fmaf(sb[2 * h + m], (float)(cc[2] * 128 + cc[3]), acc1);
+        }
       }
     }
   }
@@ -306,33 +356,22 @@ __device__ __forceinline__ void mma_block(const uint8_t *blk, int pad_a, int pad
 template <int TYPE, int NB>
 __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) {
   using C = Cfg<TYPE>;
+  using A = Area<TYPE>;
   constexpr int NCX = 4 * NB;                    // columns of the quantised-x layout
   constexpr int UNIT_BYTES = NCX * 64;
-  constexpr int AREA_FLOATS = NB * C::NG * 16 + NB * 16;
+  constexpr int AREA_FLOATS = NB * A::BATCH;
   extern __shared__ __align__(128) uint8_t smem[];
-  // mbarriers: full[S] | empty[S] | tile partials complete[kFoldBufs] | tile buffer free[kFoldBufs],
-  // then the work counter
+  // mbarriers full[S] | empty[S] in the first 128 bytes; monotone counters from byte 192:
+  // chunks armed by the producer | partial sums stored per tile buffer | folds done per tile buffer
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
+  int *issued = reinterpret_cast<int *>(smem + 192);
+  int *arrivals = issued + 1, *folded = arrivals + kFoldBufs;
   const int S = p.stages;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef COGNI_TRACE
   int tr_n = 0;
 #endif
   TRACE(1);
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < S; s++) {
-      mbar_init(smem_u32(&bars[s]), 1);
-      mbar_init(smem_u32(&bars[S + s]), C::KB);
-    }
-    for (int i = 0; i < kFoldBufs; i++) {
-      mbar_init(smem_u32(&bars[2 * S + i]), p.nblk);
-      mbar_init(smem_u32(&bars[2 * S + kFoldBufs + i]), 1);
-    }
-    *reinterpret_cast<int *>(&bars[2 * S + 2 * kFoldBufs]) = 0;
-    mbar_fence_init();
-  }
-  __syncthreads();
   pdl_launch_dependents();
 
   uint8_t *stages = smem + p.off_stage;
@@ -344,49 +383,79 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
     while (gt < p.tcum[j]) j--;
   };
 
-  if (warp == kNW) {
-    // ------------------------------------------------------------------ producer warp
+  if (warp >= kNW) {
+    // ------------------------------------------------------------------ producer warps
+    // The first producer warp initialises the mbarriers, so that streaming starts without
+    // waiting for the consumers' set-up; the consumers meet the producers at named barrier 3.
+    const int pw = warp - kNW;
+    if (pw == 0) {
+      if (lane < S) mbar_init(smem_u32(&bars[lane]), kPW);
+      else if (lane < 2 * S) mbar_init(smem_u32(&bars[lane]), C::KB);
+      else if (lane < 2 * S + 1 + 2 * kFoldBufs) issued[lane - 2 * S] = 0;
+      mbar_fence_init();
+    }
+    asm volatile("bar.sync 2, %0;" ::"n"(kPW * 32) : "memory");
+    asm volatile("bar.arrive 3, %0;" ::"n"(kThreads) : "memory");
     if (!p.resident) pdl_wait_prior_grid();
-    int it = 0, pj = 0;
+    // every producer warp walks the same chunk sequence; warp pw issues rows 4*pw .. 4*pw+3 and
+    // arrives once per chunk with the byte count of its own rows
+    int s = 0, par = 1, pj = 0, cc = 0;  // stage, parity of its empty barrier, chunk number
     for (int li = 0; li < ntl; li++) {
       const int gt = blockIdx.x + li * gridDim.x;
       locate(gt, pj);
       const int row = (gt - p.tcum[pj]) * kR + lane;
       const bool rvalid = lane < kR && row < p.jobs[pj].out_dim;
       const uint8_t *rsrc = p.jobs[pj].w + (long long)row * p.row_bytes;
-      for (int c = 0; c < p.nchunks; c++, it++) {
-        const int s = it % S;
-        TRACE(100 + it);
-        mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1);
-        TRACE(200 + it);
+      for (int c = 0; c < p.nchunks; c++) {
+        TRACE(100 + li * p.nchunks + c);
+        if (!mbar_wait(smem_u32(&bars[S + s]), par)) {  // broken pipeline: stop, let copies land
+          drain_copies_in_flight();
+          return;
+        }
+        TRACE(200 + li * p.nchunks + c);
         const int nb = min(C::KB, p.nblk - c * C::KB);
         const uint8_t *src = rsrc + (long long)c * C::KB * C::BB;
         const uint32_t padb = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15);
         const uint32_t bytes = rvalid ? ((padb + nb * C::BB + 15u) & ~15u) : 0u;
-        const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
         const uint32_t full = smem_u32(&bars[s]);
-        if (lane == 0) mbar_arrive_expect_tx(full, total);
-        __syncwarp();
-        if (rvalid)
-          bulk_g2s(smem_u32(stages + (size_t)s * p.stage_bytes + lane * C::RS), src - padb, bytes,
-                   full);
+        const bool mine = rvalid && (lane >> 2) == pw;
+        const uint32_t my_bytes = __reduce_add_sync(0xffffffffu, mine ? bytes : 0u);
+        if (p.debug == 3) {  // compute only: the stage is declared full without any copy
+          if (lane == 0) mbar_arrive(full);
+        } else {
+          if (lane == 0) mbar_arrive_expect_tx(full, my_bytes);
+          __syncwarp();
+          if (mine)
+            bulk_g2s(smem_u32(stages + (size_t)s * p.stage_bytes + lane * C::RS), src - padb,
+                     bytes, full);
+        }
+        // Consumers test the full barrier of chunk cc by phase parity only once this says that
+        // the barrier is in (or past) that chunk's phase: a warp whose items lie far apart could
+        // otherwise mistake the stage's previous fill for it.
+        cc++;
+        if (pw == 0 && lane == 0) {
+          __threadfence_block();
+          *reinterpret_cast<volatile int *>(issued) = cc;
+        }
+        if (++s == S) { s = 0; par ^= 1; }
       }
     }
+    if (pipe_broken()) drain_copies_in_flight();  // the consumers may not have waited for the copies
     return;
   }
 
   // -------------------------------------------------------------------- consumer warps
-  const int ctid = threadIdx.x;  // 0 .. 511
+  const int ctid = threadIdx.x;  // 0 .. kNW*32-1
   uint8_t *xq = smem + p.off_xq;
   float *SX = reinterpret_cast<float *>(smem + p.off_sx);
   float *XX = reinterpret_cast<float *>(smem + p.off_xx);
   const int K = p.in_dim;
 
-  {  // zero the fragment-ordered activation area (half of its words are structural zeros)
+  {  // zero the fragment-ordered activation area (its unused words are structural zeros)
     const int n16 = (K >> 6) * UNIT_BYTES / 16;
     for (int i = ctid; i < n16; i += kNW * 32) reinterpret_cast<uint4 *>(xq)[i] = make_uint4(0, 0, 0, 0);
   }
-  consumer_sync();
+  asm volatile("bar.sync 3, %0;" ::"n"(kThreads) : "memory");  // zeros written, mbarriers ready
   TRACE(3);
   pdl_wait_prior_grid();  // x (and y / the addend) may be produced by the preceding kernel
   TRACE(4);
@@ -403,18 +472,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
       for (int e = 0; e < 8; e++) mx = fmaxf(mx, fabsf(v[e]));
 #pragma unroll
       for (int off = 1; off < LPG; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-      const float sx = mx > 0.f ? mx * (1.f / kNMax) : 1.f;
-      const float inv = mx > 0.f ? (float)kNMax / mx : 0.f;
-      uint32_t hw[2] = {0, 0}, lw[2] = {0, 0};
-      int nsum = 0;
+      // groups below 1e-30 contribute nothing (their scale would underflow anyway)
+      const bool live = mx > 1e-30f;
+      const float sx = live ? mx * (1.f / kNMax) : 1.f;
+      const float inv = live ? (float)kNMax / mx : 0.f;
+      int hi[8], lo[8], nsum = 0;
 #pragma unroll
       for (int e = 0; e < 8; e++) {
-        int n = __float2int_rn(v[e] * inv);
-        n = max(-kNMax, min(kNMax, n));
-        const int hi = (n + 64) >> 7, lo = n - (hi << 7);
+        // round to nearest through the 1.5 * 2^23 bias: |x * inv| <= 16256 * (1 + 2^-21)
+        const int n = __float_as_int(fmaf(v[e], inv, 12582912.f)) - 0x4B400000;
+        hi[e] = (n + 64) >> 7;
+        lo[e] = n - (hi[e] << 7);
         nsum += n;
-        hw[e >> 2] |= (uint32_t)(hi & 0xff) << (8 * (e & 3));
-        lw[e >> 2] |= (uint32_t)(lo & 0xff) << (8 * (e & 3));
       }
 #pragma unroll
       for (int off = 1; off < LPG; off <<= 1) nsum += __shfl_xor_sync(0xffffffffu, nsum, off);
@@ -423,14 +492,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
         SX[grp * NB + b] = sx;
         XX[grp * NB + b] = sx * (float)nsum;
       }
+      auto pack4 = [](const int *q) {  // low bytes of four ints
+        return __byte_perm(__byte_perm(q[0], q[1], 0x0040), __byte_perm(q[2], q[3], 0x0040), 0x5410);
+      };
       uint8_t *blk_base = xq + (size_t)(k >> 8) * 4 * UNIT_BYTES;
       const int e_in = k & 255;
 #pragma unroll
       for (int w4 = 0; w4 < 2; w4++) {  // the two 4-element words of this thread's 8 elements
         int sub;
         const int off = xq_word_offset<TYPE>(e_in + 4 * w4, NCX, 4 * b, sub);
-        *reinterpret_cast<uint32_t *>(blk_base + off) = hw[w4];       // hi plane: column + 0
-        *reinterpret_cast<uint32_t *>(blk_base + off + 64) = lw[w4];  // lo plane: column + 1
+        const uint32_t hw = pack4(hi + 4 * w4), lw = pack4(lo + 4 * w4);
+        *reinterpret_cast<uint32_t *>(blk_base + off) = hw;       // hi plane: column + 0
+        *reinterpret_cast<uint32_t *>(blk_base + off + 64) = lw;  // lo plane: column + 1
+        if (TYPE == kQ4_K && sub == 0) {  // the even group's second half: -x against H
+          *reinterpret_cast<uint32_t *>(blk_base + off + 4) = __vneg4(hw);
+          *reinterpret_cast<uint32_t *>(blk_base + off + 68) = __vneg4(lw);
+        }
       }
     }
   }
@@ -440,94 +517,97 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
   const int g = lane >> 2, t = lane & 3;
   const int sub = t & 1, bt = (t >> 1) & (NB - 1);  // this lane's group slot and batch row
   float *area = reinterpret_cast<float *>(smem + p.off_area) + warp * AREA_FLOATS;
-  const float *dscx = area + bt * C::NG * 16;
-  const float *corr = area + NB * C::NG * 16 + bt * 16;
+  const float *area_b = area + bt * A::BATCH;
   // partial sums: [tile buffer][superblock of the row][g][batch row] float2 (rows g, g+8)
   float2 *red = reinterpret_cast<float2 *>(smem + p.off_red);
   const int red_tile = p.nblk * 8 * NB;
   // this lane's 16 bytes of a unit's B fragments
   const uint8_t *xlane = xq + ((g & (NCX - 1)) * 4 + t) * 16;
-  int *work_ctr = reinterpret_cast<int *>(&bars[2 * S + 2 * kFoldBufs]);
+  const uint32_t bar0 = smem_u32(bars);
 
   long long best = LLONG_MIN, best_b1 = LLONG_MIN;  // fused top-1: running maxima (batch row 0 / 1)
 
-  // Work items are handed out in order from one shared counter, so every warp is busy until the
-  // CTA runs dry and neighbouring warps are always in different phases.  Per tile: one item per
-  // superblock of the row (decode + MMAs of 16 rows x 256 columns, partial sums to the tile
-  // buffer), then one item that folds the PREVIOUS tile (its partials are complete by then).
-  const int per_tile = p.nblk + 1, total = ntl * per_tile + 1;
-  int cj = 0;  // job hint of this warp
+  // The CTA's work is one ordered sequence of items: per tile one item per superblock of the
+  // row (decode + MMAs of 16 rows x 256 columns, partial sums to the tile buffer) followed by
+  // one item that folds the PREVIOUS tile (its partials are complete by then); after the last
+  // tile one more fold.  Warp w takes items w, w + kNW, ...: items only ever wait for items
+  // earlier in the sequence (and for the producer), so the order is deadlock-free, and the
+  // warps of a scheduler are always in different phases of their items.
+  const int per_tile = p.nblk + 1;
+  int li = warp / per_tile, e = warp - li * per_tile;  // this warp's item: entry e of tile li
+  int cc0 = li * p.nchunks;                   // number of the tile's chunk 0, its stage and parity
+  int s0 = cc0 % S, par0 = (cc0 / S) & 1;
+  int cj = 0, pad_a = 0, pad_b = 0, pad_d = 0, pad_li = -1;
   for (;;) {
-    int q = 0;
-    if (lane == 0) q = atomicAdd(work_ctr, 1);
-    q = __shfl_sync(0xffffffffu, q, 0);
-    if (q >= total) break;
-    const int li = q / per_tile, e = q - li * per_tile;
+    if (li > ntl || (li == ntl && e > 0)) break;
     if (e < p.nblk && li < ntl) {
       // ------------------------------------------------ one superblock of tile li
       const int c = e / C::KB, bi = e - c * C::KB;
-      const int cc = li * p.nchunks + c, s = cc % S;
-      int pad_a = 0, pad_b = 0, pad_d = 0;
-      if (TYPE == kQ6_K) {  // only Q6_K rows can start off a 16-byte boundary
+      int s = s0 + c, par = par0;
+      while (s >= S) { s -= S; par ^= 1; }
+      if (TYPE == kQ6_K && pad_li != li) {  // only Q6_K rows can start off a 16-byte boundary
+        pad_li = li;
         const int gt = blockIdx.x + li * gridDim.x;
         locate(gt, cj);
         const int tile = gt - p.tcum[cj];
-        const uintptr_t wbase = reinterpret_cast<uintptr_t>(p.jobs[cj].w);
-        pad_a = (int)((wbase + ((long long)tile * kR + g) * p.row_bytes) & 15);
-        pad_b = (int)((wbase + ((long long)tile * kR + g + 8) * p.row_bytes) & 15);
-        pad_d = (int)((wbase + ((long long)tile * kR + (lane & 15)) * p.row_bytes) & 15);
+        const uint32_t wlow = (uint32_t)reinterpret_cast<uintptr_t>(p.jobs[cj].w);
+        const uint32_t rb = (uint32_t)p.row_bytes;  // the low four bits are all that matter
+        pad_a = (int)((wlow + (uint32_t)(tile * kR + g) * rb) & 15u);
+        pad_b = (int)((wlow + (uint32_t)(tile * kR + g + 8) * rb) & 15u);
+        pad_d = (int)((wlow + (uint32_t)(tile * kR + (lane & 15)) * rb) & 15u);
       }
       float acc0 = 0.f, acc1 = 0.f;  // rows g and g+8 of (group slot sub, batch row bt)
-      TRACE(1000 + q);
-      mbar_wait(smem_u32(&bars[s]), (cc / S) & 1);
-      TRACE(2000 + q);
+      TRACE(1000 + li * per_tile + e);
+      spin_until_ge(issued, cc0 + c + 1);
+      mbar_wait(bar0 + 8 * s, par);
+      TRACE(2000 + li * per_tile + e);
       if (p.debug != 1) {
         const uint8_t *blk = stages + (size_t)s * p.stage_bytes + bi * C::BB;
         decode_scales<TYPE, NB>(blk + (lane & 15) * C::RS + pad_d, lane, e, SX, XX, area);
         __syncwarp();
         if (p.debug != 2)
-          mma_block<TYPE, UNIT_BYTES>(blk, pad_a, pad_b, xlane + (size_t)e * 4 * UNIT_BYTES, dscx,
-                                      g, t, sub, acc0, acc1);
-        if (sub == 0) {
-          acc0 += corr[g];
-          acc1 += corr[g + 8];
-        }
+          mma_block<TYPE, UNIT_BYTES>(blk, pad_a, pad_b, xlane + (size_t)e * 4 * UNIT_BYTES,
+                                      area_b, g, t, sub, acc0, acc1);
         __syncwarp();  // the area is rewritten by this warp's next decode
       }
       // release the stage; the warp that takes the last superblock of a short final chunk also
       // arrives for the superblocks that do not exist
       if (lane == 0) {
         const int nb = min(C::KB, p.nblk - c * C::KB);
-        mbar_arrive_n(smem_u32(&bars[S + s]), bi == nb - 1 ? C::KB - nb + 1 : 1);
+        mbar_arrive_n(bar0 + 8 * (S + s), bi == nb - 1 ? C::KB - nb + 1 : 1);
       }
       // the two group slots of a batch row sit in neighbouring lanes
       acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
       acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
-      const int tb = li % kFoldBufs;
-      mbar_wait(smem_u32(&bars[2 * S + kFoldBufs + tb]), ((li / kFoldBufs) & 1) ^ 1);  // buffer free
+      const int tb = li & (kFoldBufs - 1);
+      spin_until_ge(&folded[tb], li / kFoldBufs);  // the buffer's previous tile has been folded
       if (sub == 0 && (t >> 1) < NB)
         red[tb * red_tile + (e * 8 + g) * NB + (t >> 1)] = make_float2(acc0, acc1);
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bars[2 * S + tb]));
-      TRACE(3000 + q);
-    } else {
-      // ------------------------------------------------ fold tile li - 1 (or the last tile)
-      const int fl = e < p.nblk ? ntl - 1 : li - 1;  // q == total - 1 has li == ntl, e == 0
-      if (fl < 0) continue;
-      const int tb = fl % kFoldBufs;
-      TRACE(4000 + q);
-      mbar_wait(smem_u32(&bars[2 * S + tb]), (fl / kFoldBufs) & 1);
-      TRACE(5000 + q);
+      if (lane == 0) {
+        __threadfence_block();
+        atomicAdd(&arrivals[tb], 1);
+      }
+      TRACE(3000 + li * per_tile + e);
+    } else if (li > 0) {
+      // ------------------------------------------------ fold tile li - 1
+      const int fl = li - 1;
+      const int tb = fl & (kFoldBufs - 1);
+      TRACE(4000 + li * per_tile + e);
+      spin_until_ge(&arrivals[tb], (fl / kFoldBufs + 1) * p.nblk);  // all partials of tile fl stored
+      __threadfence_block();
+      TRACE(5000 + li * per_tile + e);
       // lane = (batch row, row of the tile): a fixed-order sum over the superblocks
       const int r16 = lane & 15, b = lane >> 4;
-      const float2 *src = red + tb * red_tile + (r16 & 7) * NB + (b & (NB - 1));
+      const float *src = reinterpret_cast<const float *>(red + tb * red_tile + (r16 & 7) * NB + (b & (NB - 1))) + (r16 >> 3);
       float v = 0.f;
-      for (int k = 0; k < p.nblk; k++) {
-        const float2 pv = src[k * 8 * NB];
-        v += (r16 >> 3) ? pv.y : pv.x;
-      }
+#pragma unroll 4
+      for (int k = 0; k < p.nblk; k++) v += src[k * 16 * NB];
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bars[2 * S + kFoldBufs + tb]));
+      if (lane == 0) {
+        __threadfence_block();
+        *reinterpret_cast<volatile int *>(&folded[tb]) = fl / kFoldBufs + 1;
+      }
       const int gt = blockIdx.x + fl * gridDim.x;
       locate(gt, cj);
       const Job &job = p.jobs[cj];
@@ -542,6 +622,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
           job.y[(long long)b * job.out_dim + row] = a + v;
         }
       }
+    }
+    // next item of this warp
+    e += kNW;
+    while (e >= per_tile) {
+      e -= per_tile;
+      li++;
+      cc0 += p.nchunks;
+      s0 += p.nchunks;
+      while (s0 >= S) { s0 -= S; par0 ^= 1; }
     }
   }
 
@@ -611,7 +700,7 @@ bool make_plan(int in_dim, int nb, Params &p, size_t &smem) {
   auto al = [](size_t v) { return (v + 127) & ~(size_t)127; };
   size_t off = 256;  // mbarriers
   const size_t off_red = off;    off = al(off + (size_t)kFoldBufs * nblk * 8 * nb * 8);  // [tile buffer][superblock][g][batch] float2
-  const size_t off_area = off;   off = al(off + (size_t)kNW * (nb * C::NG * 16 + nb * 16) * 4);
+  const size_t off_area = off;   off = al(off + (size_t)kNW * nb * Area<TYPE>::BATCH * 4);
   const size_t off_sx = off;     off = al(off + (size_t)ngroups * nb * 4);
   const size_t off_xx = off;     off = al(off + (size_t)ngroups * nb * 4);
   const size_t off_xq = off;     off = al(off + (size_t)(in_dim / 64) * (4 * nb) * 64);
@@ -619,7 +708,7 @@ bool make_plan(int in_dim, int nb, Params &p, size_t &smem) {
   const size_t stage_bytes = al((size_t)kR * C::RS);
   if (off_stage + 3 * stage_bytes > kDynSmemMax) return false;
   int stages = (int)((kDynSmemMax - off_stage) / stage_bytes);
-  if (stages > 8) stages = 8;  // 2*stages + 2*kFoldBufs mbarriers + the work counter: 200 bytes
+  if (stages > 8) stages = 8;  // 2*stages mbarriers in the first 128 bytes of shared memory
   p.in_dim = in_dim;
   p.nblk = nblk; p.nchunks = (nblk + C::KB - 1) / C::KB;
   p.stages = stages; p.row_bytes = (long long)nblk * C::BB;
@@ -703,7 +792,15 @@ bool gemv_imma_supports(int type, const void *d_w, const float *d_x, int in_dim,
   if (type != kQ4_K && type != kQ5_K && type != kQ6_K) return false;
   if (batch < 1 || batch > 2) return false;
   if ((reinterpret_cast<uintptr_t>(d_w) & 15) || (reinterpret_cast<uintptr_t>(d_x) & 15)) return false;
-  return in_dim % 256 == 0 && in_dim <= 16384;
+  if (in_dim % 256 != 0 || in_dim > 16384) return false;
+  // the activations, the warps' areas and at least three stages must fit into shared memory
+  Params p{};
+  size_t smem = 0;
+  switch (type) {
+    case kQ4_K: return make_plan<kQ4_K>(in_dim, batch, p, smem);
+    case kQ5_K: return make_plan<kQ5_K>(in_dim, batch, p, smem);
+    default: return make_plan<kQ6_K>(in_dim, batch, p, smem);
+  }
 }
 
 int launch_gemv_imma_many(int type, int njobs, const void *const *d_w, const float *d_x,

@@ -52,19 +52,49 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 // Waits for the phase with the given parity; gives up after kPipeWaitLimitNs.  Once any wait of
 // the process has expired, later waits give up at their first slow-path check, so a broken
-// pipeline costs one time limit in total rather than one per wait.
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return;
+// pipeline costs one time limit in total rather than one per wait.  Returns false when it gave
+// up: a consumer may carry on with invalid data, a producer must stop issuing copies.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_ns();
   for (unsigned spin = 1;; spin++) {
-    if (mbar_try_wait(bar, parity)) return;
+    if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 63u) == 0) {
-      if (*reinterpret_cast<volatile unsigned int *>(&g_pipe_wait_timeouts) != 0u) return;
+      if (*reinterpret_cast<volatile unsigned int *>(&g_pipe_wait_timeouts) != 0u) return false;
       if (global_ns() - t0 > kPipeWaitLimitNs) {
         atomicAdd(&g_pipe_wait_timeouts, 1u);
-        return;
+        return false;
       }
     }
+  }
+}
+// Waits until a monotone counter in shared memory reaches `target`, with the same limit and
+// give-up rule as mbar_wait.  Counters cannot be misread the way a phase parity can when a
+// waiter is several phases ahead of the barrier.
+__device__ __forceinline__ bool spin_until_ge(const int *counter, int target) {
+  const volatile int *c = counter;
+  if (*c >= target) return true;
+  const unsigned long long t0 = global_ns();
+  for (unsigned spin = 1;; spin++) {
+    if (*c >= target) return true;
+    if ((spin & 63u) == 0) {
+      if (*reinterpret_cast<volatile unsigned int *>(&g_pipe_wait_timeouts) != 0u) return false;
+      if (global_ns() - t0 > kPipeWaitLimitNs) {
+        atomicAdd(&g_pipe_wait_timeouts, 1u);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ bool pipe_broken() {
+  return *reinterpret_cast<volatile unsigned int *>(&g_pipe_wait_timeouts) != 0u;
+}
+// A producer that stops after a failed wait must not let its CTA retire while bulk copies it
+// issued are still landing in the CTA's shared memory: it sits out a time that any copy in
+// flight completes in (they take microseconds), independent of the state of the mbarriers.
+__device__ __forceinline__ void drain_copies_in_flight() {
+  const unsigned long long t0 = global_ns();
+  while (global_ns() - t0 < 200000ull) {
   }
 }
 // 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier.

@@ -100,6 +100,22 @@ def test_config1_9b_ffn_gemv_batch1(cuda, oracle, qtype, out_dim, in_dim):
     assert_close(y.ravel(), ref, f"type {qtype} {out_dim}x{in_dim}")
 
 
+@pytest.mark.parametrize("qtype,in_dim", [(Q4_K, 2048), (Q5_K, 1024), (Q6_K, 8192), (Q6_K, 1024),
+                                          (Q4_K, 256)])
+@pytest.mark.parametrize("batch", [1, 2])
+def test_many_tiles_per_cta(cuda, oracle, qtype, in_dim, batch):
+    """Tall weights: every persistent CTA walks ten or more row tiles, so the stage ring and the
+    tile buffers of the tiled kernel wrap several times, with several stages per tile (Q6_K at
+    8192 columns) and with tiles much smaller than a stage (256 and 1024 columns)."""
+    sms = torch.cuda.get_device_properties(cuda).multi_processor_count
+    out_dim = sms * 16 * 10 + 21
+    w, x, y, _ = run_gemv(cuda, qtype, out_dim, in_dim, batch, seed=9)
+    ref = oracle.matmul_add(x, batch, in_dim, w, qtype, out_dim, np.zeros(out_dim, np.float32),
+                            threads=oracle.max_threads())
+    assert not np.isnan(y).any()
+    assert_close(y.ravel(), ref, f"type {qtype} {out_dim}x{in_dim} batch {batch}")
+
+
 LAYER = [("q_proj", Q4_K, 4096, 4096), ("k_proj", Q4_K, 1024, 4096), ("v_proj", Q4_K, 1024, 4096),
          ("o_proj", Q4_K, 4096, 4096), ("ffn_gate", Q4_K, 12288, 4096),
          ("ffn_down", Q6_K, 4096, 12288), ("q5k_variant", Q5_K, 4096, 4096)]
