@@ -46,9 +46,14 @@ const char *cogni_qmm_status_string(int status) {
 }
 
 int cogni_qmm_set_kernel_choice(int choice) {
-  if (choice >= 16 && choice <= 19) {  // timing diagnostics of the tiled kernel (results invalid)
-    gemv_mma_set_debug(choice - 16);
-    gemv_imma_set_debug(choice - 16);
+  if (choice >= 16 && choice <= 21) {  // timing diagnostics of the tiled kernels (results invalid)
+    // 16 normal, 17 stream only, 18 stream + scale decode; 19-21 the same without the copies
+    gemv_mma_set_debug(choice <= 18 ? choice - 16 : 0);
+    gemv_imma_set_debug(choice <= 18 ? choice - 16 : 4 + (choice == 19 ? 0 : choice - 19));
+    return COGNI_QMM_OK;
+  }
+  if (choice >= 24 && choice <= 26) {  // superblocks per work item of the tiled GEMV: automatic / 1 / 2
+    gemv_imma_set_pair(choice - 24);
     return COGNI_QMM_OK;
   }
   if (choice != 0 && choice != 1) return COGNI_QMM_ERR_ARG;

@@ -100,9 +100,10 @@ struct Params {
   int tcum[kMaxJobs + 1];  // tcum[j] = first global tile of job j; tcum[njobs] = all tiles
   Job jobs[kMaxJobs];
   long long row_bytes;
-  int off_red, off_area, off_sx, off_xx, off_xq, off_stage, stage_bytes;
+  int off_flags, off_red, off_area, off_sx, off_xx, off_xq, off_stage, stage_bytes;
+  int pair;      // superblocks per work item (1 or 2)
   int resident;  // weights were complete before the preceding kernel started
-  int debug;     // diagnostics: 1 = stream only, 2 = stream + decode, 3 = compute only (no copies)
+  int debug;     // diagnostics: bits 0-1: 1 = no work on the stages, 2 = decode only; bit 2: no copies
   long long *part_keys;  // fused top-1 (nullptr: plain GEMV)
   unsigned *counter;
   int32_t *top_idx;
@@ -189,76 +190,90 @@ template <int TYPE> struct Area {
   static constexpr int BATCH = 16 * ROW;         // floats per batch row
 };
 
-// Lanes (r = lane & 15, half = lane >> 4) decode one half of the scale groups of row r; the two
-// halves' corrections are combined with one shuffle.
+// An item covers two neighbouring superblocks of a tile.  Lane (r = lane & 15, which = lane >> 4)
+// decodes all scale groups of row r of superblock `which` of the pair into that superblock's half
+// of the warp's area.
 template <int TYPE, int NB>
 __device__ __forceinline__ void decode_scales(const uint8_t *blk_row, int lane, int kblk,
                                               const float *SX, const float *XX, float *area) {
   using C = Cfg<TYPE>;
   using A = Area<TYPE>;
-  constexpr int NH = C::NG / 2;  // groups per lane
-  const int r = lane & 15, half = lane >> 4;
-  float dsc[NH], kk[NH];
+  constexpr int NH = C::NG / 2;  // groups per pass
+  const int r = lane & 15;
+  float *rows = area + (lane >> 4) * NB * A::BATCH + r * A::ROW;
+  float corr[NB];
+#pragma unroll
+  for (int b = 0; b < NB; b++) corr[b] = 0.f;
+  uint32_t u0 = 0, u1 = 0, u2 = 0;
+  float d = 0.f, dmin = 0.f;
   if constexpr (C::HAS_MIN) {
     const uint4 h = *reinterpret_cast<const uint4 *>(blk_row);
     const __half2 dd = *reinterpret_cast<const __half2 *>(&h.x);
-    const float d = __low2float(dd), dmin = __high2float(dd);
-    const uint32_t u0 = h.y, u1 = h.z, u2 = h.w;
-    // four 6-bit scales / mins of this half as bytes (dequant.cr:240-249, four at a time)
-    const uint32_t scw = half ? ((u2 & 0x0f0f0f0fu) | ((u0 >> 2) & 0x30303030u)) : (u0 & 0x3f3f3f3fu);
-    const uint32_t mnw = half ? (((u2 >> 4) & 0x0f0f0f0fu) | ((u1 >> 2) & 0x30303030u)) : (u1 & 0x3f3f3f3fu);
-    const float d23 = d * 8388608.f, ndmin = -dmin, ndmin23 = ndmin * 8388608.f;
-    // Q4_K: the odd groups' integer sums arrive multiplied by 16 (see mma_block)
-    const float dodd = TYPE == kQ4_K ? d * 0.0625f : d, dodd23 = dodd * 8388608.f;
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-      dsc[i] = (i & 1) ? byte_times(scw, i, dodd, dodd23) : byte_times(scw, i, d, d23);
-      kk[i] = byte_times(mnw, i, ndmin, ndmin23);
-    }
+    d = __low2float(dd);
+    dmin = __high2float(dd);
+    u0 = h.y; u1 = h.z; u2 = h.w;
   } else {
-    const float d = load_half_as_float(blk_row + 208);
-    const int8_t *sc = reinterpret_cast<const int8_t *>(blk_row + 192 + 8 * half);
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-      dsc[i] = d * (float)sc[i];
-      kk[i] = -32.f * dsc[i];
-    }
-  }
-  // this lane's groups are consecutive in the tables: NH * NB floats each, 16-byte aligned
-  const int grp0 = kblk * C::NG + NH * half;
-  float sxv[NH * NB], xxv[NH * NB];
-#pragma unroll
-  for (int i = 0; i < NH * NB / 4; i++) {
-    const float4 a = reinterpret_cast<const float4 *>(SX + grp0 * NB)[i];
-    const float4 c = reinterpret_cast<const float4 *>(XX + grp0 * NB)[i];
-    sxv[4 * i] = a.x; sxv[4 * i + 1] = a.y; sxv[4 * i + 2] = a.z; sxv[4 * i + 3] = a.w;
-    xxv[4 * i] = c.x; xxv[4 * i + 1] = c.y; xxv[4 * i + 2] = c.z; xxv[4 * i + 3] = c.w;
+    d = load_half_as_float(blk_row + 208);
   }
 #pragma unroll
-  for (int b = 0; b < NB; b++) {
-    float *row = area + b * A::BATCH + r * A::ROW;
-    float v[NH], corr = 0.f;
+  for (int half = 0; half < 2; half++) {
+    float dsc[NH], kk[NH];
+    if constexpr (C::HAS_MIN) {
+      // four 6-bit scales / mins of this half as bytes (dequant.cr:240-249, four at a time)
+      const uint32_t scw = half ? ((u2 & 0x0f0f0f0fu) | ((u0 >> 2) & 0x30303030u)) : (u0 & 0x3f3f3f3fu);
+      const uint32_t mnw = half ? (((u2 >> 4) & 0x0f0f0f0fu) | ((u1 >> 2) & 0x30303030u)) : (u1 & 0x3f3f3f3fu);
+      const float d23 = d * 8388608.f, ndmin = -dmin, ndmin23 = ndmin * 8388608.f;
+      // Q4_K: the odd groups' integer sums arrive multiplied by 16 (see mma_block)
+      const float dodd = TYPE == kQ4_K ? d * 0.0625f : d, dodd23 = dodd * 8388608.f;
 #pragma unroll
-    for (int i = 0; i < NH; i++) {
-      v[i] = dsc[i] * sxv[i * NB + b];
-      corr = fmaf(kk[i], xxv[i * NB + b], corr);
+      for (int i = 0; i < 4; i++) {
+        dsc[i] = (i & 1) ? byte_times(scw, i, dodd, dodd23) : byte_times(scw, i, d, d23);
+        kk[i] = byte_times(mnw, i, ndmin, ndmin23);
+      }
+    } else {
+      const int8_t *sc = reinterpret_cast<const int8_t *>(blk_row + 192 + 8 * half);
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        dsc[i] = d * (float)sc[i];
+        kk[i] = dsc[i];  // times -32 once, at the end
+      }
     }
-    if constexpr (C::HAS_MIN) {  // lane's groups 4*half + i: g4 = 2*half + (i >> 1), sub = i & 1
-      *reinterpret_cast<float2 *>(row + 2 * half) = make_float2(v[0], v[2]);
-      *reinterpret_cast<float2 *>(row + 4 + 2 * half) = make_float2(v[1], v[3]);
-    } else {  // lane's groups 8*half + i: n = half, h = i & 1, sub = (i >> 1) & 1, m = i >> 2
-      *reinterpret_cast<float4 *>(row + 4 * half) = make_float4(v[0], v[4], v[1], v[5]);
-      *reinterpret_cast<float4 *>(row + 8 + 4 * half) = make_float4(v[2], v[6], v[3], v[7]);
+    // the half's groups are consecutive in the tables: NH * NB floats each, 16-byte aligned
+    const int grp0 = kblk * C::NG + NH * half;
+    float sxv[NH * NB], xxv[NH * NB];
+#pragma unroll
+    for (int i = 0; i < NH * NB / 4; i++) {
+      const float4 a = reinterpret_cast<const float4 *>(SX + grp0 * NB)[i];
+      const float4 c = reinterpret_cast<const float4 *>(XX + grp0 * NB)[i];
+      sxv[4 * i] = a.x; sxv[4 * i + 1] = a.y; sxv[4 * i + 2] = a.z; sxv[4 * i + 3] = a.w;
+      xxv[4 * i] = c.x; xxv[4 * i + 1] = c.y; xxv[4 * i + 2] = c.z; xxv[4 * i + 3] = c.w;
     }
-    corr += __shfl_xor_sync(0xffffffffu, corr, 16);
-    if (half == 0) row[C::NG] = corr;
+#pragma unroll
+    for (int b = 0; b < NB; b++) {
+      float *row = rows + b * A::BATCH;
+      float v[NH];
+#pragma unroll
+      for (int i = 0; i < NH; i++) {
+        v[i] = dsc[i] * sxv[i * NB + b];
+        corr[b] = fmaf(kk[i], xxv[i * NB + b], corr[b]);
+      }
+      if constexpr (C::HAS_MIN) {  // groups 4*half + i: g4 = 2*half + (i >> 1), sub = i & 1
+        *reinterpret_cast<float2 *>(row + 2 * half) = make_float2(v[0], v[2]);
+        *reinterpret_cast<float2 *>(row + 4 + 2 * half) = make_float2(v[1], v[3]);
+      } else {  // groups 8*half + i: n = half, h = i & 1, sub = (i >> 1) & 1, m = i >> 2
+        *reinterpret_cast<float4 *>(row + 4 * half) = make_float4(v[0], v[4], v[1], v[5]);
+        *reinterpret_cast<float4 *>(row + 8 + 4 * half) = make_float4(v[2], v[6], v[3], v[7]);
+      }
+    }
   }
+#pragma unroll
+  for (int b = 0; b < NB; b++) rows[b * A::BATCH + C::NG] = C::HAS_MIN ? corr[b] : -32.f * corr[b];
 }
 
 // MMAs of one superblock (16 rows x 256 columns) for this lane's (group slot sub, batch row).
 // blk: the superblock of row 0 of the tile inside the stage; xu: this lane's B fragments of the
-// superblock's first unit; ab: this lane's batch row of the warp's area.  Returns the partial
-// sums of rows g and g+8 (the correction included in the sub == 0 lanes).
+// superblock's first unit; ab: this lane's batch row of the superblock's area.  Adds the partial
+// sums of rows g and g+8 (the correction included in the sub == 0 lanes) to acc0 / acc1.
 template <int TYPE, int UNIT_BYTES>
 __device__ __forceinline__ void mma_block(const uint8_t *blk, int pad_a, int pad_b,
                                           const uint8_t *xu, const float *ab, int g, int t,
@@ -267,8 +282,10 @@ __device__ __forceinline__ void mma_block(const uint8_t *blk, int pad_a, int pad
   using A = Area<TYPE>;
   constexpr uint32_t M4 = 0x0f0f0f0fu;
   const float *rowa = ab + g * A::ROW, *rowb = ab + (g + 8) * A::ROW;
-  acc0 = sub ? 0.f : rowa[C::NG];
-  acc1 = sub ? 0.f : rowb[C::NG];
+  if (sub == 0) {
+    acc0 += rowa[C::NG];
+    acc1 += rowb[C::NG];
+  }
   if constexpr (C::HAS_MIN) {
     constexpr bool Q5 = TYPE == kQ5_K;
     constexpr int QOFF = Q5 ? 48 : 16;
@@ -352,20 +369,89 @@ __device__ __forceinline__ void mma_block(const uint8_t *blk, int pad_a, int pad
   }
 }
 
-// ---------------------------------------------------------------------------- the kernel
+// Quantises superblock kblk of x (256 elements per batch row) into the fragment-ordered layout:
+// per scale group sx = max|x| / 16256, n = rint(x / sx) = 128*hi + lo.  One warp, lane = 8
+// consecutive elements.  The superblock's area is zeroed first: its unused words are the
+// structural zeros of the layout.
 template <int TYPE, int NB>
+__device__ __forceinline__ void quantise_superblock(const float *x, int K, int kblk, int lane,
+                                                    uint8_t *xq, float *SX, float *XX) {
+  using C = Cfg<TYPE>;
+  constexpr int NCX = 4 * NB, UNIT_BYTES = NCX * 64;
+  constexpr int LPG = C::GROUP / 8;  // lanes per scale group
+  uint8_t *blk_base = xq + (size_t)kblk * 4 * UNIT_BYTES;
+#pragma unroll
+  for (int i = 0; i < 4 * UNIT_BYTES / 512; i++)
+    reinterpret_cast<uint4 *>(blk_base)[i * 32 + lane] = make_uint4(0, 0, 0, 0);
+  const int k = kblk * 256 + lane * 8, e_in = lane * 8;
+  float4 v0[NB], v1[NB];
+#pragma unroll
+  for (int b = 0; b < NB; b++) {
+    v0[b] = __ldg(reinterpret_cast<const float4 *>(x + (long long)b * K + k));
+    v1[b] = __ldg(reinterpret_cast<const float4 *>(x + (long long)b * K + k + 4));
+  }
+  __syncwarp();
+#pragma unroll
+  for (int b = 0; b < NB; b++) {
+    const float v[8] = {v0[b].x, v0[b].y, v0[b].z, v0[b].w, v1[b].x, v1[b].y, v1[b].z, v1[b].w};
+    float mx = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; e++) mx = fmaxf(mx, fabsf(v[e]));
+#pragma unroll
+    for (int off = 1; off < LPG; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    // groups below 1e-30 contribute nothing (their scale would underflow anyway)
+    const bool live = mx > 1e-30f;
+    const float sx = live ? mx * (1.f / kNMax) : 1.f;
+    const float inv = live ? (float)kNMax / mx : 0.f;
+    int hi[8], lo[8], nsum = 0;
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+      // round to nearest through the 1.5 * 2^23 bias: |x * inv| <= 16256 * (1 + 2^-21)
+      const int n = __float_as_int(fmaf(v[e], inv, 12582912.f)) - 0x4B400000;
+      hi[e] = (n + 64) >> 7;
+      lo[e] = n - (hi[e] << 7);
+      nsum += n;
+    }
+#pragma unroll
+    for (int off = 1; off < LPG; off <<= 1) nsum += __shfl_xor_sync(0xffffffffu, nsum, off);
+    if ((lane & (LPG - 1)) == 0) {
+      const int grp = k / C::GROUP;
+      SX[grp * NB + b] = sx;
+      XX[grp * NB + b] = sx * (float)nsum;
+    }
+    auto pack4 = [](const int *q) {  // low bytes of four ints
+      return __byte_perm(__byte_perm(q[0], q[1], 0x0040), __byte_perm(q[2], q[3], 0x0040), 0x5410);
+    };
+#pragma unroll
+    for (int w4 = 0; w4 < 2; w4++) {  // the two 4-element words of this lane's 8 elements
+      int sub;
+      const int off = xq_word_offset<TYPE>(e_in + 4 * w4, NCX, 4 * b, sub);
+      const uint32_t hw = pack4(hi + 4 * w4), lw = pack4(lo + 4 * w4);
+      *reinterpret_cast<uint32_t *>(blk_base + off) = hw;       // hi plane: column + 0
+      *reinterpret_cast<uint32_t *>(blk_base + off + 64) = lw;  // lo plane: column + 1
+      if (TYPE == kQ4_K && sub == 0) {  // the even group's second half: -x against H
+        *reinterpret_cast<uint32_t *>(blk_base + off + 4) = __vneg4(hw);
+        *reinterpret_cast<uint32_t *>(blk_base + off + 68) = __vneg4(lw);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------- the kernel
+template <int TYPE, int NB, int PAIR>
 __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) {
   using C = Cfg<TYPE>;
   using A = Area<TYPE>;
   constexpr int NCX = 4 * NB;                    // columns of the quantised-x layout
   constexpr int UNIT_BYTES = NCX * 64;
-  constexpr int AREA_FLOATS = NB * A::BATCH;
+  constexpr int AREA_FLOATS = PAIR * NB * A::BATCH;  // PAIR superblocks per item
   extern __shared__ __align__(128) uint8_t smem[];
   // mbarriers full[S] | empty[S] in the first 128 bytes; monotone counters from byte 192:
   // chunks armed by the producer | partial sums stored per tile buffer | folds done per tile buffer
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
   int *issued = reinterpret_cast<int *>(smem + 192);
   int *arrivals = issued + 1, *folded = arrivals + kFoldBufs;
+  int *xready = reinterpret_cast<int *>(smem + p.off_flags);  // per superblock pair of x: quantised
   const int S = p.stages;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef COGNI_TRACE
@@ -392,6 +478,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
       if (lane < S) mbar_init(smem_u32(&bars[lane]), kPW);
       else if (lane < 2 * S) mbar_init(smem_u32(&bars[lane]), C::KB);
       else if (lane < 2 * S + 1 + 2 * kFoldBufs) issued[lane - 2 * S] = 0;
+      xready[lane] = 0;
+      xready[lane + 32] = 0;
       mbar_fence_init();
     }
     asm volatile("bar.sync 2, %0;" ::"n"(kPW * 32) : "memory");
@@ -420,7 +508,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
         const uint32_t full = smem_u32(&bars[s]);
         const bool mine = rvalid && (lane >> 2) == pw;
         const uint32_t my_bytes = __reduce_add_sync(0xffffffffu, mine ? bytes : 0u);
-        if (p.debug == 3) {  // compute only: the stage is declared full without any copy
+        if (p.debug & 4) {  // the stage is declared full without any copy
           if (lane == 0) mbar_arrive(full);
         } else {
           if (lane == 0) mbar_arrive_expect_tx(full, my_bytes);
@@ -451,98 +539,42 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
   float *XX = reinterpret_cast<float *>(smem + p.off_xx);
   const int K = p.in_dim;
 
-  {  // zero the fragment-ordered activation area (its unused words are structural zeros)
-    const int n16 = (K >> 6) * UNIT_BYTES / 16;
-    for (int i = ctid; i < n16; i += kNW * 32) reinterpret_cast<uint4 *>(xq)[i] = make_uint4(0, 0, 0, 0);
-  }
-  asm volatile("bar.sync 3, %0;" ::"n"(kThreads) : "memory");  // zeros written, mbarriers ready
+  asm volatile("bar.sync 3, %0;" ::"n"(kThreads) : "memory");  // mbarriers and counters ready
   TRACE(3);
   pdl_wait_prior_grid();  // x (and y / the addend) may be produced by the preceding kernel
   TRACE(4);
-  {  // quantise x: per group sx = max|x| / 16256, n = rint(x / sx) = 128*hi + lo
-    const int k8n = K >> 3, items = NB * k8n;
-    constexpr int LPG = C::GROUP / 8;  // lanes per scale group
-    for (int i = ctid; i < items; i += kNW * 32) {
-      const int b = i / k8n, k = (i - b * k8n) * 8;
-      const float4 v0 = __ldg(reinterpret_cast<const float4 *>(p.x + (long long)b * K + k));
-      const float4 v1 = __ldg(reinterpret_cast<const float4 *>(p.x + (long long)b * K + k + 4));
-      const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-      float mx = 0.f;
-#pragma unroll
-      for (int e = 0; e < 8; e++) mx = fmaxf(mx, fabsf(v[e]));
-#pragma unroll
-      for (int off = 1; off < LPG; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-      // groups below 1e-30 contribute nothing (their scale would underflow anyway)
-      const bool live = mx > 1e-30f;
-      const float sx = live ? mx * (1.f / kNMax) : 1.f;
-      const float inv = live ? (float)kNMax / mx : 0.f;
-      int hi[8], lo[8], nsum = 0;
-#pragma unroll
-      for (int e = 0; e < 8; e++) {
-        // round to nearest through the 1.5 * 2^23 bias: |x * inv| <= 16256 * (1 + 2^-21)
-        const int n = __float_as_int(fmaf(v[e], inv, 12582912.f)) - 0x4B400000;
-        hi[e] = (n + 64) >> 7;
-        lo[e] = n - (hi[e] << 7);
-        nsum += n;
-      }
-#pragma unroll
-      for (int off = 1; off < LPG; off <<= 1) nsum += __shfl_xor_sync(0xffffffffu, nsum, off);
-      if ((lane & (LPG - 1)) == 0) {
-        const int grp = k / C::GROUP;
-        SX[grp * NB + b] = sx;
-        XX[grp * NB + b] = sx * (float)nsum;
-      }
-      auto pack4 = [](const int *q) {  // low bytes of four ints
-        return __byte_perm(__byte_perm(q[0], q[1], 0x0040), __byte_perm(q[2], q[3], 0x0040), 0x5410);
-      };
-      uint8_t *blk_base = xq + (size_t)(k >> 8) * 4 * UNIT_BYTES;
-      const int e_in = k & 255;
-#pragma unroll
-      for (int w4 = 0; w4 < 2; w4++) {  // the two 4-element words of this thread's 8 elements
-        int sub;
-        const int off = xq_word_offset<TYPE>(e_in + 4 * w4, NCX, 4 * b, sub);
-        const uint32_t hw = pack4(hi + 4 * w4), lw = pack4(lo + 4 * w4);
-        *reinterpret_cast<uint32_t *>(blk_base + off) = hw;       // hi plane: column + 0
-        *reinterpret_cast<uint32_t *>(blk_base + off + 64) = lw;  // lo plane: column + 1
-        if (TYPE == kQ4_K && sub == 0) {  // the even group's second half: -x against H
-          *reinterpret_cast<uint32_t *>(blk_base + off + 4) = __vneg4(hw);
-          *reinterpret_cast<uint32_t *>(blk_base + off + 68) = __vneg4(lw);
-        }
-      }
-    }
-  }
-  consumer_sync();
-  TRACE(5);
 
   const int g = lane >> 2, t = lane & 3;
   const int sub = t & 1, bt = (t >> 1) & (NB - 1);  // this lane's group slot and batch row
   float *area = reinterpret_cast<float *>(smem + p.off_area) + warp * AREA_FLOATS;
   const float *area_b = area + bt * A::BATCH;
-  // partial sums: [tile buffer][superblock of the row][g][batch row] float2 (rows g, g+8)
+  // partial sums: [tile buffer][superblock pair of the row][g][batch row] float2 (rows g, g+8)
   float2 *red = reinterpret_cast<float2 *>(smem + p.off_red);
-  const int red_tile = p.nblk * 8 * NB;
+  const int npairs = (p.nblk + PAIR - 1) / PAIR;  // items per tile
+  const int red_tile = npairs * 8 * NB;
   // this lane's 16 bytes of a unit's B fragments
   const uint8_t *xlane = xq + ((g & (NCX - 1)) * 4 + t) * 16;
   const uint32_t bar0 = smem_u32(bars);
 
   long long best = LLONG_MIN, best_b1 = LLONG_MIN;  // fused top-1: running maxima (batch row 0 / 1)
 
-  // The CTA's work is one ordered sequence of items: per tile one item per superblock of the
-  // row (decode + MMAs of 16 rows x 256 columns, partial sums to the tile buffer) followed by
-  // one item that folds the PREVIOUS tile (its partials are complete by then); after the last
-  // tile one more fold.  Warp w takes items w, w + kNW, ...: items only ever wait for items
-  // earlier in the sequence (and for the producer), so the order is deadlock-free, and the
-  // warps of a scheduler are always in different phases of their items.
-  const int per_tile = p.nblk + 1;
+  // The CTA's work is one ordered sequence of items: per tile one item per PAIR neighbouring
+  // superblocks of the row (scale decode + MMAs of 16 rows x PAIR*256 columns, partial sums to the
+  // tile buffer) followed by one item that folds the PREVIOUS tile (its partials are complete by
+  // then); after the last tile one more fold.  Warp w takes items w, w + kNW, ...: items only ever
+  // wait for items earlier in the sequence (and for the producer), so the order is deadlock-free,
+  // and the warps of a scheduler are always in different phases of their items.
+  const int per_tile = npairs + 1;
   int li = warp / per_tile, e = warp - li * per_tile;  // this warp's item: entry e of tile li
   int cc0 = li * p.nchunks;                   // number of the tile's chunk 0, its stage and parity
   int s0 = cc0 % S, par0 = (cc0 / S) & 1;
   int cj = 0, pad_a = 0, pad_b = 0, pad_d = 0, pad_li = -1;
   for (;;) {
     if (li > ntl || (li == ntl && e > 0)) break;
-    if (e < p.nblk && li < ntl) {
-      // ------------------------------------------------ one superblock of tile li
-      const int c = e / C::KB, bi = e - c * C::KB;
+    if (e < npairs && li < ntl) {
+      // ------------------------------------------------ superblocks 2e, 2e+1 of tile li
+      const int e0 = PAIR * e, n2 = min(PAIR, p.nblk - e0);
+      const int c = e0 / C::KB, bi = e0 - c * C::KB;  // KB is even: a pair lies in one chunk
       int s = s0 + c, par = par0;
       while (s >= S) { s -= S; par ^= 1; }
       if (TYPE == kQ6_K && pad_li != li) {  // only Q6_K rows can start off a 16-byte boundary
@@ -556,25 +588,47 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
         pad_b = (int)((wlow + (uint32_t)(tile * kR + g + 8) * rb) & 15u);
         pad_d = (int)((wlow + (uint32_t)(tile * kR + (lane & 15)) * rb) & 15u);
       }
+      // The activations are quantised on the way: the warp that takes a superblock pair of the
+      // CTA's first tile does x's two superblocks first; later tiles find them done.
+      if (li == 0) {
+        quantise_superblock<TYPE, NB>(p.x, K, e0, lane, xq, SX, XX);
+        if (PAIR == 2 && n2 == 2) quantise_superblock<TYPE, NB>(p.x, K, e0 + 1, lane, xq, SX, XX);
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_block();
+          *reinterpret_cast<volatile int *>(&xready[e]) = 1;
+        }
+      } else {
+        spin_until_ge(&xready[e], 1);
+        __threadfence_block();
+      }
       float acc0 = 0.f, acc1 = 0.f;  // rows g and g+8 of (group slot sub, batch row bt)
       TRACE(1000 + li * per_tile + e);
       spin_until_ge(issued, cc0 + c + 1);
       mbar_wait(bar0 + 8 * s, par);
       TRACE(2000 + li * per_tile + e);
-      if (p.debug != 1) {
+      if ((p.debug & 3) != 1) {
         const uint8_t *blk = stages + (size_t)s * p.stage_bytes + bi * C::BB;
-        decode_scales<TYPE, NB>(blk + (lane & 15) * C::RS + pad_d, lane, e, SX, XX, area);
+        const int which = lane >> 4;
+        if (which < n2)
+          decode_scales<TYPE, NB>(blk + (lane & 15) * C::RS + pad_d + which * C::BB, lane,
+                                  e0 + which, SX, XX, area);
         __syncwarp();
-        if (p.debug != 2)
-          mma_block<TYPE, UNIT_BYTES>(blk, pad_a, pad_b, xlane + (size_t)e * 4 * UNIT_BYTES,
+        if ((p.debug & 3) != 2) {
+          mma_block<TYPE, UNIT_BYTES>(blk, pad_a, pad_b, xlane + (size_t)e0 * 4 * UNIT_BYTES,
                                       area_b, g, t, sub, acc0, acc1);
+          if (PAIR == 2 && n2 == 2)
+            mma_block<TYPE, UNIT_BYTES>(blk + C::BB, pad_a, pad_b,
+                                        xlane + (size_t)(e0 + 1) * 4 * UNIT_BYTES,
+                                        area_b + NB * A::BATCH, g, t, sub, acc0, acc1);
+        }
         __syncwarp();  // the area is rewritten by this warp's next decode
       }
-      // release the stage; the warp that takes the last superblock of a short final chunk also
-      // arrives for the superblocks that do not exist
+      // release the stage; the warp that takes the last pair of a short final chunk also arrives
+      // for the superblocks that do not exist
       if (lane == 0) {
         const int nb = min(C::KB, p.nblk - c * C::KB);
-        mbar_arrive_n(bar0 + 8 * (S + s), bi == nb - 1 ? C::KB - nb + 1 : 1);
+        mbar_arrive_n(bar0 + 8 * (S + s), bi + n2 == nb ? C::KB - nb + n2 : n2);
       }
       // the two group slots of a batch row sit in neighbouring lanes
       acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
@@ -594,15 +648,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
       const int fl = li - 1;
       const int tb = fl & (kFoldBufs - 1);
       TRACE(4000 + li * per_tile + e);
-      spin_until_ge(&arrivals[tb], (fl / kFoldBufs + 1) * p.nblk);  // all partials of tile fl stored
+      spin_until_ge(&arrivals[tb], (fl / kFoldBufs + 1) * npairs);  // all partials of tile fl stored
       __threadfence_block();
       TRACE(5000 + li * per_tile + e);
-      // lane = (batch row, row of the tile): a fixed-order sum over the superblocks
+      // lane = (batch row, row of the tile): a fixed-order sum over the superblock pairs
       const int r16 = lane & 15, b = lane >> 4;
       const float *src = reinterpret_cast<const float *>(red + tb * red_tile + (r16 & 7) * NB + (b & (NB - 1))) + (r16 >> 3);
       float v = 0.f;
 #pragma unroll 4
-      for (int k = 0; k < p.nblk; k++) v += src[k * 16 * NB];
+      for (int k = 0; k < npairs; k++) v += src[k * 16 * NB];
       __syncwarp();
       if (lane == 0) {
         __threadfence_block();
@@ -692,15 +746,18 @@ int sm_count() {
   return cached[dev] > 0 ? cached[dev] : 148;
 }
 
+int g_imma_force_pair = 0;  // diagnostics: 0 = automatic, 1 / 2 = superblocks per item
+
 template <int TYPE>
-bool make_plan(int in_dim, int nb, Params &p, size_t &smem) {
+bool make_plan_pair(int in_dim, int nb, int pair, Params &p, size_t &smem) {
   using C = Cfg<TYPE>;
   const int nblk = in_dim / 256;
   const int ngroups = in_dim / C::GROUP;
   auto al = [](size_t v) { return (v + 127) & ~(size_t)127; };
-  size_t off = 256;  // mbarriers
-  const size_t off_red = off;    off = al(off + (size_t)kFoldBufs * nblk * 8 * nb * 8);  // [tile buffer][superblock][g][batch] float2
-  const size_t off_area = off;   off = al(off + (size_t)kNW * nb * Area<TYPE>::BATCH * 4);
+  size_t off = 256;  // mbarriers and counters
+  const size_t off_flags = off;  off += 256;  // one flag per superblock of x (in_dim <= 16384)
+  const size_t off_red = off;    off = al(off + (size_t)kFoldBufs * ((nblk + pair - 1) / pair) * 8 * nb * 8);  // [tile buffer][item][g][batch] float2
+  const size_t off_area = off;   off = al(off + (size_t)kNW * pair * nb * Area<TYPE>::BATCH * 4);
   const size_t off_sx = off;     off = al(off + (size_t)ngroups * nb * 4);
   const size_t off_xx = off;     off = al(off + (size_t)ngroups * nb * 4);
   const size_t off_xq = off;     off = al(off + (size_t)(in_dim / 64) * (4 * nb) * 64);
@@ -712,20 +769,32 @@ bool make_plan(int in_dim, int nb, Params &p, size_t &smem) {
   p.in_dim = in_dim;
   p.nblk = nblk; p.nchunks = (nblk + C::KB - 1) / C::KB;
   p.stages = stages; p.row_bytes = (long long)nblk * C::BB;
-  p.off_red = (int)off_red; p.off_area = (int)off_area; p.off_sx = (int)off_sx;
+  p.off_flags = (int)off_flags; p.off_red = (int)off_red; p.off_area = (int)off_area; p.off_sx = (int)off_sx;
   p.off_xx = (int)off_xx; p.off_xq = (int)off_xq; p.off_stage = (int)off_stage;
   p.stage_bytes = (int)stage_bytes;
+  p.pair = pair;
   smem = off_stage + (size_t)stages * stage_bytes;
   return true;
 }
 
-template <int TYPE, int NB>
+// Two superblocks per item halve the per-item bookkeeping and let every lane decode scales, but
+// the items a CTA can hold in its stages halve too: pairs are used when the stages still hold
+// enough of them to keep the warps busy.
+template <int TYPE>
+bool make_plan(int in_dim, int nb, Params &p, size_t &smem) {
+  if (g_imma_force_pair != 1 && make_plan_pair<TYPE>(in_dim, nb, 2, p, smem) &&
+      (g_imma_force_pair == 2 || p.stages * Cfg<TYPE>::KB / 2 >= 20))
+    return true;
+  return make_plan_pair<TYPE>(in_dim, nb, 1, p, smem);
+}
+
+template <int TYPE, int NB, int PAIR>
 int launch_instance(const Params &p, size_t smem, int grid, cudaStream_t s) {
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_imma_kernel<TYPE, NB>,
+    cudaError_t e = cudaFuncSetAttribute(gemv_imma_kernel<TYPE, NB, PAIR>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)kDynSmemMax);
     if (e != cudaSuccess) return (int)e;
@@ -741,7 +810,7 @@ int launch_instance(const Params &p, size_t smem, int grid, cudaStream_t s) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return (int)cudaLaunchKernelEx(&cfg, gemv_imma_kernel<TYPE, NB>, p);
+  return (int)cudaLaunchKernelEx(&cfg, gemv_imma_kernel<TYPE, NB, PAIR>, p);
 }
 
 // njobs weight matrices (same type and in_dim), one x: the reference's qmatvec_many
@@ -777,8 +846,10 @@ int gemv_typed(int njobs, const void *const *d_w, const float *d_x, const float 
       p.top_key = top1->top_key;
       p.index_base = top1->index_base;
     }
-    const int st = batch == 1 ? launch_instance<TYPE, 1>(p, smem, grid, s)
-                              : launch_instance<TYPE, 2>(p, smem, grid, s);
+    const int st = batch == 1 ? (p.pair == 2 ? launch_instance<TYPE, 1, 2>(p, smem, grid, s)
+                                             : launch_instance<TYPE, 1, 1>(p, smem, grid, s))
+                              : (p.pair == 2 ? launch_instance<TYPE, 2, 2>(p, smem, grid, s)
+                                             : launch_instance<TYPE, 2, 1>(p, smem, grid, s));
     if (st) return st;
   }
   return COGNI_QMM_OK;
@@ -787,6 +858,7 @@ int gemv_typed(int njobs, const void *const *d_w, const float *d_x, const float 
 }  // namespace
 
 void gemv_imma_set_debug(int mode) { g_imma_debug = mode; }
+void gemv_imma_set_pair(int pair) { g_imma_force_pair = pair; }
 
 bool gemv_imma_supports(int type, const void *d_w, const float *d_x, int in_dim, int batch) {
   if (type != kQ4_K && type != kQ5_K && type != kQ6_K) return false;

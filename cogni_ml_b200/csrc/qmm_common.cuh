@@ -130,6 +130,7 @@ int launch_gemv_imma_many(int type, int njobs, const void *const *d_w, const flo
 unsigned gemv_imma_timeouts();
 unsigned gemm_prefill_timeouts();
 void gemv_imma_set_debug(int mode);
+void gemv_imma_set_pair(int pair);
 
 // Kernel selection (dispatch.cu): picks the tiled kernel when the shape allows it, else the
 // general row-per-warp kernel.

@@ -45,6 +45,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait that lets the hardware keep the warp suspended for up to `hint_ns` while the phase is
+// incomplete, instead of returning to a polling loop that competes for issue slots
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -58,8 +71,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_ns();
   for (unsigned spin = 1;; spin++) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 63u) == 0) {
+    if (mbar_try_wait_suspend(bar, parity, 20000u)) return true;
+    if ((spin & 15u) == 0) {
       if (*reinterpret_cast<volatile unsigned int *>(&g_pipe_wait_timeouts) != 0u) return false;
       if (global_ns() - t0 > kPipeWaitLimitNs) {
         atomicAdd(&g_pipe_wait_timeouts, 1u);
@@ -77,6 +90,7 @@ __device__ __forceinline__ bool spin_until_ge(const int *counter, int target) {
   const unsigned long long t0 = global_ns();
   for (unsigned spin = 1;; spin++) {
     if (*c >= target) return true;
+    __nanosleep(64);
     if ((spin & 63u) == 0) {
       if (*reinterpret_cast<volatile unsigned int *>(&g_pipe_wait_timeouts) != 0u) return false;
       if (global_ns() - t0 > kPipeWaitLimitNs) {
