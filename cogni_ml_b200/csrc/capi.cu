@@ -52,6 +52,10 @@ int cogni_qmm_set_kernel_choice(int choice) {
     gemv_imma_set_debug(choice <= 18 ? choice - 16 : 4 + (choice == 19 ? 0 : choice - 19));
     return COGNI_QMM_OK;
   }
+  if (choice >= 32 && choice < 48) {  // raw diagnostic bits of the tiled GEMV
+    gemv_imma_set_debug(choice - 32);
+    return COGNI_QMM_OK;
+  }
   if (choice >= 24 && choice <= 26) {  // superblocks per work item of the tiled GEMV: automatic / 1 / 2
     gemv_imma_set_pair(choice - 24);
     return COGNI_QMM_OK;

@@ -14,7 +14,9 @@
 //    aligned (Q6_K) are fetched from the 16-byte boundary below their start.
 //  * Activations are quantised once per CTA to 15-bit block floating point: per scale group
 //    (32 elements for Q4_K/Q5_K, 16 for Q6_K) x = sx * n with |n| <= 16256, n = 128*hi + lo, hi
-//    and lo int8.  The rounding step is 2^-14 of the group maximum, i.e. ~4e-5 relative rms.
+//    and lo int8 (hi = n >> 7, lo = n & 127).  The rounding step is 2^-14 of the group maximum,
+//    i.e. ~4e-5 relative rms.  The warps do this on the way, superblock by superblock, while they
+//    work through the CTA's first tile.
 //  * The quants feed mma.sync.m16n8k32 (u8 x s8 -> s32) as they are.  One MMA covers two scale
 //    groups at once: the hi and lo planes of group A occupy columns 0-1 with zeros in group B's
 //    k-slots, group B's planes columns 2-3 with zeros in A's slots, so each lane ends up with the
@@ -103,7 +105,7 @@ struct Params {
   int off_flags, off_red, off_area, off_sx, off_xx, off_xq, off_stage, stage_bytes;
   int pair;      // superblocks per work item (1 or 2)
   int resident;  // weights were complete before the preceding kernel started
-  int debug;     // diagnostics: bits 0-1: 1 = no work on the stages, 2 = decode only; bit 2: no copies
+  int debug;     // diagnostics: bits 0-1: 1 = no work on the stages, 2 = decode only; bit 2: no copies; bit 3: items sleep
   long long *part_keys;  // fused top-1 (nullptr: plain GEMV)
   unsigned *counter;
   int32_t *top_idx;
@@ -369,69 +371,81 @@ __device__ __forceinline__ void mma_block(const uint8_t *blk, int pad_a, int pad
   }
 }
 
-// Quantises superblock kblk of x (256 elements per batch row) into the fragment-ordered layout:
-// per scale group sx = max|x| / 16256, n = rint(x / sx) = 128*hi + lo.  One warp, lane = 8
-// consecutive elements.  The superblock's area is zeroed first: its unused words are the
-// structural zeros of the layout.
-template <int TYPE, int NB>
-__device__ __forceinline__ void quantise_superblock(const float *x, int K, int kblk, int lane,
-                                                    uint8_t *xq, float *SX, float *XX) {
+// Quantises NBLK consecutive superblocks of x, starting at kblk (256 elements per batch row
+// each), into the fragment-ordered layout: per scale group sx = max|x| / 16256,
+// n = rint(x / sx) = 128*hi + lo with hi = n >> 7 in [-127, 127] and lo = n & 127.  One warp,
+// lane = 8 consecutive elements.  The superblocks' areas are zeroed first: their unused words are
+// the structural zeros of the layout.  All loads are issued before the first use.
+template <int TYPE, int NB, int NBLK>
+__device__ __forceinline__ void quantise_superblocks(const float *x, int K, int kblk, int lane,
+                                                     uint8_t *xq, float *SX, float *XX) {
   using C = Cfg<TYPE>;
   constexpr int NCX = 4 * NB, UNIT_BYTES = NCX * 64;
   constexpr int LPG = C::GROUP / 8;  // lanes per scale group
-  uint8_t *blk_base = xq + (size_t)kblk * 4 * UNIT_BYTES;
+  uint8_t *base0 = xq + (size_t)kblk * 4 * UNIT_BYTES;
 #pragma unroll
-  for (int i = 0; i < 4 * UNIT_BYTES / 512; i++)
-    reinterpret_cast<uint4 *>(blk_base)[i * 32 + lane] = make_uint4(0, 0, 0, 0);
-  const int k = kblk * 256 + lane * 8, e_in = lane * 8;
-  float4 v0[NB], v1[NB];
+  for (int i = 0; i < NBLK * 4 * UNIT_BYTES / 512; i++)
+    reinterpret_cast<uint4 *>(base0)[i * 32 + lane] = make_uint4(0, 0, 0, 0);
+  const int e_in = lane * 8;
+  float4 v0[NBLK][NB], v1[NBLK][NB];
 #pragma unroll
-  for (int b = 0; b < NB; b++) {
-    v0[b] = __ldg(reinterpret_cast<const float4 *>(x + (long long)b * K + k));
-    v1[b] = __ldg(reinterpret_cast<const float4 *>(x + (long long)b * K + k + 4));
-  }
+  for (int q = 0; q < NBLK; q++)
+#pragma unroll
+    for (int b = 0; b < NB; b++) {
+      const float *src = x + (long long)b * K + (kblk + q) * 256 + e_in;
+      v0[q][b] = __ldg(reinterpret_cast<const float4 *>(src));
+      v1[q][b] = __ldg(reinterpret_cast<const float4 *>(src + 4));
+    }
   __syncwarp();
 #pragma unroll
-  for (int b = 0; b < NB; b++) {
-    const float v[8] = {v0[b].x, v0[b].y, v0[b].z, v0[b].w, v1[b].x, v1[b].y, v1[b].z, v1[b].w};
-    float mx = 0.f;
+  for (int q = 0; q < NBLK; q++) {
+    uint8_t *blk_base = base0 + q * 4 * UNIT_BYTES;
+    const int k = (kblk + q) * 256 + e_in;
 #pragma unroll
-    for (int e = 0; e < 8; e++) mx = fmaxf(mx, fabsf(v[e]));
+    for (int b = 0; b < NB; b++) {
+      const float v[8] = {v0[q][b].x, v0[q][b].y, v0[q][b].z, v0[q][b].w,
+                          v1[q][b].x, v1[q][b].y, v1[q][b].z, v1[q][b].w};
+      float mx = 0.f;
 #pragma unroll
-    for (int off = 1; off < LPG; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-    // groups below 1e-30 contribute nothing (their scale would underflow anyway)
-    const bool live = mx > 1e-30f;
-    const float sx = live ? mx * (1.f / kNMax) : 1.f;
-    const float inv = live ? (float)kNMax / mx : 0.f;
-    int hi[8], lo[8], nsum = 0;
+      for (int e = 0; e < 8; e++) mx = fmaxf(mx, fabsf(v[e]));
 #pragma unroll
-    for (int e = 0; e < 8; e++) {
-      // round to nearest through the 1.5 * 2^23 bias: |x * inv| <= 16256 * (1 + 2^-21)
-      const int n = __float_as_int(fmaf(v[e], inv, 12582912.f)) - 0x4B400000;
-      hi[e] = (n + 64) >> 7;
-      lo[e] = n - (hi[e] << 7);
-      nsum += n;
-    }
+      for (int off = 1; off < LPG; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      // groups below 1e-30 contribute nothing (their scale would underflow anyway)
+      const bool live = mx > 1e-30f;
+      const float sx = live ? mx * (1.f / kNMax) : 1.f;
+      const float inv = live ? (float)kNMax / mx : 0.f;
+      // round to nearest through the 1.5 * 2^23 bias (|x * inv| <= 16256 * (1 + 2^-21)): the low
+      // bits of the sum are n in two's complement; bits 0-6 are lo, bits 7-14 the byte hi
+      uint32_t bits[8], up[8];
+      int nsum = 0;
 #pragma unroll
-    for (int off = 1; off < LPG; off <<= 1) nsum += __shfl_xor_sync(0xffffffffu, nsum, off);
-    if ((lane & (LPG - 1)) == 0) {
-      const int grp = k / C::GROUP;
-      SX[grp * NB + b] = sx;
-      XX[grp * NB + b] = sx * (float)nsum;
-    }
-    auto pack4 = [](const int *q) {  // low bytes of four ints
-      return __byte_perm(__byte_perm(q[0], q[1], 0x0040), __byte_perm(q[2], q[3], 0x0040), 0x5410);
-    };
+      for (int e = 0; e < 8; e++) {
+        bits[e] = __float_as_uint(fmaf(v[e], inv, 12582912.f));
+        up[e] = bits[e] << 1;
+        nsum += (int)(bits[e] - 0x4B400000u);
+      }
 #pragma unroll
-    for (int w4 = 0; w4 < 2; w4++) {  // the two 4-element words of this lane's 8 elements
-      int sub;
-      const int off = xq_word_offset<TYPE>(e_in + 4 * w4, NCX, 4 * b, sub);
-      const uint32_t hw = pack4(hi + 4 * w4), lw = pack4(lo + 4 * w4);
-      *reinterpret_cast<uint32_t *>(blk_base + off) = hw;       // hi plane: column + 0
-      *reinterpret_cast<uint32_t *>(blk_base + off + 64) = lw;  // lo plane: column + 1
-      if (TYPE == kQ4_K && sub == 0) {  // the even group's second half: -x against H
-        *reinterpret_cast<uint32_t *>(blk_base + off + 4) = __vneg4(hw);
-        *reinterpret_cast<uint32_t *>(blk_base + off + 68) = __vneg4(lw);
+      for (int off = 1; off < LPG; off <<= 1) nsum += __shfl_xor_sync(0xffffffffu, nsum, off);
+      if ((lane & (LPG - 1)) == 0) {
+        const int grp = k / C::GROUP;
+        SX[grp * NB + b] = sx;
+        XX[grp * NB + b] = sx * (float)nsum;
+      }
+#pragma unroll
+      for (int w4 = 0; w4 < 2; w4++) {  // the two 4-element words of this lane's 8 elements
+        int sub;
+        const int off = xq_word_offset<TYPE>(e_in + 4 * w4, NCX, 4 * b, sub);
+        const uint32_t lw = __byte_perm(__byte_perm(bits[4 * w4], bits[4 * w4 + 1], 0x0040),
+                                        __byte_perm(bits[4 * w4 + 2], bits[4 * w4 + 3], 0x0040),
+                                        0x5410) & 0x7f7f7f7fu;
+        const uint32_t hw = __byte_perm(__byte_perm(up[4 * w4], up[4 * w4 + 1], 0x0051),
+                                        __byte_perm(up[4 * w4 + 2], up[4 * w4 + 3], 0x0051), 0x5410);
+        *reinterpret_cast<uint32_t *>(blk_base + off) = hw;       // hi plane: column + 0
+        *reinterpret_cast<uint32_t *>(blk_base + off + 64) = lw;  // lo plane: column + 1
+        if (TYPE == kQ4_K && sub == 0) {  // the even group's second half: -x against H
+          *reinterpret_cast<uint32_t *>(blk_base + off + 4) = __vneg4(hw);
+          *reinterpret_cast<uint32_t *>(blk_base + off + 68) = __vneg4(lw);
+        }
       }
     }
   }
@@ -566,8 +580,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
   // and the warps of a scheduler are always in different phases of their items.
   const int per_tile = npairs + 1;
   int li = warp / per_tile, e = warp - li * per_tile;  // this warp's item: entry e of tile li
-  int cc0 = li * p.nchunks;                   // number of the tile's chunk 0, its stage and parity
-  int s0 = cc0 % S, par0 = (cc0 / S) & 1;
+  const int step_li = kNW / per_tile, step_e = kNW - step_li * per_tile;  // to its next item
+  const uint32_t s_inv = 0xffffffffu / (uint32_t)S + 1u;  // cc / S == umulhi(cc, s_inv), cc < 2^32 / S
+  const int tail_missing = p.nchunks * C::KB - p.nblk;     // superblocks the last chunk lacks
   int cj = 0, pad_a = 0, pad_b = 0, pad_d = 0, pad_li = -1;
   for (;;) {
     if (li > ntl || (li == ntl && e > 0)) break;
@@ -575,8 +590,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
       // ------------------------------------------------ superblocks 2e, 2e+1 of tile li
       const int e0 = PAIR * e, n2 = min(PAIR, p.nblk - e0);
       const int c = e0 / C::KB, bi = e0 - c * C::KB;  // KB is even: a pair lies in one chunk
-      int s = s0 + c, par = par0;
-      while (s >= S) { s -= S; par ^= 1; }
+      const int cc = li * p.nchunks + c;                // chunk number, its stage and parity
+      const int fill = (int)__umulhi((uint32_t)cc, s_inv), s = cc - fill * S, par = fill & 1;
       if (TYPE == kQ6_K && pad_li != li) {  // only Q6_K rows can start off a 16-byte boundary
         pad_li = li;
         const int gt = blockIdx.x + li * gridDim.x;
@@ -591,8 +606,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
       // The activations are quantised on the way: the warp that takes a superblock pair of the
       // CTA's first tile does x's two superblocks first; later tiles find them done.
       if (li == 0) {
-        quantise_superblock<TYPE, NB>(p.x, K, e0, lane, xq, SX, XX);
-        if (PAIR == 2 && n2 == 2) quantise_superblock<TYPE, NB>(p.x, K, e0 + 1, lane, xq, SX, XX);
+        if (PAIR == 2 && n2 == 2) quantise_superblocks<TYPE, NB, 2>(p.x, K, e0, lane, xq, SX, XX);
+        else quantise_superblocks<TYPE, NB, 1>(p.x, K, e0, lane, xq, SX, XX);
         __syncwarp();
         if (lane == 0) {
           __threadfence_block();
@@ -604,9 +619,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
       }
       float acc0 = 0.f, acc1 = 0.f;  // rows g and g+8 of (group slot sub, batch row bt)
       TRACE(1000 + li * per_tile + e);
-      spin_until_ge(issued, cc0 + c + 1);
+      spin_until_ge(issued, cc + 1);
       mbar_wait(bar0 + 8 * s, par);
       TRACE(2000 + li * per_tile + e);
+      if (p.debug & 8) __nanosleep(1500);  // diagnostics: keep the consumers the bottleneck
       if ((p.debug & 3) != 1) {
         const uint8_t *blk = stages + (size_t)s * p.stage_bytes + bi * C::BB;
         const int which = lane >> 4;
@@ -624,12 +640,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
         }
         __syncwarp();  // the area is rewritten by this warp's next decode
       }
-      // release the stage; the warp that takes the last pair of a short final chunk also arrives
-      // for the superblocks that do not exist
-      if (lane == 0) {
-        const int nb = min(C::KB, p.nblk - c * C::KB);
-        mbar_arrive_n(bar0 + 8 * (S + s), bi + n2 == nb ? C::KB - nb + n2 : n2);
-      }
       // the two group slots of a batch row sit in neighbouring lanes
       acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
       acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
@@ -639,6 +649,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
         red[tb * red_tile + (e * 8 + g) * NB + (t >> 1)] = make_float2(acc0, acc1);
       __syncwarp();
       if (lane == 0) {
+        // release the stage (the tile's last item also arrives for the superblocks that a short
+        // final chunk lacks) and count the partial sums in
+        mbar_arrive_n(bar0 + 8 * (S + s), e == npairs - 1 ? n2 + tail_missing : n2);
         __threadfence_block();
         atomicAdd(&arrivals[tb], 1);
       }
@@ -678,13 +691,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
       }
     }
     // next item of this warp
-    e += kNW;
-    while (e >= per_tile) {
+    e += step_e;
+    li += step_li;
+    if (e >= per_tile) {
       e -= per_tile;
       li++;
-      cc0 += p.nchunks;
-      s0 += p.nchunks;
-      while (s0 >= S) { s0 -= S; par0 ^= 1; }
     }
   }
 

@@ -72,6 +72,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   const unsigned long long t0 = global_ns();
   for (unsigned spin = 1;; spin++) {
     if (mbar_try_wait_suspend(bar, parity, 20000u)) return true;
+    __nanosleep(spin < 4 ? 32 : 256);
     if ((spin & 15u) == 0) {
       if (*reinterpret_cast<volatile unsigned int *>(&g_pipe_wait_timeouts) != 0u) return false;
       if (global_ns() - t0 > kPipeWaitLimitNs) {
