@@ -35,7 +35,10 @@ namespace cogni {
 namespace {
 
 constexpr int kNW = 16;                      // consumer warps
-constexpr int kThreads = (kNW + 1) * 32;     // + 1 producer warp
+// One warp issues bulk copies at roughly one per 70-90 cycles however many of its lanes take
+// part; the copy unit accepts several times that, so four producer warps share a stage's rows.
+constexpr int kPW = 4;                       // producer warps
+constexpr int kThreads = (kNW + kPW) * 32;
 constexpr int kR = 16;                       // rows per tile
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 // 227 KB per CTA on sm_100, minus room for the kernel's few static __shared__ variables
@@ -400,7 +403,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const Params p) {
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; s++) {
-      mbar_init(smem_u32(&bars[s]), 1);
+      mbar_init(smem_u32(&bars[s]), kPW);
       mbar_init(smem_u32(&bars[S + s]), kNW);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -409,8 +412,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const Params p) {
 
   uint8_t *stages = smem + p.off_stage;
 
-  if (warp == kNW) {
-    // ------------------------------------------------------------------ producer warp
+  if (warp >= kNW) {
+    // ------------------------------------------------------------------ producer warps
+    // every producer warp walks the same chunk sequence; warp pw issues rows 4*pw .. 4*pw+3 and
+    // arrives once per chunk with the byte count of its own rows
+    const int pw = warp - kNW;
     int it = 0;
     for (int tile = blockIdx.x; tile < p.ntiles; tile += gridDim.x) {
       const int row = tile * kR + lane;
@@ -423,11 +429,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const Params p) {
         const uint8_t *src = rsrc + (long long)c * C::KB * C::BB;
         const uint32_t padb = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15);
         const uint32_t bytes = rvalid ? ((padb + nb * C::BB + 15u) & ~15u) : 0u;
-        const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
+        const bool mine = rvalid && (lane >> 2) == pw;
+        const uint32_t my_bytes = __reduce_add_sync(0xffffffffu, mine ? bytes : 0u);
         const uint32_t full = smem_u32(&bars[s]);
-        if (lane == 0) mbar_arrive_expect_tx(full, total);
+        if (lane == 0) mbar_arrive_expect_tx(full, my_bytes);
         __syncwarp();
-        if (rvalid)
+        if (mine)
           bulk_g2s(smem_u32(stages + (size_t)s * p.stage_bytes + lane * C::RS), src - padb, bytes,
                    full);
       }
