@@ -272,6 +272,118 @@ __device__ __forceinline__ void decode_scales(const uint8_t *blk_row, int lane, 
   for (int b = 0; b < NB; b++) rows[b * A::BATCH + C::NG] = C::HAS_MIN ? corr[b] : -32.f * corr[b];
 }
 
+// Single-superblock items: lanes (r = lane & 15, half = lane >> 4) decode one half of the scale
+// groups of row r; the two halves' corrections are combined with one shuffle.
+template <int TYPE, int NB>
+__device__ __forceinline__ void decode_scales_half(const uint8_t *blk_row, int lane, int kblk,
+                                              const float *SX, const float *XX, float *area) {
+  using C = Cfg<TYPE>;
+  using A = Area<TYPE>;
+  constexpr int NH = C::NG / 2;  // groups per lane
+  const int r = lane & 15, half = lane >> 4;
+  float dsc[NH], kk[NH];
+  if constexpr (C::HAS_MIN) {
+    const uint4 h = *reinterpret_cast<const uint4 *>(blk_row);
+    const __half2 dd = *reinterpret_cast<const __half2 *>(&h.x);
+    const float d = __low2float(dd), dmin = __high2float(dd);
+    const uint32_t u0 = h.y, u1 = h.z, u2 = h.w;
+    // four 6-bit scales / mins of this half as bytes (dequant.cr:240-249, four at a time)
+    const uint32_t scw = half ? ((u2 & 0x0f0f0f0fu) | ((u0 >> 2) & 0x30303030u)) : (u0 & 0x3f3f3f3fu);
+    const uint32_t mnw = half ? (((u2 >> 4) & 0x0f0f0f0fu) | ((u1 >> 2) & 0x30303030u)) : (u1 & 0x3f3f3f3fu);
+    const float d23 = d * 8388608.f, ndmin = -dmin, ndmin23 = ndmin * 8388608.f;
+    // Q4_K: the odd groups' integer sums arrive multiplied by 16 (see mma_block)
+    const float dodd = TYPE == kQ4_K ? d * 0.0625f : d, dodd23 = dodd * 8388608.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      dsc[i] = (i & 1) ? byte_times(scw, i, dodd, dodd23) : byte_times(scw, i, d, d23);
+      kk[i] = byte_times(mnw, i, ndmin, ndmin23);
+    }
+  } else {
+    const float d = load_half_as_float(blk_row + 208);
+    const int8_t *sc = reinterpret_cast<const int8_t *>(blk_row + 192 + 8 * half);
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      dsc[i] = d * (float)sc[i];
+      kk[i] = dsc[i];  // times -32 once, at the end
+    }
+  }
+  // this lane's groups are consecutive in the tables: NH * NB floats each, 16-byte aligned
+  const int grp0 = kblk * C::NG + NH * half;
+  float sxv[NH * NB], xxv[NH * NB];
+#pragma unroll
+  for (int i = 0; i < NH * NB / 4; i++) {
+    const float4 a = reinterpret_cast<const float4 *>(SX + grp0 * NB)[i];
+    const float4 c = reinterpret_cast<const float4 *>(XX + grp0 * NB)[i];
+    sxv[4 * i] = a.x; sxv[4 * i + 1] = a.y; sxv[4 * i + 2] = a.z; sxv[4 * i + 3] = a.w;
+    xxv[4 * i] = c.x; xxv[4 * i + 1] = c.y; xxv[4 * i + 2] = c.z; xxv[4 * i + 3] = c.w;
+  }
+#pragma unroll
+  for (int b = 0; b < NB; b++) {
+    float *row = area + b * A::BATCH + r * A::ROW;
+    float v[NH], corr = 0.f;
+#pragma unroll
+    for (int i = 0; i < NH; i++) {
+      v[i] = dsc[i] * sxv[i * NB + b];
+      corr = fmaf(kk[i], xxv[i * NB + b], corr);
+    }
+    if constexpr (C::HAS_MIN) {  // lane's groups 4*half + i: g4 = 2*half + (i >> 1), sub = i & 1
+      *reinterpret_cast<float2 *>(row + 2 * half) = make_float2(v[0], v[2]);
+      *reinterpret_cast<float2 *>(row + 4 + 2 * half) = make_float2(v[1], v[3]);
+    } else {  // lane's groups 8*half + i: n = half, h = i & 1, sub = (i >> 1) & 1, m = i >> 2
+      *reinterpret_cast<float4 *>(row + 4 * half) = make_float4(v[0], v[4], v[1], v[5]);
+      *reinterpret_cast<float4 *>(row + 8 + 4 * half) = make_float4(v[2], v[6], v[3], v[7]);
+    }
+    corr += __shfl_xor_sync(0xffffffffu, corr, 16);
+    if (half == 0) row[C::NG] = C::HAS_MIN ? corr : -32.f * corr;
+  }
+}
+
+// Q6_K part of mma_block: aa / ab8 are the addresses of this lane's first ql bytes in rows g and
+// g+8 (4 * t into the superblock).
+template <int UNIT_BYTES, bool ALIGNED>
+__device__ __forceinline__ void mma_q6(uintptr_t aa, uintptr_t ab8, const uint8_t *xu,
+                                       const float *rowa, const float *rowb, int sub, float &acc0,
+                                       float &acc1) {
+  constexpr uint32_t M4 = 0x0f0f0f0fu, M2 = 0x30303030u;
+  const uint8_t *base[2] = {reinterpret_cast<const uint8_t *>(aa & ~(uintptr_t)3),
+                            reinterpret_cast<const uint8_t *>(ab8 & ~(uintptr_t)3)};
+  const uint32_t sh[2] = {(uint32_t)(aa & 2) * 8, (uint32_t)(ab8 & 2) * 8};
+#pragma unroll
+  for (int n = 0; n < 2; n++) {
+    const float4 sa4 = *reinterpret_cast<const float4 *>(rowa + 8 * sub + 4 * n);
+    const float4 sb4 = *reinterpret_cast<const float4 *>(rowb + 8 * sub + 4 * n);
+    const float sa[4] = {sa4.x, sa4.y, sa4.z, sa4.w}, sb[4] = {sb4.x, sb4.y, sb4.z, sb4.w};
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const uint4 bv = *reinterpret_cast<const uint4 *>(xu + (2 * n + h) * UNIT_BYTES);
+      uint32_t q[2][4];
+#pragma unroll
+      for (int r = 0; r < 2; r++) {
+        auto ld = [&](int off) {
+          const uint32_t *w32 = reinterpret_cast<const uint32_t *>(base[r] + off);
+          if constexpr (ALIGNED) return w32[0];
+          else return __funnelshift_r(w32[0], w32[1], sh[r]);
+        };
+        const uint32_t ql0 = ld(64 * n + 16 * h), ql1 = ld(64 * n + 32 + 16 * h);
+        const uint32_t qhw = ld(128 + 32 * n + 16 * h);
+        q[r][0] = (ql0 & M4) | ((qhw << 4) & M2);
+        q[r][1] = (ql1 & M4) | ((qhw << 2) & M2);
+        q[r][2] = ((ql0 >> 4) & M4) | (qhw & M2);
+        q[r][3] = ((ql1 >> 4) & M4) | ((qhw >> 2) & M2);
+      }
+#pragma unroll
+      for (int m = 0; m < 2; m++) {
+        int cc[4];
+        // k-slots 0..15: run k = 2m, 16..31: run k = 2m+1 (scale group 8n + h + 2k)
+        imma_zero(cc, q[0][2 * m], q[1][2 * m], q[0][2 * m + 1], q[1][2 * m + 1],
+                  m ? bv.z : bv.x, m ? bv.w : bv.y);
+        acc0 = fmaf(sa[2 * h + m], (float)(cc[0] * 128 + cc[1]), acc0);
+        acc1 = fmaf(sb[2 * h + m], (float)(cc[2] * 128 + cc[3]), acc1);
+      }
+    }
+  }
+}
+
 // MMAs of one superblock (16 rows x 256 columns) for this lane's (group slot sub, batch row).
 // blk: the superblock of row 0 of the tile inside the stage; xu: this lane's B fragments of the
 // superblock's first unit; ab: this lane's batch row of the superblock's area.  Adds the partial
@@ -329,45 +441,15 @@ __device__ __forceinline__ void mma_block(const uint8_t *blk, int pad_a, int pad
       acc1 = fmaf(sb[g4], (float)(cc[2] * 128 + cc[3]), acc1);
     }
   } else {
-    constexpr uint32_t M2 = 0x30303030u;
     const uintptr_t aa = reinterpret_cast<uintptr_t>(blk + g * C::RS + pad_a + 4 * t);
     const uintptr_t ab8 = reinterpret_cast<uintptr_t>(blk + (g + 8) * C::RS + pad_b + 4 * t);
-    const uint8_t *base[2] = {reinterpret_cast<const uint8_t *>(aa & ~(uintptr_t)3),
-                              reinterpret_cast<const uint8_t *>(ab8 & ~(uintptr_t)3)};
-    const uint32_t sh[2] = {(uint32_t)(aa & 2) * 8, (uint32_t)(ab8 & 2) * 8};
-#pragma unroll
-    for (int n = 0; n < 2; n++) {
-      const float4 sa4 = *reinterpret_cast<const float4 *>(rowa + 8 * sub + 4 * n);
-      const float4 sb4 = *reinterpret_cast<const float4 *>(rowb + 8 * sub + 4 * n);
-      const float sa[4] = {sa4.x, sa4.y, sa4.z, sa4.w}, sb[4] = {sb4.x, sb4.y, sb4.z, sb4.w};
-#pragma unroll
-      for (int h = 0; h < 2; h++) {
-        const uint4 bv = *reinterpret_cast<const uint4 *>(xu + (2 * n + h) * UNIT_BYTES);
-        uint32_t q[2][4];
-#pragma unroll
-        for (int r = 0; r < 2; r++) {
-          auto ld = [&](int off) {
-            const uint32_t *w32 = reinterpret_cast<const uint32_t *>(base[r] + off);
-            return __funnelshift_r(w32[0], w32[1], sh[r]);
-          };
-          const uint32_t ql0 = ld(64 * n + 16 * h), ql1 = ld(64 * n + 32 + 16 * h);
-          const uint32_t qhw = ld(128 + 32 * n + 16 * h);
-          q[r][0] = (ql0 & M4) | ((qhw << 4) & M2);
-          q[r][1] = (ql1 & M4) | ((qhw << 2) & M2);
-          q[r][2] = ((ql0 >> 4) & M4) | (qhw & M2);
-          q[r][3] = ((ql1 >> 4) & M4) | ((qhw >> 2) & M2);
-        }
-#pragma unroll
-        for (int m = 0; m < 2; m++) {
-          int cc[4];
-          // k-slots 0..15: run k = 2m, 16..31: run k = 2m+1 (scale group 8n + h + 2k)
-          imma_zero(cc, q[0][2 * m], q[1][2 * m], q[0][2 * m + 1], q[1][2 * m + 1],
-                    m ? bv.z : bv.x, m ? bv.w : bv.y);
-          acc0 = fmaf(sa[2 * h + m], (float)(cc[0] * 128 + cc[1]), acc0);
-          acc1 = fmaf(sb[2 * h + m], (float)(cc[2] * 128 + cc[3]), acc1);
-        }
-      }
-    }
+    // Superblocks are 210 bytes: every other one starts 2 bytes off a word boundary.  When the
+    // whole warp reads word-aligned rows, one load per word does; otherwise two loads and a
+    // funnel shift.
+    if (__all_sync(0xffffffffu, ((aa | ab8) & 2) == 0))
+      mma_q6<UNIT_BYTES, true>(aa, ab8, xu, rowa, rowb, sub, acc0, acc1);
+    else
+      mma_q6<UNIT_BYTES, false>(aa, ab8, xu, rowa, rowb, sub, acc0, acc1);
   }
 }
 
@@ -626,9 +708,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
       if ((p.debug & 3) != 1) {
         const uint8_t *blk = stages + (size_t)s * p.stage_bytes + bi * C::BB;
         const int which = lane >> 4;
-        if (which < n2)
+        if constexpr (PAIR == 1) {
+          decode_scales_half<TYPE, NB>(blk + (lane & 15) * C::RS + pad_d, lane, e0, SX, XX, area);
+        } else if (which < n2) {
           decode_scales<TYPE, NB>(blk + (lane & 15) * C::RS + pad_d + which * C::BB, lane,
                                   e0 + which, SX, XX, area);
+        }
         __syncwarp();
         if ((p.debug & 3) != 2) {
           mma_block<TYPE, UNIT_BYTES>(blk, pad_a, pad_b, xlane + (size_t)e0 * 4 * UNIT_BYTES,
