@@ -44,16 +44,15 @@
 namespace cogni {
 namespace {
 
-#ifndef COGNI_IMMA_WARPS
-#define COGNI_IMMA_WARPS 24
-#endif
-constexpr int kNW = COGNI_IMMA_WARPS;        // consumer warps
+// Consumer warps per CTA.  Every warp holds the stage bytes of its item until it is done, so
+// more warps leave fewer stages for the copies in flight; 16 (20 for single-superblock items of
+// the 210-byte Q6_K blocks) measured best.
+__host__ __device__ constexpr int consumer_warps(int type, int pair) { return type == kQ6_K && pair == 1 ? 20 : 16; }
 constexpr int kFoldBufs = 4;                 // tiles whose partial sums can be pending (power of 2)
 // One warp issues bulk copies at roughly one per 70-90 cycles however many of its lanes take
 // part; the copy unit itself accepts several times that, so the rows of a stage are split over
 // kPW producer warps.
 constexpr int kPW = 4;                       // producer warps
-constexpr int kThreads = (kNW + kPW) * 32;
 constexpr int kR = 16;                       // rows per tile
 constexpr size_t kDynSmemMax = 227 * 1024 - 1024;
 constexpr int kNMax = 16256;                 // |n| bound: 127 * 128
@@ -129,8 +128,9 @@ __device__ __forceinline__ void trace(int warp, int lane, int &n, int ev) {
 #define TRACE(ev)
 #endif
 
+template <int NW>
 __device__ __forceinline__ void consumer_sync() {
-  asm volatile("bar.sync 1, %0;" ::"n"(kNW * 32) : "memory");
+  asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
 }
 __device__ __forceinline__ void imma_zero(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                           uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -535,7 +535,9 @@ __device__ __forceinline__ void quantise_superblocks(const float *x, int K, int 
 
 // ---------------------------------------------------------------------------- the kernel
 template <int TYPE, int NB, int PAIR>
-__global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) {
+__global__ void __launch_bounds__((consumer_warps(TYPE, PAIR) + kPW) * 32, 1)
+    gemv_imma_kernel(const Params p) {
+  constexpr int kNW = consumer_warps(TYPE, PAIR), kThreads = (kNW + kPW) * 32;
   using C = Cfg<TYPE>;
   using A = Area<TYPE>;
   constexpr int NCX = 4 * NB;                    // columns of the quantised-x layout
@@ -791,19 +793,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_imma_kernel(const Params p) 
   __shared__ long long s_best[2];
   __shared__ bool s_last;
   if (ctid < 2) s_best[ctid] = LLONG_MIN;
-  consumer_sync();
+  consumer_sync<kNW>();
   atomicMax(&s_best[0], best);
   if (NB > 1) atomicMax(&s_best[1], best_b1);
-  consumer_sync();
+  consumer_sync<kNW>();
   const int nparts = gridDim.x;
   if (ctid < NB) p.part_keys[(long long)ctid * nparts + blockIdx.x] = s_best[ctid];
   __threadfence();
-  consumer_sync();
+  consumer_sync<kNW>();
   if (ctid == 0) {
     const unsigned ticket = atomicAdd(p.counter, 1u);
     s_last = ticket == (unsigned)nparts - 1u;
   }
-  consumer_sync();
+  consumer_sync<kNW>();
   if (!s_last) return;
   __threadfence();
   if (warp < NB) {
@@ -853,7 +855,7 @@ bool make_plan_pair(int in_dim, int nb, int pair, Params &p, size_t &smem) {
   size_t off = 256;  // mbarriers and counters
   const size_t off_flags = off;  off += 256;  // one flag per superblock of x (in_dim <= 16384)
   const size_t off_red = off;    off = al(off + (size_t)kFoldBufs * ((nblk + pair - 1) / pair) * 8 * nb * 8);  // [tile buffer][item][g][batch] float2
-  const size_t off_area = off;   off = al(off + (size_t)kNW * pair * nb * Area<TYPE>::BATCH * 4);
+  const size_t off_area = off;   off = al(off + (size_t)consumer_warps(TYPE, pair) * pair * nb * Area<TYPE>::BATCH * 4);
   const size_t off_sx = off;     off = al(off + (size_t)ngroups * nb * 4);
   const size_t off_xx = off;     off = al(off + (size_t)ngroups * nb * 4);
   const size_t off_xq = off;     off = al(off + (size_t)(in_dim / 64) * (4 * nb) * 64);
@@ -898,7 +900,7 @@ int launch_instance(const Params &p, size_t smem, int grid, cudaStream_t s) {
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3((consumer_warps(TYPE, PAIR) + kPW) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
   cudaLaunchAttribute attr[1];
