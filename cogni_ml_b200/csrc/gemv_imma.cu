@@ -619,10 +619,7 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR) + kPW) * 32, 1)
         // the barrier is in (or past) that chunk's phase: a warp whose items lie far apart could
         // otherwise mistake the stage's previous fill for it.
         cc++;
-        if (pw == 0 && lane == 0) {
-          __threadfence_block();
-          *reinterpret_cast<volatile int *>(issued) = cc;
-        }
+        if (pw == 0 && lane == 0) st_release_shared(issued, cc);
         if (++s == S) { s = 0; par ^= 1; }
       }
     }
@@ -693,13 +690,9 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR) + kPW) * 32, 1)
         if (PAIR == 2 && n2 == 2) quantise_superblocks<TYPE, NB, 2>(p.x, K, e0, lane, xq, SX, XX);
         else quantise_superblocks<TYPE, NB, 1>(p.x, K, e0, lane, xq, SX, XX);
         __syncwarp();
-        if (lane == 0) {
-          __threadfence_block();
-          *reinterpret_cast<volatile int *>(&xready[e]) = 1;
-        }
+        if (lane == 0) st_release_shared(&xready[e], 1);
       } else {
         spin_until_ge(&xready[e], 1);
-        __threadfence_block();
       }
       float acc0 = 0.f, acc1 = 0.f;  // rows g and g+8 of (group slot sub, batch row bt)
       TRACE(1000 + li * per_tile + e);
@@ -739,8 +732,7 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR) + kPW) * 32, 1)
         // release the stage (the tile's last item also arrives for the superblocks that a short
         // final chunk lacks) and count the partial sums in
         mbar_arrive_n(bar0 + 8 * (S + s), e == npairs - 1 ? n2 + tail_missing : n2);
-        __threadfence_block();
-        atomicAdd(&arrivals[tb], 1);
+        add_release_shared(&arrivals[tb], 1);
       }
       TRACE(3000 + li * per_tile + e);
     } else if (li > 0) {
@@ -749,7 +741,6 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR) + kPW) * 32, 1)
       const int tb = fl & (kFoldBufs - 1);
       TRACE(4000 + li * per_tile + e);
       spin_until_ge(&arrivals[tb], (fl / kFoldBufs + 1) * npairs);  // all partials of tile fl stored
-      __threadfence_block();
       TRACE(5000 + li * per_tile + e);
       // lane = (batch row, row of the tile): a fixed-order sum over the superblock pairs
       const int r16 = lane & 15, b = lane >> 4;
@@ -758,10 +749,7 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR) + kPW) * 32, 1)
 #pragma unroll 4
       for (int k = 0; k < npairs; k++) v += src[k * 16 * NB];
       __syncwarp();
-      if (lane == 0) {
-        __threadfence_block();
-        *reinterpret_cast<volatile int *>(&folded[tb]) = fl / kFoldBufs + 1;
-      }
+      if (lane == 0) st_release_shared(&folded[tb], fl / kFoldBufs + 1);
       const int gt = blockIdx.x + fl * gridDim.x;
       locate(gt, cj);
       const Job &job = p.jobs[cj];

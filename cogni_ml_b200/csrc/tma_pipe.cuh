@@ -82,15 +82,27 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     }
   }
 }
+// Acquire / release accesses to counters and flags in shared memory at CTA scope: the data they
+// publish is ordinary shared memory written before the release and read after the acquire.
+__device__ __forceinline__ int ld_acquire_shared(const int *p) {
+  int v;
+  asm volatile("ld.acquire.cta.shared::cta.b32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_shared(int *p, int v) {
+  asm volatile("st.release.cta.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void add_release_shared(int *p, int v) {
+  asm volatile("red.release.cta.shared::cta.add.s32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
 // Waits until a monotone counter in shared memory reaches `target`, with the same limit and
 // give-up rule as mbar_wait.  Counters cannot be misread the way a phase parity can when a
 // waiter is several phases ahead of the barrier.
 __device__ __forceinline__ bool spin_until_ge(const int *counter, int target) {
-  const volatile int *c = counter;
-  if (*c >= target) return true;
+  if (ld_acquire_shared(counter) >= target) return true;
   const unsigned long long t0 = global_ns();
   for (unsigned spin = 1;; spin++) {
-    if (*c >= target) return true;
+    if (ld_acquire_shared(counter) >= target) return true;
     __nanosleep(64);
     if ((spin & 63u) == 0) {
       if (*reinterpret_cast<volatile unsigned int *>(&g_pipe_wait_timeouts) != 0u) return false;
