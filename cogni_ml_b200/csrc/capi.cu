@@ -56,6 +56,10 @@ int cogni_qmm_set_kernel_choice(int choice) {
     gemv_imma_set_debug(choice - 32);
     return COGNI_QMM_OK;
   }
+  if (choice >= 48 && choice <= 51) {  // prefill token-tile width: automatic / 128 / 256 / 512
+    gemm_prefill_set_tile(choice == 48 ? 0 : 64 << (choice - 48));
+    return COGNI_QMM_OK;
+  }
   if (choice >= 24 && choice <= 26) {  // superblocks per work item of the tiled GEMV: automatic / 1 / 2
     gemv_imma_set_pair(choice - 24);
     return COGNI_QMM_OK;

@@ -26,7 +26,8 @@ namespace {
 
 constexpr int kBM = 128;      // weight rows per tile (UMMA M)
 constexpr int kBK = 64;       // k elements per stage: 128 bytes of bf16 = one swizzle row
-constexpr int kStages = 4;
+// stages of the ring: four 48 KB stages for 256-token tiles, two 80 KB stages for 512-token tiles
+__host__ __device__ constexpr int stages_for(int bn) { return bn > 256 ? 2 : 4; }
 constexpr int kThreads = 192; // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: dequant + epilogue
 constexpr int kATile = kBM * kBK * 2;  // 16 KB
 
@@ -117,6 +118,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // byte i of v as an exact float
 __device__ __forceinline__ float byte_f(uint32_t v, int i) {
   return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7650 + i)) - 8388608.f;
+}
+// byte i of v minus 32 as an exact float: (2^23 + b) - (2^23 + 32)
+__device__ __forceinline__ float byte_f_m32(uint32_t v, int i) {
+  return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7650 + i)) - 8388640.f;
 }
 // Stores chunk c (8 consecutive k elements = 16 bytes) of tile row r at its swizzled position.
 __device__ __forceinline__ void store_chunk(uint8_t *tile, int r, int c, uint4 v) {
@@ -243,8 +248,8 @@ __device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, uint8
         const uint32_t qlw = raw.ql[8 * (c >> 2) + 2 * (c & 3) + w2];
         const uint32_t qhw = raw.qh[2 * (c & 3) + w2];
         const uint32_t q = ((qlw >> (4 * hi)) & 0x0f0f0f0fu) | (((qhw >> (2 * kk)) & 0x03030303u) << 4);
-        const float w0 = __fmul_rn(dsc, byte_f(q, 0) - 32.f), w1 = __fmul_rn(dsc, byte_f(q, 1) - 32.f);
-        const float w2f = __fmul_rn(dsc, byte_f(q, 2) - 32.f), w3 = __fmul_rn(dsc, byte_f(q, 3) - 32.f);
+        const float w0 = __fmul_rn(dsc, byte_f_m32(q, 0)), w1 = __fmul_rn(dsc, byte_f_m32(q, 1));
+        const float w2f = __fmul_rn(dsc, byte_f_m32(q, 2)), w3 = __fmul_rn(dsc, byte_f_m32(q, 3));
         out[2 * w2] = pack_bf16(w0, w1);
         out[2 * w2 + 1] = pack_bf16(w2f, w3);
       }
@@ -257,8 +262,12 @@ __device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, uint8
 template <int TYPE, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+  constexpr int kStages = stages_for(BN);
   constexpr int kBTile = BN * kBK * 2;
   constexpr int kStageBytes = kATile + kBTile;
+  // UMMA N is at most 256: a 512-token tile is two accumulators of 256 TMEM columns, fed by the
+  // two 256-row halves of the stage's B tile
+  constexpr int kNMma = BN > 256 ? 256 : BN, kNSub = BN / kNMma;
   extern __shared__ uint8_t smem_raw[];
   // stage tiles must sit on 1024-byte boundaries (the swizzle pattern repeats every 1024 bytes)
   uint8_t *smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
@@ -295,13 +304,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         mbar_wait(smem_u32(&bars[2 * kStages + s]), ((ks / kStages) & 1) ^ 1);
         const uint32_t full = smem_u32(&bars[kStages + s]);
         mbar_arrive_expect_tx(full, kBTile);
-        tma_load_2d(smem_u32(smem + s * kStageBytes + kATile), &tmap_x, ks * kBK, m0, full);
+#pragma unroll
+        for (int h = 0; h < kNSub; h++)
+          tma_load_2d(smem_u32(smem + s * kStageBytes + kATile + h * kNMma * kBK * 2), &tmap_x,
+                      ks * kBK, m0 + h * kNMma, full);
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issue
     if (lane == 0) {
-      constexpr uint32_t idesc = idesc_bf16(kBM, BN);
+      constexpr uint32_t idesc = idesc_bf16(kBM, kNMma);
       for (int ks = 0; ks < nks; ks++) {
         const int s = ks % kStages;
         const uint32_t ph = (ks / kStages) & 1;
@@ -312,8 +324,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t b_addr = a_addr + kATile;
 #pragma unroll
         for (int k = 0; k < kBK / 16; k++)   // 16 bf16 = 32 bytes further along the swizzled row
-          umma_bf16(tmem_base, smem_desc_sw128(a_addr + 32 * k), smem_desc_sw128(b_addr + 32 * k),
-                    idesc, (ks | k) != 0);
+#pragma unroll
+          for (int h = 0; h < kNSub; h++)
+            umma_bf16(tmem_base + h * kNMma, smem_desc_sw128(a_addr + 32 * k),
+                      smem_desc_sw128(b_addr + h * kNMma * kBK * 2 + 32 * k), idesc, (ks | k) != 0);
         umma_commit(smem_u32(&bars[2 * kStages + s]));     // frees the stage when the MMAs are done
       }
       umma_commit(smem_u32(&bars[3 * kStages]));           // accumulator ready
@@ -386,6 +400,8 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+int g_prefill_force_bn = 0;  // diagnostics: 0 = automatic, else the token-tile width to use
+
 template <int TYPE, int BN>
 int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows, int n_out,
            int k_in, cudaStream_t s) {
@@ -394,13 +410,13 @@ int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows
   CUtensorMap tmap;
   const cuuint64_t dims[2] = {(cuuint64_t)k_in, (cuuint64_t)m_rows};
   const cuuint64_t strides[1] = {(cuuint64_t)k_in * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)BN};
+  const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)(BN > 256 ? 256 : BN)};
   const cuuint32_t estr[2] = {1, 1};
   CUresult cr = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(d_x), dims,
                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (cr != CUDA_SUCCESS) return (int)cr;
-  constexpr int smem = kStages * (kATile + BN * kBK * 2) + 1024 /*alignment*/ + 256 /*barriers*/;
+  constexpr int smem = stages_for(BN) * (kATile + BN * kBK * 2) + 1024 /*alignment*/ + 256 /*barriers*/;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -424,11 +440,33 @@ int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows
 template <int TYPE>
 int launch_typed(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows, int n_out,
                  int k_in, cudaStream_t s) {
-  // 256-token tiles halve the dequant work per flop; fall back to 128 when that would leave
-  // most SMs without a tile
-  const long long tiles256 = (long long)((n_out + kBM - 1) / kBM) * ((m_rows + 255) / 256);
-  if (m_rows > 128 && tiles256 >= 120)
-    return launch<TYPE, 256>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, s);
+  // Token-tile width: wider tiles do less dequant work per flop (a tile's time is about 1 : 1.27 :
+  // 1.97 for 128 / 256 / 512 tokens of Q4_K, whose dequant is cheap, and 1 : 1.1 : 1.15 for Q6_K,
+  // which is bound by it), narrower ones fill the SMs in fewer, fuller waves.  Pick the width
+  // with the least waves x tile time.
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  const long long row_tiles = (n_out + kBM - 1) / kBM;
+  const double rel256 = TYPE == kQ4_K ? 1.27 : TYPE == kQ5_K ? 1.2 : 1.1;
+  const double rel512 = TYPE == kQ4_K ? 1.97 : TYPE == kQ5_K ? 1.6 : 1.15;
+  auto cost = [&](int bn, double rel) {
+    const long long tiles = row_tiles * ((m_rows + bn - 1) / bn);
+    return (double)((tiles + sms - 1) / sms) * rel;
+  };
+  int bn = g_prefill_force_bn;
+  if (bn == 0) {
+    bn = 128;
+    double best = cost(128, 1.0);
+    if (cost(256, rel256) <= best) { best = cost(256, rel256); bn = 256; }
+    if (cost(512, rel512) <= best) { best = cost(512, rel512); bn = 512; }
+  }
+  if (bn == 512) return launch<TYPE, 512>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, s);
+  if (bn == 256) return launch<TYPE, 256>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, s);
   return launch<TYPE, 128>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, s);
 }
 
@@ -443,6 +481,8 @@ int launch_gemm_prefill(int type, const void *d_w, const void *d_x_bf16, void *d
     default: return COGNI_QMM_ERR_TYPE;
   }
 }
+
+void gemm_prefill_set_tile(int bn) { g_prefill_force_bn = bn; }
 
 unsigned gemm_prefill_timeouts() {
   unsigned v = 0;

@@ -131,6 +131,7 @@ unsigned gemv_imma_timeouts();
 unsigned gemm_prefill_timeouts();
 void gemv_imma_set_debug(int mode);
 void gemv_imma_set_pair(int pair);
+void gemm_prefill_set_tile(int bn);
 
 // Kernel selection (dispatch.cu): picks the tiled kernel when the shape allows it, else the
 // general row-per-warp kernel.

@@ -42,6 +42,22 @@ def test_gemm_matches_bf16_operand_reference(cuda, oracle, engine, qtype, m, n, 
     assert engine.lib.cogni_qmm_wait_timeouts() == 0
 
 
+@pytest.mark.parametrize("tile", [128, 256, 512])
+@pytest.mark.parametrize("qtype,m,n,k", [(Q4_K, 700, 300, 512), (Q6_K, 513, 128, 1024),
+                                         (Q5_K, 1100, 260, 256), (Q4_K, 40, 128, 2048)])
+def test_gemm_every_token_tile_width(cuda, oracle, engine, tile, qtype, m, n, k):
+    """The token-tile width (128 / 256 / 512 tokens per CTA) is normally chosen from the shape;
+    here each width is forced, with token counts that leave ragged and empty tile halves."""
+    engine.lib.cogni_qmm_set_kernel_choice({128: 49, 256: 50, 512: 51}[tile])
+    try:
+        w, x, y, ref = run_case(cuda, oracle, qtype, m, n, k, seed=13)
+    finally:
+        engine.lib.cogni_qmm_set_kernel_choice(48)
+    assert not np.isnan(y).any()
+    assert np.abs(y - ref).max() <= 1e-4 * np.abs(ref).max()
+    assert engine.lib.cogni_qmm_wait_timeouts() == 0
+
+
 @pytest.mark.parametrize("qtype,n,k", [(Q4_K, 1024, 4096), (Q6_K, 512, 12288)])
 def test_gemm_within_stated_tolerance_of_cpu_quant_matmul(cuda, oracle, qtype, n, k):
     m = 512
