@@ -2,19 +2,24 @@
 //
 //     y[m, n] = sum_k bf16(x[m, k]) * bf16(dequant(W[n, k]))        fp32 accumulation in TMEM
 //
-// One CTA computes a 128 (weight rows n) x BN (tokens m) tile of y^T:
-//   * A operand = weights.  Four dequant warps read the raw GGUF superblocks of their 128 rows
-//     straight from global memory (L2-resident across the token tiles), rebuild the f32 weight
-//     with the reference's operation order (src/ml/gguf/dequant.cr), round it to bf16 and write
-//     a 128 x 64 K-major tile into shared memory in the 128-byte-swizzled canonical layout.
-//   * B operand = activations.  One thread issues a TMA tile load (bf16 [BN x 64], 128-byte
-//     swizzle) per k-step.
-//   * One thread issues tcgen05.mma (kind::f16, M = 128, N = BN, K = 16) four times per k-step,
-//     accumulating in BN columns of tensor memory, and tcgen05.commit releases the stage.
-//   * After the last k-step the same four warps read the accumulator back with tcgen05.ld
-//     (each warp owns 32 TMEM lanes = 32 weight rows) and store y[m, n]: for a fixed token the
-//     warp's 32 lanes write 32 consecutive n, one 128-byte segment.
-// A 4-stage mbarrier ring decouples the three roles.  Every wait is bounded (tma_pipe.cuh).
+// One CTA computes a 128 (weight rows n) x BN (tokens m) tile of y^T, BN = 128, 256 or 512:
+//   * A operand = weights.  Eight dequant warps (two threads per row, one per 32-element half of
+//     a k-step) read the raw GGUF superblocks of the tile's 128 rows straight from global memory
+//     (L2-resident across the token tiles), rebuild the f32 weight with the reference's
+//     operation order (src/ml/gguf/dequant.cr), round it to bf16 and write a 128 x 64 K-major
+//     tile into shared memory in the 128-byte-swizzled canonical layout.
+//   * B operand = activations.  One thread issues TMA tile loads (bf16 [<= 256 x 64] boxes,
+//     128-byte swizzle) per k-step.
+//   * One thread issues tcgen05.mma (kind::f16, M = 128, N = min(BN, 256), K = 16) four times per
+//     k-step (eight for BN = 512: two accumulators of 256 columns fill the tensor memory), and
+//     tcgen05.commit releases the stage.
+//   * After the last k-step the dequant warps read the accumulator back with tcgen05.ld (each
+//     warp may read 32 TMEM lanes = 32 weight rows; the two warps of a lane quarter take half
+//     of the columns each) and store y[m, n]: for a fixed token a warp's 32 lanes write 32
+//     consecutive n, one 128-byte segment.
+// An mbarrier ring (four 48 KB stages, two 80 KB stages for BN = 512) decouples the three roles.
+// The dequant warps bound the kernel: wider token tiles do less dequant work per flop.  Every
+// wait is bounded (tma_pipe.cuh).
 #include <cuda.h>
 #include <cuda_bf16.h>
 
@@ -28,7 +33,8 @@ constexpr int kBM = 128;      // weight rows per tile (UMMA M)
 constexpr int kBK = 64;       // k elements per stage: 128 bytes of bf16 = one swizzle row
 // stages of the ring: four 48 KB stages for 256-token tiles, two 80 KB stages for 512-token tiles
 __host__ __device__ constexpr int stages_for(int bn) { return bn > 256 ? 2 : 4; }
-constexpr int kThreads = 192; // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: dequant + epilogue
+constexpr int kDequantWarps = 8;  // two threads per tile row, one per 32-element half of a k-step
+constexpr int kThreads = 64 + 32 * kDequantWarps;  // warp 0: TMA, warp 1: MMA + TMEM, then dequant + epilogue
 constexpr int kATile = kBM * kBK * 2;  // 16 KB
 
 struct GemmParams {
@@ -148,10 +154,11 @@ __device__ __forceinline__ void ldg_words_unaligned(const uint8_t *p, uint32_t (
 template <int TYPE> struct Raw;
 template <> struct Raw<kQ4_K> { uint4 hdr, q0, q1; };
 template <> struct Raw<kQ5_K> { uint4 hdr, h0, h1, q0, q1; };
-template <> struct Raw<kQ6_K> { uint32_t ql[16], qh[8], sc[2]; uint32_t d; };
+template <> struct Raw<kQ6_K> { uint32_t ql[8], qh[8], sc; uint32_t d; };
 
+// `h`: which 32-element half of the k-step this thread expands (Q6_K fetches only that half's ql)
 template <int TYPE>
-__device__ __forceinline__ void fetch_raw(const uint8_t *row, int ks, Raw<TYPE> &r) {
+__device__ __forceinline__ void fetch_raw(const uint8_t *row, int ks, int h, Raw<TYPE> &r) {
   const uint8_t *blk = row + (size_t)(ks >> 2) * BlockGeom<TYPE>::bytes;
   const int j = ks & 3;
   if constexpr (TYPE == kQ4_K) {
@@ -166,9 +173,11 @@ __device__ __forceinline__ void fetch_raw(const uint8_t *row, int ks, Raw<TYPE> 
     r.q1 = __ldg(reinterpret_cast<const uint4 *>(blk + 64 + 32 * j));
   } else {
     const int n = j >> 1;
-    ldg_words_unaligned<16>(blk + 64 * n, r.ql);
+    ldg_words_unaligned<8>(blk + 64 * n + 32 * h, r.ql);
     ldg_words_unaligned<8>(blk + 128 + 32 * n, r.qh);
-    ldg_words_unaligned<2>(blk + 192 + 8 * n, r.sc);
+    uint32_t scw[1];
+    ldg_words_unaligned<1>(blk + 192 + 8 * n + 4 * (j & 1), scw);
+    r.sc = scw[0];
     r.d = __ldg(reinterpret_cast<const unsigned short *>(blk + 208));
   }
 }
@@ -189,17 +198,19 @@ __device__ __forceinline__ void scale_min_regs(const uint4 &h, int s, float &sc,
   mn = (float)b;
 }
 
-// Rebuilds the 64 weights of k-step ks of tile row r as bf16 and stores them swizzled.
+// Rebuilds half h (32 weights: chunks 4h .. 4h+3) of k-step ks of tile row r as bf16 and stores
+// them swizzled.
 template <int TYPE>
-__device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, uint8_t *tile, int r,
-                                             bool valid) {
+__device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, int h, uint8_t *tile,
+                                             int r, bool valid) {
   if (!valid) {
 #pragma unroll
-    for (int c = 0; c < 8; c++) store_chunk(tile, r, c, make_uint4(0, 0, 0, 0));
+    for (int c4 = 0; c4 < 4; c4++) store_chunk(tile, r, 4 * h + c4, make_uint4(0, 0, 0, 0));
     return;
   }
   const int j = ks & 3;
   if constexpr (TYPE == kQ4_K || TYPE == kQ5_K) {
+    // low nibbles (h = 0): sub-block 2j, high nibbles (h = 1): sub-block 2j+1
     const __half2 dd = *reinterpret_cast<const __half2 *>(&raw.hdr.x);
     const float d = __low2float(dd), dmin = __high2float(dd);
     const uint32_t qw[8] = {raw.q0.x, raw.q0.y, raw.q0.z, raw.q0.w,
@@ -209,51 +220,46 @@ __device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, uint8
       hw[0] = raw.h0.x; hw[1] = raw.h0.y; hw[2] = raw.h0.z; hw[3] = raw.h0.w;
       hw[4] = raw.h1.x; hw[5] = raw.h1.y; hw[6] = raw.h1.z; hw[7] = raw.h1.w;
     }
+    float sc, mn;
+    scale_min_regs(raw.hdr, 2 * j + h, sc, mn);
+    const float d1 = __fmul_rn(d, sc), m1 = __fmul_rn(dmin, mn);
 #pragma unroll
-    for (int half = 0; half < 2; half++) {       // low nibbles: sub-block 2j, high: 2j+1
-      float sc, mn;
-      scale_min_regs(raw.hdr, 2 * j + half, sc, mn);
-      const float d1 = __fmul_rn(d, sc), m1 = __fmul_rn(dmin, mn);
+    for (int c4 = 0; c4 < 4; c4++) {           // 8 elements: bytes 8*c4 .. 8*c4+7
+      uint32_t out[4];
 #pragma unroll
-      for (int c4 = 0; c4 < 4; c4++) {           // 8 elements: bytes 8*c4 .. 8*c4+7
-        uint32_t out[4];
-#pragma unroll
-        for (int w2 = 0; w2 < 2; w2++) {
-          uint32_t q = (qw[2 * c4 + w2] >> (4 * half)) & 0x0f0f0f0fu;
-          if constexpr (TYPE == kQ5_K)
-            q |= ((hw[2 * c4 + w2] >> (2 * j + half)) & 0x01010101u) << 4;
-          const float w0 = __fmaf_rn(d1, byte_f(q, 0), -m1), w1 = __fmaf_rn(d1, byte_f(q, 1), -m1);
-          const float w2f = __fmaf_rn(d1, byte_f(q, 2), -m1), w3 = __fmaf_rn(d1, byte_f(q, 3), -m1);
-          out[2 * w2] = pack_bf16(w0, w1);
-          out[2 * w2 + 1] = pack_bf16(w2f, w3);
-        }
-        store_chunk(tile, r, 4 * half + c4, make_uint4(out[0], out[1], out[2], out[3]));
+      for (int w2 = 0; w2 < 2; w2++) {
+        uint32_t q = (qw[2 * c4 + w2] >> (4 * h)) & 0x0f0f0f0fu;
+        if constexpr (TYPE == kQ5_K)
+          q |= ((hw[2 * c4 + w2] >> (2 * j + h)) & 0x01010101u) << 4;
+        const float w0 = __fmaf_rn(d1, byte_f(q, 0), -m1), w1 = __fmaf_rn(d1, byte_f(q, 1), -m1);
+        const float w2f = __fmaf_rn(d1, byte_f(q, 2), -m1), w3 = __fmaf_rn(d1, byte_f(q, 3), -m1);
+        out[2 * w2] = pack_bf16(w0, w1);
+        out[2 * w2 + 1] = pack_bf16(w2f, w3);
       }
+      store_chunk(tile, r, 4 * h + c4, make_uint4(out[0], out[1], out[2], out[3]));
     }
   } else {
+    // the k-step is elements 64*hi .. 64*hi+63 of the superblock's half n = j >> 1: two runs of 32,
+    // kk = 2*hi + h is this thread's; its quants are nibble hi of ql bytes 32*h .. 32*h+31 of the
+    // half and bits 2*kk, 2*kk+1 of the half's 32 qh bytes; scales l/16 + 2*kk of the half
     const float d = __half2float(__ushort_as_half((unsigned short)raw.d));
-    const int hi = j & 1;
+    const int hi = j & 1, kk = 2 * hi + h;
 #pragma unroll
-    for (int c = 0; c < 8; c++) {
-      const int kk = 2 * hi + (c >> 2);          // which of the four 32-element runs of the half
-      const int sidx = ((c & 3) >> 1) + 2 * kk;  // scale within the half: l/16 + 2*kk
-      // sidx >> 2 == hi for every chunk, sidx & 3 is a compile-time constant per chunk
-      const uint32_t scw = hi ? raw.sc[1] : raw.sc[0];
-      const int scb = (int)(int8_t)((scw >> (8 * ((((c & 3) >> 1) + 2 * (c >> 2)) & 3))) & 0xff);
-      (void)sidx;
+    for (int c4 = 0; c4 < 4; c4++) {
+      const int scb = (int)(int8_t)((raw.sc >> (8 * ((c4 >> 1) + 2 * h))) & 0xff);
       const float dsc = __fmul_rn(d, (float)scb);
       uint32_t out[4];
 #pragma unroll
       for (int w2 = 0; w2 < 2; w2++) {
-        const uint32_t qlw = raw.ql[8 * (c >> 2) + 2 * (c & 3) + w2];
-        const uint32_t qhw = raw.qh[2 * (c & 3) + w2];
+        const uint32_t qlw = raw.ql[2 * c4 + w2];
+        const uint32_t qhw = raw.qh[2 * c4 + w2];
         const uint32_t q = ((qlw >> (4 * hi)) & 0x0f0f0f0fu) | (((qhw >> (2 * kk)) & 0x03030303u) << 4);
         const float w0 = __fmul_rn(dsc, byte_f_m32(q, 0)), w1 = __fmul_rn(dsc, byte_f_m32(q, 1));
         const float w2f = __fmul_rn(dsc, byte_f_m32(q, 2)), w3 = __fmul_rn(dsc, byte_f_m32(q, 3));
         out[2 * w2] = pack_bf16(w0, w1);
         out[2 * w2 + 1] = pack_bf16(w2f, w3);
       }
-      store_chunk(tile, r, c, make_uint4(out[0], out[1], out[2], out[3]));
+      store_chunk(tile, r, 4 * h + c4, make_uint4(out[0], out[1], out[2], out[3]));
     }
   }
 }
@@ -280,7 +286,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; s++) {
-      mbar_init(smem_u32(&bars[s]), 4);                    // full_a: one arrive per dequant warp
+      mbar_init(smem_u32(&bars[s]), kDequantWarps);        // full_a: one arrive per dequant warp
       mbar_init(smem_u32(&bars[kStages + s]), 1);          // full_b: the TMA thread
       mbar_init(smem_u32(&bars[2 * kStages + s]), 1);      // empty: tcgen05.commit
     }
@@ -334,16 +340,17 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else {
     // ---------------------------------------------------------------- dequant producers
-    const int r = threadIdx.x - 64;                        // tile row 0..127
+    const int r = (threadIdx.x - 64) & 127;                // tile row 0..127
+    const int h = (threadIdx.x - 64) >> 7;                 // which half of every k-step
     const bool valid = n0 + r < p.n_out;
     const uint8_t *row = p.w + (long long)(valid ? n0 + r : 0) * p.row_bytes;
     Raw<TYPE> cur, nxt;
-    fetch_raw<TYPE>(row, 0, cur);
+    fetch_raw<TYPE>(row, 0, h, cur);
     for (int ks = 0; ks < nks; ks++) {
       const int s = ks % kStages;
-      if (ks + 1 < nks) fetch_raw<TYPE>(row, ks + 1, nxt);  // in flight while this k-step expands
+      if (ks + 1 < nks) fetch_raw<TYPE>(row, ks + 1, h, nxt);  // in flight while this k-step expands
       mbar_wait(smem_u32(&bars[2 * kStages + s]), ((ks / kStages) & 1) ^ 1);
-      expand_kstep<TYPE>(cur, ks, smem + s * kStageBytes, r, valid);
+      expand_kstep<TYPE>(cur, ks, h, smem + s * kStageBytes, r, valid);
       fence_async_smem();                                   // generic-proxy writes -> tensor core
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars[s]));
@@ -356,8 +363,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int q = warp & 3;                                // TMEM lane quarter this warp may read
     const int n = n0 + 32 * q + lane;
     const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16);
+    // the two warps of a lane quarter take one half of the token columns each
+    const int cbeg = ((warp - 2) >> 2) * (BN / 2);
 #pragma unroll 1
-    for (int c0 = 0; c0 < BN; c0 += 32) {
+    for (int c0 = cbeg; c0 < cbeg + BN / 2; c0 += 32) {
       uint32_t v[32];
       tmem_ld32(taddr + c0, v);
       tmem_ld_wait();

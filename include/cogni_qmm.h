@@ -56,6 +56,10 @@ const char *cogni_qmm_status_string(int status);
 /* Diagnostics (no counterpart in the reference).
  * cogni_qmm_set_kernel_choice: 0 = automatic (tiled tensor-core GEMV where the shape allows it,
  * the default), 1 = always the general row-per-warp GEMV; process-wide, for A/B checks.
+ * Further codes select timing modes and tile shapes of the tiled kernels: 16-21 (16 = normal,
+ * others stream / decode only, with or without the weight copies: results invalid), 24-26
+ * superblocks per GEMV work item (automatic / 1 / 2), 32-47 raw diagnostic bits (results
+ * invalid), 48-51 prefill token-tile width (automatic / 128 / 256 / 512).
  * cogni_qmm_wait_timeouts: how many bounded device-side waits have expired since the library
  * was loaded (0 in a healthy process; a non-zero value means the results of some launch are
  * invalid).  Synchronises the device. */
