@@ -4,7 +4,8 @@
 //
 // One CTA computes a 128 (weight rows n) x BN (tokens m) tile of y^T, BN = 128, 256 or 512:
 //   * A operand = weights.  Eight dequant warps (two threads per row, one per 32-element half of
-//     a k-step) read the raw GGUF superblocks of the tile's 128 rows straight from global memory
+//     a k-step; four warps, one thread per row, for Q6_K) read the raw GGUF superblocks of the
+//     tile's 128 rows straight from global memory
 //     (L2-resident across the token tiles), rebuild the f32 weight with the reference's
 //     operation order (src/ml/gguf/dequant.cr), round it to bf16 and write a 128 x 64 K-major
 //     tile into shared memory in the 128-byte-swizzled canonical layout.
@@ -33,8 +34,11 @@ constexpr int kBM = 128;      // weight rows per tile (UMMA M)
 constexpr int kBK = 64;       // k elements per stage: 128 bytes of bf16 = one swizzle row
 // stages of the ring: four 48 KB stages for 256-token tiles, two 80 KB stages for 512-token tiles
 __host__ __device__ constexpr int stages_for(int bn) { return bn > 256 ? 2 : 4; }
-constexpr int kDequantWarps = 8;  // two threads per tile row, one per 32-element half of a k-step
-constexpr int kThreads = 64 + 32 * kDequantWarps;  // warp 0: TMA, warp 1: MMA + TMEM, then dequant + epilogue
+// Dequant warps: eight (two threads per tile row, one per 32-element half of a k-step) where the
+// expansion arithmetic bounds the kernel (Q4_K, Q5_K); four (one thread per row, both halves) for
+// Q6_K, whose two halves share the qh bytes and whose loads are the bound (measured both ways).
+__host__ __device__ constexpr int dequant_warps(int type) { return type == kQ6_K ? 4 : 8; }
+__host__ __device__ constexpr int threads_for(int type) { return 64 + 32 * dequant_warps(type); }  // warp 0: TMA, warp 1: MMA + TMEM
 constexpr int kATile = kBM * kBK * 2;  // 16 KB
 
 struct GemmParams {
@@ -156,8 +160,10 @@ template <> struct Raw<kQ4_K> { uint4 hdr, q0, q1; };
 template <> struct Raw<kQ5_K> { uint4 hdr, h0, h1, q0, q1; };
 template <> struct Raw<kQ6_K> { uint32_t ql[8], qh[8], sc; uint32_t d; };
 
-// `h`: which 32-element half of the k-step this thread expands (Q6_K fetches only that half's ql)
-template <int TYPE>
+// `h`: which 32-element half of the k-step this thread expands (Q6_K fetches only that half's ql).
+// SHARED_TOO = false skips what both halves of a Q6_K k-step share (qh, d): a thread that expands
+// both halves copies them from its first half.
+template <int TYPE, bool SHARED_TOO = true>
 __device__ __forceinline__ void fetch_raw(const uint8_t *row, int ks, int h, Raw<TYPE> &r) {
   const uint8_t *blk = row + (size_t)(ks >> 2) * BlockGeom<TYPE>::bytes;
   const int j = ks & 3;
@@ -174,11 +180,13 @@ __device__ __forceinline__ void fetch_raw(const uint8_t *row, int ks, int h, Raw
   } else {
     const int n = j >> 1;
     ldg_words_unaligned<8>(blk + 64 * n + 32 * h, r.ql);
-    ldg_words_unaligned<8>(blk + 128 + 32 * n, r.qh);
-    uint32_t scw[1];
-    ldg_words_unaligned<1>(blk + 192 + 8 * n + 4 * (j & 1), scw);
-    r.sc = scw[0];
-    r.d = __ldg(reinterpret_cast<const unsigned short *>(blk + 208));
+    if constexpr (SHARED_TOO) {
+      ldg_words_unaligned<8>(blk + 128 + 32 * n, r.qh);
+      uint32_t scw[1];
+      ldg_words_unaligned<1>(blk + 192 + 8 * n + 4 * (j & 1), scw);
+      r.sc = scw[0];
+      r.d = __ldg(reinterpret_cast<const unsigned short *>(blk + 208));
+    }
   }
 }
 
@@ -266,9 +274,10 @@ __device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, int h
 
 // ---------------------------------------------------------------------------- the kernel
 template <int TYPE, int BN>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(threads_for(TYPE), 1)
     gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
   constexpr int kStages = stages_for(BN);
+  constexpr int kDequantWarps = dequant_warps(TYPE), kHalves = 8 / kDequantWarps;  // halves per thread
   constexpr int kBTile = BN * kBK * 2;
   constexpr int kStageBytes = kATile + kBTile;
   // UMMA N is at most 256: a 512-token tile is two accumulators of 256 TMEM columns, fed by the
@@ -341,20 +350,37 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else {
     // ---------------------------------------------------------------- dequant producers
     const int r = (threadIdx.x - 64) & 127;                // tile row 0..127
-    const int h = (threadIdx.x - 64) >> 7;                 // which half of every k-step
+    const int h0 = (threadIdx.x - 64) >> 7;                // first (or only) half of every k-step
     const bool valid = n0 + r < p.n_out;
     const uint8_t *row = p.w + (long long)(valid ? n0 + r : 0) * p.row_bytes;
-    Raw<TYPE> cur, nxt;
-    fetch_raw<TYPE>(row, 0, h, cur);
+    Raw<TYPE> cur[kHalves], nxt[kHalves];
+    auto fetch_all = [&](int ks, Raw<TYPE>(&dst)[kHalves]) {
+      fetch_raw<TYPE>(row, ks, h0, dst[0]);
+      if constexpr (kHalves == 2) {
+        if constexpr (TYPE == kQ6_K) {
+          fetch_raw<TYPE, false>(row, ks, 1, dst[1]);
+#pragma unroll
+          for (int w = 0; w < 8; w++) dst[1].qh[w] = dst[0].qh[w];
+          dst[1].sc = dst[0].sc;
+          dst[1].d = dst[0].d;
+        } else {
+          dst[1] = dst[0];  // Q4_K / Q5_K: both halves read the same bytes
+        }
+      }
+    };
+    fetch_all(0, cur);
     for (int ks = 0; ks < nks; ks++) {
       const int s = ks % kStages;
-      if (ks + 1 < nks) fetch_raw<TYPE>(row, ks + 1, h, nxt);  // in flight while this k-step expands
+      if (ks + 1 < nks) fetch_all(ks + 1, nxt);             // in flight while this k-step expands
       mbar_wait(smem_u32(&bars[2 * kStages + s]), ((ks / kStages) & 1) ^ 1);
-      expand_kstep<TYPE>(cur, ks, h, smem + s * kStageBytes, r, valid);
+#pragma unroll
+      for (int i = 0; i < kHalves; i++)
+        expand_kstep<TYPE>(cur[i], ks, h0 + i, smem + s * kStageBytes, r, valid);
       fence_async_smem();                                   // generic-proxy writes -> tensor core
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars[s]));
-      cur = nxt;
+#pragma unroll
+      for (int i = 0; i < kHalves; i++) cur[i] = nxt[i];
     }
 
     // ---------------------------------------------------------------- epilogue
@@ -363,10 +389,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int q = warp & 3;                                // TMEM lane quarter this warp may read
     const int n = n0 + 32 * q + lane;
     const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16);
-    // the two warps of a lane quarter take one half of the token columns each
-    const int cbeg = ((warp - 2) >> 2) * (BN / 2);
+    // with eight warps the two of a lane quarter take one half of the token columns each
+    constexpr int kCols = BN / (kDequantWarps / 4);
+    const int cbeg = ((warp - 2) >> 2) * kCols;
 #pragma unroll 1
-    for (int c0 = cbeg; c0 < cbeg + BN / 2; c0 += 32) {
+    for (int c0 = cbeg; c0 < cbeg + kCols; c0 += 32) {
       uint32_t v[32];
       tmem_ld32(taddr + c0, v);
       tmem_ld_wait();
@@ -442,7 +469,7 @@ int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows
   p.out_bf16 = out_type == COGNI_QMM_OUT_BF16;
   p.row_bytes = (long long)(k_in / 256) * BlockGeom<TYPE>::bytes;
   dim3 grid((n_out + kBM - 1) / kBM, (m_rows + BN - 1) / BN);
-  gemm_prefill_kernel<TYPE, BN><<<grid, kThreads, smem, s>>>(tmap, p);
+  gemm_prefill_kernel<TYPE, BN><<<grid, threads_for(TYPE), smem, s>>>(tmap, p);
   return (int)cudaGetLastError();
 }
 
