@@ -153,6 +153,36 @@ __device__ __forceinline__ void ldg_words_unaligned(const uint8_t *p, uint32_t (
     prev = next;
   }
 }
+// Eight 32-bit words (32 bytes) starting at a 2-byte aligned global address, fetched as three
+// 16-byte vectors from the 16-byte boundary below it: the rows of a tile are kilobytes apart, so
+// every lane's load is its own L1 wavefront whatever its width, and 4-byte loads would cost four
+// times as many.  Reads at most 15 bytes beyond the 32 (still inside the 210-byte block for the
+// ql and qh fields this is used on).
+__device__ __forceinline__ void ldg_8words_wide(const uint8_t *p, uint32_t (&out)[8]) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  const uint4 *q = reinterpret_cast<const uint4 *>(a & ~(uintptr_t)15);
+  const uint4 v0 = __ldg(q), v1 = __ldg(q + 1), v2 = __ldg(q + 2);
+  const uint32_t w[12] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w, v2.x, v2.y, v2.z, v2.w};
+  const uint32_t sh = (uint32_t)(a & 2) * 8;
+  switch ((a & 15) >> 2) {  // word offset inside the first vector; the same for all rows of a tile
+    case 0:                 // whenever the row size is a multiple of 16 bytes
+#pragma unroll
+      for (int i = 0; i < 8; i++) out[i] = __funnelshift_r(w[i], w[i + 1], sh);
+      break;
+    case 1:
+#pragma unroll
+      for (int i = 0; i < 8; i++) out[i] = __funnelshift_r(w[i + 1], w[i + 2], sh);
+      break;
+    case 2:
+#pragma unroll
+      for (int i = 0; i < 8; i++) out[i] = __funnelshift_r(w[i + 2], w[i + 3], sh);
+      break;
+    default:
+#pragma unroll
+      for (int i = 0; i < 8; i++) out[i] = __funnelshift_r(w[i + 3], w[i + 4], sh);
+      break;
+  }
+}
 
 // The raw bytes one thread needs to rebuild 64 consecutive weights (one k-step) of its row.
 template <int TYPE> struct Raw;
@@ -179,9 +209,9 @@ __device__ __forceinline__ void fetch_raw(const uint8_t *row, int ks, int h, Raw
     r.q1 = __ldg(reinterpret_cast<const uint4 *>(blk + 64 + 32 * j));
   } else {
     const int n = j >> 1;
-    ldg_words_unaligned<8>(blk + 64 * n + 32 * h, r.ql);
+    ldg_8words_wide(blk + 64 * n + 32 * h, r.ql);
     if constexpr (SHARED_TOO) {
-      ldg_words_unaligned<8>(blk + 128 + 32 * n, r.qh);
+      ldg_8words_wide(blk + 128 + 32 * n, r.qh);
       uint32_t scw[1];
       ldg_words_unaligned<1>(blk + 192 + 8 * n + 4 * (j & 1), scw);
       r.sc = scw[0];
