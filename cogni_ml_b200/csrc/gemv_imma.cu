@@ -1,4 +1,4 @@
-// Decode GEMV for batch 1-2, Q4_K / Q5_K / Q6_K straight from the raw GGUF superblocks (sm_100a):
+// Decode GEMV for batch 1-2, Q4_K / Q5_K / Q6_K / Q8_0 straight from the raw GGUF blocks (sm_100a):
 // bulk-async staging + integer tensor-core MMAs on the raw quants.
 //
 // The kernel is HBM-bound; at 6.5 TB/s an SM has about three issue slots per weight, and the
@@ -77,6 +77,13 @@ template <> struct Cfg<kQ5_K> {
   static constexpr int RS = stage_row_stride(BB, KB, false);
   static constexpr bool HAS_MIN = true;
 };
+// Q8_0: eight 34-byte blocks (fp16 d + 32 int8) are treated as one 272-byte superblock of eight
+// scale groups; rows and superblocks are 16-byte aligned, the quants of a block 2 bytes off.
+template <> struct Cfg<kQ8_0> {
+  static constexpr int BB = 272, KB = 8, NG = 8, GROUP = 32;
+  static constexpr int RS = stage_row_stride(BB, KB, false);
+  static constexpr bool HAS_MIN = false;
+};
 template <> struct Cfg<kQ6_K> {
   static constexpr int BB = 210, KB = 8, NG = 16, GROUP = 16;
   static constexpr int RS = stage_row_stride(BB, KB, true);
@@ -148,6 +155,23 @@ __device__ __forceinline__ void imma_acc(int (&d)[4], uint32_t a0, uint32_t a1, 
       : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// s8 x s8 variants (Q8_0 quants are signed)
+__device__ __forceinline__ void imma_s8_zero(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                             uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%10,%10,%10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+__device__ __forceinline__ void imma_s8_acc(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                            uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 // scale * (byte i of v), exactly rounded once: 0x4B0000bb is the float 2^23 + b, and
 // fma(2^23 + b, scale, -2^23 * scale) = b * scale (the product 2^23 * scale is exact).
 __device__ __forceinline__ float byte_times(uint32_t v, int i, float scale, float scale_2p23) {
@@ -185,7 +209,7 @@ __device__ __forceinline__ int xq_word_offset(int e_in /*element within superblo
 // Area of one warp: per batch row 16 tile rows of AREA_ROW floats.  Row r holds d*sc*sx of the
 // superblock's scale groups, ordered so that an MMA lane fetches the ones of its group slot `sub`
 // with vector loads, then the row's correction term at index NG:
-//   Q4_K/Q5_K  index 4*sub + g4                group 2*g4 + sub
+//   Q4_K/Q5_K/Q8_0  index 4*sub + g4           group 2*g4 + sub
 //   Q6_K       index 8*sub + 4*n + 2*h + m     group 8*n + h + 2*sub + 4*m
 template <int TYPE> struct Area {
   static constexpr int ROW = Cfg<TYPE>::NG + 4;  // 12 / 20 floats: rows stay 16-byte aligned
@@ -214,13 +238,19 @@ __device__ __forceinline__ void decode_scales(const uint8_t *blk_row, int lane, 
     d = __low2float(dd);
     dmin = __high2float(dd);
     u0 = h.y; u1 = h.z; u2 = h.w;
-  } else {
+  } else if constexpr (TYPE == kQ6_K) {
     d = load_half_as_float(blk_row + 208);
   }
 #pragma unroll
   for (int half = 0; half < 2; half++) {
     float dsc[NH], kk[NH];
-    if constexpr (C::HAS_MIN) {
+    if constexpr (TYPE == kQ8_0) {  // the eight blocks' own fp16 scales; no minimum, no offset
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        dsc[i] = load_half_as_float(blk_row + 34 * (4 * half + i));
+        kk[i] = 0.f;
+      }
+    } else if constexpr (C::HAS_MIN) {
       // four 6-bit scales / mins of this half as bytes (dequant.cr:240-249, four at a time)
       const uint32_t scw = half ? ((u2 & 0x0f0f0f0fu) | ((u0 >> 2) & 0x30303030u)) : (u0 & 0x3f3f3f3fu);
       const uint32_t mnw = half ? (((u2 >> 4) & 0x0f0f0f0fu) | ((u1 >> 2) & 0x30303030u)) : (u1 & 0x3f3f3f3fu);
@@ -259,7 +289,7 @@ __device__ __forceinline__ void decode_scales(const uint8_t *blk_row, int lane, 
         v[i] = dsc[i] * sxv[i * NB + b];
         corr[b] = fmaf(kk[i], xxv[i * NB + b], corr[b]);
       }
-      if constexpr (C::HAS_MIN) {  // groups 4*half + i: g4 = 2*half + (i >> 1), sub = i & 1
+      if constexpr (C::NG == 8) {  // groups 4*half + i: g4 = 2*half + (i >> 1), sub = i & 1
         *reinterpret_cast<float2 *>(row + 2 * half) = make_float2(v[0], v[2]);
         *reinterpret_cast<float2 *>(row + 4 + 2 * half) = make_float2(v[1], v[3]);
       } else {  // groups 8*half + i: n = half, h = i & 1, sub = (i >> 1) & 1, m = i >> 2
@@ -269,7 +299,7 @@ __device__ __forceinline__ void decode_scales(const uint8_t *blk_row, int lane, 
     }
   }
 #pragma unroll
-  for (int b = 0; b < NB; b++) rows[b * A::BATCH + C::NG] = C::HAS_MIN ? corr[b] : -32.f * corr[b];
+  for (int b = 0; b < NB; b++) rows[b * A::BATCH + C::NG] = TYPE == kQ6_K ? -32.f * corr[b] : corr[b];
 }
 
 // Single-superblock items: lanes (r = lane & 15, half = lane >> 4) decode one half of the scale
@@ -282,7 +312,13 @@ __device__ __forceinline__ void decode_scales_half(const uint8_t *blk_row, int l
   constexpr int NH = C::NG / 2;  // groups per lane
   const int r = lane & 15, half = lane >> 4;
   float dsc[NH], kk[NH];
-  if constexpr (C::HAS_MIN) {
+  if constexpr (TYPE == kQ8_0) {  // the blocks' own fp16 scales; no minimum, no offset
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      dsc[i] = load_half_as_float(blk_row + 34 * (4 * half + i));
+      kk[i] = 0.f;
+    }
+  } else if constexpr (C::HAS_MIN) {
     const uint4 h = *reinterpret_cast<const uint4 *>(blk_row);
     const __half2 dd = *reinterpret_cast<const __half2 *>(&h.x);
     const float d = __low2float(dd), dmin = __high2float(dd);
@@ -326,7 +362,7 @@ __device__ __forceinline__ void decode_scales_half(const uint8_t *blk_row, int l
       v[i] = dsc[i] * sxv[i * NB + b];
       corr = fmaf(kk[i], xxv[i * NB + b], corr);
     }
-    if constexpr (C::HAS_MIN) {  // lane's groups 4*half + i: g4 = 2*half + (i >> 1), sub = i & 1
+    if constexpr (C::NG == 8) {  // lane's groups 4*half + i: g4 = 2*half + (i >> 1), sub = i & 1
       *reinterpret_cast<float2 *>(row + 2 * half) = make_float2(v[0], v[2]);
       *reinterpret_cast<float2 *>(row + 4 + 2 * half) = make_float2(v[1], v[3]);
     } else {  // lane's groups 8*half + i: n = half, h = i & 1, sub = (i >> 1) & 1, m = i >> 2
@@ -334,7 +370,7 @@ __device__ __forceinline__ void decode_scales_half(const uint8_t *blk_row, int l
       *reinterpret_cast<float4 *>(row + 8 + 4 * half) = make_float4(v[2], v[6], v[3], v[7]);
     }
     corr += __shfl_xor_sync(0xffffffffu, corr, 16);
-    if (half == 0) row[C::NG] = C::HAS_MIN ? corr : -32.f * corr;
+    if (half == 0) row[C::NG] = TYPE == kQ6_K ? -32.f * corr : corr;
   }
 }
 
@@ -400,7 +436,41 @@ __device__ __forceinline__ void mma_block(const uint8_t *blk, int pad_a, int pad
     acc0 += rowa[C::NG];
     acc1 += rowb[C::NG];
   }
-  if constexpr (C::HAS_MIN) {
+  if constexpr (TYPE == kQ8_0) {
+    // ra / rb are 8-byte aligned (superblocks and the stage's rows are 16-byte aligned).  The quants
+    // of block j start at 34*j + 2: 2 bytes past a word for even j (three words and two funnel
+    // shifts give this lane's 8 bytes), on a word for odd j.
+    const uint8_t *ra = blk + g * C::RS + 8 * t, *rb = blk + (g + 8) * C::RS + 8 * t;
+    const float4 sa4 = *reinterpret_cast<const float4 *>(rowa + 4 * sub);
+    const float4 sb4 = *reinterpret_cast<const float4 *>(rowb + 4 * sub);
+    const float sa[4] = {sa4.x, sa4.y, sa4.z, sa4.w}, sb[4] = {sb4.x, sb4.y, sb4.z, sb4.w};
+    auto even_block = [](const uint8_t *p, uint32_t &w0, uint32_t &w1) {  // p: the block's d
+      const uint32_t *q = reinterpret_cast<const uint32_t *>(p);
+      const uint32_t a = q[0], b = q[1], c = q[2];
+      w0 = __funnelshift_r(a, b, 16);
+      w1 = __funnelshift_r(b, c, 16);
+    };
+    auto odd_block = [](const uint8_t *p, uint32_t &w0, uint32_t &w1) {  // p: the block's quants
+      const uint32_t *q = reinterpret_cast<const uint32_t *>(p);
+      w0 = q[0];
+      w1 = q[1];
+    };
+#pragma unroll
+    for (int g4 = 0; g4 < 4; g4++) {
+      const uint4 bv = *reinterpret_cast<const uint4 *>(xu + g4 * UNIT_BYTES);
+      uint32_t la0, la1, ha0, ha1, lb0, lb1, hb0, hb1;
+      even_block(ra + 68 * g4, la0, la1);
+      odd_block(ra + 68 * g4 + 36, ha0, ha1);
+      even_block(rb + 68 * g4, lb0, lb1);
+      odd_block(rb + 68 * g4 + 36, hb0, hb1);
+      int cc[4];
+      // k-slots 0..15: block 2*g4, 16..31: block 2*g4+1
+      imma_s8_zero(cc, la0, lb0, ha0, hb0, bv.x, bv.y);
+      imma_s8_acc(cc, la1, lb1, ha1, hb1, bv.z, bv.w);
+      acc0 = fmaf(sa[g4], (float)(cc[0] * 128 + cc[1]), acc0);
+      acc1 = fmaf(sb[g4], (float)(cc[2] * 128 + cc[3]), acc1);
+    }
+  } else if constexpr (C::HAS_MIN) {
     constexpr bool Q5 = TYPE == kQ5_K;
     constexpr int QOFF = Q5 ? 48 : 16;
     constexpr uint32_t M1 = 0x10101010u;
@@ -947,7 +1017,7 @@ void gemv_imma_set_debug(int mode) { g_imma_debug = mode; }
 void gemv_imma_set_pair(int pair) { g_imma_force_pair = pair; }
 
 bool gemv_imma_supports(int type, const void *d_w, const float *d_x, int in_dim, int batch) {
-  if (type != kQ4_K && type != kQ5_K && type != kQ6_K) return false;
+  if (type != kQ8_0 && type != kQ4_K && type != kQ5_K && type != kQ6_K) return false;
   if (batch < 1 || batch > 2) return false;
   if ((reinterpret_cast<uintptr_t>(d_w) & 15) || (reinterpret_cast<uintptr_t>(d_x) & 15)) return false;
   if (in_dim % 256 != 0 || in_dim > 16384) return false;
@@ -957,6 +1027,7 @@ bool gemv_imma_supports(int type, const void *d_w, const float *d_x, int in_dim,
   switch (type) {
     case kQ4_K: return make_plan<kQ4_K>(in_dim, batch, p, smem);
     case kQ5_K: return make_plan<kQ5_K>(in_dim, batch, p, smem);
+    case kQ8_0: return make_plan<kQ8_0>(in_dim, batch, p, smem);
     default: return make_plan<kQ6_K>(in_dim, batch, p, smem);
   }
 }
@@ -967,6 +1038,7 @@ int launch_gemv_imma_many(int type, int njobs, const void *const *d_w, const flo
   switch (type) {
     case kQ4_K: return gemv_typed<kQ4_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s);
     case kQ5_K: return gemv_typed<kQ5_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s);
+    case kQ8_0: return gemv_typed<kQ8_0>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s);
     case kQ6_K: return gemv_typed<kQ6_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s);
     default: return COGNI_QMM_ERR_TYPE;
   }
@@ -993,6 +1065,7 @@ int launch_gemv_top1_imma(int type, const void *d_w, const float *d_x, int in_di
   switch (type) {
     case kQ4_K: return gemv_typed<kQ4_K>(1, &d_w, d_x, nullptr, 0, nullptr, &out_dim, in_dim, batch, resident, &t, s);
     case kQ5_K: return gemv_typed<kQ5_K>(1, &d_w, d_x, nullptr, 0, nullptr, &out_dim, in_dim, batch, resident, &t, s);
+    case kQ8_0: return gemv_typed<kQ8_0>(1, &d_w, d_x, nullptr, 0, nullptr, &out_dim, in_dim, batch, resident, &t, s);
     case kQ6_K: return gemv_typed<kQ6_K>(1, &d_w, d_x, nullptr, 0, nullptr, &out_dim, in_dim, batch, resident, &t, s);
     default: return COGNI_QMM_ERR_TYPE;
   }

@@ -101,7 +101,7 @@ def test_config1_9b_ffn_gemv_batch1(cuda, oracle, qtype, out_dim, in_dim):
 
 
 @pytest.mark.parametrize("qtype,in_dim", [(Q4_K, 2048), (Q5_K, 1024), (Q6_K, 8192), (Q6_K, 1024),
-                                          (Q4_K, 256)])
+                                          (Q4_K, 256), (Q8_0, 2048), (Q8_0, 768)])
 @pytest.mark.parametrize("batch", [1, 2])
 def test_many_tiles_per_cta(cuda, oracle, qtype, in_dim, batch):
     """Tall weights: every persistent CTA walks ten or more row tiles, so the stage ring and the
