@@ -194,7 +194,7 @@ def measure_extras(dev, gate_h, down_h, peaks):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / reps
 
-    out = {"prefill": [], "lm_head": None}
+    out = {"prefill": [], "lm_head": None, "swiglu_down": None}
     tf_burst, tf_sust = peaks.get("bf16_tflops"), peaks.get("bf16_tflops_sustained")
     for qtype, raw, n, k in ((Q4_K, gate_h, FFN, HIDDEN), (Q6_K, down_h, HIDDEN, FFN)):
         dw = DeviceQuantWeight.upload(QuantWeight(raw, qtype, n, k), dev)
@@ -208,6 +208,27 @@ def measure_extras(dev, gate_h, down_h, peaks):
                                    "frac_of_measured_burst": tf / tf_burst if tf_burst else None,
                                    "frac_of_measured_sustained": tf / tf_sust if tf_sust else None})
         del dw
+    # ffn_down with the SwiGLU product fused into its activation pass, against the product written
+    # by a separate elementwise kernel and then the plain GEMV; four weight copies (165 MB) defeat L2
+    downs = [DeviceQuantWeight.upload(QuantWeight(down_h, Q6_K, HIDDEN, FFN), dev) for _ in range(4)]
+    gate_v = torch.from_numpy(synth.make_activation(1, FFN, seed=3, tensor_id=21)).to(dev)
+    up_v = torch.from_numpy(synth.make_activation(1, FFN, seed=3, tensor_id=22)).to(dev)
+    yv = torch.empty(1, HIDDEN, dtype=torch.float32, device=dev)
+    prod = torch.empty_like(gate_v)
+
+    def fused():
+        for d in downs:
+            d.gemv_swiglu(gate_v, up_v, out=yv)
+
+    def separate():
+        for d in downs:
+            torch.mul(torch.nn.functional.silu(gate_v), up_v, out=prod)
+            d.gemv(prod, out=yv)
+
+    out["swiglu_down"] = {"kernel": "Q6_K 4096x12288 b1: y = W (silu(gate) * up)",
+                          "fused_us": timed(fused, 20) * 1e3 / len(downs),
+                          "separate_us": timed(separate, 20) * 1e3 / len(downs)}
+    del downs
     vocab, hid = 151936, 5120
     head = DeviceQuantWeight.upload(
         QuantWeight(synth.make_weight(Q6_K, vocab, hid, seed=7, tensor_id=9), Q6_K, vocab, hid), dev)

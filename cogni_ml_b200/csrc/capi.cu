@@ -125,6 +125,27 @@ int cogni_qmm_gemv_resident(int type, const void *d_w, const float *d_x, const f
   return gemv_common(type, d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, 1, stream);
 }
 
+int cogni_qmm_gemv_swiglu(int type, const void *d_w, const float *d_gate, const float *d_up,
+                          const float *d_addend, int64_t addend_stride, float *d_y,
+                          float *d_x_scratch, int in_dim, int out_dim, int batch, int resident,
+                          void *stream) {
+  int st = check_gemv_args(type, d_w, d_gate, d_y, in_dim, out_dim, batch);
+  if (st) return st;
+  if (!d_up) return COGNI_QMM_ERR_ARG;
+  if (d_addend && addend_stride != 0 && addend_stride != out_dim) return COGNI_QMM_ERR_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (g_force_rowwarp == 0 && (reinterpret_cast<uintptr_t>(d_up) & 15) == 0 &&
+      gemv_imma_supports(type, d_w, d_gate, in_dim, batch))
+    return launch_gemv_swiglu_imma(type, d_w, d_gate, d_up, d_addend, addend_stride, d_y, in_dim,
+                                   out_dim, batch, resident, s);
+  // shapes the fused kernel does not take: form the product in the caller's scratch, then the GEMV
+  if (!d_x_scratch) return COGNI_QMM_ERR_SCRATCH;
+  st = launch_swiglu(d_gate, d_up, d_x_scratch, (int64_t)batch * in_dim, s);
+  if (st) return st;
+  return gemv_common(type, d_w, d_x_scratch, d_addend, addend_stride, d_y, in_dim, out_dim, batch, 0,
+                     stream);
+}
+
 int cogni_qmm_gemv_many(int type, int n_weights, const void *const *d_w, const float *d_x,
                         const float *const *d_addend, int64_t addend_stride, float *const *d_y,
                         const int *out_dims, int in_dim, int batch, int resident, void *stream) {

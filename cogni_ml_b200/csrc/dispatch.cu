@@ -42,6 +42,22 @@ int launch_gemv_top1(int type, const void *d_w, const float *d_x, int in_dim, in
                                   d_idx, d_val, d_key, s);
 }
 
+namespace {
+// out = silu(gate) * up, silu(v) = v / (1 + exp(-v)) in f32 (qwen35_cpu.cr:512-519, 1716-1717)
+__global__ void swiglu_kernel(const float *gate, const float *up, float *out, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    const float g = gate[i];
+    out[i] = g / (1.f + expf(-g)) * up[i];
+  }
+}
+}  // namespace
+
+int launch_swiglu(const float *d_gate, const float *d_up, float *d_out, int64_t n, cudaStream_t s) {
+  swiglu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(d_gate, d_up, d_out, n);
+  return (int)cudaGetLastError();
+}
+
 int launch_top1_unpack(const long long *d_keys, int batch, int32_t *d_idx, float *d_val,
                        cudaStream_t s) {
   top1_unpack_kernel<<<(batch + 127) / 128, 128, 0, s>>>(d_keys, batch, d_idx, d_val);

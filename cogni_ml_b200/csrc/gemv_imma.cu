@@ -101,6 +101,7 @@ struct Job {
 
 struct Params {
   const float *x;
+  const float *x_up;  // non-null: the activations are silu(x) * x_up (SwiGLU), formed while quantising
   long long addend_stride;
   int in_dim;
   int nblk, nchunks, stages;
@@ -529,8 +530,9 @@ __device__ __forceinline__ void mma_block(const uint8_t *blk, int pad_a, int pad
 // lane = 8 consecutive elements.  The superblocks' areas are zeroed first: their unused words are
 // the structural zeros of the layout.  All loads are issued before the first use.
 template <int TYPE, int NB, int NBLK>
-__device__ __forceinline__ void quantise_superblocks(const float *x, int K, int kblk, int lane,
-                                                     uint8_t *xq, float *SX, float *XX) {
+__device__ __forceinline__ void quantise_superblocks(const float *x, const float *x_up, int K,
+                                                     int kblk, int lane, uint8_t *xq, float *SX,
+                                                     float *XX) {
   using C = Cfg<TYPE>;
   constexpr int NCX = 4 * NB, UNIT_BYTES = NCX * 64;
   constexpr int LPG = C::GROUP / 8;  // lanes per scale group
@@ -544,9 +546,16 @@ __device__ __forceinline__ void quantise_superblocks(const float *x, int K, int 
   for (int q = 0; q < NBLK; q++)
 #pragma unroll
     for (int b = 0; b < NB; b++) {
-      const float *src = x + (long long)b * K + (kblk + q) * 256 + e_in;
-      v0[q][b] = __ldg(reinterpret_cast<const float4 *>(src));
-      v1[q][b] = __ldg(reinterpret_cast<const float4 *>(src + 4));
+      const long long off = (long long)b * K + (kblk + q) * 256 + e_in;
+      v0[q][b] = __ldg(reinterpret_cast<const float4 *>(x + off));
+      v1[q][b] = __ldg(reinterpret_cast<const float4 *>(x + off + 4));
+      if (x_up) {  // SwiGLU: silu(gate) * up in f32, silu(v) = v / (1 + exp(-v)) (qwen35_cpu.cr:512-519, 1716-1717)
+        const float4 u0 = __ldg(reinterpret_cast<const float4 *>(x_up + off));
+        const float4 u1 = __ldg(reinterpret_cast<const float4 *>(x_up + off + 4));
+        auto sw = [](float gte, float up) { return gte / (1.f + expf(-gte)) * up; };
+        v0[q][b] = make_float4(sw(v0[q][b].x, u0.x), sw(v0[q][b].y, u0.y), sw(v0[q][b].z, u0.z), sw(v0[q][b].w, u0.w));
+        v1[q][b] = make_float4(sw(v1[q][b].x, u1.x), sw(v1[q][b].y, u1.y), sw(v1[q][b].z, u1.z), sw(v1[q][b].w, u1.w));
+      }
     }
   __syncwarp();
 #pragma unroll
@@ -757,8 +766,8 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR) + kPW) * 32, 1)
       // The activations are quantised on the way: the warp that takes a superblock pair of the
       // CTA's first tile does x's two superblocks first; later tiles find them done.
       if (li == 0) {
-        if (PAIR == 2 && n2 == 2) quantise_superblocks<TYPE, NB, 2>(p.x, K, e0, lane, xq, SX, XX);
-        else quantise_superblocks<TYPE, NB, 1>(p.x, K, e0, lane, xq, SX, XX);
+        if (PAIR == 2 && n2 == 2) quantise_superblocks<TYPE, NB, 2>(p.x, p.x_up, K, e0, lane, xq, SX, XX);
+        else quantise_superblocks<TYPE, NB, 1>(p.x, p.x_up, K, e0, lane, xq, SX, XX);
         __syncwarp();
         if (lane == 0) st_release_shared(&xready[e], 1);
       } else {
@@ -974,13 +983,14 @@ int launch_instance(const Params &p, size_t smem, int grid, cudaStream_t s) {
 template <int TYPE>
 int gemv_typed(int njobs, const void *const *d_w, const float *d_x, const float *const *d_addend,
                int64_t addend_stride, float *const *d_y, const int *out_dims, int in_dim, int batch,
-               int resident, const Params *top1, cudaStream_t s) {
+               int resident, const Params *top1, cudaStream_t s, const float *d_x_up = nullptr) {
   for (int j0 = 0; j0 < njobs; j0 += kMaxJobs) {
     const int nj = njobs - j0 < kMaxJobs ? njobs - j0 : kMaxJobs;
     Params p{};
     size_t smem = 0;
     if (!make_plan<TYPE>(in_dim, batch, p, smem)) return COGNI_QMM_ERR_LIMIT;
     p.x = d_x;
+    p.x_up = d_x_up;
     p.addend_stride = addend_stride;
     p.resident = resident;
     p.debug = g_imma_debug;
@@ -1049,6 +1059,20 @@ int launch_gemv_imma(int type, const void *d_w, const float *d_x, const float *d
                      int resident, cudaStream_t s) {
   return launch_gemv_imma_many(type, 1, &d_w, d_x, d_addend ? &d_addend : nullptr, addend_stride,
                                &d_y, &out_dim, in_dim, batch, resident, s);
+}
+
+// y = addend + W (silu(gate) * up): the SwiGLU product is formed while the activations are quantised
+int launch_gemv_swiglu_imma(int type, const void *d_w, const float *d_gate, const float *d_up,
+                            const float *d_addend, int64_t addend_stride, float *d_y, int in_dim,
+                            int out_dim, int batch, int resident, cudaStream_t s) {
+  const float *const *add = d_addend ? &d_addend : nullptr;
+  switch (type) {
+    case kQ4_K: return gemv_typed<kQ4_K>(1, &d_w, d_gate, add, addend_stride, &d_y, &out_dim, in_dim, batch, resident, nullptr, s, d_up);
+    case kQ5_K: return gemv_typed<kQ5_K>(1, &d_w, d_gate, add, addend_stride, &d_y, &out_dim, in_dim, batch, resident, nullptr, s, d_up);
+    case kQ6_K: return gemv_typed<kQ6_K>(1, &d_w, d_gate, add, addend_stride, &d_y, &out_dim, in_dim, batch, resident, nullptr, s, d_up);
+    case kQ8_0: return gemv_typed<kQ8_0>(1, &d_w, d_gate, add, addend_stride, &d_y, &out_dim, in_dim, batch, resident, nullptr, s, d_up);
+    default: return COGNI_QMM_ERR_TYPE;
+  }
 }
 
 int launch_gemv_top1_imma(int type, const void *d_w, const float *d_x, int in_dim, int out_dim,

@@ -118,6 +118,10 @@ void gemv_mma_set_debug(int mode);
 
 // Integer tensor-core GEMV for batch 1-2 (gemv_imma.cu): Q4_K / Q5_K / Q6_K.
 bool gemv_imma_supports(int type, const void *d_w, const float *d_x, int in_dim, int batch);
+int launch_gemv_swiglu_imma(int type, const void *d_w, const float *d_gate, const float *d_up,
+                            const float *d_addend, int64_t addend_stride, float *d_y, int in_dim,
+                            int out_dim, int batch, int resident, cudaStream_t s);
+int launch_swiglu(const float *d_gate, const float *d_up, float *d_out, int64_t n, cudaStream_t s);
 int launch_gemv_imma(int type, const void *d_w, const float *d_x, const float *d_addend,
                      int64_t addend_stride, float *d_y, int in_dim, int out_dim, int batch,
                      int resident, cudaStream_t s);

@@ -159,6 +159,30 @@ class DeviceQuantWeight:
               "cogni_qmm_gemv")
         return out
 
+    def gemv_swiglu(self, gate: torch.Tensor, up: torch.Tensor, out: Optional[torch.Tensor] = None,
+                    residual: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        """y[b, :] = residual[b, :] + W @ (silu(gate[b, :]) * up[b, :]): the FFN down projection with
+        the SwiGLU product fused in (qwen35_cpu.cr:1716-1718).  gate, up f32 [batch, in_dim]."""
+        for t in (gate, up):
+            if t.dtype != torch.float32 or not t.is_contiguous() or t.shape[-1] != self.in_dim:
+                raise ValueError("gate and up must be contiguous f32 [batch, in_dim]")
+        batch = gate.numel() // self.in_dim
+        if out is None:
+            out = torch.empty(batch, self.out_dim, dtype=torch.float32, device=gate.device)
+        # shapes the fused kernel does not take (and the diagnostic row-per-warp mode) need room
+        # for the product; the buffer is kept with the weight
+        scratch = getattr(self, "_swiglu_scratch", None)
+        if scratch is None or scratch.numel() < gate.numel() or scratch.device != gate.device:
+            scratch = self._swiglu_scratch = torch.empty(gate.numel(), dtype=torch.float32,
+                                                         device=gate.device)
+        check(lib.cogni_qmm_gemv_swiglu(self.type, self.raw.data_ptr(), gate.data_ptr(), up.data_ptr(),
+                                        residual.data_ptr() if residual is not None else None,
+                                        self.out_dim if residual is not None else 0, out.data_ptr(),
+                                        scratch.data_ptr(),
+                                        self.in_dim, self.out_dim, batch, 1 if self.resident else 0,
+                                        _stream_ptr(stream)), "cogni_qmm_gemv_swiglu")
+        return out
+
     def top1_scratch(self, batch: int) -> torch.Tensor:
         need = lib.cogni_qmm_gemv_top1_scratch_bytes(self.out_dim, batch)
         if self._top1_scratch is None or self._top1_scratch.numel() < need:

@@ -122,6 +122,22 @@ int cogni_qmm_gemv_resident(int type, const void *d_w, const float *d_x, const f
                             void *stream);
 
 /*
+ * The FFN down projection with the SwiGLU product fused into its activation pass:
+ *     y[b, o] = addend[b*addend_stride + o] + sum_k (silu(gate[b, k]) * up[b, k]) * dequant(W[o, k])
+ * with silu(v) = v / (1 + exp(-v)) in f32 (src/ml/gguf/qwen35_cpu.cr:512-519, 1716-1718; the
+ * reference's swiglu_probe kernel, src/ml/cuda/kernels/deltanet_step_probe.ptx:1076, followed by
+ * the down-projection GEMV).  gate and up are f32 [batch, in_dim] device buffers, 16-byte aligned.
+ * Where the tiled kernel takes the shape (batch <= 2, in_dim a multiple of 256) the product is
+ * formed while the activations are quantised and never written to memory; otherwise it is
+ * written to d_x_scratch (f32 [batch, in_dim], COGNI_QMM_ERR_SCRATCH if NULL) and the plain GEMV
+ * runs on that.  `resident` as in cogni_qmm_gemv_resident.
+ */
+int cogni_qmm_gemv_swiglu(int type, const void *d_w, const float *d_gate, const float *d_up,
+                          const float *d_addend, int64_t addend_stride, float *d_y,
+                          float *d_x_scratch, int in_dim, int out_dim, int batch, int resident,
+                          void *stream);
+
+/*
  * Several weight matrices of one type and in_dim against the SAME x in one launch:
  *     y_j[b, o] = addend_j[b*addend_stride + o] + sum_k x[b, k] * dequant(W_j[o, k])
  * Replaces Qwen35CPU.qmatvec_many (src/ml/gguf/qwen35_cpu.cr:1419-1490: qkv / gate / alpha / beta

@@ -102,6 +102,16 @@ struct DeviceQuantWeight {
              stream),
           "cogni_qmm_gemv");
   }
+  // y[b, :] = residual[b, :] + W (silu(gate[b, :]) * up[b, :]) (qwen35_cpu.cr:1716-1718);
+  // d_x_scratch (f32 [batch, in_dim]) is only needed for shapes the fused kernel does not take
+  void gemv_swiglu(const float *d_gate, const float *d_up, float *d_y, int batch,
+                   const float *d_residual = nullptr, float *d_x_scratch = nullptr,
+                   void *stream = nullptr) const {
+    check(cogni_qmm_gemv_swiglu(static_cast<int>(type), d_raw, d_gate, d_up, d_residual,
+                                d_residual ? out_dim : 0, d_y, d_x_scratch, in_dim, out_dim, batch,
+                                resident ? 1 : 0, stream),
+          "cogni_qmm_gemv_swiglu");
+  }
   // y[M, out_dim] = x_bf16[M, in_dim] W^T on the tensor cores
   void gemm_bf16(const void *d_x_bf16, void *d_y, int m_rows, int out_type = COGNI_QMM_OUT_F32,
                  void *stream = nullptr) const {

@@ -101,5 +101,17 @@ def top1(logits: np.ndarray):
     return idx.value, np.float32(val.value)
 
 
+def swiglu(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    """silu(gate) * up in f32 (qwen35_cpu.cr:512-519, 1716-1717)."""
+    g = np.ascontiguousarray(gate, dtype=np.float32).reshape(-1)
+    u = np.ascontiguousarray(up, dtype=np.float32).reshape(-1)
+    out = np.empty_like(g)
+    L = lib()
+    L.qmm_oracle_swiglu.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
+    L.qmm_oracle_swiglu.restype = None
+    L.qmm_oracle_swiglu(g.ctypes.data, u.ctypes.data, g.size, out.ctypes.data)
+    return out
+
+
 def max_threads() -> int:
     return lib().qmm_oracle_max_threads()

@@ -94,3 +94,11 @@ def matmul_add(x, rows, in_dim, w_raw, w_type, out_dim, bias) -> np.ndarray:
     x = np.asarray(x, dtype=np.float32).reshape(rows, in_dim).astype(np.float64)
     y = np.asarray(bias, dtype=np.float32).astype(np.float64)[None, :out_dim] + x @ w.T
     return y.astype(np.float32).reshape(-1)
+
+
+def swiglu(gate, up) -> np.ndarray:
+    """silu(gate) * up in f32, silu(v) = v / (1 + exp(-v)) (qwen35_cpu.cr:512-519, 1716-1717)."""
+    g = np.asarray(gate, dtype=np.float32)
+    u = np.asarray(up, dtype=np.float32)
+    s = g / (np.float32(1.0) + np.exp(-g, dtype=np.float32))
+    return (s * u).astype(np.float32)

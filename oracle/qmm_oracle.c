@@ -394,6 +394,15 @@ int qmm_oracle_matmul_add_mt(int type, const float *x, int rows, int in_dim,
                                      out_dim, threads);
 }
 
+/* src/ml/gguf/qwen35_cpu.cr:517-519 (silu) and :1716-1717 (combined = silu(gate) * up), f32 */
+void qmm_oracle_swiglu(const float *gate, const float *up, int64_t n, float *out) {
+  for (int64_t i = 0; i < n; i++) {
+    const float v = gate[i];
+    const float s = v / (1.0f + expf(-v));
+    out[i] = s * up[i];
+  }
+}
+
 void qmm_oracle_top1(const float *logits, int64_t n, int32_t *index, float *value) {
   /* qwen35_cpu.cr:2053-2055: maxv = logits.max; index of its first occurrence.
    * Equivalent to an ascending scan that replaces only on strict '>'. */

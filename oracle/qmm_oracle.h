@@ -73,6 +73,10 @@ int qmm_oracle_matmul_add_range(int type, const float *x, int rows, int in_dim,
  * lowest index wins ties). */
 void qmm_oracle_top1(const float *logits, int64_t n, int32_t *index, float *value);
 
+/* SwiGLU product of the FFN: out[i] = silu(gate[i]) * up[i], silu(v) = v / (1 + exp(-v)), all in
+ * f32 (src/ml/gguf/qwen35_cpu.cr:512-519 silu, :1716-1717 gate_ff * up_ff). */
+void qmm_oracle_swiglu(const float *gate, const float *up, int64_t n, float *out);
+
 int qmm_oracle_max_threads(void);
 
 #ifdef __cplusplus

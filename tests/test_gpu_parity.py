@@ -116,6 +116,38 @@ def test_many_tiles_per_cta(cuda, oracle, qtype, in_dim, batch):
     assert_close(y.ravel(), ref, f"type {qtype} {out_dim}x{in_dim} batch {batch}")
 
 
+@pytest.mark.parametrize("qtype,out_dim,in_dim,batch", [
+    (Q6_K, 4096, 12288, 1),   # the 9B ffn_down shape: fused path
+    (Q4_K, 512, 2048, 2), (Q8_0, 300, 1024, 1), (Q5_K, 257, 768, 2),
+    (Q6_K, 128, 1024, 5),     # batch the fused kernel does not take: product goes through scratch
+    (Q8_0, 64, 96, 1),        # in_dim not a multiple of 256: scratch path as well
+])
+def test_gemv_swiglu_fused_down_projection(cuda, oracle, qtype, out_dim, in_dim, batch):
+    """y = residual + W (silu(gate) * up) (qwen35_cpu.cr:1716-1718) against the CPU restatement:
+    SwiGLU product in f32, then QuantMatmul with the residual as the accumulator start."""
+    w = synth.make_weight(qtype, out_dim, in_dim, seed=31, tensor_id=qtype)
+    gate = synth.make_activation(batch, in_dim, seed=31, tensor_id=5) * np.float32(2.0)
+    up = synth.make_activation(batch, in_dim, seed=31, tensor_id=6)
+    res = synth.make_activation(batch, out_dim, seed=31, tensor_id=7)
+    dw = DeviceQuantWeight.upload(QuantWeight(w, qtype, out_dim, in_dim), cuda)
+    y = dw.gemv_swiglu(torch.from_numpy(gate).to(cuda), torch.from_numpy(up).to(cuda),
+                       residual=torch.from_numpy(res).to(cuda)).cpu().numpy()
+    comb = oracle.swiglu(gate, up).reshape(batch, in_dim)
+    ref = np.stack([oracle.matmul_add(comb[b], 1, in_dim, w, qtype, out_dim, res[b],
+                                      threads=oracle.max_threads()) for b in range(batch)])
+    assert_close(y, ref, f"swiglu type {qtype} {out_dim}x{in_dim} batch {batch}")
+
+
+def test_gemv_swiglu_needs_scratch_for_unfused_shapes(cuda, engine):
+    w = synth.make_weight(Q4_K, 64, 256, seed=3)
+    dw = DeviceQuantWeight.upload(QuantWeight(w, Q4_K, 64, 256), cuda)
+    g = torch.zeros(5, 256, device=cuda)
+    y = torch.empty(5, 64, device=cuda)
+    st = engine.lib.cogni_qmm_gemv_swiglu(Q4_K, dw.raw.data_ptr(), g.data_ptr(), g.data_ptr(), None, 0,
+                                          y.data_ptr(), None, 256, 64, 5, 0, None)
+    assert st == 1004  # COGNI_QMM_ERR_SCRATCH
+
+
 LAYER = [("q_proj", Q4_K, 4096, 4096), ("k_proj", Q4_K, 1024, 4096), ("v_proj", Q4_K, 1024, 4096),
          ("o_proj", Q4_K, 4096, 4096), ("ffn_gate", Q4_K, 12288, 4096),
          ("ffn_down", Q6_K, 4096, 12288), ("q5k_variant", Q5_K, 4096, 4096)]

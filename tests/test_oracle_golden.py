@@ -163,3 +163,20 @@ def test_top1_highest_value_lowest_index(oracle):
     assert oracle.top1(np.array([1.0, 5.0, 5.0, -2.0], np.float32)) == (1, np.float32(5.0))
     assert oracle.top1(np.array([-3.0, -3.0], np.float32)) == (0, np.float32(-3.0))
     assert oracle.top1(np.array([0.0, -0.0, 0.0], np.float32))[0] == 0
+
+
+def test_swiglu_restatements_agree_and_known_values():
+    """silu(v) = v / (1 + exp(-v)) (qwen35_cpu.cr:517-519): silu(0) = 0, silu(v) -> v for large v,
+    silu(-v) = -v * (1 - sigmoid(v)); C and numpy restatements agree to the last bit or ulp."""
+    from oracle import loader, oracle_np
+    g = np.array([0.0, 1.0, -1.0, 20.0, -20.0, 0.5, 88.0, -88.0], dtype=np.float32)
+    u = np.array([3.0, 2.0, 2.0, 1.0, 1.0, -4.0, 1.0, 1.0], dtype=np.float32)
+    c = loader.swiglu(g, u)
+    n = oracle_np.swiglu(g, u)
+    assert c[0] == 0.0 and abs(c[1] - 2.0 * 0.7310586) < 1e-6 and abs(c[2] + 2.0 * 0.26894143) < 1e-6
+    assert abs(c[3] - 20.0) < 1e-5 and abs(c[4]) < 1e-6 and c[6] == 88.0 and abs(c[7]) < 1e-30
+    assert np.allclose(c, n, rtol=3e-7, atol=1e-30)
+    rng = np.random.default_rng(0)
+    g = (rng.standard_normal(4096) * 4).astype(np.float32)
+    u = rng.standard_normal(4096).astype(np.float32)
+    assert np.allclose(loader.swiglu(g, u), oracle_np.swiglu(g, u), rtol=3e-7, atol=1e-12)
