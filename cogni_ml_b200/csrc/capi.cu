@@ -125,6 +125,16 @@ int cogni_qmm_gemv_resident(int type, const void *d_w, const float *d_x, const f
   return gemv_common(type, d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, 1, stream);
 }
 
+int cogni_qmm_embedding_lookup(int type, const void *d_table, int vocab, int n_embd,
+                               const int32_t *d_token_ids, int n_tokens, float *d_out,
+                               int32_t *d_status, void *stream) {
+  if (!supported(type)) return COGNI_QMM_ERR_TYPE;
+  if (!d_table || !d_token_ids || !d_out || vocab <= 0 || n_embd <= 0 || n_tokens < 0) return COGNI_QMM_ERR_ARG;
+  if (n_embd % cogni_qmm_block_elements(type) != 0) return COGNI_QMM_ERR_ARG;
+  return launch_embedding_rows(type, d_table, d_token_ids, n_tokens, vocab, n_embd, d_out, d_status,
+                               static_cast<cudaStream_t>(stream));
+}
+
 int cogni_qmm_gemv_swiglu(int type, const void *d_w, const float *d_gate, const float *d_up,
                           const float *d_addend, int64_t addend_stride, float *d_y,
                           float *d_x_scratch, int in_dim, int out_dim, int batch, int resident,

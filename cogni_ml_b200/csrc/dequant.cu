@@ -94,6 +94,44 @@ __global__ void __launch_bounds__(256) dequantize_blocks_kernel(const uint8_t *_
     expand_block<TYPE>(w + blk * BlockGeom<TYPE>::bytes, out + blk * BlockGeom<TYPE>::elems, lane);
 }
 
+// Token-embedding gather: out[t, :] = dequant(row token_ids[t] of the table), the same block
+// expansion as the bulk dequantiser (bit-exact against Dequant.dequantize of that row,
+// src/ml/gguf/qwen35_cpu.cr:3305-3332).  One warp per block of a token's row.  An id outside
+// [0, vocab) yields a row of zeros and raises *status to 1 + the index of such a token.
+template <int TYPE>
+__global__ void __launch_bounds__(256) embedding_rows_kernel(const uint8_t *__restrict__ table,
+                                                             const int32_t *__restrict__ token_ids,
+                                                             int n_tokens, int vocab, int blocks_per_row,
+                                                             float *__restrict__ out, int32_t *status) {
+  constexpr int BE = BlockGeom<TYPE>::elems, BB = BlockGeom<TYPE>::bytes;
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)n_tokens * blocks_per_row;
+  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long i = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < total; i += nwarps) {
+    const int t = (int)(i / blocks_per_row), blk = (int)(i - (long long)t * blocks_per_row);
+    const int id = token_ids[t];
+    float *y = out + ((long long)t * blocks_per_row + blk) * BE;
+    if (id < 0 || id >= vocab) {
+      for (int e = lane; e < BE; e += 32) y[e] = 0.f;
+      if (status && blk == 0 && lane == 0) atomicMax(status, t + 1);
+      continue;
+    }
+    expand_block<TYPE>(table + ((long long)id * blocks_per_row + blk) * BB, y, lane);
+  }
+}
+
+template <int TYPE>
+int run_embedding(const void *d_table, const int32_t *d_ids, int n_tokens, int vocab, int n_embd,
+                  float *d_out, int32_t *d_status, cudaStream_t s) {
+  const int bpr = n_embd / BlockGeom<TYPE>::elems;
+  const long long want = ((long long)n_tokens * bpr + 7) / 8;
+  if (want == 0) return COGNI_QMM_OK;
+  const int grid = (int)(want < 148LL * 16 ? want : 148LL * 16);
+  embedding_rows_kernel<TYPE><<<grid, 256, 0, s>>>(static_cast<const uint8_t *>(d_table), d_ids,
+                                                  n_tokens, vocab, bpr, d_out, d_status);
+  return (int)cudaGetLastError();
+}
+
 template <int TYPE>
 int run(const void *d_w, int64_t n, float *d_out, cudaStream_t s) {
   long long nblocks = n / BlockGeom<TYPE>::elems;
@@ -113,6 +151,17 @@ int launch_dequantize(int type, const void *d_w, int64_t n, float *d_out, cudaSt
     case kQ4_K: return run<kQ4_K>(d_w, n, d_out, s);
     case kQ5_K: return run<kQ5_K>(d_w, n, d_out, s);
     case kQ6_K: return run<kQ6_K>(d_w, n, d_out, s);
+    default: return COGNI_QMM_ERR_TYPE;
+  }
+}
+
+int launch_embedding_rows(int type, const void *d_table, const int32_t *d_ids, int n_tokens, int vocab,
+                          int n_embd, float *d_out, int32_t *d_status, cudaStream_t s) {
+  switch (type) {
+    case kQ8_0: return run_embedding<kQ8_0>(d_table, d_ids, n_tokens, vocab, n_embd, d_out, d_status, s);
+    case kQ4_K: return run_embedding<kQ4_K>(d_table, d_ids, n_tokens, vocab, n_embd, d_out, d_status, s);
+    case kQ5_K: return run_embedding<kQ5_K>(d_table, d_ids, n_tokens, vocab, n_embd, d_out, d_status, s);
+    case kQ6_K: return run_embedding<kQ6_K>(d_table, d_ids, n_tokens, vocab, n_embd, d_out, d_status, s);
     default: return COGNI_QMM_ERR_TYPE;
   }
 }

@@ -159,6 +159,27 @@ class DeviceQuantWeight:
               "cogni_qmm_gemv")
         return out
 
+    def embedding_lookup(self, token_ids: torch.Tensor, out: Optional[torch.Tensor] = None,
+                         check_range: bool = True, stream=None) -> torch.Tensor:
+        """Rows `token_ids` (int32 on the device) of this [vocab, n_embd] table as f32, bit-identical
+        to the CPU dequantiser (Qwen35CPU#embedding_lookup, qwen35_cpu.cr:3305-3332).  With
+        check_range an id outside the table raises like the reference (this synchronises)."""
+        if token_ids.dtype != torch.int32 or not token_ids.is_contiguous():
+            raise ValueError("token_ids must be a contiguous int32 tensor")
+        n = token_ids.numel()
+        if out is None:
+            out = torch.empty(n, self.in_dim, dtype=torch.float32, device=token_ids.device)
+        status = torch.zeros(1, dtype=torch.int32, device=token_ids.device) if check_range else None
+        check(lib.cogni_qmm_embedding_lookup(self.type, self.raw.data_ptr(), self.out_dim, self.in_dim,
+                                             token_ids.data_ptr(), n, out.data_ptr(),
+                                             status.data_ptr() if status is not None else None,
+                                             _stream_ptr(stream)), "cogni_qmm_embedding_lookup")
+        if status is not None:
+            bad = int(status.item())
+            if bad:
+                raise IndexError(f"embedding: token_id {int(token_ids.view(-1)[bad - 1])} out of range")
+        return out
+
     def gemv_swiglu(self, gate: torch.Tensor, up: torch.Tensor, out: Optional[torch.Tensor] = None,
                     residual: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
         """y[b, :] = residual[b, :] + W @ (silu(gate[b, :]) * up[b, :]): the FFN down projection with

@@ -122,6 +122,22 @@ int cogni_qmm_gemv_resident(int type, const void *d_w, const float *d_x, const f
                             void *stream);
 
 /*
+ * Token-embedding gather from the quantized table (one of the steps next to the matmul path):
+ *     out[t, :] = dequant(row d_token_ids[t] of the [vocab, n_embd] table),  f32 [n_tokens, n_embd]
+ * bit-identical to Dequant.dequantize of that row, as Qwen35CPU#embedding_lookup does
+ * (src/ml/gguf/qwen35_cpu.cr:3305-3332); replaces embed_q4k_f32_from_token_id_cuda
+ * (src/ml/cuda/kernels/embed_q4k_probe.ptx:5) and the Metal embedding_q4k/q6k_from_token_id
+ * (src/ml/gguf/qwen35_metal.cr:848-900) for all four types.  d_token_ids is a device array of
+ * int32, e.g. the top_index written by cogni_qmm_gemv_top1, so that argmax -> next embedding stays
+ * on the device.  The reference raises for an id outside [0, vocab); here such a row is filled with
+ * zeros and, if d_status is not NULL, *d_status (device int32, zeroed by the caller) is raised to
+ * 1 + the index of such a token.  n_embd must be a multiple of the block size.
+ */
+int cogni_qmm_embedding_lookup(int type, const void *d_table, int vocab, int n_embd,
+                               const int32_t *d_token_ids, int n_tokens, float *d_out,
+                               int32_t *d_status, void *stream);
+
+/*
  * The FFN down projection with the SwiGLU product fused into its activation pass:
  *     y[b, o] = addend[b*addend_stride + o] + sum_k (silu(gate[b, k]) * up[b, k]) * dequant(W[o, k])
  * with silu(v) = v / (1 + exp(-v)) in f32 (src/ml/gguf/qwen35_cpu.cr:512-519, 1716-1718; the

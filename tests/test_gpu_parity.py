@@ -148,6 +148,46 @@ def test_gemv_swiglu_needs_scratch_for_unfused_shapes(cuda, engine):
     assert st == 1004  # COGNI_QMM_ERR_SCRATCH
 
 
+@pytest.mark.parametrize("qtype", ALL_TYPES)
+def test_embedding_lookup_bit_exact_and_range_check(cuda, oracle, qtype):
+    """Rows of a quantized [vocab, n_embd] table by device-resident token ids, bit-identical to the
+    CPU dequantiser on the row slice (Qwen35CPU#embedding_lookup, qwen35_cpu.cr:3305-3332)."""
+    vocab, n_embd = 1000, 1024
+    w = synth.make_weight(qtype, vocab, n_embd, seed=17, tensor_id=qtype)
+    dw = DeviceQuantWeight.upload(QuantWeight(w, qtype, vocab, n_embd), cuda)
+    ids = np.array([0, 999, 17, 17, 512, 3], dtype=np.int32)
+    got = dw.embedding_lookup(torch.from_numpy(ids).to(cuda)).cpu().numpy()
+    rb = len(w) // vocab
+    for t, tid in enumerate(ids):
+        ref = oracle.dequantize(qtype, w[tid * rb:(tid + 1) * rb], n_embd)
+        assert np.array_equal(got[t].view(np.uint32), ref.view(np.uint32)), (t, tid)
+    with pytest.raises(IndexError):
+        dw.embedding_lookup(torch.tensor([5, vocab], dtype=torch.int32, device=cuda))
+    with pytest.raises(IndexError):
+        dw.embedding_lookup(torch.tensor([-1], dtype=torch.int32, device=cuda))
+    # without the check an id outside the table yields zeros, the others are unaffected
+    out = dw.embedding_lookup(torch.tensor([vocab + 7, 3], dtype=torch.int32, device=cuda),
+                              check_range=False).cpu().numpy()
+    assert not out[0].any() and np.array_equal(out[1], got[5])
+
+
+def test_top1_feeds_embedding_lookup_on_device(cuda, oracle):
+    """argmax -> next-token embedding without leaving the device: the int32 index the fused lm_head
+    writes is the token id the gather reads."""
+    vocab, hid = 4096, 1024
+    w = synth.make_weight(Q6_K, vocab, hid, seed=23, tensor_id=3)
+    dw = DeviceQuantWeight.upload(QuantWeight(w, Q6_K, vocab, hid), cuda)
+    x = synth.make_activation(1, hid, seed=23)
+    idx, _val = dw.gemv_top1(torch.from_numpy(x).to(cuda))
+    emb = dw.embedding_lookup(idx).cpu().numpy()
+    logits = oracle.matmul_add(x, 1, hid, w, Q6_K, vocab, np.zeros(vocab, np.float32),
+                               threads=oracle.max_threads())
+    tid, _ = oracle.top1(logits)
+    rb = len(w) // vocab
+    ref = oracle.dequantize(Q6_K, w[tid * rb:(tid + 1) * rb], hid)
+    assert int(idx.item()) == tid and np.array_equal(emb[0].view(np.uint32), ref.view(np.uint32))
+
+
 LAYER = [("q_proj", Q4_K, 4096, 4096), ("k_proj", Q4_K, 1024, 4096), ("v_proj", Q4_K, 1024, 4096),
          ("o_proj", Q4_K, 4096, 4096), ("ffn_gate", Q4_K, 12288, 4096),
          ("ffn_down", Q6_K, 4096, 12288), ("q5k_variant", Q5_K, 4096, 4096)]
