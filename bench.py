@@ -194,7 +194,7 @@ def measure_extras(dev, gate_h, down_h, peaks):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / reps
 
-    out = {"prefill": [], "lm_head": None, "swiglu_down": None}
+    out = {"prefill": [], "lm_head": None, "swiglu_down": None, "ffn_block_fused": None}
     tf_burst, tf_sust = peaks.get("bf16_tflops"), peaks.get("bf16_tflops_sustained")
     for qtype, raw, n, k in ((Q4_K, gate_h, FFN, HIDDEN), (Q6_K, down_h, HIDDEN, FFN)):
         dw = DeviceQuantWeight.upload(QuantWeight(raw, qtype, n, k), dev)
@@ -228,7 +228,26 @@ def measure_extras(dev, gate_h, down_h, peaks):
     out["swiglu_down"] = {"kernel": "Q6_K 4096x12288 b1: y = W (silu(gate) * up)",
                           "fused_us": timed(fused, 20) * 1e3 / len(downs),
                           "separate_us": timed(separate, 20) * 1e3 / len(downs)}
-    del downs
+    # a whole FFN block per layer in two launches: RMSNorm fused into ffn_gate + ffn_up, SwiGLU and
+    # the residual add fused into ffn_down; four layers of weights (390 MB) defeat L2
+    from cogni_ml_b200 import GemvMany
+    gates = [DeviceQuantWeight.upload(QuantWeight(gate_h, Q4_K, FFN, HIDDEN), dev) for _ in range(8)]
+    hidden = torch.from_numpy(synth.make_activation(1, HIDDEN, seed=5, tensor_id=31)).to(dev)
+    hidden2 = torch.empty_like(hidden)
+    norm_w = torch.ones(HIDDEN, dtype=torch.float32, device=dev)
+    g_out = torch.empty(1, FFN, dtype=torch.float32, device=dev)
+    u_out = torch.empty(1, FFN, dtype=torch.float32, device=dev)
+    calls = [GemvMany([gates[2 * i], gates[2 * i + 1]], hidden, [g_out, u_out], norm_weight=norm_w)
+             for i in range(4)]
+
+    def ffn_blocks():
+        for i in range(4):
+            calls[i].run()
+            downs[i].gemv_swiglu(g_out, u_out, out=hidden2, residual=hidden)
+
+    out["ffn_block_fused"] = {"kernel": "per layer: RMSNorm + ffn_gate/ffn_up (1 launch), SwiGLU + ffn_down + residual (1 launch), b1",
+                              "us_per_layer": timed(ffn_blocks, 20) * 1e3 / 4}
+    del downs, gates, calls
     vocab, hid = 151936, 5120
     head = DeviceQuantWeight.upload(
         QuantWeight(synth.make_weight(Q6_K, vocab, hid, seed=7, tensor_id=9), Q6_K, vocab, hid), dev)

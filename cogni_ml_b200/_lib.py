@@ -26,6 +26,7 @@ SIGNATURES = {
     "cogni_qmm_gemv": (_i, [_i, _vp, _vp, _vp, _i64, _vp, _i, _i, _i, _vp]),
     "cogni_qmm_gemv_resident": (_i, [_i, _vp, _vp, _vp, _i64, _vp, _i, _i, _i, _vp]),
     "cogni_qmm_gemv_many": (_i, [_i, _i, _vp, _vp, _vp, _i64, _vp, _vp, _i, _i, _i, _vp]),
+    "cogni_qmm_gemv_many_rmsnorm": (_i, [_i, _i, _vp, _vp, _vp, C.c_float, _vp, _i64, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "cogni_qmm_embedding_lookup": (_i, [_i, _vp, _i, _i, _vp, _i, _vp, _vp, _vp]),
     "cogni_qmm_gemv_swiglu": (_i, [_i, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i, _i, _i, _i, _vp]),
     "cogni_qmm_gemv_top1_scratch_bytes": (_sz, [_i, _i]),

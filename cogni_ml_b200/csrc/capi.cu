@@ -181,6 +181,33 @@ int cogni_qmm_gemv_many(int type, int n_weights, const void *const *d_w, const f
   return COGNI_QMM_OK;
 }
 
+int cogni_qmm_gemv_many_rmsnorm(int type, int n_weights, const void *const *d_w, const float *d_x,
+                                const float *d_norm_weight, float eps,
+                                const float *const *d_addend, int64_t addend_stride,
+                                float *const *d_y, const int *out_dims, float *d_x_scratch,
+                                int in_dim, int batch, int resident, void *stream) {
+  if (!supported(type)) return COGNI_QMM_ERR_TYPE;
+  if (n_weights <= 0 || !d_w || !d_y || !out_dims || !d_norm_weight) return COGNI_QMM_ERR_ARG;
+  bool tiled = g_force_rowwarp == 0 && (reinterpret_cast<uintptr_t>(d_norm_weight) & 15) == 0;
+  for (int j = 0; j < n_weights; j++) {
+    int st = check_gemv_args(type, d_w[j], d_x, d_y[j], in_dim, out_dims[j], batch);
+    if (st) return st;
+    if (d_addend && d_addend[j] && addend_stride != 0 && addend_stride != out_dims[j])
+      return COGNI_QMM_ERR_ARG;
+    tiled = tiled && gemv_imma_supports(type, d_w[j], d_x, in_dim, batch);
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (tiled && n_weights <= 32)
+    return launch_gemv_many_rmsnorm_imma(type, n_weights, d_w, d_x, d_norm_weight, eps, d_addend,
+                                         addend_stride, d_y, out_dims, in_dim, batch, resident, s);
+  // shapes the fused kernel does not take: normalise into the caller's scratch, then the GEMVs
+  if (!d_x_scratch) return COGNI_QMM_ERR_SCRATCH;
+  int st = launch_rmsnorm(d_x, d_norm_weight, eps, d_x_scratch, batch, in_dim, s);
+  if (st) return st;
+  return cogni_qmm_gemv_many(type, n_weights, d_w, d_x_scratch, d_addend, addend_stride, d_y, out_dims,
+                             in_dim, batch, 0, stream);
+}
+
 size_t cogni_qmm_gemv_top1_scratch_bytes(int out_dim, int batch) {
   if (out_dim <= 0 || batch <= 0) return 0;
   return top1_scratch_bytes(out_dim, batch);

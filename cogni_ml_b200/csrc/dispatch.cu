@@ -51,7 +51,35 @@ __global__ void swiglu_kernel(const float *gate, const float *up, float *out, in
     out[i] = g / (1.f + expf(-g)) * up[i];
   }
 }
+// out[r, :] = x[r, :] * (1 / sqrt(mean(x[r, :]^2) + eps)) * w, sum of squares in f64, the products
+// in f32 left to right (qwen35_cpu.cr:484-490, 1492-1504).  One CTA per row.
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const float *x, const float *w, float eps,
+                                                      float *out, int dim) {
+  __shared__ double s_ss[8];
+  __shared__ float s_inv;
+  const float *xr = x + (long long)blockIdx.x * dim;
+  double ss = 0.0;
+  for (int k = threadIdx.x; k < dim; k += blockDim.x) ss += (double)xr[k] * xr[k];
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if ((threadIdx.x & 31) == 0) s_ss[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int i = 0; i < 8; i++) t += s_ss[i];
+    s_inv = (float)(1.0 / sqrt(t / (double)dim + (double)eps));
+  }
+  __syncthreads();
+  const float r = s_inv;
+  for (int k = threadIdx.x; k < dim; k += blockDim.x)
+    out[(long long)blockIdx.x * dim + k] = xr[k] * r * w[k];
+}
 }  // namespace
+
+int launch_rmsnorm(const float *d_x, const float *d_w, float eps, float *d_out, int rows, int dim,
+                   cudaStream_t s) {
+  rmsnorm_kernel<<<rows, 256, 0, s>>>(d_x, d_w, eps, d_out, dim);
+  return (int)cudaGetLastError();
+}
 
 int launch_swiglu(const float *d_gate, const float *d_up, float *d_out, int64_t n, cudaStream_t s) {
   swiglu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(d_gate, d_up, d_out, n);

@@ -102,6 +102,8 @@ struct Job {
 struct Params {
   const float *x;
   const float *x_up;  // non-null: the activations are silu(x) * x_up (SwiGLU), formed while quantising
+  const float *norm_w;  // non-null: the activations are RMSNorm(x) * norm_w, normalised while quantising
+  float norm_eps;
   long long addend_stride;
   int in_dim;
   int nblk, nchunks, stages;
@@ -530,9 +532,10 @@ __device__ __forceinline__ void mma_block(const uint8_t *blk, int pad_a, int pad
 // lane = 8 consecutive elements.  The superblocks' areas are zeroed first: their unused words are
 // the structural zeros of the layout.  All loads are issued before the first use.
 template <int TYPE, int NB, int NBLK>
-__device__ __forceinline__ void quantise_superblocks(const float *x, const float *x_up, int K,
-                                                     int kblk, int lane, uint8_t *xq, float *SX,
-                                                     float *XX) {
+__device__ __forceinline__ void quantise_superblocks(const float *x, const float *x_up,
+                                                     const float *norm_w, const float *inv_rms,
+                                                     int K, int kblk, int lane, uint8_t *xq,
+                                                     float *SX, float *XX) {
   using C = Cfg<TYPE>;
   constexpr int NCX = 4 * NB, UNIT_BYTES = NCX * 64;
   constexpr int LPG = C::GROUP / 8;  // lanes per scale group
@@ -555,6 +558,13 @@ __device__ __forceinline__ void quantise_superblocks(const float *x, const float
         auto sw = [](float gte, float up) { return gte / (1.f + expf(-gte)) * up; };
         v0[q][b] = make_float4(sw(v0[q][b].x, u0.x), sw(v0[q][b].y, u0.y), sw(v0[q][b].z, u0.z), sw(v0[q][b].w, u0.w));
         v1[q][b] = make_float4(sw(v1[q][b].x, u1.x), sw(v1[q][b].y, u1.y), sw(v1[q][b].z, u1.z), sw(v1[q][b].w, u1.w));
+      }
+      if (norm_w) {  // RMSNorm: x * inv_rms * w in f32, left to right (qwen35_cpu.cr:484-490)
+        const float4 w0 = __ldg(reinterpret_cast<const float4 *>(norm_w + (kblk + q) * 256 + e_in));
+        const float4 w1 = __ldg(reinterpret_cast<const float4 *>(norm_w + (kblk + q) * 256 + e_in + 4));
+        const float r = inv_rms[b];
+        v0[q][b] = make_float4(v0[q][b].x * r * w0.x, v0[q][b].y * r * w0.y, v0[q][b].z * r * w0.z, v0[q][b].w * r * w0.w);
+        v1[q][b] = make_float4(v1[q][b].x * r * w1.x, v1[q][b].y * r * w1.y, v1[q][b].z * r * w1.z, v1[q][b].w * r * w1.w);
       }
     }
   __syncwarp();
@@ -718,6 +728,32 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR) + kPW) * 32, 1)
   pdl_wait_prior_grid();  // x (and y / the addend) may be produced by the preceding kernel
   TRACE(4);
 
+  // RMSNorm prologue: 1 / sqrt(mean(x^2) + eps) per batch row, the sum of squares in f64 as the
+  // reference has it (qwen35_cpu.cr:484-490); per-warp partial sums are added in warp order, so
+  // every warp (and every CTA) arrives at the same value.
+  __shared__ double s_ss[24 * 2];
+  __shared__ float s_inv_rms[2];
+  if (p.norm_w) {
+#pragma unroll
+    for (int b = 0; b < NB; b++) {
+      double ss = 0.0;
+      for (int k = ctid * 4; k < K; k += kNW * 32 * 4) {
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(p.x + (long long)b * K + k));
+        ss += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+      if (lane == 0) s_ss[warp * 2 + b] = ss;
+    }
+    consumer_sync<kNW>();
+    if (ctid < NB) {
+      double ss = 0.0;
+      for (int w = 0; w < kNW; w++) ss += s_ss[w * 2 + ctid];
+      s_inv_rms[ctid] = (float)(1.0 / sqrt(ss / (double)K + (double)p.norm_eps));
+    }
+    consumer_sync<kNW>();
+  }
+
   const int g = lane >> 2, t = lane & 3;
   const int sub = t & 1, bt = (t >> 1) & (NB - 1);  // this lane's group slot and batch row
   float *area = reinterpret_cast<float *>(smem + p.off_area) + warp * AREA_FLOATS;
@@ -766,8 +802,8 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR) + kPW) * 32, 1)
       // The activations are quantised on the way: the warp that takes a superblock pair of the
       // CTA's first tile does x's two superblocks first; later tiles find them done.
       if (li == 0) {
-        if (PAIR == 2 && n2 == 2) quantise_superblocks<TYPE, NB, 2>(p.x, p.x_up, K, e0, lane, xq, SX, XX);
-        else quantise_superblocks<TYPE, NB, 1>(p.x, p.x_up, K, e0, lane, xq, SX, XX);
+        if (PAIR == 2 && n2 == 2) quantise_superblocks<TYPE, NB, 2>(p.x, p.x_up, p.norm_w, s_inv_rms, K, e0, lane, xq, SX, XX);
+        else quantise_superblocks<TYPE, NB, 1>(p.x, p.x_up, p.norm_w, s_inv_rms, K, e0, lane, xq, SX, XX);
         __syncwarp();
         if (lane == 0) st_release_shared(&xready[e], 1);
       } else {
@@ -983,7 +1019,8 @@ int launch_instance(const Params &p, size_t smem, int grid, cudaStream_t s) {
 template <int TYPE>
 int gemv_typed(int njobs, const void *const *d_w, const float *d_x, const float *const *d_addend,
                int64_t addend_stride, float *const *d_y, const int *out_dims, int in_dim, int batch,
-               int resident, const Params *top1, cudaStream_t s, const float *d_x_up = nullptr) {
+               int resident, const Params *top1, cudaStream_t s, const float *d_x_up = nullptr,
+               const float *d_norm_w = nullptr, float norm_eps = 0.f) {
   for (int j0 = 0; j0 < njobs; j0 += kMaxJobs) {
     const int nj = njobs - j0 < kMaxJobs ? njobs - j0 : kMaxJobs;
     Params p{};
@@ -991,6 +1028,8 @@ int gemv_typed(int njobs, const void *const *d_w, const float *d_x, const float 
     if (!make_plan<TYPE>(in_dim, batch, p, smem)) return COGNI_QMM_ERR_LIMIT;
     p.x = d_x;
     p.x_up = d_x_up;
+    p.norm_w = d_norm_w;
+    p.norm_eps = norm_eps;
     p.addend_stride = addend_stride;
     p.resident = resident;
     p.debug = g_imma_debug;
@@ -1071,6 +1110,20 @@ int launch_gemv_swiglu_imma(int type, const void *d_w, const float *d_gate, cons
     case kQ5_K: return gemv_typed<kQ5_K>(1, &d_w, d_gate, add, addend_stride, &d_y, &out_dim, in_dim, batch, resident, nullptr, s, d_up);
     case kQ6_K: return gemv_typed<kQ6_K>(1, &d_w, d_gate, add, addend_stride, &d_y, &out_dim, in_dim, batch, resident, nullptr, s, d_up);
     case kQ8_0: return gemv_typed<kQ8_0>(1, &d_w, d_gate, add, addend_stride, &d_y, &out_dim, in_dim, batch, resident, nullptr, s, d_up);
+    default: return COGNI_QMM_ERR_TYPE;
+  }
+}
+
+// y_j = addend_j + W_j (RMSNorm(x) * norm_w): the normalisation happens while x is quantised
+int launch_gemv_many_rmsnorm_imma(int type, int njobs, const void *const *d_w, const float *d_x,
+                                  const float *d_norm_w, float eps, const float *const *d_addend,
+                                  int64_t addend_stride, float *const *d_y, const int *out_dims,
+                                  int in_dim, int batch, int resident, cudaStream_t s) {
+  switch (type) {
+    case kQ4_K: return gemv_typed<kQ4_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, d_norm_w, eps);
+    case kQ5_K: return gemv_typed<kQ5_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, d_norm_w, eps);
+    case kQ6_K: return gemv_typed<kQ6_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, d_norm_w, eps);
+    case kQ8_0: return gemv_typed<kQ8_0>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, d_norm_w, eps);
     default: return COGNI_QMM_ERR_TYPE;
   }
 }

@@ -123,6 +123,12 @@ int launch_gemv_swiglu_imma(int type, const void *d_w, const float *d_gate, cons
                             int out_dim, int batch, int resident, cudaStream_t s);
 int launch_embedding_rows(int type, const void *d_table, const int32_t *d_ids, int n_tokens, int vocab,
                           int n_embd, float *d_out, int32_t *d_status, cudaStream_t s);
+int launch_gemv_many_rmsnorm_imma(int type, int njobs, const void *const *d_w, const float *d_x,
+                                  const float *d_norm_w, float eps, const float *const *d_addend,
+                                  int64_t addend_stride, float *const *d_y, const int *out_dims,
+                                  int in_dim, int batch, int resident, cudaStream_t s);
+int launch_rmsnorm(const float *d_x, const float *d_w, float eps, float *d_out, int rows, int dim,
+                   cudaStream_t s);
 int launch_swiglu(const float *d_gate, const float *d_up, float *d_out, int64_t n, cudaStream_t s);
 int launch_gemv_imma(int type, const void *d_w, const float *d_x, const float *d_addend,
                      int64_t addend_stride, float *d_y, int in_dim, int out_dim, int batch,

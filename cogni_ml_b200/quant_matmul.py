@@ -249,8 +249,17 @@ class GemvMany:
     x (src/ml/gguf/qwen35_cpu.cr:1419-1490).  The pointer tables are built once; `run` issues one
     launch."""
 
-    def __init__(self, weights, x: torch.Tensor, outs, residuals=None):
+    def __init__(self, weights, x: torch.Tensor, outs, residuals=None, norm_weight=None,
+                 eps: float = 1.0e-6):
+        """norm_weight (f32 [in_dim] on the device): the matrices see RMSNorm(x) * norm_weight,
+        normalised inside the launch (Qwen35CPU#rms_norm, qwen35_cpu.cr:484-490)."""
         import ctypes as C
+        self.norm_weight, self.eps, self._scratch = norm_weight, float(eps), None
+        if norm_weight is not None:
+            if norm_weight.dtype != torch.float32 or norm_weight.numel() != weights[0].in_dim:
+                raise ValueError("norm_weight must be f32 [in_dim]")
+            # room for the normalised x, for shapes the fused kernel does not take
+            self._scratch = torch.empty_like(x)
         if not weights or len({(w.type, w.in_dim) for w in weights}) != 1:
             raise ValueError("weights must share type and in_dim")
         self.weights, self.x, self.outs = list(weights), x, list(outs)
@@ -276,6 +285,14 @@ class GemvMany:
 
     def run(self, stream=None):
         w0 = self.weights[0]
+        if self.norm_weight is not None:
+            check(lib.cogni_qmm_gemv_many_rmsnorm(w0.type, len(self.weights), self._w,
+                                                  self.x.data_ptr(), self.norm_weight.data_ptr(),
+                                                  self.eps, self._add, self._stride, self._y,
+                                                  self._n, self._scratch.data_ptr(), w0.in_dim,
+                                                  self.batch, self._resident, _stream_ptr(stream)),
+                  "cogni_qmm_gemv_many_rmsnorm")
+            return self.outs
         check(lib.cogni_qmm_gemv_many(w0.type, len(self.weights), self._w, self.x.data_ptr(),
                                       self._add, self._stride, self._y, self._n, w0.in_dim,
                                       self.batch, self._resident, _stream_ptr(stream)),
@@ -283,12 +300,13 @@ class GemvMany:
         return self.outs
 
 
-def gemv_many(weights, x: torch.Tensor, outs=None, stream=None):
-    """y_j = W_j @ x for several weights sharing x, in one launch."""
+def gemv_many(weights, x: torch.Tensor, outs=None, stream=None, norm_weight=None, eps: float = 1.0e-6):
+    """y_j = W_j @ x (or W_j @ (RMSNorm(x) * norm_weight)) for several weights sharing x, in one
+    launch."""
     batch = x.numel() // weights[0].in_dim
     if outs is None:
         outs = [torch.empty(batch, w.out_dim, dtype=torch.float32, device=x.device) for w in weights]
-    return GemvMany(weights, x, outs).run(stream)
+    return GemvMany(weights, x, outs, norm_weight=norm_weight, eps=eps).run(stream)
 
 
 def unpack_top1_keys(keys: torch.Tensor):

@@ -122,6 +122,25 @@ int cogni_qmm_gemv_resident(int type, const void *d_w, const float *d_x, const f
                             void *stream);
 
 /*
+ * cogni_qmm_gemv_many with the RMSNorm of the hidden state fused into the activation pass:
+ *     xn[b, k] = x[b, k] * (1 / sqrt(mean_k(x[b, k]^2) + eps)) * norm_weight[k]
+ *     y_j[b, o] = addend_j[b*addend_stride + o] + sum_k xn[b, k] * dequant(W_j[o, k])
+ * the sum of squares in f64, the two products in f32 from left to right, as Qwen35CPU#rms_norm
+ * does (src/ml/gguf/qwen35_cpu.cr:484-490), followed by qmatvec_many (qwen35_cpu.cr:1793, 1883:
+ * attn_norm -> qkv / gate / alpha / beta, post_attention_norm -> ffn_gate / ffn_up); replaces the
+ * reference's add_rmsnorm / rmsnorm probe kernels (deltanet_step_probe.ptx:1324) plus the GEMVs.
+ * Where the tiled kernel takes the shapes (batch <= 2, in_dim a multiple of 256, at most 32
+ * matrices) xn is never written; otherwise it goes to d_x_scratch (f32 [batch, in_dim],
+ * COGNI_QMM_ERR_SCRATCH if NULL) and cogni_qmm_gemv_many runs on that.  norm_weight: f32 [in_dim]
+ * on the device, 16-byte aligned.  Other arguments as cogni_qmm_gemv_many.
+ */
+int cogni_qmm_gemv_many_rmsnorm(int type, int n_weights, const void *const *d_w, const float *d_x,
+                                const float *d_norm_weight, float eps,
+                                const float *const *d_addend, int64_t addend_stride,
+                                float *const *d_y, const int *out_dims, float *d_x_scratch,
+                                int in_dim, int batch, int resident, void *stream);
+
+/*
  * Token-embedding gather from the quantized table (one of the steps next to the matmul path):
  *     out[t, :] = dequant(row d_token_ids[t] of the [vocab, n_embd] table),  f32 [n_tokens, n_embd]
  * bit-identical to Dequant.dequantize of that row, as Qwen35CPU#embedding_lookup does

@@ -113,5 +113,17 @@ def swiglu(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
     return out
 
 
+def rmsnorm(x: np.ndarray, w: np.ndarray, eps: float = 1.0e-6) -> np.ndarray:
+    """Rows of x normalised as Qwen35CPU#rms_norm does (qwen35_cpu.cr:484-490)."""
+    w = np.ascontiguousarray(w, dtype=np.float32).reshape(-1)
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, w.size)
+    out = np.empty_like(x)
+    L = lib()
+    L.qmm_oracle_rmsnorm.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_float, C.c_void_p]
+    L.qmm_oracle_rmsnorm.restype = None
+    L.qmm_oracle_rmsnorm(x.ctypes.data, x.shape[0], x.shape[1], w.ctypes.data, eps, out.ctypes.data)
+    return out
+
+
 def max_threads() -> int:
     return lib().qmm_oracle_max_threads()

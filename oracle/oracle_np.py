@@ -102,3 +102,12 @@ def swiglu(gate, up) -> np.ndarray:
     u = np.asarray(up, dtype=np.float32)
     s = g / (np.float32(1.0) + np.exp(-g, dtype=np.float32))
     return (s * u).astype(np.float32)
+
+
+def rmsnorm(x, w, eps=1.0e-6) -> np.ndarray:
+    """x * inv_rms * w per row, sum of squares in f64 (qwen35_cpu.cr:484-490)."""
+    w = np.asarray(w, dtype=np.float32).reshape(-1)
+    x = np.asarray(x, dtype=np.float32).reshape(-1, w.size)
+    ss = (x.astype(np.float64) ** 2).sum(axis=1)
+    inv = (1.0 / np.sqrt(ss / x.shape[1] + np.float64(np.float32(eps)))).astype(np.float32)
+    return ((x * inv[:, None]).astype(np.float32) * w[None, :]).astype(np.float32)

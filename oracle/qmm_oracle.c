@@ -403,6 +403,20 @@ void qmm_oracle_swiglu(const float *gate, const float *up, int64_t n, float *out
   }
 }
 
+/* src/ml/gguf/qwen35_cpu.cr:484-490 / 1492-1504 */
+void qmm_oracle_rmsnorm(const float *x, int rows, int dim, const float *w, float eps, float *out) {
+  for (int r = 0; r < rows; r++) {
+    const float *xr = x + (int64_t)r * dim;
+    double ss = 0.0;
+    for (int j = 0; j < dim; j++) ss += (double)xr[j] * (double)xr[j];
+    const float inv_rms = (float)(1.0 / sqrt(ss / (double)dim + (double)eps));
+    for (int j = 0; j < dim; j++) {
+      const float t = xr[j] * inv_rms;
+      out[(int64_t)r * dim + j] = t * w[j];
+    }
+  }
+}
+
 void qmm_oracle_top1(const float *logits, int64_t n, int32_t *index, float *value) {
   /* qwen35_cpu.cr:2053-2055: maxv = logits.max; index of its first occurrence.
    * Equivalent to an ascending scan that replaces only on strict '>'. */

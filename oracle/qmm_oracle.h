@@ -77,6 +77,11 @@ void qmm_oracle_top1(const float *logits, int64_t n, int32_t *index, float *valu
  * f32 (src/ml/gguf/qwen35_cpu.cr:512-519 silu, :1716-1717 gate_ff * up_ff). */
 void qmm_oracle_swiglu(const float *gate, const float *up, int64_t n, float *out);
 
+/* RMSNorm of `rows` rows of `dim` elements: out = x * inv_rms * w with the sum of squares in f64,
+ * inv_rms = (float)(1 / sqrt(ss / dim + eps)) and the two products in f32 from left to right
+ * (src/ml/gguf/qwen35_cpu.cr:484-490 rms_norm, :1492-1504 rms_norm_rows). */
+void qmm_oracle_rmsnorm(const float *x, int rows, int dim, const float *w, float eps, float *out);
+
 int qmm_oracle_max_threads(void);
 
 #ifdef __cplusplus

@@ -188,6 +188,28 @@ def test_top1_feeds_embedding_lookup_on_device(cuda, oracle):
     assert int(idx.item()) == tid and np.array_equal(emb[0].view(np.uint32), ref.view(np.uint32))
 
 
+@pytest.mark.parametrize("qtype,in_dim,out_dims,batch", [
+    (Q4_K, 4096, [12288, 12288], 1),        # post_attention_norm -> ffn_gate + ffn_up (9B shapes)
+    (Q4_K, 1024, [512, 96, 32, 32], 2),     # attn_norm -> qkv / gate / alpha / beta
+    (Q6_K, 2048, [300], 1), (Q8_0, 1024, [257, 64], 2), (Q5_K, 768, [128], 1),
+    (Q4_K, 512, [64, 64], 4),               # batch the fused kernel does not take: via scratch
+])
+def test_gemv_many_rmsnorm_fused_prologue(cuda, oracle, qtype, in_dim, out_dims, batch):
+    """y_j = W_j (RMSNorm(x) * w_norm) for matrices sharing x (qwen35_cpu.cr:484-490, 1793, 1883)
+    against the CPU restatement: rms_norm rows, then QuantMatmul per matrix."""
+    from cogni_ml_b200 import gemv_many
+    x = synth.make_activation(batch, in_dim, seed=41, tensor_id=1) * np.float32(3.0)
+    wn = (1.0 + 0.1 * synth.make_activation(1, in_dim, seed=41, tensor_id=2)).ravel()
+    raws = [synth.make_weight(qtype, n, in_dim, seed=41 + j, tensor_id=qtype) for j, n in enumerate(out_dims)]
+    dws = [DeviceQuantWeight.upload(QuantWeight(r, qtype, n, in_dim), cuda) for r, n in zip(raws, out_dims)]
+    ys = gemv_many(dws, torch.from_numpy(x).to(cuda), norm_weight=torch.from_numpy(wn).to(cuda), eps=1e-6)
+    xn = oracle.rmsnorm(x, wn, 1e-6)
+    for r, n, y in zip(raws, out_dims, ys):
+        ref = oracle.matmul_add(xn, batch, in_dim, r, qtype, n, np.zeros(n, np.float32),
+                                threads=oracle.max_threads()).reshape(batch, n)
+        assert_close(y.cpu().numpy(), ref, f"rmsnorm + gemv type {qtype} {n}x{in_dim} batch {batch}")
+
+
 LAYER = [("q_proj", Q4_K, 4096, 4096), ("k_proj", Q4_K, 1024, 4096), ("v_proj", Q4_K, 1024, 4096),
          ("o_proj", Q4_K, 4096, 4096), ("ffn_gate", Q4_K, 12288, 4096),
          ("ffn_down", Q6_K, 4096, 12288), ("q5k_variant", Q5_K, 4096, 4096)]

@@ -180,3 +180,20 @@ def test_swiglu_restatements_agree_and_known_values():
     g = (rng.standard_normal(4096) * 4).astype(np.float32)
     u = rng.standard_normal(4096).astype(np.float32)
     assert np.allclose(loader.swiglu(g, u), oracle_np.swiglu(g, u), rtol=3e-7, atol=1e-12)
+
+
+def test_rmsnorm_restatements_agree_and_known_values():
+    """rms_norm (qwen35_cpu.cr:484-490): a row of equal values v normalises to w * v / sqrt(v^2 + eps);
+    the C and numpy restatements agree bit for bit."""
+    from oracle import loader, oracle_np
+    w = np.array([1.0, 2.0, -1.0, 0.5], dtype=np.float32)
+    x = np.array([[2.0, 2.0, 2.0, 2.0], [0.0, 0.0, 0.0, 0.0], [3.0, -4.0, 0.0, 0.0]], dtype=np.float32)
+    c = loader.rmsnorm(x, w, 1e-6)
+    inv0 = np.float32(1.0 / np.sqrt(4.0 + 1e-6))
+    assert np.array_equal(c[0], (np.float32(2.0) * inv0) * w) and not c[1].any()
+    inv2 = np.float32(1.0 / np.sqrt(25.0 / 4.0 + np.float64(np.float32(1e-6))))
+    assert np.array_equal(c[2], (x[2] * inv2) * w)
+    rng = np.random.default_rng(1)
+    x = (rng.standard_normal((5, 1536)) * 7).astype(np.float32)
+    w = rng.standard_normal(1536).astype(np.float32)
+    assert np.array_equal(loader.rmsnorm(x, w, 1e-6), oracle_np.rmsnorm(x, w, 1e-6))
