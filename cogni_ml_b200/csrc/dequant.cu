@@ -6,6 +6,7 @@
 //   Q4_K/Q5_K  d1 = d*sc; m1 = dmin*m; w = d1*q - m1     (dequant.cr:120-133, 168-185)
 //   Q6_K       w = (d*sc)*q                              (dequant.cr:224-227)
 //   Q8_0       w = d*q                                   (dequant.cr:66-68)
+//   IQ4_NL     w = d*table[nibble]                       (dequant.cr:76-101)
 // One warp expands one 256-element superblock (one 32-element block for Q8_0); lane l
 // writes element l of every 32-wide group, so each store instruction covers 128 contiguous
 // bytes.  HBM-bound: 4 B written per element against 0.56-1.06 B read.
@@ -22,6 +23,13 @@ __device__ __forceinline__ void expand_block<kQ8_0>(const uint8_t *b, float *y, 
   float d = load_half_as_float(b);
   int q = reinterpret_cast<const int8_t *>(b + 2)[lane];
   y[lane] = __fmul_rn(d, (float)q);
+}
+
+template <>
+__device__ __forceinline__ void expand_block<kIQ4_NL>(const uint8_t *b, float *y, int lane) {
+  float d = load_half_as_float(b);
+  int q = b[2 + (lane & 15)];
+  y[lane] = __fmul_rn(d, (float)iq4nl_value(lane < 16 ? (q & 0x0F) : (q >> 4)));
 }
 
 template <>
@@ -148,6 +156,7 @@ int run(const void *d_w, int64_t n, float *d_out, cudaStream_t s) {
 int launch_dequantize(int type, const void *d_w, int64_t n, float *d_out, cudaStream_t s) {
   switch (type) {
     case kQ8_0: return run<kQ8_0>(d_w, n, d_out, s);
+    case kIQ4_NL: return run<kIQ4_NL>(d_w, n, d_out, s);
     case kQ4_K: return run<kQ4_K>(d_w, n, d_out, s);
     case kQ5_K: return run<kQ5_K>(d_w, n, d_out, s);
     case kQ6_K: return run<kQ6_K>(d_w, n, d_out, s);
@@ -159,6 +168,7 @@ int launch_embedding_rows(int type, const void *d_table, const int32_t *d_ids, i
                           int n_embd, float *d_out, int32_t *d_status, cudaStream_t s) {
   switch (type) {
     case kQ8_0: return run_embedding<kQ8_0>(d_table, d_ids, n_tokens, vocab, n_embd, d_out, d_status, s);
+    case kIQ4_NL: return run_embedding<kIQ4_NL>(d_table, d_ids, n_tokens, vocab, n_embd, d_out, d_status, s);
     case kQ4_K: return run_embedding<kQ4_K>(d_table, d_ids, n_tokens, vocab, n_embd, d_out, d_status, s);
     case kQ5_K: return run_embedding<kQ5_K>(d_table, d_ids, n_tokens, vocab, n_embd, d_out, d_status, s);
     case kQ6_K: return run_embedding<kQ6_K>(d_table, d_ids, n_tokens, vocab, n_embd, d_out, d_status, s);

@@ -35,6 +35,16 @@ template <int NB> struct BlockDot<kQ8_0, NB> {
   }
 };
 
+template <int NB> struct BlockDot<kIQ4_NL, NB> {
+  static __device__ __forceinline__ void run(const uint8_t *b, const float *x, int64_t xs, int lane,
+                                             float (&acc)[NB]) {
+    float d = load_half_as_float(b);
+    int q = b[2 + (lane & 15)];
+    float w = d * (float)iq4nl_value(lane < 16 ? (q & 0x0F) : (q >> 4));
+    fma_cols<NB>(w, x + lane, xs, acc);
+  }
+};
+
 template <int NB> struct BlockDot<kQ4_K, NB> {
   static __device__ __forceinline__ void run(const uint8_t *b, const float *x, int64_t xs, int lane,
                                              float (&acc)[NB]) {
@@ -259,6 +269,7 @@ int launch_gemv_rowwarp(int type, const void *d_w, const float *d_x, const float
                         cudaStream_t s) {
   switch (type) {
     case kQ8_0: return run_gemv<kQ8_0>(d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, s);
+    case kIQ4_NL: return run_gemv<kIQ4_NL>(d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, s);
     case kQ4_K: return run_gemv<kQ4_K>(d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, s);
     case kQ5_K: return run_gemv<kQ5_K>(d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, s);
     case kQ6_K: return run_gemv<kQ6_K>(d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, s);
@@ -271,6 +282,7 @@ int launch_gemv_top1_rowwarp(int type, const void *d_w, const float *d_x, int in
                              float *d_val, long long *d_key, cudaStream_t s) {
   switch (type) {
     case kQ8_0: return run_top1<kQ8_0>(d_w, d_x, in_dim, out_dim, batch, index_base, d_scratch, d_idx, d_val, d_key, s);
+    case kIQ4_NL: return run_top1<kIQ4_NL>(d_w, d_x, in_dim, out_dim, batch, index_base, d_scratch, d_idx, d_val, d_key, s);
     case kQ4_K: return run_top1<kQ4_K>(d_w, d_x, in_dim, out_dim, batch, index_base, d_scratch, d_idx, d_val, d_key, s);
     case kQ5_K: return run_top1<kQ5_K>(d_w, d_x, in_dim, out_dim, batch, index_base, d_scratch, d_idx, d_val, d_key, s);
     case kQ6_K: return run_top1<kQ6_K>(d_w, d_x, in_dim, out_dim, batch, index_base, d_scratch, d_idx, d_val, d_key, s);

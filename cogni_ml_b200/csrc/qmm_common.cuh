@@ -5,6 +5,7 @@
 //   Q4_K 144 B / 256 el: d f16 @0, dmin f16 @2, scales[12] @4, qs[128] @16
 //   Q5_K 176 B / 256 el: d f16 @0, dmin f16 @2, scales[12] @4, qh[32] @16, ql[128] @48
 //   Q6_K 210 B / 256 el: ql[128] @0, qh[64] @128, scales int8[16] @192, d f16 @208
+//   IQ4_NL 18 B / 32 el: d f16 @0, qs[16] @2: element j < 16 = table[qs[j] & 15], 16 + j = table[qs[j] >> 4]
 #pragma once
 
 #include <cuda_fp16.h>
@@ -20,12 +21,14 @@ constexpr int kQ8_0 = COGNI_QMM_TYPE_Q8_0;
 constexpr int kQ4_K = COGNI_QMM_TYPE_Q4_K;
 constexpr int kQ5_K = COGNI_QMM_TYPE_Q5_K;
 constexpr int kQ6_K = COGNI_QMM_TYPE_Q6_K;
+constexpr int kIQ4_NL = COGNI_QMM_TYPE_IQ4_NL;
 
 template <int TYPE> struct BlockGeom;
 template <> struct BlockGeom<kQ8_0> { static constexpr int bytes = 34, elems = 32; };
 template <> struct BlockGeom<kQ4_K> { static constexpr int bytes = 144, elems = 256; };
 template <> struct BlockGeom<kQ5_K> { static constexpr int bytes = 176, elems = 256; };
 template <> struct BlockGeom<kQ6_K> { static constexpr int bytes = 210, elems = 256; };
+template <> struct BlockGeom<kIQ4_NL> { static constexpr int bytes = 18, elems = 32; };
 
 __host__ __device__ inline int block_bytes(int type) {
   switch (type) {
@@ -33,17 +36,26 @@ __host__ __device__ inline int block_bytes(int type) {
     case kQ4_K: return 144;
     case kQ5_K: return 176;
     case kQ6_K: return 210;
+    case kIQ4_NL: return 18;
     default: return -1;
   }
 }
 __host__ __device__ inline int block_elems(int type) {
   switch (type) {
-    case kQ8_0: return 32;
+    case kQ8_0:
+    case kIQ4_NL: return 32;
     case kQ4_K:
     case kQ5_K:
     case kQ6_K: return 256;
     default: return -1;
   }
+}
+
+// The 16 non-linear levels of IQ4_NL (dequant.cr:11-16), packed eight to a 64-bit constant.
+__device__ __forceinline__ int iq4nl_value(int q) {
+  // -127, -104, -83, -65, -49, -35, -22, -10 | 1, 13, 25, 38, 53, 69, 89, 113
+  const unsigned long long lo = 0xF6EADDCFBFAD9881ull, hi = 0x7159453526190D01ull;
+  return (int)(signed char)(((q & 8) ? hi : lo) >> (8 * (q & 7)));
 }
 
 // Exact IEEE half -> float of two little-endian bytes at a 2-byte aligned address

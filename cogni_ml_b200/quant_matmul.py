@@ -34,6 +34,7 @@ class TensorType(enum.IntEnum):
     Q4_K = 12
     Q5_K = 13
     Q6_K = 14
+    IQ4_NL = 20  # dequantize, embedding lookup and the general GEMV; no tiled kernel
 
     @property
     def block_bytes(self) -> int:

@@ -11,16 +11,17 @@ Per block (offsets as in src/ml/gguf/dequant.cr):
         packed the way get_scale_min_k4 unpacks them, 128 B uniform nibbles
   Q5_K  as Q4_K plus a uniform 32 B fifth-bit plane
   Q6_K  128 B ql + 64 B qh uniform, 16 int8 scales uniform [-64,63], d = half(|N(0,0.001)|)
+  IQ4_NL d = half(|N(0,0.02)|/127), 16 B uniform nibbles (indices into the 16-level table)
 Activations are f32 N(0,1).
 """
 from __future__ import annotations
 
 import numpy as np
 
-Q8_0, Q4_K, Q5_K, Q6_K = 8, 12, 13, 14
-BLOCK_BYTES = {Q8_0: 34, Q4_K: 144, Q5_K: 176, Q6_K: 210}
-BLOCK_ELEMS = {Q8_0: 32, Q4_K: 256, Q5_K: 256, Q6_K: 256}
-TYPE_NAMES = {Q8_0: "Q8_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K"}
+Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL = 8, 12, 13, 14, 20
+BLOCK_BYTES = {Q8_0: 34, Q4_K: 144, Q5_K: 176, Q6_K: 210, IQ4_NL: 18}
+BLOCK_ELEMS = {Q8_0: 32, Q4_K: 256, Q5_K: 256, Q6_K: 256, IQ4_NL: 32}
+TYPE_NAMES = {Q8_0: "Q8_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K", IQ4_NL: "IQ4_NL"}
 
 
 def row_bytes(qtype: int, in_dim: int) -> int:
@@ -57,6 +58,9 @@ def _blocks(qtype: int, nb: int, rng: np.random.Generator) -> np.ndarray:
     if qtype == Q8_0:
         out[:, 0:2] = _half_bytes(np.abs(rng.normal(0.0, 0.02, nb)) / 127.0)
         out[:, 2:34] = rng.integers(-127, 128, size=(nb, 32), dtype=np.int8).view(np.uint8)
+    elif qtype == IQ4_NL:
+        out[:, 0:2] = _half_bytes(np.abs(rng.normal(0.0, 0.02, nb)) / 127.0)
+        out[:, 2:18] = rng.integers(0, 256, size=(nb, 16), dtype=np.uint8)
     elif qtype in (Q4_K, Q5_K):
         out[:, 0:2] = _half_bytes(np.abs(rng.normal(0.0, 0.01, nb)))
         out[:, 2:4] = _half_bytes(np.abs(rng.normal(0.0, 0.01, nb)))

@@ -34,6 +34,7 @@ extern "C" {
 #define COGNI_QMM_TYPE_Q4_K 12
 #define COGNI_QMM_TYPE_Q5_K 13
 #define COGNI_QMM_TYPE_Q6_K 14
+#define COGNI_QMM_TYPE_IQ4_NL 20 /* dequantize, embedding lookup and the general GEMV; no tiled kernel yet */
 
 #define COGNI_QMM_OK 0
 #define COGNI_QMM_ERR_TYPE 1001      /* tensor type not supported by this engine           */

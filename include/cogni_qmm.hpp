@@ -29,6 +29,7 @@ enum class TensorType : int {
   Q4_K = COGNI_QMM_TYPE_Q4_K,
   Q5_K = COGNI_QMM_TYPE_Q5_K,
   Q6_K = COGNI_QMM_TYPE_Q6_K,
+  IQ4_NL = COGNI_QMM_TYPE_IQ4_NL,
 };
 
 inline void check(int status, const char *what) {

@@ -16,8 +16,8 @@ from cogni_ml_b200 import (DeviceQuantWeight, Projection, QuantMatmul, QuantProj
 
 pytestmark = pytest.mark.gpu
 
-Q8_0, Q4_K, Q5_K, Q6_K = synth.Q8_0, synth.Q4_K, synth.Q5_K, synth.Q6_K
-ALL_TYPES = [Q8_0, Q4_K, Q5_K, Q6_K]
+Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL = synth.Q8_0, synth.Q4_K, synth.Q5_K, synth.Q6_K, synth.IQ4_NL
+ALL_TYPES = [Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL]
 REL_TOL = 1e-3
 
 
@@ -81,6 +81,34 @@ def test_dequantize_subnormal_and_extreme_scales(cuda, oracle, qtype):
     ref = oracle.dequantize(qtype, w, in_dim)
     got = DeviceQuantWeight.upload(QuantWeight(w, qtype, 1, in_dim), cuda).dequantize()
     assert np.array_equal(got.cpu().numpy().ravel().view(np.uint32), ref.view(np.uint32))
+
+
+def _f16_le(h):
+    return [h & 0xFF, h >> 8]
+
+
+def test_iq4_nl_reference_golden_vectors_on_the_device(cuda, oracle):
+    """The reference's own known-answer spec for IQ4_NL (spec/iq4_nl_dequant_spec.cr:34-106) run
+    through the device: the full-block dequant is exact, and the fused matmul with the bias as the
+    accumulator start agrees with the spec's bulk-dequant reference (f32 accumulation here against
+    f64 there, so to 1e-6 relative instead of bit for bit)."""
+    kvalues = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], np.float32)
+    raw = np.array(_f16_le(0x3C00) + [j | ((15 - j) << 4) for j in range(16)], np.uint8)
+    got = DeviceQuantWeight.upload(QuantWeight(raw, IQ4_NL, 1, 32), cuda).dequantize().cpu().numpy().ravel()
+    assert np.array_equal(got[:16], kvalues) and np.array_equal(got[16:], kvalues[::-1])
+    # spec :73-106: two rows of weights, two rows of activations, bias [0.25, -0.75]
+    in_dim, out_dim, rows = 32, 2, 2
+    raw2 = _f16_le(0x3C00) + [j | ((15 - j) << 4) for j in range(16)]
+    raw2 += _f16_le(0x3800) + [(15 - j) | (j << 4) for j in range(16)]
+    raw2 = np.array(raw2, np.uint8)
+    x = np.array([(((i * 17) % 23) - 11) for i in range(rows * in_dim)], np.float32) / np.float32(7.0)
+    bias = np.array([0.25, -0.75], np.float32)
+    y = QuantMatmul.matmul_add(x, rows, in_dim, raw2, IQ4_NL, out_dim, bias)
+    dense = got_dense = oracle.dequantize(IQ4_NL, raw2, in_dim * out_dim).reshape(out_dim, in_dim)
+    ref = bias[None, :].astype(np.float64) + x.reshape(rows, in_dim).astype(np.float64) @ dense.astype(np.float64).T
+    assert np.abs(y.reshape(rows, out_dim) - ref).max() <= 1e-6 * np.abs(ref).max()
+    assert np.array_equal(oracle.matmul_add(x, rows, in_dim, raw2, IQ4_NL, out_dim, bias),
+                          ref.astype(np.float32).ravel())
 
 
 def test_config0_q8_0_gemv_batch1(cuda, oracle):
