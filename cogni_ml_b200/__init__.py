@@ -9,7 +9,8 @@ from ._lib import CogniQmmError, lib  # noqa: F401
 from .quant_matmul import (DeviceQuantWeight, GemvMany, QuantMatmul, QuantWeight,  # noqa: F401
                            TensorType, gemv_many, row_bytes, unpack_top1_keys)
 from .runner import Projection, QuantProjectionRunner, ResidentSequenceRunner  # noqa: F401
+from .loader import WeightUploader, plan_chunks  # noqa: F401
 
 __all__ = ["CogniQmmError", "DeviceQuantWeight", "GemvMany", "gemv_many", "Projection", "QuantMatmul", "QuantProjectionRunner",
-           "QuantWeight", "ResidentSequenceRunner", "TensorType", "lib", "row_bytes", "synth",
-           "unpack_top1_keys"]
+           "QuantWeight", "ResidentSequenceRunner", "TensorType", "WeightUploader", "lib", "plan_chunks",
+           "row_bytes", "synth", "unpack_top1_keys"]

@@ -17,6 +17,7 @@ fails, without a GPU the calls raise.
 from __future__ import annotations
 
 import enum
+import warnings
 from dataclasses import dataclass
 from typing import Optional
 
@@ -122,7 +123,10 @@ class DeviceQuantWeight:
         _require_cuda()
         row_end = qw.out_dim if row_end is None else row_end
         rb = row_bytes(qw.type, qw.in_dim)
-        host = torch.from_numpy(qw.raw[row_begin * rb:row_end * rb])
+        with warnings.catch_warnings():
+            # a read-only mmap slice is fine here: the tensor is only ever the source of a copy
+            warnings.filterwarnings("ignore", message="The given NumPy array is not writable")
+            host = torch.from_numpy(qw.raw[row_begin * rb:row_end * rb])
         dev = torch.empty(host.numel(), dtype=torch.uint8, device=device)
         dev.copy_(host)
         torch.cuda.current_stream(dev.device).synchronize()
