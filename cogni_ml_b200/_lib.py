@@ -31,6 +31,8 @@ SIGNATURES = {
     "cogni_qmm_gemv_swiglu": (_i, [_i, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i, _i, _i, _i, _vp]),
     "cogni_qmm_gemv_top1_scratch_bytes": (_sz, [_i, _i]),
     "cogni_qmm_gemv_top1": (_i, [_i, _vp, _vp, _i, _i, _i, C.c_int32, _vp, _sz, _vp, _vp, _vp, _vp]),
+    "cogni_qmm_gemv_top2_scratch_bytes": (_sz, [_i, _i]),
+    "cogni_qmm_gemv_top2": (_i, [_i, _vp, _vp, _i, _i, _i, C.c_int32, _vp, _sz, _vp, _vp, _vp, _i, _vp]),
     "cogni_qmm_gemv_top1_noalloc_max_scratch": (_sz, []),
     "cogni_qmm_gemv_top1_noalloc": (_i, [_i, _vp, _vp, _i, _i, _i, C.c_int32, _vp, _vp, _vp, _vp]),
     "cogni_qmm_top1_unpack_keys": (_i, [_vp, _i, _vp, _vp, _vp]),

@@ -227,6 +227,25 @@ int cogni_qmm_gemv_top1(int type, const void *d_w, const float *d_x, int in_dim,
                           static_cast<cudaStream_t>(stream));
 }
 
+size_t cogni_qmm_gemv_top2_scratch_bytes(int out_dim, int batch) {
+  if (out_dim <= 0 || batch <= 0) return 0;
+  return top2_scratch_bytes(out_dim, batch);
+}
+
+int cogni_qmm_gemv_top2(int type, const void *d_w, const float *d_x, int in_dim, int out_dim,
+                        int batch, int32_t index_base, void *d_scratch, size_t scratch_bytes,
+                        int32_t *d_top_index, float *d_top_value, int64_t *d_top_key, int resident,
+                        void *stream) {
+  int st = check_gemv_args(type, d_w, d_x, d_top_value, in_dim, out_dim, batch);
+  if (st) return st;
+  if (!d_top_index || !d_scratch || index_base < 0 || out_dim < 2) return COGNI_QMM_ERR_ARG;
+  if (reinterpret_cast<uintptr_t>(d_scratch) & 7) return COGNI_QMM_ERR_ALIGN;
+  if (scratch_bytes < top2_scratch_bytes(out_dim, batch)) return COGNI_QMM_ERR_SCRATCH;
+  return launch_gemv_top2(type, d_w, d_x, in_dim, out_dim, batch, index_base, d_scratch, d_top_index,
+                          d_top_value, reinterpret_cast<long long *>(d_top_key), resident,
+                          static_cast<cudaStream_t>(stream));
+}
+
 int cogni_qmm_top1_unpack_keys(const int64_t *d_keys, int batch, int32_t *d_top_index,
                                float *d_top_value, void *stream) {
   if (!d_keys || !d_top_index || !d_top_value || batch <= 0) return COGNI_QMM_ERR_ARG;

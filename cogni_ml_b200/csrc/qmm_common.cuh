@@ -116,6 +116,10 @@ int launch_gemv_top1_rowwarp(int type, const void *d_w, const float *d_x, int in
                              int out_dim, int batch, int32_t index_base, void *d_scratch,
                              int32_t *d_idx, float *d_val, long long *d_key, cudaStream_t s);
 size_t top1_scratch_bytes(int out_dim, int batch);
+size_t top2_scratch_bytes(int out_dim, int batch);
+int launch_gemv_top2(int type, const void *d_w, const float *d_x, int in_dim, int out_dim, int batch,
+                     int32_t index_base, void *d_scratch, int32_t *d_idx, float *d_val,
+                     long long *d_key, int resident, cudaStream_t s);
 
 // Tiled tensor-core GEMV (gemv_mma.cu): Q4_K / Q5_K / Q6_K, 16-byte aligned w and x.
 bool gemv_mma_supports(int type, const void *d_w, const float *d_x, int in_dim);

@@ -164,6 +164,28 @@ class DeviceQuantWeight:
               "cogni_qmm_gemv")
         return out
 
+    def gemv_top2(self, x: torch.Tensor, stream=None, want_keys: bool = False):
+        """The two best rows per batch row: (index int32 [batch, 2], value f32 [batch, 2][, key
+        int64 [batch, 2]]); column 0 is the argmax with the reference's tie rule, column 1 the
+        runner-up (the verifier's margin is value[:, 0] - value[:, 1])."""
+        if x.dtype != torch.float32 or not x.is_contiguous() or x.shape[-1] != self.in_dim:
+            raise ValueError("x must be contiguous f32 [batch, in_dim]")
+        batch = x.numel() // self.in_dim
+        need = lib.cogni_qmm_gemv_top2_scratch_bytes(self.out_dim, batch)
+        scratch = getattr(self, "_top2_scratch", None)
+        if scratch is None or scratch.numel() < need:
+            scratch = self._top2_scratch = torch.zeros(need, dtype=torch.uint8, device=self.raw.device)
+        idx = torch.empty(batch, 2, dtype=torch.int32, device=x.device)
+        val = torch.empty(batch, 2, dtype=torch.float32, device=x.device)
+        key = torch.empty(batch, 2, dtype=torch.int64, device=x.device) if want_keys else None
+        check(lib.cogni_qmm_gemv_top2(self.type, self.raw.data_ptr(), x.data_ptr(), self.in_dim,
+                                      self.out_dim, batch, self.row_begin, scratch.data_ptr(),
+                                      scratch.numel(), idx.data_ptr(), val.data_ptr(),
+                                      key.data_ptr() if key is not None else None,
+                                      1 if self.resident else 0, _stream_ptr(stream)),
+              "cogni_qmm_gemv_top2")
+        return (idx, val, key) if want_keys else (idx, val)
+
     def embedding_lookup(self, token_ids: torch.Tensor, out: Optional[torch.Tensor] = None,
                          check_range: bool = True, stream=None) -> torch.Tensor:
         """Rows `token_ids` (int32 on the device) of this [vocab, n_embd] table as f32, bit-identical

@@ -112,6 +112,21 @@ class ShardedLmHead:
         self.in_dim = qw.in_dim
         self.local = local_factory(qw, self.r0, self.r1, self.device)
 
+    def top2(self, x: torch.Tensor):
+        """(index int32 [batch, 2], value f32 [batch, 2]) of the global best and runner-up: every
+        shard contributes its two best keys, one all-gather, the two largest keys win."""
+        _idx, _val, key = self.local.gemv_top2(x, want_keys=True)          # [batch, 2]
+        if self.world > 1:
+            allk = torch.empty(self.world, *key.shape, dtype=key.dtype, device=key.device)
+            dist.all_gather_into_tensor(allk.view(-1), key.reshape(-1), group=self.group)
+            key = allk.permute(1, 0, 2).reshape(key.shape[0], -1).topk(2, dim=1).values.contiguous()
+        if key.is_cuda:
+            from .quant_matmul import unpack_top1_keys
+            idx, val = unpack_top1_keys(key.view(-1))
+            return idx.view(-1, 2), val.view(-1, 2)
+        idx, val = unpack_top1_key(key.numpy())
+        return torch.from_numpy(idx.copy()), torch.from_numpy(val.copy())
+
     def top1(self, x: torch.Tensor):
         """(index int32 [batch], value f32 [batch]) of the global maximum, identical on all ranks."""
         _idx, _val, key = self.local.gemv_top1(x, want_keys=True)

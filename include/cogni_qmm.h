@@ -158,6 +158,24 @@ int cogni_qmm_embedding_lookup(int type, const void *d_table, int vocab, int n_e
                                int32_t *d_status, void *stream);
 
 /*
+ * lm_head with the two best tokens per row (the verifier's top-1 / top-2 and their margin):
+ * the logits of all `batch` rows go to the scratch buffer with the GEMV of this engine, one more
+ * launch scans them and leaves, for row b, d_top_index[2b], d_top_value[2b] (the argmax, same tie
+ * rule as cogni_qmm_gemv_top1) and d_top_index[2b+1], d_top_value[2b+1] (the runner-up); d_top_key
+ * (optional, 2 * batch int64) receives the packed keys for a cross-shard merge (the two largest
+ * keys over all shards are the global answer).  Replaces the logits GEMV followed by
+ * output_top2_partial_scan_probe / output_top2_partial_reduce_probe
+ * (src/ml/cuda/qwen_output_head_runner.cr:158-338, 864-904).  out_dim >= 2.  The scratch buffer
+ * (cogni_qmm_gemv_top2_scratch_bytes, 8-byte aligned) must be zero-filled once before its first
+ * use; the logits stay readable in it after the call, f32 [batch, out_dim] at its end.
+ */
+size_t cogni_qmm_gemv_top2_scratch_bytes(int out_dim, int batch);
+int cogni_qmm_gemv_top2(int type, const void *d_w, const float *d_x, int in_dim, int out_dim,
+                        int batch, int32_t index_base, void *d_scratch, size_t scratch_bytes,
+                        int32_t *d_top_index, float *d_top_value, int64_t *d_top_key, int resident,
+                        void *stream);
+
+/*
  * The FFN down projection with the SwiGLU product fused into its activation pass:
  *     y[b, o] = addend[b*addend_stride + o] + sum_k (silu(gate[b, k]) * up[b, k]) * dequant(W[o, k])
  * with silu(v) = v / (1 + exp(-v)) in f32 (src/ml/gguf/qwen35_cpu.cr:512-519, 1716-1718; the

@@ -339,6 +339,47 @@ def test_lm_head_top1(cuda, oracle, qtype, batch):
         assert torch.equal(i2, idx) and torch.equal(v2, val)
 
 
+@pytest.mark.parametrize("qtype", ALL_TYPES)
+@pytest.mark.parametrize("batch", [1, 2, 5])
+def test_lm_head_top2_and_margin(cuda, oracle, qtype, batch):
+    """Best and runner-up per row (the verifier's margin), against a sort of the oracle's logits;
+    twice, because the scratch buffer must come back ready for reuse."""
+    out_dim, in_dim, base = 5003, 1024, 100
+    w = synth.make_weight(qtype, out_dim, in_dim, seed=63, tensor_id=qtype)
+    x = synth.make_activation(batch, in_dim, seed=63)
+    dw = DeviceQuantWeight.upload(QuantWeight(w, qtype, out_dim, in_dim), cuda)
+    dw.row_begin = base
+    xd = torch.from_numpy(x).to(cuda)
+    logits = oracle.matmul_add(x, batch, in_dim, w, qtype, out_dim,
+                               np.zeros(out_dim, np.float32)).reshape(batch, out_dim)
+    for _ in range(2):
+        idx, val, key = dw.gemv_top2(xd, want_keys=True)
+        for b in range(batch):
+            order = np.argsort(-logits[b], kind="stable")[:2]      # stable: lower index first on ties
+            scale = np.abs(logits[b]).max()
+            gap12 = logits[b][order[0]] - logits[b][order[1]]
+            third = np.sort(logits[b])[-3]
+            if gap12 > 4 * REL_TOL * scale and logits[b][order[1]] - third > 4 * REL_TOL * scale:
+                assert [int(idx[b, 0]) - base, int(idx[b, 1]) - base] == list(order)
+            assert abs(float(val[b, 0]) - logits[b][order[0]]) <= REL_TOL * scale
+            assert abs(float(val[b, 1]) - logits[b][order[1]]) <= REL_TOL * scale
+            assert float(val[b, 0]) >= float(val[b, 1])
+        assert (key[:, 0] > key[:, 1]).all()
+    # the first column is what the fused top-1 returns
+    i1, v1 = dw.gemv_top1(xd)
+    assert torch.equal(i1, idx[:, 0].contiguous()) or batch > 2   # batch > 2 takes another GEMV kernel
+
+
+def test_lm_head_top2_tie_takes_the_two_lowest_indices(cuda):
+    in_dim, out_dim = 256, 300
+    row = synth.make_weight(Q6_K, 1, in_dim, seed=71)
+    w = np.tile(row, out_dim)
+    x = synth.make_activation(1, in_dim, seed=71)
+    dw = DeviceQuantWeight.upload(QuantWeight(w, Q6_K, out_dim, in_dim), cuda)
+    idx, val = dw.gemv_top2(torch.from_numpy(x).to(cuda))
+    assert idx[0].tolist() == [0, 1] and float(val[0, 0]) == float(val[0, 1])
+
+
 def test_lm_head_top1_tie_takes_lowest_index(cuda):
     """Identical rows give identical logits: the lowest row index must win."""
     in_dim, out_dim = 256, 300

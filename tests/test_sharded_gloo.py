@@ -35,6 +35,14 @@ class OracleShard:
         out.copy_(torch.from_numpy(self._logits(x)))
         return out
 
+    def gemv_top2(self, x, want_keys=False):
+        y = self._logits(x)
+        order = np.argsort(-y, axis=1, kind="stable")[:, :2]
+        val = np.take_along_axis(y, order, axis=1)
+        key = pack_top1_key(val, order + self.row_begin)
+        return (torch.from_numpy((order + self.row_begin).astype(np.int32)), torch.from_numpy(val),
+                torch.from_numpy(key))
+
     def gemv_top1(self, x, want_keys=False):
         y = self._logits(x)
         idx = y.argmax(axis=1)                       # first maximum, as the CPU reference
@@ -71,6 +79,10 @@ def _worker(rank, world, port, out_dim, in_dim, batch, tie):
         for b in range(batch):
             ri, rv = loader.top1(full[b])
             assert int(idx[b]) == ri and float(val[b]) == float(rv)
+        idx2, val2 = ShardedLmHead(qw, "cpu", local_factory=OracleShard).top2(x)
+        for b in range(batch):
+            order = np.argsort(-full[b], kind="stable")[:2]
+            assert idx2[b].tolist() == order.tolist() and val2[b].tolist() == full[b][order].tolist()
     finally:
         dist.destroy_process_group()
 
