@@ -31,6 +31,7 @@ SIGNATURES = {
     "cogni_qmm_gemv_swiglu": (_i, [_i, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i, _i, _i, _i, _vp]),
     "cogni_qmm_gemv_top1_scratch_bytes": (_sz, [_i, _i]),
     "cogni_qmm_gemv_top1": (_i, [_i, _vp, _vp, _i, _i, _i, C.c_int32, _vp, _sz, _vp, _vp, _vp, _vp]),
+    "cogni_qmm_gemv_top1_rmsnorm": (_i, [_i, _vp, _vp, _vp, C.c_float, _i, _i, _i, C.c_int32, _vp, _sz, _vp, _vp, _vp, _vp, _i, _vp]),
     "cogni_qmm_gemv_top2_scratch_bytes": (_sz, [_i, _i]),
     "cogni_qmm_gemv_top2": (_i, [_i, _vp, _vp, _i, _i, _i, C.c_int32, _vp, _sz, _vp, _vp, _vp, _i, _vp]),
     "cogni_qmm_gemv_top1_noalloc_max_scratch": (_sz, []),

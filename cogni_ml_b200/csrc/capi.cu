@@ -227,6 +227,29 @@ int cogni_qmm_gemv_top1(int type, const void *d_w, const float *d_x, int in_dim,
                           static_cast<cudaStream_t>(stream));
 }
 
+int cogni_qmm_gemv_top1_rmsnorm(int type, const void *d_w, const float *d_x,
+                                const float *d_norm_weight, float eps, int in_dim, int out_dim,
+                                int batch, int32_t index_base, void *d_scratch, size_t scratch_bytes,
+                                float *d_x_scratch, int32_t *d_top_index, float *d_top_value,
+                                int64_t *d_top_key, int resident, void *stream) {
+  int st = check_gemv_args(type, d_w, d_x, d_top_value, in_dim, out_dim, batch);
+  if (st) return st;
+  if (!d_top_index || !d_scratch || !d_norm_weight || index_base < 0) return COGNI_QMM_ERR_ARG;
+  if (reinterpret_cast<uintptr_t>(d_scratch) & 7) return COGNI_QMM_ERR_ALIGN;
+  if (scratch_bytes < top1_scratch_bytes(out_dim, batch)) return COGNI_QMM_ERR_SCRATCH;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (g_force_rowwarp == 0 && (reinterpret_cast<uintptr_t>(d_norm_weight) & 15) == 0 &&
+      gemv_imma_supports(type, d_w, d_x, in_dim, batch))
+    return launch_gemv_top1_imma(type, d_w, d_x, in_dim, out_dim, batch, index_base, d_scratch,
+                                 d_top_index, d_top_value, reinterpret_cast<long long *>(d_top_key),
+                                 resident, s, d_norm_weight, eps);
+  if (!d_x_scratch) return COGNI_QMM_ERR_SCRATCH;
+  st = launch_rmsnorm(d_x, d_norm_weight, eps, d_x_scratch, batch, in_dim, s);
+  if (st) return st;
+  return launch_gemv_top1(type, d_w, d_x_scratch, in_dim, out_dim, batch, index_base, d_scratch,
+                          d_top_index, d_top_value, reinterpret_cast<long long *>(d_top_key), s);
+}
+
 size_t cogni_qmm_gemv_top2_scratch_bytes(int out_dim, int batch) {
   if (out_dim <= 0 || batch <= 0) return 0;
   return top2_scratch_bytes(out_dim, batch);

@@ -1130,7 +1130,8 @@ int launch_gemv_many_rmsnorm_imma(int type, int njobs, const void *const *d_w, c
 
 int launch_gemv_top1_imma(int type, const void *d_w, const float *d_x, int in_dim, int out_dim,
                           int batch, int32_t index_base, void *d_scratch, int32_t *d_idx,
-                          float *d_val, long long *d_key, int resident, cudaStream_t s) {
+                          float *d_val, long long *d_key, int resident, cudaStream_t s,
+                          const float *d_norm_w, float norm_eps) {
   Params t{};
   t.counter = static_cast<unsigned *>(d_scratch);
   t.part_keys = reinterpret_cast<long long *>(static_cast<char *>(d_scratch) +
@@ -1140,10 +1141,10 @@ int launch_gemv_top1_imma(int type, const void *d_w, const float *d_x, int in_di
   t.top_key = d_key;
   t.index_base = index_base;
   switch (type) {
-    case kQ4_K: return gemv_typed<kQ4_K>(1, &d_w, d_x, nullptr, 0, nullptr, &out_dim, in_dim, batch, resident, &t, s);
-    case kQ5_K: return gemv_typed<kQ5_K>(1, &d_w, d_x, nullptr, 0, nullptr, &out_dim, in_dim, batch, resident, &t, s);
-    case kQ8_0: return gemv_typed<kQ8_0>(1, &d_w, d_x, nullptr, 0, nullptr, &out_dim, in_dim, batch, resident, &t, s);
-    case kQ6_K: return gemv_typed<kQ6_K>(1, &d_w, d_x, nullptr, 0, nullptr, &out_dim, in_dim, batch, resident, &t, s);
+    case kQ4_K: return gemv_typed<kQ4_K>(1, &d_w, d_x, nullptr, 0, nullptr, &out_dim, in_dim, batch, resident, &t, s, nullptr, d_norm_w, norm_eps);
+    case kQ5_K: return gemv_typed<kQ5_K>(1, &d_w, d_x, nullptr, 0, nullptr, &out_dim, in_dim, batch, resident, &t, s, nullptr, d_norm_w, norm_eps);
+    case kQ8_0: return gemv_typed<kQ8_0>(1, &d_w, d_x, nullptr, 0, nullptr, &out_dim, in_dim, batch, resident, &t, s, nullptr, d_norm_w, norm_eps);
+    case kQ6_K: return gemv_typed<kQ6_K>(1, &d_w, d_x, nullptr, 0, nullptr, &out_dim, in_dim, batch, resident, &t, s, nullptr, d_norm_w, norm_eps);
     default: return COGNI_QMM_ERR_TYPE;
   }
 }

@@ -151,7 +151,8 @@ int launch_gemv_imma(int type, const void *d_w, const float *d_x, const float *d
                      int resident, cudaStream_t s);
 int launch_gemv_top1_imma(int type, const void *d_w, const float *d_x, int in_dim, int out_dim,
                           int batch, int32_t index_base, void *d_scratch, int32_t *d_idx,
-                          float *d_val, long long *d_key, int resident, cudaStream_t s);
+                          float *d_val, long long *d_key, int resident, cudaStream_t s,
+                          const float *d_norm_w = nullptr, float norm_eps = 0.f);
 int launch_gemv_imma_many(int type, int njobs, const void *const *d_w, const float *d_x,
                           const float *const *d_addend, int64_t addend_stride, float *const *d_y,
                           const int *out_dims, int in_dim, int batch, int resident, cudaStream_t s);

@@ -237,10 +237,12 @@ class DeviceQuantWeight:
             self._top1_scratch = torch.zeros(need, dtype=torch.uint8, device=self.raw.device)
         return self._top1_scratch
 
-    def gemv_top1(self, x: torch.Tensor, stream=None, want_keys: bool = False):
+    def gemv_top1(self, x: torch.Tensor, stream=None, want_keys: bool = False,
+                  norm_weight: Optional[torch.Tensor] = None, eps: float = 1.0e-6):
         """Fused lm_head: returns (index int32 [batch], value f32 [batch][, key int64 [batch]]).
 
-        Indices are global: row_begin is added on the device."""
+        Indices are global: row_begin is added on the device.  With norm_weight (f32 [in_dim]) the
+        rows are RMS-normalised inside the launch first (output_norm -> lm_head -> argmax)."""
         if x.dtype != torch.float32 or not x.is_contiguous() or x.shape[-1] != self.in_dim:
             raise ValueError("x must be contiguous f32 [batch, in_dim]")
         batch = x.numel() // self.in_dim
@@ -248,6 +250,17 @@ class DeviceQuantWeight:
         idx = torch.empty(batch, dtype=torch.int32, device=x.device)
         val = torch.empty(batch, dtype=torch.float32, device=x.device)
         key = torch.empty(batch, dtype=torch.int64, device=x.device) if want_keys else None
+        if norm_weight is not None:
+            xs = torch.empty_like(x)   # for shapes the fused kernel does not take
+            check(lib.cogni_qmm_gemv_top1_rmsnorm(self.type, self.raw.data_ptr(), x.data_ptr(),
+                                                  norm_weight.data_ptr(), float(eps), self.in_dim,
+                                                  self.out_dim, batch, self.row_begin,
+                                                  scratch.data_ptr(), scratch.numel(), xs.data_ptr(),
+                                                  idx.data_ptr(), val.data_ptr(),
+                                                  key.data_ptr() if key is not None else None,
+                                                  1 if self.resident else 0, _stream_ptr(stream)),
+                  "cogni_qmm_gemv_top1_rmsnorm")
+            return (idx, val, key) if want_keys else (idx, val)
         check(lib.cogni_qmm_gemv_top1(self.type, self.raw.data_ptr(), x.data_ptr(), self.in_dim,
                                       self.out_dim, batch, self.row_begin, scratch.data_ptr(),
                                       scratch.numel(), idx.data_ptr(), val.data_ptr(),

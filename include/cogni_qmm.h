@@ -158,6 +158,21 @@ int cogni_qmm_embedding_lookup(int type, const void *d_table, int vocab, int n_e
                                int32_t *d_status, void *stream);
 
 /*
+ * cogni_qmm_gemv_top1 with the output RMSNorm fused in: the argmax of W (RMSNorm(x) * norm_weight)
+ * per row, the norm as in cogni_qmm_gemv_many_rmsnorm.  This is the reference's
+ * rmsnorm_project_top1_rows (src/ml/gguf/qwen35_metal.cr:9187) and the CUDA head runner's
+ * rmsnorm -> lm_head -> top-1 chain (src/ml/cuda/qwen_output_head_runner.cr:884-947) as one launch
+ * where the tiled kernel takes the shape (batch <= 2, in_dim a multiple of 256); otherwise the
+ * normalised rows go to d_x_scratch (f32 [batch, in_dim], COGNI_QMM_ERR_SCRATCH if NULL) first.
+ * d_scratch / scratch_bytes as for cogni_qmm_gemv_top1.
+ */
+int cogni_qmm_gemv_top1_rmsnorm(int type, const void *d_w, const float *d_x,
+                                const float *d_norm_weight, float eps, int in_dim, int out_dim,
+                                int batch, int32_t index_base, void *d_scratch, size_t scratch_bytes,
+                                float *d_x_scratch, int32_t *d_top_index, float *d_top_value,
+                                int64_t *d_top_key, int resident, void *stream);
+
+/*
  * lm_head with the two best tokens per row (the verifier's top-1 / top-2 and their margin):
  * the logits of all `batch` rows go to the scratch buffer with the GEMV of this engine, one more
  * launch scans them and leaves, for row b, d_top_index[2b], d_top_value[2b] (the argmax, same tie

@@ -380,6 +380,24 @@ def test_lm_head_top2_tie_takes_the_two_lowest_indices(cuda):
     assert idx[0].tolist() == [0, 1] and float(val[0, 0]) == float(val[0, 1])
 
 
+@pytest.mark.parametrize("qtype,batch", [(Q6_K, 1), (Q4_K, 2), (Q8_0, 1), (Q6_K, 5)])
+def test_lm_head_top1_with_fused_output_norm(cuda, oracle, qtype, batch):
+    """output_norm -> lm_head -> argmax per row in one call (rmsnorm_project_top1_rows,
+    qwen35_metal.cr:9187) against rms_norm rows + QuantMatmul + argmax on the CPU."""
+    out_dim, in_dim = 4000, 1024
+    w = synth.make_weight(qtype, out_dim, in_dim, seed=65, tensor_id=qtype)
+    x = synth.make_activation(batch, in_dim, seed=65) * np.float32(4.0)
+    wn = (1.0 + 0.2 * synth.make_activation(1, in_dim, seed=65, tensor_id=9)).ravel()
+    dw = DeviceQuantWeight.upload(QuantWeight(w, qtype, out_dim, in_dim), cuda)
+    idx, val = dw.gemv_top1(torch.from_numpy(x).to(cuda), norm_weight=torch.from_numpy(wn).to(cuda))
+    xn = oracle.rmsnorm(x, wn, 1e-6)
+    logits = oracle.matmul_add(xn, batch, in_dim, w, qtype, out_dim,
+                               np.zeros(out_dim, np.float32)).reshape(batch, out_dim)
+    for b in range(batch):
+        ri, rv = oracle.top1(logits[b])
+        assert int(idx[b]) == ri and abs(float(val[b]) - rv) <= REL_TOL * np.abs(logits[b]).max()
+
+
 def test_lm_head_top1_tie_takes_lowest_index(cuda):
     """Identical rows give identical logits: the lowest row index must win."""
     in_dim, out_dim = 256, 300
