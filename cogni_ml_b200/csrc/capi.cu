@@ -239,7 +239,7 @@ int cogni_qmm_gemv_top1_rmsnorm(int type, const void *d_w, const float *d_x,
   if (scratch_bytes < top1_scratch_bytes(out_dim, batch)) return COGNI_QMM_ERR_SCRATCH;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (g_force_rowwarp == 0 && (reinterpret_cast<uintptr_t>(d_norm_weight) & 15) == 0 &&
-      gemv_imma_supports(type, d_w, d_x, in_dim, batch))
+      gemv_imma_supports(type, d_w, d_x, in_dim, batch, true))
     return launch_gemv_top1_imma(type, d_w, d_x, in_dim, out_dim, batch, index_base, d_scratch,
                                  d_top_index, d_top_value, reinterpret_cast<long long *>(d_top_key),
                                  resident, s, d_norm_weight, eps);

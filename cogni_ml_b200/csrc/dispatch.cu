@@ -34,7 +34,7 @@ int launch_gemv(int type, const void *d_w, const float *d_x, const float *d_adde
 int launch_gemv_top1(int type, const void *d_w, const float *d_x, int in_dim, int out_dim,
                      int batch, int32_t index_base, void *d_scratch, int32_t *d_idx, float *d_val,
                      long long *d_key, cudaStream_t s) {
-  if (g_force_rowwarp == 0 && gemv_imma_supports(type, d_w, d_x, in_dim, batch))
+  if (g_force_rowwarp == 0 && gemv_imma_supports(type, d_w, d_x, in_dim, batch, true))
     return launch_gemv_top1_imma(type, d_w, d_x, in_dim, out_dim, batch, index_base, d_scratch,
                                  d_idx, d_val, d_key, 0, s);
   if (g_force_rowwarp == 0 && gemv_mma_supports(type, d_w, d_x, in_dim))

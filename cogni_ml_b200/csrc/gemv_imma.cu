@@ -37,6 +37,7 @@
 // launching at once and itself waits for its predecessor only before it touches x or y.  With
 // `resident` weights the producer starts fetching weights before that wait.
 #include <climits>
+#include <type_traits>
 
 #include "qmm_common.cuh"
 #include "tma_pipe.cuh"
@@ -47,8 +48,11 @@ namespace {
 // Consumer warps per CTA.  Every warp holds the stage bytes of its item until it is done, so
 // more warps leave fewer stages for the copies in flight; 16 (20 for single-superblock items of
 // the 210-byte Q6_K blocks) measured best.
-__host__ __device__ constexpr int consumer_warps(int type, int pair) { return type == kQ6_K && pair == 1 ? 20 : 16; }
-constexpr int kFoldBufs = 4;                 // tiles whose partial sums can be pending (power of 2)
+__host__ __device__ constexpr int consumer_warps(int type, int pair, int nb = 1) {
+  return type == kQ6_K && pair == 1 && nb <= 2 ? 20 : 16;
+}
+// tiles whose partial sums can be pending (power of 2)
+__host__ __device__ constexpr int fold_bufs(int nb) { return nb > 2 ? 2 : 4; }
 // One warp issues bulk copies at roughly one per 70-90 cycles however many of its lanes take
 // part; the copy unit itself accepts several times that, so the rows of a stage are split over
 // kPW producer warps.
@@ -103,9 +107,13 @@ struct Params {
   const float *x;
   const float *x_up;  // non-null: the activations are silu(x) * x_up (SwiGLU), formed while quantising
   const float *norm_w;  // non-null: the activations are RMSNorm(x) * norm_w, normalised while quantising
+  const float *norm_x;  // the rows the norm is taken over: norm_dim elements each (a launch may cover a column range of them)
+  int norm_dim;
+  int x_pitch;          // floats between the batch rows of x / x_up
   float norm_eps;
-  long long addend_stride;
+  long long addend_stride;  // floats between the batch rows of an addend; -1: the job's out_dim
   int in_dim;
+  int batch;     // rows of x (batches above 2: may be below the kernel's NB)
   int nblk, nchunks, stages;
   int njobs;
   int tcum[kMaxJobs + 1];  // tcum[j] = first global tile of job j; tcum[njobs] = all tiles
@@ -174,6 +182,14 @@ __device__ __forceinline__ void imma_s8_acc(int (&d)[4], uint32_t a0, uint32_t a
       "{%0,%1,%2,%3};"
       : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// 16 x 8 x 16 variants: one 16-element scale group per MMA (Q6_K with batches above 2)
+__device__ __forceinline__ void imma16_zero(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+  asm(
+      "mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, "
+      "{%7,%7,%7,%7};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(b0), "r"(0));
 }
 // scale * (byte i of v), exactly rounded once: 0x4B0000bb is the float 2^23 + b, and
 // fma(2^23 + b, scale, -2^23 * scale) = b * scale (the product 2^23 * scale is exact).
@@ -307,14 +323,13 @@ __device__ __forceinline__ void decode_scales(const uint8_t *blk_row, int lane, 
 
 // Single-superblock items: lanes (r = lane & 15, half = lane >> 4) decode one half of the scale
 // groups of row r; the two halves' corrections are combined with one shuffle.
-template <int TYPE, int NB>
-__device__ __forceinline__ void decode_scales_half(const uint8_t *blk_row, int lane, int kblk,
-                                              const float *SX, const float *XX, float *area) {
+// d*sc (Q4_K's odd groups: d*sc/16, see mma_block) and the offset factors of one half (NG/2
+// groups) of a row's superblock.
+template <int TYPE>
+__device__ __forceinline__ void half_scales(const uint8_t *blk_row, int half,
+                                            float (&dsc)[Cfg<TYPE>::NG / 2],
+                                            float (&kk)[Cfg<TYPE>::NG / 2]) {
   using C = Cfg<TYPE>;
-  using A = Area<TYPE>;
-  constexpr int NH = C::NG / 2;  // groups per lane
-  const int r = lane & 15, half = lane >> 4;
-  float dsc[NH], kk[NH];
   if constexpr (TYPE == kQ8_0) {  // the blocks' own fp16 scales; no minimum, no offset
 #pragma unroll
     for (int i = 0; i < 4; i++) {
@@ -346,6 +361,17 @@ __device__ __forceinline__ void decode_scales_half(const uint8_t *blk_row, int l
       kk[i] = dsc[i];  // times -32 once, at the end
     }
   }
+}
+
+template <int TYPE, int NB>
+__device__ __forceinline__ void decode_scales_half(const uint8_t *blk_row, int lane, int kblk,
+                                              const float *SX, const float *XX, float *area) {
+  using C = Cfg<TYPE>;
+  using A = Area<TYPE>;
+  constexpr int NH = C::NG / 2;  // groups per lane
+  const int r = lane & 15, half = lane >> 4;
+  float dsc[NH], kk[NH];
+  half_scales<TYPE>(blk_row, half, dsc, kk);
   // this lane's groups are consecutive in the tables: NH * NB floats each, 16-byte aligned
   const int grp0 = kblk * C::NG + NH * half;
   float sxv[NH * NB], xxv[NH * NB];
@@ -622,16 +648,295 @@ __device__ __forceinline__ void quantise_superblocks(const float *x, const float
   }
 }
 
+// ---------------------------------------------------------------------------- batches 3 .. 8
+// With more than two batch rows the MMA columns are (batch row b' of a set of four, plane):
+// column 2b' + plane, one MMA per scale group and set (m16n8k32 for the 32-element groups,
+// m16n8k16 for Q6_K's 16-element groups), no structural zeros.  Lane (g, t) of the result holds
+// the hi and lo sums of batch row 4j + t for weight rows g and g+8 of set j.  The warp's area holds
+// d*sc per (row, group) in group order, without the activation scale, which the lane multiplies in
+// per (group, batch row); the row's corrections follow at index NG + b.
+template <int TYPE> struct Dense {
+  static constexpr int W = TYPE == kQ6_K ? 4 : 8;  // bytes of a lane's B fragment per (group, set)
+  static constexpr int GB = 32 * W;                // bytes of a (group, set)
+};
+// floats per area row: NG scales + NB corrections, padded so that the 8 rows a warp reads with
+// 16-byte loads fall into distinct banks
+__host__ __device__ constexpr int dense_area_row(int ng, int nb) {
+  return nb <= 4 ? ng + 4 : (ng == 8 ? 20 : 28);
+}
+
+// Quantises superblock kblk of x for NB batch rows (rows beyond `batch` repeat the last one) into
+// the dense fragment order: byte offset ((group * J + set) * 32 + column * 4 + t) * W.
+template <int TYPE, int NB>
+__device__ __forceinline__ void quantise_dense(const float *x, const float *x_up,
+                                               const float *norm_w, const float *inv_rms, int K,
+                                               int batch, int kblk, int lane, uint8_t *xq,
+                                               float *SX, float *XX) {
+  using C = Cfg<TYPE>;
+  constexpr int J = NB / 4, W = Dense<TYPE>::W;
+  constexpr int LPG = C::GROUP / 8;  // lanes per scale group
+  const int k = kblk * 256 + lane * 8;
+  const int grp = k / C::GROUP;
+  // this lane's 8 bytes inside a column's 4 * W: lanes t of the MMA take W bytes each
+  const int tpos = (lane & (LPG - 1)) * 8;
+  float4 w0 = make_float4(1.f, 1.f, 1.f, 1.f), w1 = w0;
+  if (norm_w) {
+    w0 = __ldg(reinterpret_cast<const float4 *>(norm_w + k));
+    w1 = __ldg(reinterpret_cast<const float4 *>(norm_w + k + 4));
+  }
+#pragma unroll
+  for (int b4 = 0; b4 < NB; b4 += 4) {
+    float4 v0[4], v1[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int br = min(b4 + i, batch - 1);
+      const long long off = (long long)br * K + k;
+      v0[i] = __ldg(reinterpret_cast<const float4 *>(x + off));
+      v1[i] = __ldg(reinterpret_cast<const float4 *>(x + off + 4));
+      if (x_up) {  // SwiGLU: silu(gate) * up in f32, silu(v) = v / (1 + exp(-v)) (qwen35_cpu.cr:512-519, 1716-1717)
+        const float4 u0 = __ldg(reinterpret_cast<const float4 *>(x_up + off));
+        const float4 u1 = __ldg(reinterpret_cast<const float4 *>(x_up + off + 4));
+        auto sw = [](float gte, float up) { return gte / (1.f + expf(-gte)) * up; };
+        v0[i] = make_float4(sw(v0[i].x, u0.x), sw(v0[i].y, u0.y), sw(v0[i].z, u0.z), sw(v0[i].w, u0.w));
+        v1[i] = make_float4(sw(v1[i].x, u1.x), sw(v1[i].y, u1.y), sw(v1[i].z, u1.z), sw(v1[i].w, u1.w));
+      }
+      if (norm_w) {  // RMSNorm: x * inv_rms * w in f32, left to right (qwen35_cpu.cr:484-490)
+        const float r = inv_rms[br];
+        v0[i] = make_float4(v0[i].x * r * w0.x, v0[i].y * r * w0.y, v0[i].z * r * w0.z, v0[i].w * r * w0.w);
+        v1[i] = make_float4(v1[i].x * r * w1.x, v1[i].y * r * w1.y, v1[i].z * r * w1.z, v1[i].w * r * w1.w);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int b = b4 + i;
+      const float v[8] = {v0[i].x, v0[i].y, v0[i].z, v0[i].w, v1[i].x, v1[i].y, v1[i].z, v1[i].w};
+      float mx = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; e++) mx = fmaxf(mx, fabsf(v[e]));
+#pragma unroll
+      for (int off = 1; off < LPG; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      const bool live = mx > 1e-30f;  // as in quantise_superblocks
+      const float sx = live ? mx * (1.f / kNMax) : 1.f;
+      const float inv = live ? (float)kNMax / mx : 0.f;
+      uint32_t bits[8], up[8];
+      int nsum = 0;
+#pragma unroll
+      for (int e = 0; e < 8; e++) {
+        bits[e] = __float_as_uint(fmaf(v[e], inv, 12582912.f));
+        up[e] = bits[e] << 1;
+        nsum += (int)(bits[e] - 0x4B400000u);
+      }
+#pragma unroll
+      for (int off = 1; off < LPG; off <<= 1) nsum += __shfl_xor_sync(0xffffffffu, nsum, off);
+      if ((lane & (LPG - 1)) == 0) {
+        SX[grp * NB + b] = sx;
+        XX[grp * NB + b] = sx * (float)nsum;
+      }
+      uint32_t lw[2], hw[2];
+#pragma unroll
+      for (int w4 = 0; w4 < 2; w4++) {
+        lw[w4] = __byte_perm(__byte_perm(bits[4 * w4], bits[4 * w4 + 1], 0x0040),
+                             __byte_perm(bits[4 * w4 + 2], bits[4 * w4 + 3], 0x0040), 0x5410) & 0x7f7f7f7fu;
+        hw[w4] = __byte_perm(__byte_perm(up[4 * w4], up[4 * w4 + 1], 0x0051),
+                             __byte_perm(up[4 * w4 + 2], up[4 * w4 + 3], 0x0051), 0x5410);
+      }
+      uint8_t *dst = xq + ((size_t)(grp * J + (b >> 2)) * 32 + 2 * (b & 3) * 4) * W + tpos;
+      *reinterpret_cast<uint2 *>(dst) = make_uint2(hw[0], hw[1]);          // hi plane: column 2b'
+      *reinterpret_cast<uint2 *>(dst + 4 * W) = make_uint2(lw[0], lw[1]);  // lo plane: column 2b' + 1
+    }
+  }
+}
+
+// Lanes (r = lane & 15, half = lane >> 4) decode one half of the scale groups of row r into the
+// warp's area; the corrections of the NB batch rows are combined across the halves by shuffles.
+template <int TYPE, int NB>
+__device__ __forceinline__ void decode_dense(const uint8_t *blk_row, int lane, int kblk,
+                                             const float *XX, float *area) {
+  using C = Cfg<TYPE>;
+  constexpr int NH = C::NG / 2, ROW = dense_area_row(C::NG, NB);
+  const int r = lane & 15, half = lane >> 4;
+  float dsc[NH], kk[NH];
+  half_scales<TYPE>(blk_row, half, dsc, kk);
+  float *row = area + r * ROW;
+#pragma unroll
+  for (int i = 0; i < NH; i += 4)
+    *reinterpret_cast<float4 *>(row + NH * half + i) = make_float4(dsc[i], dsc[i + 1], dsc[i + 2], dsc[i + 3]);
+  if constexpr (TYPE != kQ8_0) {
+    float corr[NB];
+#pragma unroll
+    for (int b = 0; b < NB; b++) corr[b] = 0.f;
+    const float4 *xx = reinterpret_cast<const float4 *>(XX + (size_t)(kblk * C::NG + NH * half) * NB);
+#pragma unroll
+    for (int i = 0; i < NH; i++)
+#pragma unroll
+      for (int b4 = 0; b4 < NB / 4; b4++) {
+        const float4 c = xx[i * (NB / 4) + b4];
+        corr[4 * b4] = fmaf(kk[i], c.x, corr[4 * b4]);
+        corr[4 * b4 + 1] = fmaf(kk[i], c.y, corr[4 * b4 + 1]);
+        corr[4 * b4 + 2] = fmaf(kk[i], c.z, corr[4 * b4 + 2]);
+        corr[4 * b4 + 3] = fmaf(kk[i], c.w, corr[4 * b4 + 3]);
+      }
+#pragma unroll
+    for (int b = 0; b < NB; b++) {
+      corr[b] += __shfl_xor_sync(0xffffffffu, corr[b], 16);
+      if (TYPE == kQ6_K) corr[b] *= -32.f;
+    }
+    // the halves store alternate fours of the batch rows
+#pragma unroll
+    for (int b4 = 0; b4 < NB / 4; b4++)
+      if (half == (b4 & 1))
+        *reinterpret_cast<float4 *>(row + C::NG + 4 * b4) =
+            make_float4(corr[4 * b4], corr[4 * b4 + 1], corr[4 * b4 + 2], corr[4 * b4 + 3]);
+  } else {
+#pragma unroll
+    for (int b4 = 0; b4 < NB / 4; b4++)
+      if (half == (b4 & 1))
+        *reinterpret_cast<float4 *>(row + C::NG + 4 * b4) = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+// MMAs of one superblock for all NB batch rows.  xg: this lane's B fragment of the superblock's
+// first (group, set); sxg: SX of the superblock's first group at batch row t.
+template <int TYPE, int NB>
+__device__ __forceinline__ void mma_dense(const uint8_t *blk, int pad_a, int pad_b,
+                                          const uint8_t *xg, const float *area, const float *sxg,
+                                          int g, int t, float (&acc0)[NB / 4], float (&acc1)[NB / 4]) {
+  using C = Cfg<TYPE>;
+  constexpr int J = NB / 4, GB = Dense<TYPE>::GB, ROW = dense_area_row(C::NG, NB);
+  constexpr uint32_t M4 = 0x0f0f0f0fu;
+  const float *rowa = area + g * ROW, *rowb = area + (g + 8) * ROW;
+#pragma unroll
+  for (int j = 0; j < J; j++) {
+    acc0[j] = rowa[C::NG + 4 * j + t];
+    acc1[j] = rowb[C::NG + 4 * j + t];
+  }
+  // scale group gi with A fragments (a0, a1, a2, a3): rows g / g+8, first / second eight elements
+  auto group32 = [&](int gi, float fa, float fb, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
+#pragma unroll
+    for (int j = 0; j < J; j++) {
+      const uint2 bv = *reinterpret_cast<const uint2 *>(xg + (gi * J + j) * GB);
+      int cc[4];
+      if constexpr (TYPE == kQ8_0) imma_s8_zero(cc, a0, a1, a2, a3, bv.x, bv.y);
+      else imma_zero(cc, a0, a1, a2, a3, bv.x, bv.y);
+      const float sx = sxg[gi * NB + 4 * j];
+      acc0[j] = fmaf(fa * sx, (float)(cc[0] * 128 + cc[1]), acc0[j]);
+      acc1[j] = fmaf(fb * sx, (float)(cc[2] * 128 + cc[3]), acc1[j]);
+    }
+  };
+  if constexpr (TYPE == kQ8_0) {
+    const uint8_t *ra = blk + g * C::RS + 8 * t, *rb = blk + (g + 8) * C::RS + 8 * t;
+    auto even_block = [](const uint8_t *p, uint32_t &w0, uint32_t &w1) {  // p: the block's d
+      const uint32_t *q = reinterpret_cast<const uint32_t *>(p);
+      const uint32_t a = q[0], b = q[1], c = q[2];
+      w0 = __funnelshift_r(a, b, 16);
+      w1 = __funnelshift_r(b, c, 16);
+    };
+#pragma unroll
+    for (int g4 = 0; g4 < 4; g4++) {
+      const float2 sa = *reinterpret_cast<const float2 *>(rowa + 2 * g4);
+      const float2 sb = *reinterpret_cast<const float2 *>(rowb + 2 * g4);
+      uint32_t la0, la1, lb0, lb1;
+      even_block(ra + 68 * g4, la0, la1);
+      even_block(rb + 68 * g4, lb0, lb1);
+      // the odd block's quants sit on a word, not on a double word
+      const uint32_t *ha = reinterpret_cast<const uint32_t *>(ra + 68 * g4 + 36);
+      const uint32_t *hb = reinterpret_cast<const uint32_t *>(rb + 68 * g4 + 36);
+      group32(2 * g4, sa.x, sb.x, la0, lb0, la1, lb1);
+      group32(2 * g4 + 1, sa.y, sb.y, ha[0], hb[0], ha[1], hb[1]);
+    }
+  } else if constexpr (C::HAS_MIN) {
+    constexpr bool Q5 = TYPE == kQ5_K;
+    constexpr int QOFF = Q5 ? 48 : 16;
+    constexpr uint32_t M1 = 0x10101010u, MH = 0xf0f0f0f0u;
+    const uint8_t *ra = blk + g * C::RS + pad_a + 8 * t, *rb = blk + (g + 8) * C::RS + pad_b + 8 * t;
+    uint2 qha = make_uint2(0, 0), qhb = make_uint2(0, 0);
+    if constexpr (Q5) {
+      qha = *reinterpret_cast<const uint2 *>(ra + 16);
+      qhb = *reinterpret_cast<const uint2 *>(rb + 16);
+    }
+#pragma unroll
+    for (int g4 = 0; g4 < 4; g4++) {
+      const float2 sa = *reinterpret_cast<const float2 *>(rowa + 2 * g4);
+      const float2 sb = *reinterpret_cast<const float2 *>(rowb + 2 * g4);
+      const uint2 qa = *reinterpret_cast<const uint2 *>(ra + QOFF + 32 * g4);
+      const uint2 qb = *reinterpret_cast<const uint2 *>(rb + QOFF + 32 * g4);
+      uint32_t la0 = qa.x & M4, la1 = qa.y & M4, lb0 = qb.x & M4, lb1 = qb.y & M4;
+      uint32_t ha0, ha1, hb0, hb1;
+      if constexpr (!Q5) {  // high nibbles stay in place: 16 * q, the 1/16 is in the group's scale
+        ha0 = qa.x & MH; ha1 = qa.y & MH; hb0 = qb.x & MH; hb1 = qb.y & MH;
+      } else {
+        ha0 = (qa.x >> 4) & M4; ha1 = (qa.y >> 4) & M4; hb0 = (qb.x >> 4) & M4; hb1 = (qb.y >> 4) & M4;
+        // fifth bit: bit 2*g4 of qh for the low-nibble elements, bit 2*g4+1 for the high ones
+        auto bit = [&](uint32_t q, int b) { return b <= 4 ? ((q << (4 - b)) & M1) : ((q >> (b - 4)) & M1); };
+        la0 |= bit(qha.x, 2 * g4);     la1 |= bit(qha.y, 2 * g4);
+        lb0 |= bit(qhb.x, 2 * g4);     lb1 |= bit(qhb.y, 2 * g4);
+        ha0 |= bit(qha.x, 2 * g4 + 1); ha1 |= bit(qha.y, 2 * g4 + 1);
+        hb0 |= bit(qhb.x, 2 * g4 + 1); hb1 |= bit(qhb.y, 2 * g4 + 1);
+      }
+      group32(2 * g4, sa.x, sb.x, la0, lb0, la1, lb1);
+      group32(2 * g4 + 1, sa.y, sb.y, ha0, hb0, ha1, hb1);
+    }
+  } else {
+    constexpr uint32_t M2 = 0x30303030u;
+    const uintptr_t aa = reinterpret_cast<uintptr_t>(blk + g * C::RS + pad_a + 4 * t);
+    const uintptr_t ab8 = reinterpret_cast<uintptr_t>(blk + (g + 8) * C::RS + pad_b + 4 * t);
+    const uint8_t *base[2] = {reinterpret_cast<const uint8_t *>(aa & ~(uintptr_t)3),
+                              reinterpret_cast<const uint8_t *>(ab8 & ~(uintptr_t)3)};
+    const uint32_t sh[2] = {(uint32_t)(aa & 2) * 8, (uint32_t)(ab8 & 2) * 8};
+#pragma unroll
+    for (int n = 0; n < 2; n++) {
+      const float4 sa0 = *reinterpret_cast<const float4 *>(rowa + 8 * n), sa1 = *reinterpret_cast<const float4 *>(rowa + 8 * n + 4);
+      const float4 sb0 = *reinterpret_cast<const float4 *>(rowb + 8 * n), sb1 = *reinterpret_cast<const float4 *>(rowb + 8 * n + 4);
+      const float sa[8] = {sa0.x, sa0.y, sa0.z, sa0.w, sa1.x, sa1.y, sa1.z, sa1.w};
+      const float sb[8] = {sb0.x, sb0.y, sb0.z, sb0.w, sb1.x, sb1.y, sb1.z, sb1.w};
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        uint32_t q[2][4];
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+          auto ld = [&](int off) {  // rows may start 2 bytes off a word: two loads and a funnel shift
+            const uint32_t *w32 = reinterpret_cast<const uint32_t *>(base[r] + off);
+            return __funnelshift_r(w32[0], w32[1], sh[r]);
+          };
+          const uint32_t ql0 = ld(64 * n + 16 * h), ql1 = ld(64 * n + 32 + 16 * h);
+          const uint32_t qhw = ld(128 + 32 * n + 16 * h);
+          q[r][0] = (ql0 & M4) | ((qhw << 4) & M2);
+          q[r][1] = (ql1 & M4) | ((qhw << 2) & M2);
+          q[r][2] = ((ql0 >> 4) & M4) | (qhw & M2);
+          q[r][3] = ((ql1 >> 4) & M4) | ((qhw >> 2) & M2);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++) {  // elements 128n + 32k + 16h + (0..15): scale group 8n + 2k + h
+          const int gi = 8 * n + 2 * k + h;
+          const float fa = sa[2 * k + h], fb = sb[2 * k + h];
+#pragma unroll
+          for (int j = 0; j < J; j++) {
+            const uint32_t bw = *reinterpret_cast<const uint32_t *>(xg + (gi * J + j) * GB);
+            int cc[4];
+            imma16_zero(cc, q[0][k], q[1][k], bw);
+            const float sx = sxg[gi * NB + 4 * j];
+            acc0[j] = fmaf(fa * sx, (float)(cc[0] * 128 + cc[1]), acc0[j]);
+            acc1[j] = fmaf(fb * sx, (float)(cc[2] * 128 + cc[3]), acc1[j]);
+          }
+        }
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------- the kernel
 template <int TYPE, int NB, int PAIR>
-__global__ void __launch_bounds__((consumer_warps(TYPE, PAIR) + kPW) * 32, 1)
+__global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1)
     gemv_imma_kernel(const Params p) {
-  constexpr int kNW = consumer_warps(TYPE, PAIR), kThreads = (kNW + kPW) * 32;
+  constexpr int kNW = consumer_warps(TYPE, PAIR, NB), kThreads = (kNW + kPW) * 32;
   using C = Cfg<TYPE>;
   using A = Area<TYPE>;
+  constexpr bool DENSE = NB > 2;                 // batches 3 .. 8: one MMA column set per 4 batch rows
+  static_assert(!DENSE || (PAIR == 1 && NB % 4 == 0), "dense items are single superblocks");
+  constexpr int kFoldBufs = fold_bufs(NB);
   constexpr int NCX = 4 * NB;                    // columns of the quantised-x layout
   constexpr int UNIT_BYTES = NCX * 64;
-  constexpr int AREA_FLOATS = PAIR * NB * A::BATCH;  // PAIR superblocks per item
+  constexpr int AREA_FLOATS = DENSE ? 16 * dense_area_row(C::NG, NB) : PAIR * NB * A::BATCH;  // PAIR superblocks per item
   extern __shared__ __align__(128) uint8_t smem[];
   // mbarriers full[S] | empty[S] in the first 128 bytes; monotone counters from byte 192:
   // chunks armed by the producer | partial sums stored per tile buffer | folds done per tile buffer
@@ -721,7 +1026,7 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR) + kPW) * 32, 1)
   uint8_t *xq = smem + p.off_xq;
   float *SX = reinterpret_cast<float *>(smem + p.off_sx);
   float *XX = reinterpret_cast<float *>(smem + p.off_xx);
-  const int K = p.in_dim;
+  const int K = p.x_pitch;  // the quantisers only use it as the pitch of the batch rows
 
   asm volatile("bar.sync 3, %0;" ::"n"(kThreads) : "memory");  // mbarriers and counters ready
   TRACE(3);
@@ -731,31 +1036,35 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR) + kPW) * 32, 1)
   // RMSNorm prologue: 1 / sqrt(mean(x^2) + eps) per batch row, the sum of squares in f64 as the
   // reference has it (qwen35_cpu.cr:484-490); per-warp partial sums are added in warp order, so
   // every warp (and every CTA) arrives at the same value.
-  __shared__ double s_ss[24 * 2];
-  __shared__ float s_inv_rms[2];
+  __shared__ double s_ss2[24 * 2];
+  __shared__ float s_inv_rms[DENSE ? NB : 2];
   if (p.norm_w) {
+    // batches above 2 borrow the (still unused) partial-sum buffer for the warps' sums
+    constexpr int NBS = DENSE ? NB : 2;
+    double *s_ss = DENSE ? reinterpret_cast<double *>(smem + p.off_red) : s_ss2;
 #pragma unroll
     for (int b = 0; b < NB; b++) {
+      const int br = DENSE ? min(b, p.batch - 1) : b;
       double ss = 0.0;
-      for (int k = ctid * 4; k < K; k += kNW * 32 * 4) {
-        const float4 v = __ldg(reinterpret_cast<const float4 *>(p.x + (long long)b * K + k));
+      for (int k = ctid * 4; k < p.norm_dim; k += kNW * 32 * 4) {
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(p.norm_x + (long long)br * K + k));
         ss += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
       }
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
-      if (lane == 0) s_ss[warp * 2 + b] = ss;
+      if (lane == 0) s_ss[warp * NBS + b] = ss;
     }
     consumer_sync<kNW>();
     if (ctid < NB) {
       double ss = 0.0;
-      for (int w = 0; w < kNW; w++) ss += s_ss[w * 2 + ctid];
-      s_inv_rms[ctid] = (float)(1.0 / sqrt(ss / (double)K + (double)p.norm_eps));
+      for (int w = 0; w < kNW; w++) ss += s_ss[w * NBS + ctid];
+      s_inv_rms[ctid] = (float)(1.0 / sqrt(ss / (double)p.norm_dim + (double)p.norm_eps));
     }
     consumer_sync<kNW>();
   }
 
   const int g = lane >> 2, t = lane & 3;
-  const int sub = t & 1, bt = (t >> 1) & (NB - 1);  // this lane's group slot and batch row
+  const int sub = t & 1, bt = DENSE ? 0 : (t >> 1) & (NB - 1);  // this lane's group slot and batch row
   float *area = reinterpret_cast<float *>(smem + p.off_area) + warp * AREA_FLOATS;
   const float *area_b = area + bt * A::BATCH;
   // partial sums: [tile buffer][superblock pair of the row][g][batch row] float2 (rows g, g+8)
@@ -763,7 +1072,7 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR) + kPW) * 32, 1)
   const int npairs = (p.nblk + PAIR - 1) / PAIR;  // items per tile
   const int red_tile = npairs * 8 * NB;
   // this lane's 16 bytes of a unit's B fragments
-  const uint8_t *xlane = xq + ((g & (NCX - 1)) * 4 + t) * 16;
+  const uint8_t *xlane = DENSE ? xq + lane * Dense<TYPE>::W : xq + ((g & (NCX - 1)) * 4 + t) * 16;
   const uint32_t bar0 = smem_u32(bars);
 
   long long best = LLONG_MIN, best_b1 = LLONG_MIN;  // fused top-1: running maxima (batch row 0 / 1)
@@ -802,21 +1111,36 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR) + kPW) * 32, 1)
       // The activations are quantised on the way: the warp that takes a superblock pair of the
       // CTA's first tile does x's two superblocks first; later tiles find them done.
       if (li == 0) {
-        if (PAIR == 2 && n2 == 2) quantise_superblocks<TYPE, NB, 2>(p.x, p.x_up, p.norm_w, s_inv_rms, K, e0, lane, xq, SX, XX);
+        if constexpr (DENSE) quantise_dense<TYPE, NB>(p.x, p.x_up, p.norm_w, s_inv_rms, K, p.batch, e0, lane, xq, SX, XX);
+        else if (PAIR == 2 && n2 == 2) quantise_superblocks<TYPE, NB, 2>(p.x, p.x_up, p.norm_w, s_inv_rms, K, e0, lane, xq, SX, XX);
         else quantise_superblocks<TYPE, NB, 1>(p.x, p.x_up, p.norm_w, s_inv_rms, K, e0, lane, xq, SX, XX);
         __syncwarp();
         if (lane == 0) st_release_shared(&xready[e], 1);
       } else {
         spin_until_ge(&xready[e], 1);
       }
-      float acc0 = 0.f, acc1 = 0.f;  // rows g and g+8 of (group slot sub, batch row bt)
       TRACE(1000 + li * per_tile + e);
       spin_until_ge(issued, cc + 1);
       mbar_wait(bar0 + 8 * s, par);
       TRACE(2000 + li * per_tile + e);
+      const int tb = li & (kFoldBufs - 1);
+      const uint8_t *blk = stages + (size_t)s * p.stage_bytes + bi * C::BB;
+      if constexpr (DENSE) {
+        constexpr int J = NB / 4;
+        float acc0[J], acc1[J];  // rows g and g+8 of batch rows 4j + t
+        decode_dense<TYPE, NB>(blk + (lane & 15) * C::RS + pad_d, lane, e0, XX, area);
+        __syncwarp();
+        mma_dense<TYPE, NB>(blk, pad_a, pad_b, xlane + (size_t)e0 * C::NG * J * Dense<TYPE>::GB, area,
+                            SX + (size_t)e0 * C::NG * NB + t, g, t, acc0, acc1);
+        __syncwarp();  // the area is rewritten by this warp's next decode
+        spin_until_ge(&folded[tb], li / kFoldBufs);  // the buffer's previous tile has been folded
+#pragma unroll
+        for (int j = 0; j < J; j++)
+          red[tb * red_tile + (e * 8 + g) * NB + 4 * j + t] = make_float2(acc0[j], acc1[j]);
+      } else {
+      float acc0 = 0.f, acc1 = 0.f;  // rows g and g+8 of (group slot sub, batch row bt)
       if (p.debug & 8) __nanosleep(1500);  // diagnostics: keep the consumers the bottleneck
       if ((p.debug & 3) != 1) {
-        const uint8_t *blk = stages + (size_t)s * p.stage_bytes + bi * C::BB;
         const int which = lane >> 4;
         if constexpr (PAIR == 1) {
           decode_scales_half<TYPE, NB>(blk + (lane & 15) * C::RS + pad_d, lane, e0, SX, XX, area);
@@ -838,10 +1162,10 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR) + kPW) * 32, 1)
       // the two group slots of a batch row sit in neighbouring lanes
       acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
       acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
-      const int tb = li & (kFoldBufs - 1);
       spin_until_ge(&folded[tb], li / kFoldBufs);  // the buffer's previous tile has been folded
       if (sub == 0 && (t >> 1) < NB)
         red[tb * red_tile + (e * 8 + g) * NB + (t >> 1)] = make_float2(acc0, acc1);
+      }
       __syncwarp();
       if (lane == 0) {
         // release the stage (the tile's last item also arrives for the superblocks that a short
@@ -857,27 +1181,53 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR) + kPW) * 32, 1)
       TRACE(4000 + li * per_tile + e);
       spin_until_ge(&arrivals[tb], (fl / kFoldBufs + 1) * npairs);  // all partials of tile fl stored
       TRACE(5000 + li * per_tile + e);
+      const int gt = blockIdx.x + fl * gridDim.x;
+      locate(gt, cj);
+      const Job &job = p.jobs[cj];
       // lane = (batch row, row of the tile): a fixed-order sum over the superblock pairs
-      const int r16 = lane & 15, b = lane >> 4;
+      const int r16 = lane & 15;
+      const int row = (gt - p.tcum[cj]) * kR + r16;
+      if constexpr (DENSE) {
+        float v[NB / 2];  // batch rows 2i + (lane >> 4)
+#pragma unroll
+        for (int i = 0; i < NB / 2; i++) {
+          const int b = 2 * i + (lane >> 4);
+          const float *src = reinterpret_cast<const float *>(red + tb * red_tile + (r16 & 7) * NB + b) + (r16 >> 3);
+          float a = 0.f;
+#pragma unroll 4
+          for (int k = 0; k < npairs; k++) a += src[k * 16 * NB];
+          v[i] = a;
+        }
+        __syncwarp();
+        if (lane == 0) st_release_shared(&folded[tb], fl / kFoldBufs + 1);
+#pragma unroll
+        for (int i = 0; i < NB / 2; i++) {
+          const int b = 2 * i + (lane >> 4);
+          if (b < p.batch && row < job.out_dim) {
+            const long long as = p.addend_stride < 0 ? job.out_dim : p.addend_stride;
+            const float a = job.addend ? job.addend[(long long)b * as + row] : 0.f;
+            job.y[(long long)b * job.out_dim + row] = a + v[i];
+          }
+        }
+      } else {
+      const int b = lane >> 4;
       const float *src = reinterpret_cast<const float *>(red + tb * red_tile + (r16 & 7) * NB + (b & (NB - 1))) + (r16 >> 3);
       float v = 0.f;
 #pragma unroll 4
       for (int k = 0; k < npairs; k++) v += src[k * 16 * NB];
       __syncwarp();
       if (lane == 0) st_release_shared(&folded[tb], fl / kFoldBufs + 1);
-      const int gt = blockIdx.x + fl * gridDim.x;
-      locate(gt, cj);
-      const Job &job = p.jobs[cj];
-      const int row = (gt - p.tcum[cj]) * kR + r16;
       if (b < NB && row < job.out_dim) {
         if (p.part_keys) {
           const long long key = top1_key(v, (uint32_t)(p.index_base + row));
           if (b == 0) best = key > best ? key : best;
           else best_b1 = key > best_b1 ? key : best_b1;
         } else {
-          const float a = job.addend ? job.addend[(long long)b * p.addend_stride + row] : 0.f;
+          const long long as = p.addend_stride < 0 ? job.out_dim : p.addend_stride;
+          const float a = job.addend ? job.addend[(long long)b * as + row] : 0.f;
           job.y[(long long)b * job.out_dim + row] = a + v;
         }
+      }
       }
     }
     // next item of this warp
@@ -957,11 +1307,13 @@ bool make_plan_pair(int in_dim, int nb, int pair, Params &p, size_t &smem) {
   auto al = [](size_t v) { return (v + 127) & ~(size_t)127; };
   size_t off = 256;  // mbarriers and counters
   const size_t off_flags = off;  off += 256;  // one flag per superblock of x (in_dim <= 16384)
-  const size_t off_red = off;    off = al(off + (size_t)kFoldBufs * ((nblk + pair - 1) / pair) * 8 * nb * 8);  // [tile buffer][item][g][batch] float2
-  const size_t off_area = off;   off = al(off + (size_t)consumer_warps(TYPE, pair) * pair * nb * Area<TYPE>::BATCH * 4);
+  const bool dense = nb > 2;  // nb = 4 or 8 then: single-superblock items, 2 bytes of x per element and batch row
+  const size_t area_floats = dense ? (size_t)16 * dense_area_row(C::NG, nb) : (size_t)pair * nb * Area<TYPE>::BATCH;
+  const size_t off_red = off;    off = al(off + (size_t)fold_bufs(nb) * ((nblk + pair - 1) / pair) * 8 * nb * 8);  // [tile buffer][item][g][batch] float2
+  const size_t off_area = off;   off = al(off + (size_t)consumer_warps(TYPE, pair, nb) * area_floats * 4);
   const size_t off_sx = off;     off = al(off + (size_t)ngroups * nb * 4);
   const size_t off_xx = off;     off = al(off + (size_t)ngroups * nb * 4);
-  const size_t off_xq = off;     off = al(off + (size_t)(in_dim / 64) * (4 * nb) * 64);
+  const size_t off_xq = off;     off = al(off + (dense ? (size_t)in_dim * 2 * nb : (size_t)(in_dim / 64) * (4 * nb) * 64));
   const size_t off_stage = off;
   const size_t stage_bytes = al((size_t)kR * C::RS);
   if (off_stage + 3 * stage_bytes > kDynSmemMax) return false;
@@ -983,6 +1335,7 @@ bool make_plan_pair(int in_dim, int nb, int pair, Params &p, size_t &smem) {
 // enough of them to keep the warps busy.
 template <int TYPE>
 bool make_plan(int in_dim, int nb, Params &p, size_t &smem) {
+  if (nb > 2) return make_plan_pair<TYPE>(in_dim, nb, 1, p, smem);
   if (g_imma_force_pair != 1 && make_plan_pair<TYPE>(in_dim, nb, 2, p, smem) &&
       (g_imma_force_pair == 2 || p.stages * Cfg<TYPE>::KB / 2 >= 20))
     return true;
@@ -1003,7 +1356,7 @@ int launch_instance(const Params &p, size_t smem, int grid, cudaStream_t s) {
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3((consumer_warps(TYPE, PAIR) + kPW) * 32);
+  cfg.blockDim = dim3((consumer_warps(TYPE, PAIR, NB) + kPW) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
   cudaLaunchAttribute attr[1];
@@ -1014,33 +1367,74 @@ int launch_instance(const Params &p, size_t smem, int grid, cudaStream_t s) {
   return (int)cudaLaunchKernelEx(&cfg, gemv_imma_kernel<TYPE, NB, PAIR>, p);
 }
 
-// njobs weight matrices (same type and in_dim), one x: the reference's qmatvec_many
-// (src/ml/gguf/qwen35_cpu.cr:1419-1490) and dual GEMV (q4k_dual_gemv_probe.ptx:5) as one launch.
+// Column ranges a launch covers when a whole row of activations does not fit into shared memory:
+// the fewest equal ranges of whole superblocks whose plan fits.  Every weight byte is still read
+// once; the later ranges add onto y.  0 = none fits.
 template <int TYPE>
-int gemv_typed(int njobs, const void *const *d_w, const float *d_x, const float *const *d_addend,
-               int64_t addend_stride, float *const *d_y, const int *out_dims, int in_dim, int batch,
-               int resident, const Params *top1, cudaStream_t s, const float *d_x_up = nullptr,
-               const float *d_norm_w = nullptr, float norm_eps = 0.f) {
-  for (int j0 = 0; j0 < njobs; j0 += kMaxJobs) {
-    const int nj = njobs - j0 < kMaxJobs ? njobs - j0 : kMaxJobs;
+int column_splits(int in_dim, int nb) {
+  const int nblk = in_dim / 256;
+  for (int n = 1; n <= 8 && n <= nblk; n++) {
     Params p{};
     size_t smem = 0;
-    if (!make_plan<TYPE>(in_dim, batch, p, smem)) return COGNI_QMM_ERR_LIMIT;
-    p.x = d_x;
-    p.x_up = d_x_up;
-    p.norm_w = d_norm_w;
+    if (make_plan<TYPE>((nblk + n - 1) / n * 256, nb, p, smem)) return n;
+  }
+  return 0;
+}
+
+// Rows of x one launch takes when the batch is above 2: 8 (4 for batches 3 and 4); 0 = no plan.
+// A tail of one or two rows runs on the batch 1-2 kernels.
+template <int TYPE>
+int batch_pass_width(int in_dim, int batch) {
+  const int width = batch > 4 ? 8 : 4;
+  if (column_splits<TYPE>(in_dim, width) == 0) return 0;
+  const int tail = batch % width;
+  if (tail > 4 && column_splits<TYPE>(in_dim, 8) == 0) return 0;
+  if (tail > 2 && tail <= 4 && column_splits<TYPE>(in_dim, 4) == 0) return 0;
+  if ((tail == 1 || tail == 2) && column_splits<TYPE>(in_dim, tail) == 0) return 0;
+  return width;
+}
+
+// One pass: up to kMaxJobs weight matrices against `batch` rows of x (1, 2, or 3 .. 8), as one
+// launch per column range.
+template <int TYPE>
+int run_pass(int nj, const void *const *d_w, const float *d_x, const float *const *d_addend,
+             int64_t addend_stride, float *const *d_y, const int *out_dims, int in_dim, int batch,
+             int resident, const Params *top1, cudaStream_t s, const float *d_x_up,
+             const float *d_norm_w, float norm_eps) {
+  using C = Cfg<TYPE>;
+  const int nbk = batch <= 2 ? batch : (batch <= 4 ? 4 : 8);
+  const int nsplit = column_splits<TYPE>(in_dim, nbk);
+  if (nsplit == 0 || (top1 && nsplit > 1)) return COGNI_QMM_ERR_LIMIT;
+  const int nblk = in_dim / 256, per = (nblk + nsplit - 1) / nsplit;
+  for (int b0 = 0; b0 < nblk; b0 += per) {
+    const int nb_here = nblk - b0 < per ? nblk - b0 : per;
+    Params p{};
+    size_t smem = 0;
+    if (!make_plan<TYPE>(nb_here * 256, nbk, p, smem)) return COGNI_QMM_ERR_LIMIT;
+    p.row_bytes = (long long)nblk * C::BB;  // the pitch of the whole rows
+    p.x = d_x + b0 * 256;
+    p.x_up = d_x_up ? d_x_up + b0 * 256 : nullptr;
+    p.norm_w = d_norm_w ? d_norm_w + b0 * 256 : nullptr;
+    p.norm_x = d_x;
+    p.norm_dim = in_dim;
+    p.x_pitch = in_dim;
     p.norm_eps = norm_eps;
-    p.addend_stride = addend_stride;
+    p.batch = batch;
     p.resident = resident;
-    p.debug = g_imma_debug;
+    p.debug = nbk > 2 ? (g_imma_debug & 4) : g_imma_debug;
     p.njobs = nj;
     for (int j = 0; j < nj; j++) {
-      p.jobs[j].w = static_cast<const uint8_t *>(d_w[j0 + j]);
-      p.jobs[j].addend = d_addend ? d_addend[j0 + j] : nullptr;
-      p.jobs[j].y = d_y ? d_y[j0 + j] : nullptr;
-      p.jobs[j].out_dim = out_dims[j0 + j];
-      p.tcum[j + 1] = p.tcum[j] + (out_dims[j0 + j] + kR - 1) / kR;
+      p.jobs[j].w = static_cast<const uint8_t *>(d_w[j]) + (long long)b0 * C::BB;
+      p.jobs[j].y = d_y ? d_y[j] : nullptr;
+      p.jobs[j].out_dim = out_dims[j];
+      p.tcum[j + 1] = p.tcum[j] + (out_dims[j] + kR - 1) / kR;
+      if (b0 == 0) {
+        p.jobs[j].addend = d_addend ? d_addend[j] : nullptr;
+      } else {  // later column ranges add onto what the earlier ones stored
+        p.jobs[j].addend = p.jobs[j].y;
+      }
     }
+    p.addend_stride = b0 == 0 ? addend_stride : -1;  // -1: the stride of y (per job)
     const int sms = sm_count();
     const int grid = p.tcum[nj] < sms ? p.tcum[nj] : sms;
     if (top1) {
@@ -1051,11 +1445,45 @@ int gemv_typed(int njobs, const void *const *d_w, const float *d_x, const float 
       p.top_key = top1->top_key;
       p.index_base = top1->index_base;
     }
-    const int st = batch == 1 ? (p.pair == 2 ? launch_instance<TYPE, 1, 2>(p, smem, grid, s)
-                                             : launch_instance<TYPE, 1, 1>(p, smem, grid, s))
-                              : (p.pair == 2 ? launch_instance<TYPE, 2, 2>(p, smem, grid, s)
-                                             : launch_instance<TYPE, 2, 1>(p, smem, grid, s));
+    int st;
+    switch (nbk) {
+      case 1: st = p.pair == 2 ? launch_instance<TYPE, 1, 2>(p, smem, grid, s) : launch_instance<TYPE, 1, 1>(p, smem, grid, s); break;
+      case 2: st = p.pair == 2 ? launch_instance<TYPE, 2, 2>(p, smem, grid, s) : launch_instance<TYPE, 2, 1>(p, smem, grid, s); break;
+      case 4: st = launch_instance<TYPE, 4, 1>(p, smem, grid, s); break;
+      default: st = launch_instance<TYPE, 8, 1>(p, smem, grid, s); break;
+    }
     if (st) return st;
+  }
+  return COGNI_QMM_OK;
+}
+
+// njobs weight matrices (same type and in_dim), one x: the reference's qmatvec_many
+// (src/ml/gguf/qwen35_cpu.cr:1419-1490) and dual GEMV (q4k_dual_gemv_probe.ptx:5) as one launch
+// per 32 matrices, 8 batch rows and column range.
+template <int TYPE>
+int gemv_typed(int njobs, const void *const *d_w, const float *d_x, const float *const *d_addend,
+               int64_t addend_stride, float *const *d_y, const int *out_dims, int in_dim, int batch,
+               int resident, const Params *top1, cudaStream_t s, const float *d_x_up = nullptr,
+               const float *d_norm_w = nullptr, float norm_eps = 0.f) {
+  if (top1 && batch > 2) return COGNI_QMM_ERR_LIMIT;
+  const int width = batch <= 2 ? batch : batch_pass_width<TYPE>(in_dim, batch);
+  if (width == 0) return COGNI_QMM_ERR_LIMIT;
+  for (int b0 = 0; b0 < batch; b0 += width) {
+    const int nbat = batch - b0 < width ? batch - b0 : width;
+    for (int j0 = 0; j0 < njobs; j0 += kMaxJobs) {
+      const int nj = njobs - j0 < kMaxJobs ? njobs - j0 : kMaxJobs;
+      const float *add[kMaxJobs];
+      float *ys[kMaxJobs];
+      for (int j = 0; j < nj; j++) {
+        add[j] = d_addend && d_addend[j0 + j] ? d_addend[j0 + j] + (long long)b0 * addend_stride : nullptr;
+        ys[j] = d_y ? d_y[j0 + j] + (long long)b0 * out_dims[j0 + j] : nullptr;
+      }
+      const int st = run_pass<TYPE>(nj, d_w + j0, d_x + (long long)b0 * in_dim, d_addend ? add : nullptr,
+                                    addend_stride, d_y ? ys : nullptr, out_dims + j0, in_dim, nbat, resident,
+                                    top1, s, d_x_up ? d_x_up + (long long)b0 * in_dim : nullptr, d_norm_w,
+                                    norm_eps);
+      if (st) return st;
+    }
   }
   return COGNI_QMM_OK;
 }
@@ -1065,19 +1493,24 @@ int gemv_typed(int njobs, const void *const *d_w, const float *d_x, const float 
 void gemv_imma_set_debug(int mode) { g_imma_debug = mode; }
 void gemv_imma_set_pair(int pair) { g_imma_force_pair = pair; }
 
-bool gemv_imma_supports(int type, const void *d_w, const float *d_x, int in_dim, int batch) {
+bool gemv_imma_supports(int type, const void *d_w, const float *d_x, int in_dim, int batch, bool top1) {
   if (type != kQ8_0 && type != kQ4_K && type != kQ5_K && type != kQ6_K) return false;
-  if (batch < 1 || batch > 2) return false;
+  if (batch < 1 || batch > 64 || (top1 && batch > 2)) return false;
   if ((reinterpret_cast<uintptr_t>(d_w) & 15) || (reinterpret_cast<uintptr_t>(d_x) & 15)) return false;
   if (in_dim % 256 != 0 || in_dim > 16384) return false;
-  // the activations, the warps' areas and at least three stages must fit into shared memory
-  Params p{};
-  size_t smem = 0;
+  // the activations (of a column range of the rows, if need be), the warps' areas and at least
+  // three stages must fit into shared memory; the fused top-1 needs whole rows in one launch
+  auto ok = [&](auto tag) {
+    constexpr int T = decltype(tag)::value;
+    if (batch > 2) return batch_pass_width<T>(in_dim, batch) != 0;
+    const int n = column_splits<T>(in_dim, batch);
+    return n != 0 && (!top1 || n == 1);
+  };
   switch (type) {
-    case kQ4_K: return make_plan<kQ4_K>(in_dim, batch, p, smem);
-    case kQ5_K: return make_plan<kQ5_K>(in_dim, batch, p, smem);
-    case kQ8_0: return make_plan<kQ8_0>(in_dim, batch, p, smem);
-    default: return make_plan<kQ6_K>(in_dim, batch, p, smem);
+    case kQ4_K: return ok(std::integral_constant<int, kQ4_K>{});
+    case kQ5_K: return ok(std::integral_constant<int, kQ5_K>{});
+    case kQ8_0: return ok(std::integral_constant<int, kQ8_0>{});
+    default: return ok(std::integral_constant<int, kQ6_K>{});
   }
 }
 

@@ -132,8 +132,9 @@ int launch_gemv_top1_mma(int type, const void *d_w, const float *d_x, int in_dim
 unsigned gemv_mma_timeouts();
 void gemv_mma_set_debug(int mode);
 
-// Integer tensor-core GEMV for batch 1-2 (gemv_imma.cu): Q4_K / Q5_K / Q6_K.
-bool gemv_imma_supports(int type, const void *d_w, const float *d_x, int in_dim, int batch);
+// Integer tensor-core GEMV (gemv_imma.cu): Q8_0 / Q4_K / Q5_K / Q6_K; the fused top-1 for batch 1-2.
+bool gemv_imma_supports(int type, const void *d_w, const float *d_x, int in_dim, int batch,
+                        bool top1 = false);
 int launch_gemv_swiglu_imma(int type, const void *d_w, const float *d_gate, const float *d_up,
                             const float *d_addend, int64_t addend_stride, float *d_y, int in_dim,
                             int out_dim, int batch, int resident, cudaStream_t s);

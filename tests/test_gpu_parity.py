@@ -145,9 +145,24 @@ def test_many_tiles_per_cta(cuda, oracle, qtype, in_dim, batch):
 
 
 @pytest.mark.parametrize("qtype,out_dim,in_dim,batch", [
+    (Q6_K, 100, 12288, 2), (Q6_K, 333, 12288, 5), (Q4_K, 80, 16384, 8), (Q5_K, 48, 8192, 11),
+    (Q8_0, 70, 12288, 4), (Q6_K, 40, 16384, 1),
+])
+def test_long_rows_in_column_ranges(cuda, oracle, qtype, out_dim, in_dim, batch):
+    """Rows whose activations do not fit into shared memory at this batch run as several launches
+    over column ranges that add onto y; the residual goes in with the first."""
+    w, x, y, add = run_gemv(cuda, qtype, out_dim, in_dim, batch, seed=52, addend="residual")
+    ref = np.stack([oracle.matmul_add(x[b], 1, in_dim, w, qtype, out_dim, add["residual"][b])
+                    for b in range(batch)])
+    assert_close(y, ref.reshape(batch, out_dim), f"type {qtype} {out_dim}x{in_dim} batch {batch}")
+
+
+@pytest.mark.parametrize("qtype,out_dim,in_dim,batch", [
     (Q6_K, 4096, 12288, 1),   # the 9B ffn_down shape: fused path
     (Q4_K, 512, 2048, 2), (Q8_0, 300, 1024, 1), (Q5_K, 257, 768, 2),
-    (Q6_K, 128, 1024, 5),     # batch the fused kernel does not take: product goes through scratch
+    (Q6_K, 128, 1024, 5),     # batch 5: the 8-row instance of the kernel
+    (Q4_K, 192, 2048, 11),    # a pass of 8 rows and a pass of 3
+    (IQ4_NL, 128, 1024, 3),   # no fused kernel for this type: the product goes through scratch
     (Q8_0, 64, 96, 1),        # in_dim not a multiple of 256: scratch path as well
 ])
 def test_gemv_swiglu_fused_down_projection(cuda, oracle, qtype, out_dim, in_dim, batch):
@@ -167,11 +182,12 @@ def test_gemv_swiglu_fused_down_projection(cuda, oracle, qtype, out_dim, in_dim,
 
 
 def test_gemv_swiglu_needs_scratch_for_unfused_shapes(cuda, engine):
-    w = synth.make_weight(Q4_K, 64, 256, seed=3)
-    dw = DeviceQuantWeight.upload(QuantWeight(w, Q4_K, 64, 256), cuda)
+    # IQ4_NL has no fused kernel: the product needs the caller's scratch
+    w = synth.make_weight(IQ4_NL, 64, 256, seed=3)
+    dw = DeviceQuantWeight.upload(QuantWeight(w, IQ4_NL, 64, 256), cuda)
     g = torch.zeros(5, 256, device=cuda)
     y = torch.empty(5, 64, device=cuda)
-    st = engine.lib.cogni_qmm_gemv_swiglu(Q4_K, dw.raw.data_ptr(), g.data_ptr(), g.data_ptr(), None, 0,
+    st = engine.lib.cogni_qmm_gemv_swiglu(IQ4_NL, dw.raw.data_ptr(), g.data_ptr(), g.data_ptr(), None, 0,
                                           y.data_ptr(), None, 256, 64, 5, 0, None)
     assert st == 1004  # COGNI_QMM_ERR_SCRATCH
 
@@ -220,7 +236,9 @@ def test_top1_feeds_embedding_lookup_on_device(cuda, oracle):
     (Q4_K, 4096, [12288, 12288], 1),        # post_attention_norm -> ffn_gate + ffn_up (9B shapes)
     (Q4_K, 1024, [512, 96, 32, 32], 2),     # attn_norm -> qkv / gate / alpha / beta
     (Q6_K, 2048, [300], 1), (Q8_0, 1024, [257, 64], 2), (Q5_K, 768, [128], 1),
-    (Q4_K, 512, [64, 64], 4),               # batch the fused kernel does not take: via scratch
+    (Q4_K, 512, [64, 64], 4),               # batch 4: the 4-row instance of the kernel
+    (Q6_K, 1024, [96, 40], 7),
+    (IQ4_NL, 512, [64, 64], 2),             # no fused kernel for this type: via scratch
 ])
 def test_gemv_many_rmsnorm_fused_prologue(cuda, oracle, qtype, in_dim, out_dims, batch):
     """y_j = W_j (RMSNorm(x) * w_norm) for matrices sharing x (qwen35_cpu.cr:484-490, 1793, 1883)
