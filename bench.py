@@ -194,7 +194,8 @@ def measure_extras(dev, gate_h, down_h, peaks):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / reps
 
-    out = {"prefill": [], "lm_head": None, "swiglu_down": None, "ffn_block_fused": None}
+    out = {"prefill": [], "lm_head": None, "swiglu_down": None, "ffn_block_fused": None,
+           "batched_ffn": None}
     tf_burst, tf_sust = peaks.get("bf16_tflops"), peaks.get("bf16_tflops_sustained")
     for qtype, raw, n, k in ((Q4_K, gate_h, FFN, HIDDEN), (Q6_K, down_h, HIDDEN, FFN)):
         dw = DeviceQuantWeight.upload(QuantWeight(raw, qtype, n, k), dev)
@@ -247,7 +248,33 @@ def measure_extras(dev, gate_h, down_h, peaks):
 
     out["ffn_block_fused"] = {"kernel": "per layer: RMSNorm + ffn_gate/ffn_up (1 launch), SwiGLU + ffn_down + residual (1 launch), b1",
                               "us_per_layer": timed(ffn_blocks, 20) * 1e3 / 4}
-    del downs, gates, calls
+    del calls
+    # the speculative verifier's row batches: one layer's ffn_gate + ffn_up (one launch) and ffn_down
+    # at batch 2 .. 16, weight bytes per second; four layers of weights (390 MB) defeat L2
+    out["batched_ffn"] = []
+    for batch in (2, 4, 8, 16):
+        xb = torch.from_numpy(synth.make_activation(batch, HIDDEN, seed=6, tensor_id=41)).to(dev)
+        hb = torch.from_numpy(synth.make_activation(batch, FFN, seed=6, tensor_id=42)).to(dev)
+        gb = torch.empty(batch, FFN, dtype=torch.float32, device=dev)
+        ub = torch.empty(batch, FFN, dtype=torch.float32, device=dev)
+        yb = torch.empty(batch, HIDDEN, dtype=torch.float32, device=dev)
+        bcalls = [GemvMany([gates[2 * i], gates[2 * i + 1]], xb, [gb, ub]) for i in range(4)]
+
+        def gate_up():
+            for c in bcalls:
+                c.run()
+
+        def down():
+            for d in downs:
+                d.gemv(hb, out=yb)
+
+        us_gu = timed(gate_up, 20) * 1e3 / 4
+        us_dn = timed(down, 20) * 1e3 / 4
+        out["batched_ffn"].append({"batch": batch, "gate_up_q4k_us": us_gu,
+                                   "gate_up_gbs": 2 * gates[0].nbytes / us_gu / 1e3,
+                                   "down_q6k_us": us_dn, "down_gbs": downs[0].nbytes / us_dn / 1e3})
+        del bcalls
+    del downs, gates
     vocab, hid = 151936, 5120
     head = DeviceQuantWeight.upload(
         QuantWeight(synth.make_weight(Q6_K, vocab, hid, seed=7, tensor_id=9), Q6_K, vocab, hid), dev)

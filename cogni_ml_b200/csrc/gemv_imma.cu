@@ -1,5 +1,6 @@
-// Decode GEMV for batch 1-2, Q4_K / Q5_K / Q6_K / Q8_0 straight from the raw GGUF blocks (sm_100a):
-// bulk-async staging + integer tensor-core MMAs on the raw quants.
+// Decode GEMV for Q4_K / Q5_K / Q6_K / Q8_0 straight from the raw GGUF blocks (sm_100a):
+// bulk-async staging + integer tensor-core MMAs on the raw quants.  The description below is the
+// batch 1-2 arrangement; batches 3-8 per launch use the dense column sets described further down.
 //
 // The kernel is HBM-bound; at 6.5 TB/s an SM has about three issue slots per weight, and the
 // integer (ALU) pipe runs at half rate, so the design removes every per-weight instruction it can:
@@ -1181,12 +1182,9 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
       TRACE(4000 + li * per_tile + e);
       spin_until_ge(&arrivals[tb], (fl / kFoldBufs + 1) * npairs);  // all partials of tile fl stored
       TRACE(5000 + li * per_tile + e);
-      const int gt = blockIdx.x + fl * gridDim.x;
-      locate(gt, cj);
-      const Job &job = p.jobs[cj];
       // lane = (batch row, row of the tile): a fixed-order sum over the superblock pairs
       const int r16 = lane & 15;
-      const int row = (gt - p.tcum[cj]) * kR + r16;
+      const int gt = blockIdx.x + fl * gridDim.x;
       if constexpr (DENSE) {
         float v[NB / 2];  // batch rows 2i + (lane >> 4)
 #pragma unroll
@@ -1200,6 +1198,9 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
         }
         __syncwarp();
         if (lane == 0) st_release_shared(&folded[tb], fl / kFoldBufs + 1);
+        locate(gt, cj);
+        const Job &job = p.jobs[cj];
+        const int row = (gt - p.tcum[cj]) * kR + r16;
 #pragma unroll
         for (int i = 0; i < NB / 2; i++) {
           const int b = 2 * i + (lane >> 4);
@@ -1217,6 +1218,9 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
       for (int k = 0; k < npairs; k++) v += src[k * 16 * NB];
       __syncwarp();
       if (lane == 0) st_release_shared(&folded[tb], fl / kFoldBufs + 1);
+      locate(gt, cj);
+      const Job &job = p.jobs[cj];
+      const int row = (gt - p.tcum[cj]) * kR + r16;
       if (b < NB && row < job.out_dim) {
         if (p.part_keys) {
           const long long key = top1_key(v, (uint32_t)(p.index_base + row));
@@ -1298,6 +1302,7 @@ int sm_count() {
 }
 
 int g_imma_force_pair = 0;  // diagnostics: 0 = automatic, 1 / 2 = superblocks per item
+int g_imma_min_splits = 1;  // diagnostics: at least this many column ranges per row
 
 template <int TYPE>
 bool make_plan_pair(int in_dim, int nb, int pair, Params &p, size_t &smem) {
@@ -1373,7 +1378,7 @@ int launch_instance(const Params &p, size_t smem, int grid, cudaStream_t s) {
 template <int TYPE>
 int column_splits(int in_dim, int nb) {
   const int nblk = in_dim / 256;
-  for (int n = 1; n <= 8 && n <= nblk; n++) {
+  for (int n = g_imma_min_splits < nblk ? g_imma_min_splits : nblk; n <= 8 && n <= nblk; n++) {
     Params p{};
     size_t smem = 0;
     if (make_plan<TYPE>((nblk + n - 1) / n * 256, nb, p, smem)) return n;
@@ -1492,6 +1497,7 @@ int gemv_typed(int njobs, const void *const *d_w, const float *d_x, const float 
 
 void gemv_imma_set_debug(int mode) { g_imma_debug = mode; }
 void gemv_imma_set_pair(int pair) { g_imma_force_pair = pair; }
+void gemv_imma_set_min_splits(int n) { g_imma_min_splits = n < 1 ? 1 : n; }
 
 bool gemv_imma_supports(int type, const void *d_w, const float *d_x, int in_dim, int batch, bool top1) {
   if (type != kQ8_0 && type != kQ4_K && type != kQ5_K && type != kQ6_K) return false;

@@ -161,6 +161,7 @@ unsigned gemv_imma_timeouts();
 unsigned gemm_prefill_timeouts();
 void gemv_imma_set_debug(int mode);
 void gemv_imma_set_pair(int pair);
+void gemv_imma_set_min_splits(int n);
 void gemm_prefill_set_tile(int bn);
 
 // Kernel selection (dispatch.cu): picks the tiled kernel when the shape allows it, else the
