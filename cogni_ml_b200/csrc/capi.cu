@@ -60,6 +60,10 @@ int cogni_qmm_set_kernel_choice(int choice) {
     gemm_prefill_set_tile(choice == 48 ? 0 : 64 << (choice - 48));
     return COGNI_QMM_OK;
   }
+  if (choice >= 52 && choice <= 54) {  // prefill split along K: automatic / never / wherever allowed
+    gemm_prefill_set_split(choice - 52);
+    return COGNI_QMM_OK;
+  }
   if (choice >= 27 && choice <= 30) {  // at least 1 .. 4 column ranges per row of the tiled GEMV
     gemv_imma_set_min_splits(choice - 26);
     return COGNI_QMM_OK;

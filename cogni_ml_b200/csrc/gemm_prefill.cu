@@ -45,6 +45,8 @@ struct GemmParams {
   const uint8_t *w;
   void *y;
   int m_rows, n_out, k_in, out_bf16;
+  int ks_per_split;  // k-steps per blockIdx.z; with two splits the partial tiles are added onto a zeroed y
+  int splits;
   long long row_bytes;
 };
 
@@ -321,7 +323,9 @@ __global__ void __launch_bounds__(threads_for(TYPE), 1)
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * kStages + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * kBM, m0 = blockIdx.y * BN;
-  const int nks = p.k_in / kBK;
+  // this CTA's k-steps: ks0 .. ks0 + nks - 1 (all of them unless the launch is split along K)
+  const int ks0 = blockIdx.z * p.ks_per_split;
+  const int nks = min(p.ks_per_split, p.k_in / kBK - ks0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; s++) {
@@ -352,7 +356,7 @@ __global__ void __launch_bounds__(threads_for(TYPE), 1)
 #pragma unroll
         for (int h = 0; h < kNSub; h++)
           tma_load_2d(smem_u32(smem + s * kStageBytes + kATile + h * kNMma * kBK * 2), &tmap_x,
-                      ks * kBK, m0 + h * kNMma, full);
+                      (ks0 + ks) * kBK, m0 + h * kNMma, full);
       }
     }
   } else if (warp == 1) {
@@ -385,10 +389,10 @@ __global__ void __launch_bounds__(threads_for(TYPE), 1)
     const uint8_t *row = p.w + (long long)(valid ? n0 + r : 0) * p.row_bytes;
     Raw<TYPE> cur[kHalves], nxt[kHalves];
     auto fetch_all = [&](int ks, Raw<TYPE>(&dst)[kHalves]) {
-      fetch_raw<TYPE>(row, ks, h0, dst[0]);
+      fetch_raw<TYPE>(row, ks0 + ks, h0, dst[0]);
       if constexpr (kHalves == 2) {
         if constexpr (TYPE == kQ6_K) {
-          fetch_raw<TYPE, false>(row, ks, 1, dst[1]);
+          fetch_raw<TYPE, false>(row, ks0 + ks, 1, dst[1]);
 #pragma unroll
           for (int w = 0; w < 8; w++) dst[1].qh[w] = dst[0].qh[w];
           dst[1].sc = dst[0].sc;
@@ -405,7 +409,7 @@ __global__ void __launch_bounds__(threads_for(TYPE), 1)
       mbar_wait(smem_u32(&bars[2 * kStages + s]), ((ks / kStages) & 1) ^ 1);
 #pragma unroll
       for (int i = 0; i < kHalves; i++)
-        expand_kstep<TYPE>(cur[i], ks, h0 + i, smem + s * kStageBytes, r, valid);
+        expand_kstep<TYPE>(cur[i], ks0 + ks, h0 + i, smem + s * kStageBytes, r, valid);
       fence_async_smem();                                   // generic-proxy writes -> tensor core
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars[s]));
@@ -433,7 +437,9 @@ __global__ void __launch_bounds__(threads_for(TYPE), 1)
           const int m = m0 + c0 + jj;
           if (m < p.m_rows) {
             const float f = __uint_as_float(v[jj]);
-            if (p.out_bf16)
+            if (p.splits > 1)  // two partial tiles onto zeros: the sum does not depend on their order
+              atomicAdd(reinterpret_cast<float *>(p.y) + (long long)m * p.n_out + n, f);
+            else if (p.out_bf16)
               reinterpret_cast<__nv_bfloat16 *>(p.y)[(long long)m * p.n_out + n] = __float2bfloat16_rn(f);
             else
               reinterpret_cast<float *>(p.y)[(long long)m * p.n_out + n] = f;
@@ -467,10 +473,11 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 int g_prefill_force_bn = 0;  // diagnostics: 0 = automatic, else the token-tile width to use
+int g_prefill_force_split = 0;  // diagnostics: 0 = automatic, 1 = never split along K, 2 = split where allowed
 
 template <int TYPE, int BN>
 int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows, int n_out,
-           int k_in, cudaStream_t s) {
+           int k_in, int splits, cudaStream_t s) {
   EncodeTiledFn encode = encode_tiled_fn();
   if (!encode) return COGNI_QMM_ERR_DEVICE;
   CUtensorMap tmap;
@@ -498,7 +505,14 @@ int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows
   p.m_rows = m_rows; p.n_out = n_out; p.k_in = k_in;
   p.out_bf16 = out_type == COGNI_QMM_OUT_BF16;
   p.row_bytes = (long long)(k_in / 256) * BlockGeom<TYPE>::bytes;
-  dim3 grid((n_out + kBM - 1) / kBM, (m_rows + BN - 1) / BN);
+  const int nks = k_in / kBK;
+  p.splits = splits;
+  p.ks_per_split = splits > 1 ? ((nks + splits - 1) / splits + 3) / 4 * 4 : nks;  // whole superblocks
+  if (splits > 1) {
+    cudaError_t e = cudaMemsetAsync(d_y, 0, (size_t)m_rows * n_out * sizeof(float), s);
+    if (e != cudaSuccess) return (int)e;
+  }
+  dim3 grid((n_out + kBM - 1) / kBM, (m_rows + BN - 1) / BN, splits);
   gemm_prefill_kernel<TYPE, BN><<<grid, threads_for(TYPE), smem, s>>>(tmap, p);
   return (int)cudaGetLastError();
 }
@@ -520,20 +534,34 @@ int launch_typed(const void *d_w, const void *d_x, void *d_y, int out_type, int 
   const long long row_tiles = (n_out + kBM - 1) / kBM;
   const double rel256 = TYPE == kQ4_K ? 1.27 : TYPE == kQ5_K ? 1.2 : 1.1;
   const double rel512 = TYPE == kQ4_K ? 1.97 : TYPE == kQ5_K ? 1.6 : 1.15;
-  auto cost = [&](int bn, double rel) {
-    const long long tiles = row_tiles * ((m_rows + bn - 1) / bn);
-    return (double)((tiles + sms - 1) / sms) * rel;
+  // Few row tiles against many SMs (a down projection at a short prompt): two CTAs per tile take
+  // half of K each and add their partial tiles onto a zeroed f32 y.  Two addends commute, so the
+  // result stays independent of the order; more splits would not.  The price is the memset of y
+  // and read-modify-write instead of plain stores: about 12 bytes of HBM traffic per output
+  // element, weighed here against the measured time of a 128-token tile's k-step (microseconds).
+  const bool may_split = out_type == COGNI_QMM_OUT_F32 && k_in / kBK >= 16 && g_prefill_force_split != 1;
+  const double us_per_kstep = TYPE == kQ4_K ? 0.58 : TYPE == kQ5_K ? 0.75 : 1.11;
+  const double tile_us = us_per_kstep * (k_in / kBK);
+  const double split_us = 12.0 * (double)m_rows * (double)n_out / 6.0e6;
+  auto cost = [&](int bn, double rel, int splits) {
+    const long long tiles = row_tiles * ((m_rows + bn - 1) / bn) * splits;
+    return (double)((tiles + sms - 1) / sms) * rel * tile_us / splits + (splits > 1 ? split_us : 0.0);
   };
-  int bn = g_prefill_force_bn;
-  if (bn == 0) {
-    bn = 128;
-    double best = cost(128, 1.0);
-    if (cost(256, rel256) <= best) { best = cost(256, rel256); bn = 256; }
-    if (cost(512, rel512) <= best) { best = cost(512, rel512); bn = 512; }
+  const int widths[3] = {128, 256, 512};
+  const double rels[3] = {1.0, rel256, rel512};
+  int bn = 0, splits = 1;
+  double best = 1e30;
+  for (int i = 0; i < 3; i++) {
+    if (g_prefill_force_bn && g_prefill_force_bn != widths[i]) continue;
+    for (int sp = 1; sp <= (may_split ? 2 : 1); sp++) {
+      if (g_prefill_force_split == 2 && may_split && sp != 2) continue;
+      const double c = cost(widths[i], rels[i], sp);
+      if (c <= best) { best = c; bn = widths[i]; splits = sp; }
+    }
   }
-  if (bn == 512) return launch<TYPE, 512>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, s);
-  if (bn == 256) return launch<TYPE, 256>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, s);
-  return launch<TYPE, 128>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, s);
+  if (bn == 512) return launch<TYPE, 512>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
+  if (bn == 256) return launch<TYPE, 256>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
+  return launch<TYPE, 128>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
 }
 
 }  // namespace
@@ -549,6 +577,7 @@ int launch_gemm_prefill(int type, const void *d_w, const void *d_x_bf16, void *d
 }
 
 void gemm_prefill_set_tile(int bn) { g_prefill_force_bn = bn; }
+void gemm_prefill_set_split(int mode) { g_prefill_force_split = mode; }
 
 unsigned gemm_prefill_timeouts() {
   unsigned v = 0;

@@ -163,6 +163,7 @@ void gemv_imma_set_debug(int mode);
 void gemv_imma_set_pair(int pair);
 void gemv_imma_set_min_splits(int n);
 void gemm_prefill_set_tile(int bn);
+void gemm_prefill_set_split(int mode);
 
 // Kernel selection (dispatch.cu): picks the tiled kernel when the shape allows it, else the
 // general row-per-warp kernel.

@@ -61,7 +61,8 @@ const char *cogni_qmm_status_string(int status);
  * others stream / decode only, with or without the weight copies: results invalid), 24-26
  * superblocks per GEMV work item (automatic / 1 / 2), 27-30 at least 1 .. 4 column ranges per
  * row of the tiled GEMV (27 = the default), 32-47 raw diagnostic bits (results
- * invalid), 48-51 prefill token-tile width (automatic / 128 / 256 / 512).
+ * invalid), 48-51 prefill token-tile width (automatic / 128 / 256 / 512),
+ * 52-54 prefill split along K (automatic / never / wherever it is allowed).
  * cogni_qmm_wait_timeouts: how many bounded device-side waits have expired since the library
  * was loaded (0 in a healthy process; a non-zero value means the results of some launch are
  * invalid).  Synchronises the device. */

@@ -58,6 +58,26 @@ def test_gemm_every_token_tile_width(cuda, oracle, engine, tile, qtype, m, n, k)
     assert engine.lib.cogni_qmm_wait_timeouts() == 0
 
 
+@pytest.mark.parametrize("tile", [128, 256, 512])
+@pytest.mark.parametrize("qtype,m,n,k", [(Q6_K, 513, 128, 4096), (Q4_K, 300, 260, 4352),
+                                         (Q5_K, 64, 128, 8192)])
+def test_gemm_split_along_k(cuda, oracle, engine, tile, qtype, m, n, k):
+    """Two CTAs per tile, half of K each, partial tiles added onto a zeroed y (chosen by the host
+    when there are few row tiles for the SMs; forced here).  k = 4352 gives unequal halves."""
+    engine.lib.cogni_qmm_set_kernel_choice({128: 49, 256: 50, 512: 51}[tile])
+    engine.lib.cogni_qmm_set_kernel_choice(54)
+    try:
+        w, x, y, ref = run_case(cuda, oracle, qtype, m, n, k, seed=17)
+        _, _, y2, _ = run_case(cuda, oracle, qtype, m, n, k, seed=17)
+    finally:
+        engine.lib.cogni_qmm_set_kernel_choice(48)
+        engine.lib.cogni_qmm_set_kernel_choice(52)
+    assert not np.isnan(y).any()
+    assert np.abs(y - ref).max() <= 1e-4 * np.abs(ref).max()
+    assert np.array_equal(y, y2), "two addends commute: the split result must be reproducible"
+    assert engine.lib.cogni_qmm_wait_timeouts() == 0
+
+
 @pytest.mark.parametrize("qtype,n,k", [(Q4_K, 1024, 4096), (Q6_K, 512, 12288)])
 def test_gemm_within_stated_tolerance_of_cpu_quant_matmul(cuda, oracle, qtype, n, k):
     m = 512
