@@ -60,6 +60,10 @@ int cogni_qmm_set_kernel_choice(int choice) {
     gemm_prefill_set_tile(choice == 48 ? 0 : 64 << (choice - 48));
     return COGNI_QMM_OK;
   }
+  if (choice == 55 || choice == 56) {  // Q6_K prefill: raw superblocks staged by TMA (55, default) or read directly (56)
+    gemm_prefill_set_stage_raw(choice == 55);
+    return COGNI_QMM_OK;
+  }
   if (choice >= 52 && choice <= 54) {  // prefill split along K: automatic / never / wherever allowed
     gemm_prefill_set_split(choice - 52);
     return COGNI_QMM_OK;

@@ -33,7 +33,15 @@ namespace {
 constexpr int kBM = 128;      // weight rows per tile (UMMA M)
 constexpr int kBK = 64;       // k elements per stage: 128 bytes of bf16 = one swizzle row
 // stages of the ring: four 48 KB stages for 256-token tiles, two 80 KB stages for 512-token tiles
-__host__ __device__ constexpr int stages_for(int bn) { return bn > 256 ? 2 : 4; }
+__host__ __device__ constexpr int stages_for(int bn, bool staged = false) {
+  return bn > 256 ? 2 : (staged && bn == 256 ? 3 : 4);
+}
+// Staged raw superblocks (Q6_K whose rows are multiples of 16 bytes): per superblock column the
+// 256-byte window that holds the 210-byte block of each of the tile's 128 rows, as two TMA boxes
+// of 128 rows x 128 bytes (128-byte swizzle), double-buffered.
+constexpr int kRawBox = 128 * 128;
+constexpr int kRawStage = 2 * kRawBox;
+constexpr int kRawBytes = 2 * kRawStage;
 // Dequant warps: eight (two threads per tile row, one per 32-element half of a k-step) where the
 // expansion arithmetic bounds the kernel (Q4_K, Q5_K); four (one thread per row, both halves) for
 // Q6_K, whose two halves share the qh bytes and whose loads are the bound (measured both ways).
@@ -186,6 +194,45 @@ __device__ __forceinline__ void ldg_8words_wide(const uint8_t *p, uint32_t (&out
   }
 }
 
+// Row r of a staged raw window: 16-byte chunk w (0 .. 15) of the 256-byte window.
+__device__ __forceinline__ uint4 raw_chunk(const uint8_t *win, int r, int w) {
+  return *reinterpret_cast<const uint4 *>(win + (w >> 3) * kRawBox + r * 128 + (((w & 7) ^ (r & 7)) << 4));
+}
+// N (<= 8) 32-bit words starting at the even byte offset `off` of row r's window (off is the same
+// for every row of the tile): aligned 16-byte chunks + funnel shifts.
+template <int N>
+__device__ __forceinline__ void lds_words(const uint8_t *win, int r, int off, uint32_t (&out)[N]) {
+  constexpr int NC = (4 * N + 14) / 16 + 1;  // chunks that can be touched
+  uint32_t w[4 * NC + 1];
+  const int c0 = off >> 4;
+#pragma unroll
+  for (int i = 0; i < NC; i++) {
+    // the last chunk is only needed when the words run into it; the window has 16 chunks
+    const uint4 v = raw_chunk(win, r, min(c0 + i, 15));
+    w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+  }
+  w[4 * NC] = 0;
+  const uint32_t sh = (uint32_t)(off & 2) * 8;
+  switch ((off & 15) >> 2) {
+    case 0:
+#pragma unroll
+      for (int i = 0; i < N; i++) out[i] = __funnelshift_r(w[i], w[i + 1], sh);
+      break;
+    case 1:
+#pragma unroll
+      for (int i = 0; i < N; i++) out[i] = __funnelshift_r(w[i + 1], w[i + 2], sh);
+      break;
+    case 2:
+#pragma unroll
+      for (int i = 0; i < N; i++) out[i] = __funnelshift_r(w[i + 2], w[i + 3], sh);
+      break;
+    default:
+#pragma unroll
+      for (int i = 0; i < N; i++) out[i] = __funnelshift_r(w[i + 3], w[i + 4], sh);
+      break;
+  }
+}
+
 // The raw bytes one thread needs to rebuild 64 consecutive weights (one k-step) of its row.
 template <int TYPE> struct Raw;
 template <> struct Raw<kQ4_K> { uint4 hdr, q0, q1; };
@@ -236,6 +283,27 @@ __device__ __forceinline__ void scale_min_regs(const uint4 &h, int s, float &sc,
   }
   sc = (float)a;
   mn = (float)b;
+}
+
+// Q6_K, staged: both halves of k-step j (= ks & 3) of row r from the superblock's window in
+// shared memory; pad = offset of the 210-byte block inside the window.
+__device__ __forceinline__ void fetch_staged_q6(const uint8_t *win, int r, int pad, int j,
+                                                Raw<kQ6_K> (&dst)[2]) {
+  const int n = j >> 1;
+  lds_words<8>(win, r, pad + 64 * n, dst[0].ql);
+  lds_words<8>(win, r, pad + 64 * n + 32, dst[1].ql);
+  lds_words<8>(win, r, pad + 128 + 32 * n, dst[0].qh);
+  uint32_t scw[1];
+  lds_words<1>(win, r, pad + 192 + 8 * n + 4 * (j & 1), scw);
+  const int doff = pad + 208;
+  const uint32_t d = *reinterpret_cast<const unsigned short *>(
+      win + (doff >> 7) * kRawBox + r * 128 + ((((doff >> 4) & 7) ^ (r & 7)) << 4) + (doff & 15));
+  dst[0].sc = scw[0];
+  dst[0].d = d;
+#pragma unroll
+  for (int w = 0; w < 8; w++) dst[1].qh[w] = dst[0].qh[w];
+  dst[1].sc = scw[0];
+  dst[1].d = d;
 }
 
 // Rebuilds half h (32 weights: chunks 4h .. 4h+3) of k-step ks of tile row r as bf16 and stores
@@ -305,10 +373,12 @@ __device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, int h
 }
 
 // ---------------------------------------------------------------------------- the kernel
-template <int TYPE, int BN>
+template <int TYPE, int BN, bool STAGED>
 __global__ void __launch_bounds__(threads_for(TYPE), 1)
-    gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
-  constexpr int kStages = stages_for(BN);
+    gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                        const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) {
+  static_assert(!STAGED || TYPE == kQ6_K, "raw superblocks are staged for Q6_K only");
+  constexpr int kStages = stages_for(BN, STAGED);
   constexpr int kDequantWarps = dequant_warps(TYPE), kHalves = 8 / kDequantWarps;  // halves per thread
   constexpr int kBTile = BN * kBK * 2;
   constexpr int kStageBytes = kATile + kBTile;
@@ -318,9 +388,12 @@ __global__ void __launch_bounds__(threads_for(TYPE), 1)
   extern __shared__ uint8_t smem_raw[];
   // stage tiles must sit on 1024-byte boundaries (the swizzle pattern repeats every 1024 bytes)
   uint8_t *smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kStages * kStageBytes);
-  // bars: full_a[S] | full_b[S] | empty[S] | acc_full ; then the TMEM base address slot
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * kStages + 1);
+  uint8_t *raw_win = smem + kStages * kStageBytes;  // STAGED: two raw stages of two boxes each
+  uint64_t *bars = reinterpret_cast<uint64_t *>(raw_win + (STAGED ? kRawBytes : 0));
+  // bars: full_a[S] | full_b[S] | empty[S] | acc_full | raw_full[2] | raw_empty[2]; then the TMEM
+  // base address slot
+  uint64_t *raw_bars = bars + 3 * kStages + 1;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(raw_bars + 4);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * kBM, m0 = blockIdx.y * BN;
   // this CTA's k-steps: ks0 .. ks0 + nks - 1 (all of them unless the launch is split along K)
@@ -334,6 +407,12 @@ __global__ void __launch_bounds__(threads_for(TYPE), 1)
       mbar_init(smem_u32(&bars[2 * kStages + s]), 1);      // empty: tcgen05.commit
     }
     mbar_init(smem_u32(&bars[3 * kStages]), 1);            // accumulator complete
+    if constexpr (STAGED) {
+      mbar_init(smem_u32(&raw_bars[0]), 1);                // raw_full: the issuing thread + bytes
+      mbar_init(smem_u32(&raw_bars[1]), 1);
+      mbar_init(smem_u32(&raw_bars[2]), kDequantWarps);    // raw_empty: one arrive per dequant warp
+      mbar_init(smem_u32(&raw_bars[3]), kDequantWarps);
+    }
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -402,19 +481,59 @@ __global__ void __launch_bounds__(threads_for(TYPE), 1)
         }
       }
     };
-    fetch_all(0, cur);
-    for (int ks = 0; ks < nks; ks++) {
-      const int s = ks % kStages;
-      if (ks + 1 < nks) fetch_all(ks + 1, nxt);             // in flight while this k-step expands
-      mbar_wait(smem_u32(&bars[2 * kStages + s]), ((ks / kStages) & 1) ^ 1);
+    if constexpr (STAGED) {
+      // One thread keeps the next superblock column's raw windows in flight: superblock sb of the
+      // row starts 210 * sb bytes into it (rows are multiples of 16 bytes here), its window at
+      // the 16-byte boundary below.
+      const int sb0 = ks0 >> 2, nsb = (nks + 3) >> 2;
+      auto issue_raw = [&](int sbl) {
+        const int x0 = (210 * (sb0 + sbl)) & ~15;
+        const uint32_t full = smem_u32(&raw_bars[sbl & 1]);
+        mbar_arrive_expect_tx(full, kRawStage);
+        tma_load_2d(smem_u32(raw_win + (sbl & 1) * kRawStage), &tmap_w, x0, n0, full);
+        tma_load_2d(smem_u32(raw_win + (sbl & 1) * kRawStage + kRawBox), &tmap_w, x0 + 128, n0, full);
+      };
+      const bool issuer = threadIdx.x == 64;
+      if (issuer) issue_raw(0);
+      for (int ks = 0; ks < nks; ks++) {
+        const int s = ks % kStages;
+        const int sbl = ks >> 2, buf = sbl & 1;
+        if ((ks & 3) == 0) {
+          if (issuer && sbl + 1 < nsb) {
+            // the other buffer was last used by superblock sbl - 1
+            if (sbl >= 1) mbar_wait(smem_u32(&raw_bars[2 + (buf ^ 1)]), ((sbl - 1) >> 1) & 1);
+            issue_raw(sbl + 1);
+          }
+          mbar_wait(smem_u32(&raw_bars[buf]), (sbl >> 1) & 1);
+        }
+        fetch_staged_q6(raw_win + buf * kRawStage, r, (210 * (sb0 + sbl)) & 15, (ks0 + ks) & 3, cur);
+        if ((ks & 3) == 3 || ks == nks - 1) {  // this warp has read all it needs of the window
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&raw_bars[2 + buf]));
+        }
+        mbar_wait(smem_u32(&bars[2 * kStages + s]), ((ks / kStages) & 1) ^ 1);
 #pragma unroll
-      for (int i = 0; i < kHalves; i++)
-        expand_kstep<TYPE>(cur[i], ks0 + ks, h0 + i, smem + s * kStageBytes, r, valid);
-      fence_async_smem();                                   // generic-proxy writes -> tensor core
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bars[s]));
+        for (int i = 0; i < kHalves; i++)
+          expand_kstep<TYPE>(cur[i], ks0 + ks, h0 + i, smem + s * kStageBytes, r, valid);
+        fence_async_smem();                                   // generic-proxy writes -> tensor core
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars[s]));
+      }
+    } else {
+      fetch_all(0, cur);
+      for (int ks = 0; ks < nks; ks++) {
+        const int s = ks % kStages;
+        if (ks + 1 < nks) fetch_all(ks + 1, nxt);             // in flight while this k-step expands
+        mbar_wait(smem_u32(&bars[2 * kStages + s]), ((ks / kStages) & 1) ^ 1);
 #pragma unroll
-      for (int i = 0; i < kHalves; i++) cur[i] = nxt[i];
+        for (int i = 0; i < kHalves; i++)
+          expand_kstep<TYPE>(cur[i], ks0 + ks, h0 + i, smem + s * kStageBytes, r, valid);
+        fence_async_smem();                                   // generic-proxy writes -> tensor core
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars[s]));
+#pragma unroll
+        for (int i = 0; i < kHalves; i++) cur[i] = nxt[i];
+      }
     }
 
     // ---------------------------------------------------------------- epilogue
@@ -473,14 +592,27 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 int g_prefill_force_bn = 0;  // diagnostics: 0 = automatic, else the token-tile width to use
+int g_prefill_stage_raw = 1;    // diagnostics: 0 = Q6_K dequant threads read global memory directly
 int g_prefill_force_split = 0;  // diagnostics: 0 = automatic, 1 = never split along K, 2 = split where allowed
 
-template <int TYPE, int BN>
+template <int TYPE, int BN, bool STAGED>
 int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows, int n_out,
            int k_in, int splits, cudaStream_t s) {
   EncodeTiledFn encode = encode_tiled_fn();
   if (!encode) return COGNI_QMM_ERR_DEVICE;
-  CUtensorMap tmap;
+  const long long row_bytes = (long long)(k_in / 256) * BlockGeom<TYPE>::bytes;
+  CUtensorMap tmap, tmap_w;
+  if (STAGED) {
+    // the weights as a byte matrix [n_out, row_bytes]: boxes of 128 rows x 128 bytes
+    const cuuint64_t wdims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)n_out};
+    const cuuint64_t wstrides[1] = {(cuuint64_t)row_bytes};
+    const cuuint32_t wbox[2] = {128, 128};
+    const cuuint32_t westr[2] = {1, 1};
+    CUresult wr = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(d_w), wdims,
+                         wstrides, wbox, westr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (wr != CUDA_SUCCESS) return (int)wr;
+  }
   const cuuint64_t dims[2] = {(cuuint64_t)k_in, (cuuint64_t)m_rows};
   const cuuint64_t strides[1] = {(cuuint64_t)k_in * 2};
   const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)(BN > 256 ? 256 : BN)};
@@ -489,12 +621,13 @@ int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows
                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (cr != CUDA_SUCCESS) return (int)cr;
-  constexpr int smem = stages_for(BN) * (kATile + BN * kBK * 2) + 1024 /*alignment*/ + 256 /*barriers*/;
+  constexpr int smem = stages_for(BN, STAGED) * (kATile + BN * kBK * 2) + (STAGED ? kRawBytes : 0) +
+                       1024 /*alignment*/ + 256 /*barriers*/;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_prefill_kernel<TYPE, BN>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_prefill_kernel<TYPE, BN, STAGED>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured[dev] = true;
@@ -504,7 +637,8 @@ int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows
   p.y = d_y;
   p.m_rows = m_rows; p.n_out = n_out; p.k_in = k_in;
   p.out_bf16 = out_type == COGNI_QMM_OUT_BF16;
-  p.row_bytes = (long long)(k_in / 256) * BlockGeom<TYPE>::bytes;
+  p.row_bytes = row_bytes;
+  if (!STAGED) tmap_w = tmap;  // unused by the kernel
   const int nks = k_in / kBK;
   p.splits = splits;
   p.ks_per_split = splits > 1 ? ((nks + splits - 1) / splits + 3) / 4 * 4 : nks;  // whole superblocks
@@ -513,7 +647,7 @@ int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid((n_out + kBM - 1) / kBM, (m_rows + BN - 1) / BN, splits);
-  gemm_prefill_kernel<TYPE, BN><<<grid, threads_for(TYPE), smem, s>>>(tmap, p);
+  gemm_prefill_kernel<TYPE, BN, STAGED><<<grid, threads_for(TYPE), smem, s>>>(tmap, tmap_w, p);
   return (int)cudaGetLastError();
 }
 
@@ -559,9 +693,19 @@ int launch_typed(const void *d_w, const void *d_x, void *d_y, int out_type, int 
       if (c <= best) { best = c; bn = widths[i]; splits = sp; }
     }
   }
-  if (bn == 512) return launch<TYPE, 512>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
-  if (bn == 256) return launch<TYPE, 256>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
-  return launch<TYPE, 128>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
+  // Q6_K rows that are multiples of 16 bytes (in_dim a multiple of 2048) can be fetched by TMA:
+  // the raw superblocks of the tile's rows are then staged through shared memory
+  if constexpr (TYPE == kQ6_K) {
+    const long long row_bytes = (long long)(k_in / 256) * BlockGeom<TYPE>::bytes;
+    if (row_bytes % 16 == 0 && g_prefill_stage_raw) {
+      if (bn == 512) return launch<TYPE, 512, true>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
+      if (bn == 256) return launch<TYPE, 256, true>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
+      return launch<TYPE, 128, true>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
+    }
+  }
+  if (bn == 512) return launch<TYPE, 512, false>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
+  if (bn == 256) return launch<TYPE, 256, false>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
+  return launch<TYPE, 128, false>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
 }
 
 }  // namespace
@@ -578,6 +722,7 @@ int launch_gemm_prefill(int type, const void *d_w, const void *d_x_bf16, void *d
 
 void gemm_prefill_set_tile(int bn) { g_prefill_force_bn = bn; }
 void gemm_prefill_set_split(int mode) { g_prefill_force_split = mode; }
+void gemm_prefill_set_stage_raw(int on) { g_prefill_stage_raw = on; }
 
 unsigned gemm_prefill_timeouts() {
   unsigned v = 0;

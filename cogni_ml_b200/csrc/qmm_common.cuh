@@ -164,6 +164,7 @@ void gemv_imma_set_pair(int pair);
 void gemv_imma_set_min_splits(int n);
 void gemm_prefill_set_tile(int bn);
 void gemm_prefill_set_split(int mode);
+void gemm_prefill_set_stage_raw(int on);
 
 // Kernel selection (dispatch.cu): picks the tiled kernel when the shape allows it, else the
 // general row-per-warp kernel.

@@ -59,6 +59,26 @@ def test_gemm_every_token_tile_width(cuda, oracle, engine, tile, qtype, m, n, k)
 
 
 @pytest.mark.parametrize("tile", [128, 256, 512])
+@pytest.mark.parametrize("m,n,k", [(200, 200, 2048), (300, 1000, 6144), (64, 37, 4096)])
+def test_gemm_q6k_staged_superblocks(cuda, oracle, engine, tile, m, n, k):
+    """Q6_K rows that are multiples of 16 bytes (in_dim a multiple of 2048) are fetched by TMA into
+    shared-memory windows and expanded from there; rows beyond out_dim are zero-filled boxes.
+    The result must equal the direct-read path bit for bit (same expansion, same MMA order)."""
+    engine.lib.cogni_qmm_set_kernel_choice({128: 49, 256: 50, 512: 51}[tile])
+    try:
+        w, x, y, ref = run_case(cuda, oracle, Q6_K, m, n, k, seed=19)
+        engine.lib.cogni_qmm_set_kernel_choice(56)
+        _, _, y_direct, _ = run_case(cuda, oracle, Q6_K, m, n, k, seed=19)
+    finally:
+        engine.lib.cogni_qmm_set_kernel_choice(55)
+        engine.lib.cogni_qmm_set_kernel_choice(48)
+    assert not np.isnan(y).any()
+    assert np.abs(y - ref).max() <= 1e-4 * np.abs(ref).max()
+    assert np.array_equal(y, y_direct)
+    assert engine.lib.cogni_qmm_wait_timeouts() == 0
+
+
+@pytest.mark.parametrize("tile", [128, 256, 512])
 @pytest.mark.parametrize("qtype,m,n,k", [(Q6_K, 513, 128, 4096), (Q4_K, 300, 260, 4352),
                                          (Q5_K, 64, 128, 8192)])
 def test_gemm_split_along_k(cuda, oracle, engine, tile, qtype, m, n, k):
