@@ -3,12 +3,15 @@
 //     y[m, n] = sum_k bf16(x[m, k]) * bf16(dequant(W[n, k]))        fp32 accumulation in TMEM
 //
 // One CTA computes a 128 (weight rows n) x BN (tokens m) tile of y^T, BN = 128, 256 or 512:
-//   * A operand = weights.  Eight dequant warps (two threads per row, one per 32-element half of
-//     a k-step; four warps, one thread per row, for Q6_K) read the raw GGUF superblocks of the
-//     tile's 128 rows straight from global memory
-//     (L2-resident across the token tiles), rebuild the f32 weight with the reference's
+//   * A operand = weights.  The raw GGUF superblocks of the tile's 128 rows reach shared memory by
+//     TMA, one superblock column at a time (the weights as a byte matrix [rows, row bytes]; double
+//     buffered), so the fetch is one instruction per column instead of one uncoalesced load per
+//     row and word.  Eight dequant warps (two threads per row, one per 32-element half of a
+//     k-step) read their row's block from there, rebuild the f32 weight with the reference's
 //     operation order (src/ml/gguf/dequant.cr), round it to bf16 and write a 128 x 64 K-major
-//     tile into shared memory in the 128-byte-swizzled canonical layout.
+//     tile into shared memory in the 128-byte-swizzled canonical layout.  Q6_K rows that are not
+//     multiples of 16 bytes (in_dim not a multiple of 2048) cannot be described to TMA: their
+//     threads read global memory directly (four warps, one thread per row).
 //   * B operand = activations.  One thread issues TMA tile loads (bf16 [<= 256 x 64] boxes,
 //     128-byte swizzle) per k-step.
 //   * One thread issues tcgen05.mma (kind::f16, M = 128, N = min(BN, 256), K = 16) four times per
@@ -18,9 +21,9 @@
 //     warp may read 32 TMEM lanes = 32 weight rows; the two warps of a lane quarter take half
 //     of the columns each) and store y[m, n]: for a fixed token a warp's 32 lanes write 32
 //     consecutive n, one 128-byte segment.
-// An mbarrier ring (four 48 KB stages, two 80 KB stages for BN = 512) decouples the three roles.
-// The dequant warps bound the kernel: wider token tiles do less dequant work per flop.  Every
-// wait is bounded (tma_pipe.cuh).
+// An mbarrier ring (up to four 48 KB stages, two 80 KB stages for BN = 512, as many as fit beside
+// the raw windows) decouples the three roles.  The dequant warps bound the kernel: wider token
+// tiles do less dequant work per flop.  Every wait is bounded (tma_pipe.cuh).
 #include <cuda.h>
 #include <cuda_bf16.h>
 
@@ -33,20 +36,32 @@ namespace {
 constexpr int kBM = 128;      // weight rows per tile (UMMA M)
 constexpr int kBK = 64;       // k elements per stage: 128 bytes of bf16 = one swizzle row
 // stages of the ring: four 48 KB stages for 256-token tiles, two 80 KB stages for 512-token tiles
-__host__ __device__ constexpr int stages_for(int bn, bool staged = false) {
-  return bn > 256 ? 2 : (staged && bn == 256 ? 3 : 4);
-}
-// Staged raw superblocks (Q6_K whose rows are multiples of 16 bytes): per superblock column the
-// 256-byte window that holds the 210-byte block of each of the tile's 128 rows, as two TMA boxes
-// of 128 rows x 128 bytes (128-byte swizzle), double-buffered.
+// Staged raw superblocks (rows that are multiples of 16 bytes): per superblock column the raw
+// block of each of the tile's 128 rows is fetched by TMA from the weights seen as a byte matrix,
+// double-buffered.  Q4_K / Q5_K: one box of 128 rows x 144 / 176 bytes, unswizzled (the row pitch
+// already spreads 16-byte loads of eight rows over all banks).  Q6_K: the 256-byte window around
+// the 210-byte block (it starts on a 2-byte boundary) as two boxes of 128 rows x 128 bytes with
+// the 128-byte swizzle.
 constexpr int kRawBox = 128 * 128;
-constexpr int kRawStage = 2 * kRawBox;
-constexpr int kRawBytes = 2 * kRawStage;
-// Dequant warps: eight (two threads per tile row, one per 32-element half of a k-step) where the
-// expansion arithmetic bounds the kernel (Q4_K, Q5_K); four (one thread per row, both halves) for
-// Q6_K, whose two halves share the qh bytes and whose loads are the bound (measured both ways).
-__host__ __device__ constexpr int dequant_warps(int type) { return type == kQ6_K ? 4 : 8; }
-__host__ __device__ constexpr int threads_for(int type) { return 64 + 32 * dequant_warps(type); }  // warp 0: TMA, warp 1: MMA + TMEM
+__host__ __device__ constexpr int raw_stage_bytes(int type) {
+  return type == kQ6_K ? 2 * kRawBox : 128 * (type == kQ4_K ? 144 : 176);
+}
+__host__ __device__ constexpr int raw_bytes(int type, bool staged) { return staged ? 2 * raw_stage_bytes(type) : 0; }
+// stages of the ring that fit beside the raw windows (227 KB per CTA)
+__host__ __device__ constexpr int stages_for(int bn, int raw = 0) {
+  const int want = bn > 256 ? 2 : 4;
+  const int fit = (227 * 1024 - 1024 - 256 - raw) / (128 * 64 * 2 + bn * 64 * 2);
+  return fit < want ? fit : want;
+}
+// Dequant warps: eight (two threads per tile row, one per 32-element half of a k-step); four (one
+// thread per row, both halves) for Q6_K read directly from global memory, whose two halves share
+// the qh bytes and whose loads are the bound there (measured both ways).
+__host__ __device__ constexpr int dequant_warps(int type, bool staged = false) {
+  return type == kQ6_K && !staged ? 4 : 8;
+}
+__host__ __device__ constexpr int threads_for(int type, bool staged = false) {
+  return 64 + 32 * dequant_warps(type, staged);  // warp 0: TMA, warp 1: MMA + TMEM
+}
 constexpr int kATile = kBM * kBK * 2;  // 16 KB
 
 struct GemmParams {
@@ -285,13 +300,30 @@ __device__ __forceinline__ void scale_min_regs(const uint4 &h, int s, float &sc,
   mn = (float)b;
 }
 
+// Q4_K / Q5_K, staged: the words of k-step j of the block at blk (shared memory, 16-byte aligned)
+template <int TYPE>
+__device__ __forceinline__ void fetch_raw_from(const uint8_t *blk, int j, Raw<TYPE> &r) {
+  if constexpr (TYPE == kQ4_K) {
+    r.hdr = *reinterpret_cast<const uint4 *>(blk);
+    r.q0 = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * j);
+    r.q1 = *reinterpret_cast<const uint4 *>(blk + 32 + 32 * j);
+  } else if constexpr (TYPE == kQ5_K) {
+    r.hdr = *reinterpret_cast<const uint4 *>(blk);
+    r.h0 = *reinterpret_cast<const uint4 *>(blk + 16);
+    r.h1 = *reinterpret_cast<const uint4 *>(blk + 32);
+    r.q0 = *reinterpret_cast<const uint4 *>(blk + 48 + 32 * j);
+    r.q1 = *reinterpret_cast<const uint4 *>(blk + 64 + 32 * j);
+  }
+}
+
 // Q6_K, staged: both halves of k-step j (= ks & 3) of row r from the superblock's window in
 // shared memory; pad = offset of the 210-byte block inside the window.
-__device__ __forceinline__ void fetch_staged_q6(const uint8_t *win, int r, int pad, int j,
-                                                Raw<kQ6_K> (&dst)[2]) {
+template <int NH>
+__device__ __forceinline__ void fetch_staged_q6(const uint8_t *win, int r, int pad, int j, int h0,
+                                                Raw<kQ6_K> (&dst)[NH]) {
   const int n = j >> 1;
-  lds_words<8>(win, r, pad + 64 * n, dst[0].ql);
-  lds_words<8>(win, r, pad + 64 * n + 32, dst[1].ql);
+  lds_words<8>(win, r, pad + 64 * n + 32 * h0, dst[0].ql);
+  if constexpr (NH == 2) lds_words<8>(win, r, pad + 64 * n + 32, dst[1].ql);
   lds_words<8>(win, r, pad + 128 + 32 * n, dst[0].qh);
   uint32_t scw[1];
   lds_words<1>(win, r, pad + 192 + 8 * n + 4 * (j & 1), scw);
@@ -300,10 +332,12 @@ __device__ __forceinline__ void fetch_staged_q6(const uint8_t *win, int r, int p
       win + (doff >> 7) * kRawBox + r * 128 + ((((doff >> 4) & 7) ^ (r & 7)) << 4) + (doff & 15));
   dst[0].sc = scw[0];
   dst[0].d = d;
+  if constexpr (NH == 2) {
 #pragma unroll
-  for (int w = 0; w < 8; w++) dst[1].qh[w] = dst[0].qh[w];
-  dst[1].sc = scw[0];
-  dst[1].d = d;
+    for (int w = 0; w < 8; w++) dst[1].qh[w] = dst[0].qh[w];
+    dst[1].sc = scw[0];
+    dst[1].d = d;
+  }
 }
 
 // Rebuilds half h (32 weights: chunks 4h .. 4h+3) of k-step ks of tile row r as bf16 and stores
@@ -374,12 +408,13 @@ __device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, int h
 
 // ---------------------------------------------------------------------------- the kernel
 template <int TYPE, int BN, bool STAGED>
-__global__ void __launch_bounds__(threads_for(TYPE), 1)
+__global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
     gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
                         const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) {
-  static_assert(!STAGED || TYPE == kQ6_K, "raw superblocks are staged for Q6_K only");
-  constexpr int kStages = stages_for(BN, STAGED);
-  constexpr int kDequantWarps = dequant_warps(TYPE), kHalves = 8 / kDequantWarps;  // halves per thread
+  constexpr int kRawStage = raw_stage_bytes(TYPE);
+  constexpr int kStages = stages_for(BN, raw_bytes(TYPE, STAGED));
+  static_assert(kStages >= 2, "at least two stages");
+  constexpr int kDequantWarps = dequant_warps(TYPE, STAGED), kHalves = 8 / kDequantWarps;  // halves per thread
   constexpr int kBTile = BN * kBK * 2;
   constexpr int kStageBytes = kATile + kBTile;
   // UMMA N is at most 256: a 512-token tile is two accumulators of 256 TMEM columns, fed by the
@@ -389,7 +424,7 @@ __global__ void __launch_bounds__(threads_for(TYPE), 1)
   // stage tiles must sit on 1024-byte boundaries (the swizzle pattern repeats every 1024 bytes)
   uint8_t *smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
   uint8_t *raw_win = smem + kStages * kStageBytes;  // STAGED: two raw stages of two boxes each
-  uint64_t *bars = reinterpret_cast<uint64_t *>(raw_win + (STAGED ? kRawBytes : 0));
+  uint64_t *bars = reinterpret_cast<uint64_t *>(raw_win + raw_bytes(TYPE, STAGED));
   // bars: full_a[S] | full_b[S] | empty[S] | acc_full | raw_full[2] | raw_empty[2]; then the TMEM
   // base address slot
   uint64_t *raw_bars = bars + 3 * kStages + 1;
@@ -487,11 +522,16 @@ __global__ void __launch_bounds__(threads_for(TYPE), 1)
       // the 16-byte boundary below.
       const int sb0 = ks0 >> 2, nsb = (nks + 3) >> 2;
       auto issue_raw = [&](int sbl) {
-        const int x0 = (210 * (sb0 + sbl)) & ~15;
         const uint32_t full = smem_u32(&raw_bars[sbl & 1]);
         mbar_arrive_expect_tx(full, kRawStage);
-        tma_load_2d(smem_u32(raw_win + (sbl & 1) * kRawStage), &tmap_w, x0, n0, full);
-        tma_load_2d(smem_u32(raw_win + (sbl & 1) * kRawStage + kRawBox), &tmap_w, x0 + 128, n0, full);
+        if constexpr (TYPE == kQ6_K) {
+          const int x0 = (210 * (sb0 + sbl)) & ~15;
+          tma_load_2d(smem_u32(raw_win + (sbl & 1) * kRawStage), &tmap_w, x0, n0, full);
+          tma_load_2d(smem_u32(raw_win + (sbl & 1) * kRawStage + kRawBox), &tmap_w, x0 + 128, n0, full);
+        } else {  // 144- and 176-byte blocks start on 16-byte boundaries
+          tma_load_2d(smem_u32(raw_win + (sbl & 1) * kRawStage), &tmap_w,
+                      BlockGeom<TYPE>::bytes * (sb0 + sbl), n0, full);
+        }
       };
       const bool issuer = threadIdx.x == 64;
       if (issuer) issue_raw(0);
@@ -506,7 +546,10 @@ __global__ void __launch_bounds__(threads_for(TYPE), 1)
           }
           mbar_wait(smem_u32(&raw_bars[buf]), (sbl >> 1) & 1);
         }
-        fetch_staged_q6(raw_win + buf * kRawStage, r, (210 * (sb0 + sbl)) & 15, (ks0 + ks) & 3, cur);
+        if constexpr (TYPE == kQ6_K)
+          fetch_staged_q6<kHalves>(raw_win + buf * kRawStage, r, (210 * (sb0 + sbl)) & 15, (ks0 + ks) & 3, h0, cur);
+        else  // the block of row r sits at r * block bytes: the global fetch code reads it as it is
+          fetch_raw_from<TYPE>(raw_win + buf * kRawStage + r * BlockGeom<TYPE>::bytes, (ks0 + ks) & 3, cur[0]);
         if ((ks & 3) == 3 || ks == nks - 1) {  // this warp has read all it needs of the window
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&raw_bars[2 + buf]));
@@ -606,10 +649,11 @@ int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows
     // the weights as a byte matrix [n_out, row_bytes]: boxes of 128 rows x 128 bytes
     const cuuint64_t wdims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)n_out};
     const cuuint64_t wstrides[1] = {(cuuint64_t)row_bytes};
-    const cuuint32_t wbox[2] = {128, 128};
+    const cuuint32_t wbox[2] = {TYPE == kQ6_K ? 128u : (cuuint32_t)BlockGeom<TYPE>::bytes, 128};
     const cuuint32_t westr[2] = {1, 1};
     CUresult wr = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(d_w), wdims,
-                         wstrides, wbox, westr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         wstrides, wbox, westr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         TYPE == kQ6_K ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (wr != CUDA_SUCCESS) return (int)wr;
   }
@@ -621,8 +665,8 @@ int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows
                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (cr != CUDA_SUCCESS) return (int)cr;
-  constexpr int smem = stages_for(BN, STAGED) * (kATile + BN * kBK * 2) + (STAGED ? kRawBytes : 0) +
-                       1024 /*alignment*/ + 256 /*barriers*/;
+  constexpr int smem = stages_for(BN, raw_bytes(TYPE, STAGED)) * (kATile + BN * kBK * 2) +
+                       raw_bytes(TYPE, STAGED) + 1024 /*alignment*/ + 256 /*barriers*/;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -647,7 +691,7 @@ int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid((n_out + kBM - 1) / kBM, (m_rows + BN - 1) / BN, splits);
-  gemm_prefill_kernel<TYPE, BN, STAGED><<<grid, threads_for(TYPE), smem, s>>>(tmap, tmap_w, p);
+  gemm_prefill_kernel<TYPE, BN, STAGED><<<grid, threads_for(TYPE, STAGED), smem, s>>>(tmap, tmap_w, p);
   return (int)cudaGetLastError();
 }
 
@@ -655,7 +699,7 @@ template <int TYPE>
 int launch_typed(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows, int n_out,
                  int k_in, cudaStream_t s) {
   // Token-tile width: wider tiles do less dequant work per flop (a tile's time is about 1 : 1.27 :
-  // 1.97 for 128 / 256 / 512 tokens of Q4_K, whose dequant is cheap, and 1 : 1.1 : 1.15 for Q6_K,
+  // 1.97 for 128 / 256 / 512 tokens of Q4_K, whose dequant is cheap, and 1 : 1.1 : 1.3 for Q6_K,
   // which is bound by it), narrower ones fill the SMs in fewer, fuller waves.  Pick the width
   // with the least waves x tile time.
   static int sms = 0;
@@ -667,14 +711,14 @@ int launch_typed(const void *d_w, const void *d_x, void *d_y, int out_type, int 
   }
   const long long row_tiles = (n_out + kBM - 1) / kBM;
   const double rel256 = TYPE == kQ4_K ? 1.27 : TYPE == kQ5_K ? 1.2 : 1.1;
-  const double rel512 = TYPE == kQ4_K ? 1.97 : TYPE == kQ5_K ? 1.6 : 1.15;
+  const double rel512 = TYPE == kQ4_K ? 1.97 : TYPE == kQ5_K ? 1.6 : 1.3;
   // Few row tiles against many SMs (a down projection at a short prompt): two CTAs per tile take
   // half of K each and add their partial tiles onto a zeroed f32 y.  Two addends commute, so the
   // result stays independent of the order; more splits would not.  The price is the memset of y
   // and read-modify-write instead of plain stores: about 12 bytes of HBM traffic per output
   // element, weighed here against the measured time of a 128-token tile's k-step (microseconds).
   const bool may_split = out_type == COGNI_QMM_OUT_F32 && k_in / kBK >= 16 && g_prefill_force_split != 1;
-  const double us_per_kstep = TYPE == kQ4_K ? 0.58 : TYPE == kQ5_K ? 0.75 : 1.11;
+  const double us_per_kstep = TYPE == kQ4_K ? 0.58 : TYPE == kQ5_K ? 0.75 : 0.84;
   const double tile_us = us_per_kstep * (k_in / kBK);
   const double split_us = 12.0 * (double)m_rows * (double)n_out / 6.0e6;
   auto cost = [&](int bn, double rel, int splits) {
@@ -693,11 +737,15 @@ int launch_typed(const void *d_w, const void *d_x, void *d_y, int out_type, int 
       if (c <= best) { best = c; bn = widths[i]; splits = sp; }
     }
   }
-  // Q6_K rows that are multiples of 16 bytes (in_dim a multiple of 2048) can be fetched by TMA:
-  // the raw superblocks of the tile's rows are then staged through shared memory
-  if constexpr (TYPE == kQ6_K) {
+  // Rows that are multiples of 16 bytes (always for Q4_K / Q5_K; Q6_K: in_dim a multiple of 2048)
+  // can be fetched by TMA: the raw superblocks of the tile's rows are then staged through shared
+  // memory
+  {
     const long long row_bytes = (long long)(k_in / 256) * BlockGeom<TYPE>::bytes;
-    if (row_bytes % 16 == 0 && g_prefill_stage_raw) {
+    // (Q4_K with 512-token tiles measured 5 % faster reading directly: its three 16-byte loads per
+    // thread and k-step are cheap enough, and the tile's two stages leave no slack for the extra
+    // hand-over)
+    if (row_bytes % 16 == 0 && g_prefill_stage_raw && !(TYPE == kQ4_K && bn == 512)) {
       if (bn == 512) return launch<TYPE, 512, true>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
       if (bn == 256) return launch<TYPE, 256, true>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
       return launch<TYPE, 128, true>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);

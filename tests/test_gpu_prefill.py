@@ -59,16 +59,19 @@ def test_gemm_every_token_tile_width(cuda, oracle, engine, tile, qtype, m, n, k)
 
 
 @pytest.mark.parametrize("tile", [128, 256, 512])
-@pytest.mark.parametrize("m,n,k", [(200, 200, 2048), (300, 1000, 6144), (64, 37, 4096)])
-def test_gemm_q6k_staged_superblocks(cuda, oracle, engine, tile, m, n, k):
-    """Q6_K rows that are multiples of 16 bytes (in_dim a multiple of 2048) are fetched by TMA into
-    shared-memory windows and expanded from there; rows beyond out_dim are zero-filled boxes.
-    The result must equal the direct-read path bit for bit (same expansion, same MMA order)."""
+@pytest.mark.parametrize("qtype,m,n,k", [(Q6_K, 200, 200, 2048), (Q6_K, 300, 1000, 6144),
+                                         (Q6_K, 64, 37, 4096), (Q4_K, 300, 1000, 1280),
+                                         (Q5_K, 130, 129, 768), (Q4_K, 600, 50, 256)])
+def test_gemm_staged_superblocks(cuda, oracle, engine, tile, qtype, m, n, k):
+    """Rows that are multiples of 16 bytes (Q4_K / Q5_K always, Q6_K when in_dim is a multiple of
+    2048) are fetched by TMA into shared memory and expanded from there; rows beyond out_dim are
+    zero-filled boxes.  The result must equal the direct-read path bit for bit (same expansion,
+    same MMA order)."""
     engine.lib.cogni_qmm_set_kernel_choice({128: 49, 256: 50, 512: 51}[tile])
     try:
-        w, x, y, ref = run_case(cuda, oracle, Q6_K, m, n, k, seed=19)
+        w, x, y, ref = run_case(cuda, oracle, qtype, m, n, k, seed=19)
         engine.lib.cogni_qmm_set_kernel_choice(56)
-        _, _, y_direct, _ = run_case(cuda, oracle, Q6_K, m, n, k, seed=19)
+        _, _, y_direct, _ = run_case(cuda, oracle, qtype, m, n, k, seed=19)
     finally:
         engine.lib.cogni_qmm_set_kernel_choice(55)
         engine.lib.cogni_qmm_set_kernel_choice(48)
