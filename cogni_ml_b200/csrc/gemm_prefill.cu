@@ -158,6 +158,38 @@ __device__ __forceinline__ float byte_f(uint32_t v, int i) {
 __device__ __forceinline__ float byte_f_m32(uint32_t v, int i) {
   return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7650 + i)) - 8388640.f;
 }
+// Packed pairs of f32 (sm_100 has two-wide f32 add / mul / fma: same IEEE results per element, half
+// the instructions in the expansion, which is what the dequant warps are bound by).
+__device__ __forceinline__ uint64_t f2_pack(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint32_t f2_to_bf16x2(uint64_t v) {
+  float a, b;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+  return pack_bf16(a, b);
+}
+// bytes (i, i+1) of v as the floats 2^23 + b, packed
+__device__ __forceinline__ uint64_t bytes2_biased(uint32_t v, int i) {
+  return f2_pack(__uint_as_float(__byte_perm(v, 0x4B000000u, 0x7650 + i)),
+                 __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7650 + i + 1)));
+}
 // Stores chunk c (8 consecutive k elements = 16 bytes) of tile row r at its swizzled position.
 __device__ __forceinline__ void store_chunk(uint8_t *tile, int r, int c, uint4 v) {
   *reinterpret_cast<uint4 *>(tile + r * 128 + ((c ^ (r & 7)) << 4)) = v;
@@ -365,6 +397,8 @@ __device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, int h
     float sc, mn;
     scale_min_regs(raw.hdr, 2 * j + h, sc, mn);
     const float d1 = __fmul_rn(d, sc), m1 = __fmul_rn(dmin, mn);
+    const uint64_t d1_2 = f2_pack(d1, d1), nm1_2 = f2_pack(-m1, -m1);
+    const uint64_t unbias2 = f2_pack(-8388608.f, -8388608.f);
 #pragma unroll
     for (int c4 = 0; c4 < 4; c4++) {           // 8 elements: bytes 8*c4 .. 8*c4+7
       uint32_t out[4];
@@ -373,10 +407,9 @@ __device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, int h
         uint32_t q = (qw[2 * c4 + w2] >> (4 * h)) & 0x0f0f0f0fu;
         if constexpr (TYPE == kQ5_K)
           q |= ((hw[2 * c4 + w2] >> (2 * j + h)) & 0x01010101u) << 4;
-        const float w0 = __fmaf_rn(d1, byte_f(q, 0), -m1), w1 = __fmaf_rn(d1, byte_f(q, 1), -m1);
-        const float w2f = __fmaf_rn(d1, byte_f(q, 2), -m1), w3 = __fmaf_rn(d1, byte_f(q, 3), -m1);
-        out[2 * w2] = pack_bf16(w0, w1);
-        out[2 * w2 + 1] = pack_bf16(w2f, w3);
+        // d1 * q - m1, fused, on pairs: (2^23 + b) - 2^23 is exact
+        out[2 * w2] = f2_to_bf16x2(f2_fma(d1_2, f2_add(bytes2_biased(q, 0), unbias2), nm1_2));
+        out[2 * w2 + 1] = f2_to_bf16x2(f2_fma(d1_2, f2_add(bytes2_biased(q, 2), unbias2), nm1_2));
       }
       store_chunk(tile, r, 4 * h + c4, make_uint4(out[0], out[1], out[2], out[3]));
     }
@@ -390,16 +423,16 @@ __device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, int h
     for (int c4 = 0; c4 < 4; c4++) {
       const int scb = (int)(int8_t)((raw.sc >> (8 * ((c4 >> 1) + 2 * h))) & 0xff);
       const float dsc = __fmul_rn(d, (float)scb);
+      const uint64_t dsc_2 = f2_pack(dsc, dsc), unbias2 = f2_pack(-8388640.f, -8388640.f);
       uint32_t out[4];
 #pragma unroll
       for (int w2 = 0; w2 < 2; w2++) {
         const uint32_t qlw = raw.ql[2 * c4 + w2];
         const uint32_t qhw = raw.qh[2 * c4 + w2];
         const uint32_t q = ((qlw >> (4 * hi)) & 0x0f0f0f0fu) | (((qhw >> (2 * kk)) & 0x03030303u) << 4);
-        const float w0 = __fmul_rn(dsc, byte_f_m32(q, 0)), w1 = __fmul_rn(dsc, byte_f_m32(q, 1));
-        const float w2f = __fmul_rn(dsc, byte_f_m32(q, 2)), w3 = __fmul_rn(dsc, byte_f_m32(q, 3));
-        out[2 * w2] = pack_bf16(w0, w1);
-        out[2 * w2 + 1] = pack_bf16(w2f, w3);
+        // dsc * (q - 32) on pairs: (2^23 + b) - (2^23 + 32) is exact
+        out[2 * w2] = f2_to_bf16x2(f2_mul(dsc_2, f2_add(bytes2_biased(q, 0), unbias2)));
+        out[2 * w2 + 1] = f2_to_bf16x2(f2_mul(dsc_2, f2_add(bytes2_biased(q, 2), unbias2)));
       }
       store_chunk(tile, r, 4 * h + c4, make_uint4(out[0], out[1], out[2], out[3]));
     }
