@@ -1077,6 +1077,9 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
   const uint32_t bar0 = smem_u32(bars);
 
   long long best = LLONG_MIN, best_b1 = LLONG_MIN;  // fused top-1: running maxima (batch row 0 / 1)
+  long long bestd[DENSE ? NB / 2 : 1];              // batches above 2: rows 2i + (lane >> 4)
+#pragma unroll
+  for (int i = 0; i < (DENSE ? NB / 2 : 1); i++) bestd[i] = LLONG_MIN;
 
   // The CTA's work is one ordered sequence of items: per tile one item per PAIR neighbouring
   // superblocks of the row (scale decode + MMAs of 16 rows x PAIR*256 columns, partial sums to the
@@ -1205,9 +1208,14 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
         for (int i = 0; i < NB / 2; i++) {
           const int b = 2 * i + (lane >> 4);
           if (b < p.batch && row < job.out_dim) {
-            const long long as = p.addend_stride < 0 ? job.out_dim : p.addend_stride;
-            const float a = job.addend ? job.addend[(long long)b * as + row] : 0.f;
-            job.y[(long long)b * job.out_dim + row] = a + v[i];
+            if (p.part_keys) {
+              const long long key = top1_key(v[i], (uint32_t)(p.index_base + row));
+              bestd[i] = key > bestd[i] ? key : bestd[i];
+            } else {
+              const long long as = p.addend_stride < 0 ? job.out_dim : p.addend_stride;
+              const float a = job.addend ? job.addend[(long long)b * as + row] : 0.f;
+              job.y[(long long)b * job.out_dim + row] = a + v[i];
+            }
           }
         }
       } else {
@@ -1247,12 +1255,17 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
 
   // ------------------------------------------------------------ fused top-1 epilogue
   // per-CTA maximum per batch row -> scratch slot; the CTA with the last ticket folds all slots
-  __shared__ long long s_best[2];
+  __shared__ long long s_best[DENSE ? NB : 2];
   __shared__ bool s_last;
-  if (ctid < 2) s_best[ctid] = LLONG_MIN;
+  if (ctid < (DENSE ? NB : 2)) s_best[ctid] = LLONG_MIN;
   consumer_sync<kNW>();
-  atomicMax(&s_best[0], best);
-  if (NB > 1) atomicMax(&s_best[1], best_b1);
+  if constexpr (DENSE) {
+#pragma unroll
+    for (int i = 0; i < NB / 2; i++) atomicMax(&s_best[2 * i + (lane >> 4)], bestd[i]);
+  } else {
+    atomicMax(&s_best[0], best);
+    if (NB > 1) atomicMax(&s_best[1], best_b1);
+  }
   consumer_sync<kNW>();
   const int nparts = gridDim.x;
   if (ctid < NB) p.part_keys[(long long)ctid * nparts + blockIdx.x] = s_best[ctid];
@@ -1265,7 +1278,7 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
   consumer_sync<kNW>();
   if (!s_last) return;
   __threadfence();
-  if (warp < NB) {
+  if (warp < NB && warp < p.batch) {
     const int b = warp;
     long long m = LLONG_MIN;
     for (int i = lane; i < nparts; i += 32) {
@@ -1399,6 +1412,22 @@ int batch_pass_width(int in_dim, int batch) {
   return width;
 }
 
+// The same for the fused top-1, which needs whole rows in one launch: 8, else 4 rows where their
+// activations fit without column ranges; 0 = the fused kernel cannot take the shape.
+template <int TYPE>
+int top1_pass_width(int in_dim, int batch) {
+  if (batch <= 2) return column_splits<TYPE>(in_dim, batch) == 1 ? batch : 0;
+  int width = 0;
+  if (batch > 4 && column_splits<TYPE>(in_dim, 8) == 1) width = 8;
+  else if (column_splits<TYPE>(in_dim, 4) == 1) width = 4;
+  if (width == 0) return 0;
+  const int tail = batch % width;
+  if (tail > 4 && column_splits<TYPE>(in_dim, 8) != 1) return 0;
+  if (tail > 2 && tail <= 4 && column_splits<TYPE>(in_dim, 4) != 1) return 0;
+  if ((tail == 1 || tail == 2) && column_splits<TYPE>(in_dim, tail) != 1) return 0;
+  return width;
+}
+
 // One pass: up to kMaxJobs weight matrices against `batch` rows of x (1, 2, or 3 .. 8), as one
 // launch per column range.
 template <int TYPE>
@@ -1470,11 +1499,20 @@ int gemv_typed(int njobs, const void *const *d_w, const float *d_x, const float 
                int64_t addend_stride, float *const *d_y, const int *out_dims, int in_dim, int batch,
                int resident, const Params *top1, cudaStream_t s, const float *d_x_up = nullptr,
                const float *d_norm_w = nullptr, float norm_eps = 0.f) {
-  if (top1 && batch > 2) return COGNI_QMM_ERR_LIMIT;
-  const int width = batch <= 2 ? batch : batch_pass_width<TYPE>(in_dim, batch);
+  const int width = top1 ? top1_pass_width<TYPE>(in_dim, batch)
+                         : (batch <= 2 ? batch : batch_pass_width<TYPE>(in_dim, batch));
   if (width == 0) return COGNI_QMM_ERR_LIMIT;
   for (int b0 = 0; b0 < batch; b0 += width) {
     const int nbat = batch - b0 < width ? batch - b0 : width;
+    Params t1{};  // this pass's rows of the top-1 outputs and scratch slots
+    if (top1) {
+      const int tiles = (out_dims[0] + kR - 1) / kR, sms = sm_count();
+      t1 = *top1;
+      t1.part_keys = top1->part_keys + (long long)b0 * (tiles < sms ? tiles : sms);
+      t1.top_idx = top1->top_idx + b0;
+      t1.top_val = top1->top_val + b0;
+      t1.top_key = top1->top_key ? top1->top_key + b0 : nullptr;
+    }
     for (int j0 = 0; j0 < njobs; j0 += kMaxJobs) {
       const int nj = njobs - j0 < kMaxJobs ? njobs - j0 : kMaxJobs;
       const float *add[kMaxJobs];
@@ -1485,7 +1523,7 @@ int gemv_typed(int njobs, const void *const *d_w, const float *d_x, const float 
       }
       const int st = run_pass<TYPE>(nj, d_w + j0, d_x + (long long)b0 * in_dim, d_addend ? add : nullptr,
                                     addend_stride, d_y ? ys : nullptr, out_dims + j0, in_dim, nbat, resident,
-                                    top1, s, d_x_up ? d_x_up + (long long)b0 * in_dim : nullptr, d_norm_w,
+                                    top1 ? &t1 : nullptr, s, d_x_up ? d_x_up + (long long)b0 * in_dim : nullptr, d_norm_w,
                                     norm_eps);
       if (st) return st;
     }
@@ -1501,16 +1539,16 @@ void gemv_imma_set_min_splits(int n) { g_imma_min_splits = n < 1 ? 1 : n; }
 
 bool gemv_imma_supports(int type, const void *d_w, const float *d_x, int in_dim, int batch, bool top1) {
   if (type != kQ8_0 && type != kQ4_K && type != kQ5_K && type != kQ6_K) return false;
-  if (batch < 1 || batch > 64 || (top1 && batch > 2)) return false;
+  if (batch < 1 || batch > 64) return false;
   if ((reinterpret_cast<uintptr_t>(d_w) & 15) || (reinterpret_cast<uintptr_t>(d_x) & 15)) return false;
   if (in_dim % 256 != 0 || in_dim > 16384) return false;
   // the activations (of a column range of the rows, if need be), the warps' areas and at least
   // three stages must fit into shared memory; the fused top-1 needs whole rows in one launch
   auto ok = [&](auto tag) {
     constexpr int T = decltype(tag)::value;
+    if (top1) return top1_pass_width<T>(in_dim, batch) != 0;
     if (batch > 2) return batch_pass_width<T>(in_dim, batch) != 0;
-    const int n = column_splits<T>(in_dim, batch);
-    return n != 0 && (!top1 || n == 1);
+    return column_splits<T>(in_dim, batch) != 0;
   };
   switch (type) {
     case kQ4_K: return ok(std::integral_constant<int, kQ4_K>{});

@@ -336,7 +336,7 @@ def test_matmul_add_rejects_unknown_type(cuda):
 
 
 @pytest.mark.parametrize("qtype", ALL_TYPES)
-@pytest.mark.parametrize("batch", [1, 4])
+@pytest.mark.parametrize("batch", [1, 3, 4, 8, 11, 16])
 def test_lm_head_top1(cuda, oracle, qtype, batch):
     out_dim, in_dim, base = 5000, 1024, 7000
     w = synth.make_weight(qtype, out_dim, in_dim, seed=61, tensor_id=qtype)
@@ -398,7 +398,8 @@ def test_lm_head_top2_tie_takes_the_two_lowest_indices(cuda):
     assert idx[0].tolist() == [0, 1] and float(val[0, 0]) == float(val[0, 1])
 
 
-@pytest.mark.parametrize("qtype,batch", [(Q6_K, 1), (Q4_K, 2), (Q8_0, 1), (Q6_K, 5)])
+@pytest.mark.parametrize("qtype,batch", [(Q6_K, 1), (Q4_K, 2), (Q8_0, 1), (Q6_K, 5), (Q4_K, 8),
+                                         (Q5_K, 12), (Q8_0, 3)])
 def test_lm_head_top1_with_fused_output_norm(cuda, oracle, qtype, batch):
     """output_norm -> lm_head -> argmax per row in one call (rmsnorm_project_top1_rows,
     qwen35_metal.cr:9187) against rms_norm rows + QuantMatmul + argmax on the CPU."""
