@@ -42,6 +42,8 @@ constexpr int kBK = 64;       // k elements per stage: 128 bytes of bf16 = one s
 // already spreads 16-byte loads of eight rows over all banks).  Q6_K: the 256-byte window around
 // the 210-byte block (it starts on a 2-byte boundary) as two boxes of 128 rows x 128 bytes with
 // the 128-byte swizzle.
+// bytes of 256 consecutive weights of a row (a K-quant superblock; eight Q8_0 blocks)
+template <int TYPE> struct Sb { static constexpr int bytes = BlockGeom<TYPE>::bytes * (256 / BlockGeom<TYPE>::elems); };
 constexpr int kRawBox = 128 * 128;
 __host__ __device__ constexpr int raw_stage_bytes(int type) {
   return type == kQ6_K ? 2 * kRawBox : 128 * (type == kQ4_K ? 144 : 176);
@@ -285,13 +287,14 @@ template <int TYPE> struct Raw;
 template <> struct Raw<kQ4_K> { uint4 hdr, q0, q1; };
 template <> struct Raw<kQ5_K> { uint4 hdr, h0, h1, q0, q1; };
 template <> struct Raw<kQ6_K> { uint32_t ql[8], qh[8], sc; uint32_t d; };
+template <> struct Raw<kQ8_0> { uint32_t q[8]; uint32_t d; };  // one 34-byte block: half a k-step
 
 // `h`: which 32-element half of the k-step this thread expands (Q6_K fetches only that half's ql).
 // SHARED_TOO = false skips what both halves of a Q6_K k-step share (qh, d): a thread that expands
 // both halves copies them from its first half.
 template <int TYPE, bool SHARED_TOO = true>
 __device__ __forceinline__ void fetch_raw(const uint8_t *row, int ks, int h, Raw<TYPE> &r) {
-  const uint8_t *blk = row + (size_t)(ks >> 2) * BlockGeom<TYPE>::bytes;
+  const uint8_t *blk = row + (size_t)(ks >> 2) * Sb<TYPE>::bytes;
   const int j = ks & 3;
   if constexpr (TYPE == kQ4_K) {
     r.hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
@@ -303,6 +306,45 @@ __device__ __forceinline__ void fetch_raw(const uint8_t *row, int ks, int h, Raw
     r.h1 = __ldg(reinterpret_cast<const uint4 *>(blk + 32));
     r.q0 = __ldg(reinterpret_cast<const uint4 *>(blk + 48 + 32 * j));
     r.q1 = __ldg(reinterpret_cast<const uint4 *>(blk + 64 + 32 * j));
+  } else if constexpr (TYPE == kQ8_0) {
+    // block 2j + h of the eight: fp16 d, then 32 int8, at an even address.  Three 16-byte vectors
+    // from the boundary below cover its 34 bytes; the offset is the same for all rows of a tile.
+    const uintptr_t a = reinterpret_cast<uintptr_t>(blk + 68 * j + 34 * h);
+    const uint4 *q = reinterpret_cast<const uint4 *>(a & ~(uintptr_t)15);
+    const uint4 v0 = __ldg(q), v1 = __ldg(q + 1), v2 = __ldg(q + 2);
+    const uint32_t w[13] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w, v2.x, v2.y, v2.z, v2.w, 0u};
+    const uint32_t o = (uint32_t)(a & 15);
+    const uint32_t sh = ((o + 2) & 2) * 8;
+    uint32_t dw = 0;
+    switch (o >> 2) {
+      case 0: dw = w[0]; break;
+      case 1: dw = w[1]; break;
+      case 2: dw = w[2]; break;
+      default: dw = w[3]; break;
+    }
+    r.d = (dw >> ((o & 2) * 8)) & 0xffffu;
+    switch ((o + 2) >> 2) {
+      case 0:
+#pragma unroll
+        for (int i = 0; i < 8; i++) r.q[i] = __funnelshift_r(w[i], w[i + 1], sh);
+        break;
+      case 1:
+#pragma unroll
+        for (int i = 0; i < 8; i++) r.q[i] = __funnelshift_r(w[i + 1], w[i + 2], sh);
+        break;
+      case 2:
+#pragma unroll
+        for (int i = 0; i < 8; i++) r.q[i] = __funnelshift_r(w[i + 2], w[i + 3], sh);
+        break;
+      case 3:
+#pragma unroll
+        for (int i = 0; i < 8; i++) r.q[i] = __funnelshift_r(w[i + 3], w[i + 4], sh);
+        break;
+      default:
+#pragma unroll
+        for (int i = 0; i < 8; i++) r.q[i] = __funnelshift_r(w[i + 4], w[i + 5], sh);
+        break;
+    }
   } else {
     const int n = j >> 1;
     ldg_8words_wide(blk + 64 * n + 32 * h, r.ql);
@@ -348,6 +390,14 @@ __device__ __forceinline__ void fetch_raw_from(const uint8_t *blk, int j, Raw<TY
   }
 }
 
+// Start of the 256-byte window that holds Q6_K superblock sb of a row: the 16-byte boundary below
+// the block, moved down where the window would otherwise reach beyond the row (boxes that reach
+// outside the matrix are avoided altogether: with boxes whose last rows lay beyond the matrix,
+// about one launch in twenty read stale bytes in the rows that were inside).
+__device__ __forceinline__ int q6_window_start(int sb, int row_bytes) {
+  return min((210 * sb) & ~15, row_bytes - 256);
+}
+
 // Q6_K, staged: both halves of k-step j (= ks & 3) of row r from the superblock's window in
 // shared memory; pad = offset of the 210-byte block inside the window.
 template <int NH>
@@ -383,7 +433,22 @@ __device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, int h
     return;
   }
   const int j = ks & 3;
-  if constexpr (TYPE == kQ4_K || TYPE == kQ5_K) {
+  if constexpr (TYPE == kQ8_0) {
+    // w = d * q (dequant.cr Q8_0): int8 b as the float 2^23 + (b ^ 0x80), minus 2^23 + 128
+    const float d = __half2float(__ushort_as_half((unsigned short)raw.d));
+    const uint64_t d_2 = f2_pack(d, d), unbias2 = f2_pack(-8388736.f, -8388736.f);
+#pragma unroll
+    for (int c4 = 0; c4 < 4; c4++) {
+      uint32_t out[4];
+#pragma unroll
+      for (int w2 = 0; w2 < 2; w2++) {
+        const uint32_t q = raw.q[2 * c4 + w2] ^ 0x80808080u;
+        out[2 * w2] = f2_to_bf16x2(f2_mul(d_2, f2_add(bytes2_biased(q, 0), unbias2)));
+        out[2 * w2 + 1] = f2_to_bf16x2(f2_mul(d_2, f2_add(bytes2_biased(q, 2), unbias2)));
+      }
+      store_chunk(tile, r, 4 * h + c4, make_uint4(out[0], out[1], out[2], out[3]));
+    }
+  } else if constexpr (TYPE == kQ4_K || TYPE == kQ5_K) {
     // low nibbles (h = 0): sub-block 2j, high nibbles (h = 1): sub-block 2j+1
     const __half2 dd = *reinterpret_cast<const __half2 *>(&raw.hdr.x);
     const float d = __low2float(dd), dmin = __high2float(dd);
@@ -464,6 +529,9 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(raw_bars + 4);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * kBM, m0 = blockIdx.y * BN;
+  // STAGED: the raw boxes of the last row tile start early enough to lie inside the matrix (the
+  // host stages only matrices of at least 128 rows); the tile's rows are then further down the box
+  const int raw_n0 = STAGED ? min(n0, p.n_out - kBM) : n0;
   // this CTA's k-steps: ks0 .. ks0 + nks - 1 (all of them unless the launch is split along K)
   const int ks0 = blockIdx.z * p.ks_per_split;
   const int nks = min(p.ks_per_split, p.k_in / kBK - ks0);
@@ -495,8 +563,34 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
   if (warp == 0) {
     // ---------------------------------------------------------------- activations via TMA
     if (lane == 0) {
+      // STAGED: the same thread keeps the next superblock column's raw windows in flight.
+      // Superblock sb of a row starts Sb bytes * sb into it (rows are multiples of 16 bytes here);
+      // the Q6_K window: see q6_window_start.
+      const int sb0 = ks0 >> 2, nsb = (nks + 3) >> 2;
+      auto issue_raw = [&](int sbl) {
+        const uint32_t full = smem_u32(&raw_bars[sbl & 1]);
+        mbar_arrive_expect_tx(full, kRawStage);
+        if constexpr (TYPE == kQ6_K) {
+          const int x0 = q6_window_start(sb0 + sbl, (int)p.row_bytes);
+          tma_load_2d(smem_u32(raw_win + (sbl & 1) * kRawStage), &tmap_w, x0, raw_n0, full);
+          tma_load_2d(smem_u32(raw_win + (sbl & 1) * kRawStage + kRawBox), &tmap_w, x0 + 128, raw_n0, full);
+        } else {  // 144- and 176-byte blocks start on 16-byte boundaries
+          tma_load_2d(smem_u32(raw_win + (sbl & 1) * kRawStage), &tmap_w,
+                      BlockGeom<TYPE>::bytes * (sb0 + sbl), raw_n0, full);
+        }
+      };
+      if constexpr (STAGED) issue_raw(0);
       for (int ks = 0; ks < nks; ks++) {
         const int s = ks % kStages;
+        if constexpr (STAGED) {
+          const int sbl = ks >> 2;
+          if ((ks & 3) == 0 && sbl + 1 < nsb) {
+            // the other buffer was last used by superblock sbl - 1: released by the dequant warps
+            // well before the MMAs free this k-step's stage
+            if (sbl >= 1) mbar_wait(smem_u32(&raw_bars[2 + ((sbl & 1) ^ 1)]), ((sbl - 1) >> 1) & 1);
+            issue_raw(sbl + 1);
+          }
+        }
         mbar_wait(smem_u32(&bars[2 * kStages + s]), ((ks / kStages) & 1) ^ 1);
         const uint32_t full = smem_u32(&bars[kStages + s]);
         mbar_arrive_expect_tx(full, kBTile);
@@ -550,39 +644,18 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
       }
     };
     if constexpr (STAGED) {
-      // One thread keeps the next superblock column's raw windows in flight: superblock sb of the
-      // row starts 210 * sb bytes into it (rows are multiples of 16 bytes here), its window at
-      // the 16-byte boundary below.
-      const int sb0 = ks0 >> 2, nsb = (nks + 3) >> 2;
-      auto issue_raw = [&](int sbl) {
-        const uint32_t full = smem_u32(&raw_bars[sbl & 1]);
-        mbar_arrive_expect_tx(full, kRawStage);
-        if constexpr (TYPE == kQ6_K) {
-          const int x0 = (210 * (sb0 + sbl)) & ~15;
-          tma_load_2d(smem_u32(raw_win + (sbl & 1) * kRawStage), &tmap_w, x0, n0, full);
-          tma_load_2d(smem_u32(raw_win + (sbl & 1) * kRawStage + kRawBox), &tmap_w, x0 + 128, n0, full);
-        } else {  // 144- and 176-byte blocks start on 16-byte boundaries
-          tma_load_2d(smem_u32(raw_win + (sbl & 1) * kRawStage), &tmap_w,
-                      BlockGeom<TYPE>::bytes * (sb0 + sbl), n0, full);
-        }
-      };
-      const bool issuer = threadIdx.x == 64;
-      if (issuer) issue_raw(0);
+      const int sb0 = ks0 >> 2;
+      const int rr = min(r + n0 - raw_n0, kBM - 1);  // this thread's row of the raw box
       for (int ks = 0; ks < nks; ks++) {
         const int s = ks % kStages;
         const int sbl = ks >> 2, buf = sbl & 1;
-        if ((ks & 3) == 0) {
-          if (issuer && sbl + 1 < nsb) {
-            // the other buffer was last used by superblock sbl - 1
-            if (sbl >= 1) mbar_wait(smem_u32(&raw_bars[2 + (buf ^ 1)]), ((sbl - 1) >> 1) & 1);
-            issue_raw(sbl + 1);
-          }
-          mbar_wait(smem_u32(&raw_bars[buf]), (sbl >> 1) & 1);
-        }
+        if ((ks & 3) == 0) mbar_wait(smem_u32(&raw_bars[buf]), (sbl >> 1) & 1);
         if constexpr (TYPE == kQ6_K)
-          fetch_staged_q6<kHalves>(raw_win + buf * kRawStage, r, (210 * (sb0 + sbl)) & 15, (ks0 + ks) & 3, h0, cur);
+          fetch_staged_q6<kHalves>(raw_win + buf * kRawStage, rr,
+                                   210 * (sb0 + sbl) - q6_window_start(sb0 + sbl, (int)p.row_bytes),
+                                   (ks0 + ks) & 3, h0, cur);
         else  // the block of row r sits at r * block bytes: the global fetch code reads it as it is
-          fetch_raw_from<TYPE>(raw_win + buf * kRawStage + r * BlockGeom<TYPE>::bytes, (ks0 + ks) & 3, cur[0]);
+          fetch_raw_from<TYPE>(raw_win + buf * kRawStage + rr * BlockGeom<TYPE>::bytes, (ks0 + ks) & 3, cur[0]);
         if ((ks & 3) == 3 || ks == nks - 1) {  // this warp has read all it needs of the window
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&raw_bars[2 + buf]));
@@ -668,7 +741,7 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 int g_prefill_force_bn = 0;  // diagnostics: 0 = automatic, else the token-tile width to use
-int g_prefill_stage_raw = 1;    // diagnostics: 0 = Q6_K dequant threads read global memory directly
+int g_prefill_stage_raw = 1;    // diagnostics: 0 = dequant threads read global memory directly
 int g_prefill_force_split = 0;  // diagnostics: 0 = automatic, 1 = never split along K, 2 = split where allowed
 
 template <int TYPE, int BN, bool STAGED>
@@ -676,7 +749,7 @@ int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows
            int k_in, int splits, cudaStream_t s) {
   EncodeTiledFn encode = encode_tiled_fn();
   if (!encode) return COGNI_QMM_ERR_DEVICE;
-  const long long row_bytes = (long long)(k_in / 256) * BlockGeom<TYPE>::bytes;
+  const long long row_bytes = (long long)(k_in / 256) * Sb<TYPE>::bytes;
   CUtensorMap tmap, tmap_w;
   if (STAGED) {
     // the weights as a byte matrix [n_out, row_bytes]: boxes of 128 rows x 128 bytes
@@ -771,14 +844,11 @@ int launch_typed(const void *d_w, const void *d_x, void *d_y, int out_type, int 
     }
   }
   // Rows that are multiples of 16 bytes (always for Q4_K / Q5_K; Q6_K: in_dim a multiple of 2048)
-  // can be fetched by TMA: the raw superblocks of the tile's rows are then staged through shared
-  // memory
+  // of a matrix with at least one full row tile can be fetched by TMA: the raw superblocks of the
+  // tile's rows are then staged through shared memory
   {
-    const long long row_bytes = (long long)(k_in / 256) * BlockGeom<TYPE>::bytes;
-    // (Q4_K with 512-token tiles measured 5 % faster reading directly: its three 16-byte loads per
-    // thread and k-step are cheap enough, and the tile's two stages leave no slack for the extra
-    // hand-over)
-    if (row_bytes % 16 == 0 && g_prefill_stage_raw && !(TYPE == kQ4_K && bn == 512)) {
+    const long long row_bytes = (long long)(k_in / 256) * Sb<TYPE>::bytes;
+    if (TYPE != kQ8_0 && row_bytes % 16 == 0 && n_out >= kBM && g_prefill_stage_raw) {
       if (bn == 512) return launch<TYPE, 512, true>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
       if (bn == 256) return launch<TYPE, 256, true>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
       return launch<TYPE, 128, true>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
@@ -797,6 +867,7 @@ int launch_gemm_prefill(int type, const void *d_w, const void *d_x_bf16, void *d
     case kQ4_K: return launch_typed<kQ4_K>(d_w, d_x_bf16, d_y, out_type, m_rows, n_out, k_in, s);
     case kQ5_K: return launch_typed<kQ5_K>(d_w, d_x_bf16, d_y, out_type, m_rows, n_out, k_in, s);
     case kQ6_K: return launch_typed<kQ6_K>(d_w, d_x_bf16, d_y, out_type, m_rows, n_out, k_in, s);
+    case kQ8_0: return launch_typed<kQ8_0>(d_w, d_x_bf16, d_y, out_type, m_rows, n_out, k_in, s);
     default: return COGNI_QMM_ERR_TYPE;
   }
 }

@@ -62,7 +62,8 @@ const char *cogni_qmm_status_string(int status);
  * superblocks per GEMV work item (automatic / 1 / 2), 27-30 at least 1 .. 4 column ranges per
  * row of the tiled GEMV (27 = the default), 32-47 raw diagnostic bits (results
  * invalid), 48-51 prefill token-tile width (automatic / 128 / 256 / 512),
- * 52-54 prefill split along K (automatic / never / wherever it is allowed).
+ * 52-54 prefill split along K (automatic / never / wherever it is allowed), 55-56 prefill raw
+ * superblocks staged by TMA (default) / read directly by the dequant threads.
  * cogni_qmm_wait_timeouts: how many bounded device-side waits have expired since the library
  * was loaded (0 in a healthy process; a non-zero value means the results of some launch are
  * invalid).  Synchronises the device. */
@@ -286,7 +287,7 @@ int cogni_qmm_top1_unpack_keys(const int64_t *d_keys, int batch, int32_t *d_top_
  *   d_w      raw GGUF blocks [n_out][k_in], 16-byte aligned
  *   d_x      bf16 [m_rows, k_in] row-major, 16-byte aligned
  *   d_y      [m_rows, n_out] row-major, f32 or bf16 per out_type
- * k_in must be a multiple of 256.
+ * type: Q8_0, Q4_K, Q5_K or Q6_K.  k_in must be a multiple of 256.
  */
 int cogni_qmm_gemm_bf16(int type, const void *d_w, const void *d_x_bf16, void *d_y,
                         int out_type, int m_rows, int n_out, int k_in, void *stream);
