@@ -89,6 +89,14 @@ template <> struct Cfg<kQ8_0> {
   static constexpr int RS = stage_row_stride(BB, KB, false);
   static constexpr bool HAS_MIN = false;
 };
+// IQ4_NL: eight 18-byte blocks (fp16 d + 16 bytes of nibble pairs: element i in the low nibble of
+// byte i, element 16 + i in the high one; values through a 16-entry table) form a 144-byte
+// superblock of eight scale groups.  Only the 4- and 8-row instances of the kernel exist for it.
+template <> struct Cfg<kIQ4_NL> {
+  static constexpr int BB = 144, KB = 16, NG = 8, GROUP = 32;
+  static constexpr int RS = stage_row_stride(BB, KB, false);
+  static constexpr bool HAS_MIN = false;
+};
 template <> struct Cfg<kQ6_K> {
   static constexpr int BB = 210, KB = 8, NG = 16, GROUP = 16;
   static constexpr int RS = stage_row_stride(BB, KB, true);
@@ -331,10 +339,11 @@ __device__ __forceinline__ void half_scales(const uint8_t *blk_row, int half,
                                             float (&dsc)[Cfg<TYPE>::NG / 2],
                                             float (&kk)[Cfg<TYPE>::NG / 2]) {
   using C = Cfg<TYPE>;
-  if constexpr (TYPE == kQ8_0) {  // the blocks' own fp16 scales; no minimum, no offset
+  if constexpr (TYPE == kQ8_0 || TYPE == kIQ4_NL) {  // the blocks' own fp16 scales; no minimum, no offset
+    constexpr int BLK = TYPE == kQ8_0 ? 34 : 18;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-      dsc[i] = load_half_as_float(blk_row + 34 * (4 * half + i));
+      dsc[i] = load_half_as_float(blk_row + BLK * (4 * half + i));
       kk[i] = 0.f;
     }
   } else if constexpr (C::HAS_MIN) {
@@ -742,8 +751,23 @@ __device__ __forceinline__ void quantise_dense(const float *x, const float *x_up
                              __byte_perm(up[4 * w4 + 2], up[4 * w4 + 3], 0x0051), 0x5410);
       }
       uint8_t *dst = xq + ((size_t)(grp * J + (b >> 2)) * 32 + 2 * (b & 3) * 4) * W + tpos;
-      *reinterpret_cast<uint2 *>(dst) = make_uint2(hw[0], hw[1]);          // hi plane: column 2b'
-      *reinterpret_cast<uint2 *>(dst + 4 * W) = make_uint2(lw[0], lw[1]);  // lo plane: column 2b' + 1
+      if constexpr (TYPE == kIQ4_NL) {
+        // The A fragments come out of the nibble table in the order (element i, element 16 + i,
+        // element i + 1, element 17 + i) per pair of weight bytes, so the activations are laid out
+        // to match: element e of the block (byte be = e & 15 of its 16, nibble e >> 4) goes to
+        // MMA lane t = be >> 2, word m = (be >> 1) & 1, byte 2 * (be & 1) + (e >> 4).
+        const int c = lane & 3;  // this lane holds elements 8c .. 8c + 7
+        uint8_t *col = dst - tpos;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const int off = (2 * (c & 1) + (i >> 2)) * 8 + ((i >> 1) & 1) * 4 + 2 * (i & 1) + (c >> 1);
+          col[off] = (uint8_t)(hw[i >> 2] >> (8 * (i & 3)));
+          col[off + 4 * W] = (uint8_t)(lw[i >> 2] >> (8 * (i & 3)));
+        }
+      } else {
+        *reinterpret_cast<uint2 *>(dst) = make_uint2(hw[0], hw[1]);          // hi plane: column 2b'
+        *reinterpret_cast<uint2 *>(dst + 4 * W) = make_uint2(lw[0], lw[1]);  // lo plane: column 2b' + 1
+      }
     }
   }
 }
@@ -762,7 +786,7 @@ __device__ __forceinline__ void decode_dense(const uint8_t *blk_row, int lane, i
 #pragma unroll
   for (int i = 0; i < NH; i += 4)
     *reinterpret_cast<float4 *>(row + NH * half + i) = make_float4(dsc[i], dsc[i + 1], dsc[i + 2], dsc[i + 3]);
-  if constexpr (TYPE != kQ8_0) {
+  if constexpr (C::HAS_MIN || TYPE == kQ6_K) {
     float corr[NB];
 #pragma unroll
     for (int b = 0; b < NB; b++) corr[b] = 0.f;
@@ -817,14 +841,35 @@ __device__ __forceinline__ void mma_dense(const uint8_t *blk, int pad_a, int pad
     for (int j = 0; j < J; j++) {
       const uint2 bv = *reinterpret_cast<const uint2 *>(xg + (gi * J + j) * GB);
       int cc[4];
-      if constexpr (TYPE == kQ8_0) imma_s8_zero(cc, a0, a1, a2, a3, bv.x, bv.y);
+      if constexpr (TYPE == kQ8_0 || TYPE == kIQ4_NL) imma_s8_zero(cc, a0, a1, a2, a3, bv.x, bv.y);
       else imma_zero(cc, a0, a1, a2, a3, bv.x, bv.y);
       const float sx = sxg[gi * NB + 4 * j];
       acc0[j] = fmaf(fa * sx, (float)(cc[0] * 128 + cc[1]), acc0[j]);
       acc1[j] = fmaf(fb * sx, (float)(cc[2] * 128 + cc[3]), acc1[j]);
     }
   };
-  if constexpr (TYPE == kQ8_0) {
+  if constexpr (TYPE == kIQ4_NL) {
+    // this lane's four nibble-pair bytes 4t .. 4t+3 of every block, rows g and g+8; the quants of
+    // block j start 18j + 2 bytes into the superblock: on a word for odd j, 2 bytes off for even j
+    const uint8_t *ra = blk + g * C::RS + 4 * t, *rb = blk + (g + 8) * C::RS + 4 * t;
+    auto lut4 = [](uint32_t h) {  // nibbles 0 .. 3 of h -> the four table values as bytes
+      const uint32_t s7 = h & 0x7777u;
+      const uint32_t lo = __byte_perm(0xBFAD9881u, 0xF6EADDCFu, s7);   // entries 0 .. 7
+      const uint32_t hi = __byte_perm(0x26190D01u, 0x71594535u, s7);   // entries 8 .. 15
+      return __byte_perm(lo, hi, 0x3210u | ((h >> 1) & 0x4444u));
+    };
+#pragma unroll
+    for (int g4 = 0; g4 < 4; g4++) {
+      const float2 sa = *reinterpret_cast<const float2 *>(rowa + 2 * g4);
+      const float2 sb = *reinterpret_cast<const float2 *>(rowb + 2 * g4);
+      const uint32_t *ea = reinterpret_cast<const uint32_t *>(ra + 36 * g4);
+      const uint32_t *eb = reinterpret_cast<const uint32_t *>(rb + 36 * g4);
+      const uint32_t wa0 = __funnelshift_r(ea[0], ea[1], 16), wb0 = __funnelshift_r(eb[0], eb[1], 16);
+      const uint32_t wa1 = ea[5], wb1 = eb[5];  // block 2*g4 + 1: 36*g4 + 18 + 2
+      group32(2 * g4, sa.x, sb.x, lut4(wa0), lut4(wb0), lut4(wa0 >> 16), lut4(wb0 >> 16));
+      group32(2 * g4 + 1, sa.y, sb.y, lut4(wa1), lut4(wb1), lut4(wa1 >> 16), lut4(wb1 >> 16));
+    }
+  } else if constexpr (TYPE == kQ8_0) {
     const uint8_t *ra = blk + g * C::RS + 8 * t, *rb = blk + (g + 8) * C::RS + 8 * t;
     auto even_block = [](const uint8_t *p, uint32_t &w0, uint32_t &w1) {  // p: the block's d
       const uint32_t *q = reinterpret_cast<const uint32_t *>(p);
@@ -1385,11 +1430,20 @@ int launch_instance(const Params &p, size_t smem, int grid, cudaStream_t s) {
   return (int)cudaLaunchKernelEx(&cfg, gemv_imma_kernel<TYPE, NB, PAIR>, p);
 }
 
+// Batch rows of the kernel instance that takes `batch` (<= 8) rows: 1, 2, 4 or 8; IQ4_NL has only
+// the 4- and 8-row instances (unused rows repeat the last one).
+template <int TYPE>
+int kernel_rows(int batch) {
+  if (batch <= 2 && TYPE != kIQ4_NL) return batch;
+  return batch <= 4 ? 4 : 8;
+}
+
 // Column ranges a launch covers when a whole row of activations does not fit into shared memory:
 // the fewest equal ranges of whole superblocks whose plan fits.  Every weight byte is still read
 // once; the later ranges add onto y.  0 = none fits.
 template <int TYPE>
-int column_splits(int in_dim, int nb) {
+int column_splits(int in_dim, int batch) {
+  const int nb = kernel_rows<TYPE>(batch);
   const int nblk = in_dim / 256;
   for (int n = g_imma_min_splits < nblk ? g_imma_min_splits : nblk; n <= 8 && n <= nblk; n++) {
     Params p{};
@@ -1436,7 +1490,7 @@ int run_pass(int nj, const void *const *d_w, const float *d_x, const float *cons
              int resident, const Params *top1, cudaStream_t s, const float *d_x_up,
              const float *d_norm_w, float norm_eps) {
   using C = Cfg<TYPE>;
-  const int nbk = batch <= 2 ? batch : (batch <= 4 ? 4 : 8);
+  const int nbk = kernel_rows<TYPE>(batch);
   const int nsplit = column_splits<TYPE>(in_dim, nbk);
   if (nsplit == 0 || (top1 && nsplit > 1)) return COGNI_QMM_ERR_LIMIT;
   const int nblk = in_dim / 256, per = (nblk + nsplit - 1) / nsplit;
@@ -1480,11 +1534,13 @@ int run_pass(int nj, const void *const *d_w, const float *d_x, const float *cons
       p.index_base = top1->index_base;
     }
     int st;
-    switch (nbk) {
-      case 1: st = p.pair == 2 ? launch_instance<TYPE, 1, 2>(p, smem, grid, s) : launch_instance<TYPE, 1, 1>(p, smem, grid, s); break;
-      case 2: st = p.pair == 2 ? launch_instance<TYPE, 2, 2>(p, smem, grid, s) : launch_instance<TYPE, 2, 1>(p, smem, grid, s); break;
-      case 4: st = launch_instance<TYPE, 4, 1>(p, smem, grid, s); break;
-      default: st = launch_instance<TYPE, 8, 1>(p, smem, grid, s); break;
+    if constexpr (TYPE != kIQ4_NL) {
+      if (nbk == 1) st = p.pair == 2 ? launch_instance<TYPE, 1, 2>(p, smem, grid, s) : launch_instance<TYPE, 1, 1>(p, smem, grid, s);
+      else if (nbk == 2) st = p.pair == 2 ? launch_instance<TYPE, 2, 2>(p, smem, grid, s) : launch_instance<TYPE, 2, 1>(p, smem, grid, s);
+      else if (nbk == 4) st = launch_instance<TYPE, 4, 1>(p, smem, grid, s);
+      else st = launch_instance<TYPE, 8, 1>(p, smem, grid, s);
+    } else {
+      st = nbk == 4 ? launch_instance<TYPE, 4, 1>(p, smem, grid, s) : launch_instance<TYPE, 8, 1>(p, smem, grid, s);
     }
     if (st) return st;
   }
@@ -1538,7 +1594,7 @@ void gemv_imma_set_pair(int pair) { g_imma_force_pair = pair; }
 void gemv_imma_set_min_splits(int n) { g_imma_min_splits = n < 1 ? 1 : n; }
 
 bool gemv_imma_supports(int type, const void *d_w, const float *d_x, int in_dim, int batch, bool top1) {
-  if (type != kQ8_0 && type != kQ4_K && type != kQ5_K && type != kQ6_K) return false;
+  if (type != kQ8_0 && type != kQ4_K && type != kQ5_K && type != kQ6_K && type != kIQ4_NL) return false;
   if (batch < 1 || batch > 64) return false;
   if ((reinterpret_cast<uintptr_t>(d_w) & 15) || (reinterpret_cast<uintptr_t>(d_x) & 15)) return false;
   if (in_dim % 256 != 0 || in_dim > 16384) return false;
@@ -1554,6 +1610,7 @@ bool gemv_imma_supports(int type, const void *d_w, const float *d_x, int in_dim,
     case kQ4_K: return ok(std::integral_constant<int, kQ4_K>{});
     case kQ5_K: return ok(std::integral_constant<int, kQ5_K>{});
     case kQ8_0: return ok(std::integral_constant<int, kQ8_0>{});
+    case kIQ4_NL: return ok(std::integral_constant<int, kIQ4_NL>{});
     default: return ok(std::integral_constant<int, kQ6_K>{});
   }
 }
@@ -1565,6 +1622,7 @@ int launch_gemv_imma_many(int type, int njobs, const void *const *d_w, const flo
     case kQ4_K: return gemv_typed<kQ4_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s);
     case kQ5_K: return gemv_typed<kQ5_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s);
     case kQ8_0: return gemv_typed<kQ8_0>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s);
+    case kIQ4_NL: return gemv_typed<kIQ4_NL>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s);
     case kQ6_K: return gemv_typed<kQ6_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s);
     default: return COGNI_QMM_ERR_TYPE;
   }
@@ -1587,6 +1645,7 @@ int launch_gemv_swiglu_imma(int type, const void *d_w, const float *d_gate, cons
     case kQ5_K: return gemv_typed<kQ5_K>(1, &d_w, d_gate, add, addend_stride, &d_y, &out_dim, in_dim, batch, resident, nullptr, s, d_up);
     case kQ6_K: return gemv_typed<kQ6_K>(1, &d_w, d_gate, add, addend_stride, &d_y, &out_dim, in_dim, batch, resident, nullptr, s, d_up);
     case kQ8_0: return gemv_typed<kQ8_0>(1, &d_w, d_gate, add, addend_stride, &d_y, &out_dim, in_dim, batch, resident, nullptr, s, d_up);
+    case kIQ4_NL: return gemv_typed<kIQ4_NL>(1, &d_w, d_gate, add, addend_stride, &d_y, &out_dim, in_dim, batch, resident, nullptr, s, d_up);
     default: return COGNI_QMM_ERR_TYPE;
   }
 }
@@ -1601,6 +1660,7 @@ int launch_gemv_many_rmsnorm_imma(int type, int njobs, const void *const *d_w, c
     case kQ5_K: return gemv_typed<kQ5_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, d_norm_w, eps);
     case kQ6_K: return gemv_typed<kQ6_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, d_norm_w, eps);
     case kQ8_0: return gemv_typed<kQ8_0>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, d_norm_w, eps);
+    case kIQ4_NL: return gemv_typed<kIQ4_NL>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, d_norm_w, eps);
     default: return COGNI_QMM_ERR_TYPE;
   }
 }
@@ -1621,6 +1681,7 @@ int launch_gemv_top1_imma(int type, const void *d_w, const float *d_x, int in_di
     case kQ4_K: return gemv_typed<kQ4_K>(1, &d_w, d_x, nullptr, 0, nullptr, &out_dim, in_dim, batch, resident, &t, s, nullptr, d_norm_w, norm_eps);
     case kQ5_K: return gemv_typed<kQ5_K>(1, &d_w, d_x, nullptr, 0, nullptr, &out_dim, in_dim, batch, resident, &t, s, nullptr, d_norm_w, norm_eps);
     case kQ8_0: return gemv_typed<kQ8_0>(1, &d_w, d_x, nullptr, 0, nullptr, &out_dim, in_dim, batch, resident, &t, s, nullptr, d_norm_w, norm_eps);
+    case kIQ4_NL: return gemv_typed<kIQ4_NL>(1, &d_w, d_x, nullptr, 0, nullptr, &out_dim, in_dim, batch, resident, &t, s, nullptr, d_norm_w, norm_eps);
     case kQ6_K: return gemv_typed<kQ6_K>(1, &d_w, d_x, nullptr, 0, nullptr, &out_dim, in_dim, batch, resident, &t, s, nullptr, d_norm_w, norm_eps);
     default: return COGNI_QMM_ERR_TYPE;
   }

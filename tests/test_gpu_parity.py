@@ -162,7 +162,7 @@ def test_long_rows_in_column_ranges(cuda, oracle, qtype, out_dim, in_dim, batch)
     (Q4_K, 512, 2048, 2), (Q8_0, 300, 1024, 1), (Q5_K, 257, 768, 2),
     (Q6_K, 128, 1024, 5),     # batch 5: the 8-row instance of the kernel
     (Q4_K, 192, 2048, 11),    # a pass of 8 rows and a pass of 3
-    (IQ4_NL, 128, 1024, 3),   # no fused kernel for this type: the product goes through scratch
+    (IQ4_NL, 128, 1024, 3), (IQ4_NL, 300, 2048, 1),
     (Q8_0, 64, 96, 1),        # in_dim not a multiple of 256: scratch path as well
 ])
 def test_gemv_swiglu_fused_down_projection(cuda, oracle, qtype, out_dim, in_dim, batch):
@@ -182,13 +182,13 @@ def test_gemv_swiglu_fused_down_projection(cuda, oracle, qtype, out_dim, in_dim,
 
 
 def test_gemv_swiglu_needs_scratch_for_unfused_shapes(cuda, engine):
-    # IQ4_NL has no fused kernel: the product needs the caller's scratch
-    w = synth.make_weight(IQ4_NL, 64, 256, seed=3)
-    dw = DeviceQuantWeight.upload(QuantWeight(w, IQ4_NL, 64, 256), cuda)
-    g = torch.zeros(5, 256, device=cuda)
+    # in_dim that is no multiple of 256 has no fused kernel: the product needs the caller's scratch
+    w = synth.make_weight(Q8_0, 64, 96, seed=3)
+    dw = DeviceQuantWeight.upload(QuantWeight(w, Q8_0, 64, 96), cuda)
+    g = torch.zeros(5, 96, device=cuda)
     y = torch.empty(5, 64, device=cuda)
-    st = engine.lib.cogni_qmm_gemv_swiglu(IQ4_NL, dw.raw.data_ptr(), g.data_ptr(), g.data_ptr(), None, 0,
-                                          y.data_ptr(), None, 256, 64, 5, 0, None)
+    st = engine.lib.cogni_qmm_gemv_swiglu(Q8_0, dw.raw.data_ptr(), g.data_ptr(), g.data_ptr(), None, 0,
+                                          y.data_ptr(), None, 96, 64, 5, 0, None)
     assert st == 1004  # COGNI_QMM_ERR_SCRATCH
 
 
@@ -238,7 +238,7 @@ def test_top1_feeds_embedding_lookup_on_device(cuda, oracle):
     (Q6_K, 2048, [300], 1), (Q8_0, 1024, [257, 64], 2), (Q5_K, 768, [128], 1),
     (Q4_K, 512, [64, 64], 4),               # batch 4: the 4-row instance of the kernel
     (Q6_K, 1024, [96, 40], 7),
-    (IQ4_NL, 512, [64, 64], 2),             # no fused kernel for this type: via scratch
+    (IQ4_NL, 512, [64, 64], 2), (IQ4_NL, 1024, [100, 36], 6),
 ])
 def test_gemv_many_rmsnorm_fused_prologue(cuda, oracle, qtype, in_dim, out_dims, batch):
     """y_j = W_j (RMSNorm(x) * w_norm) for matrices sharing x (qwen35_cpu.cr:484-490, 1793, 1883)
