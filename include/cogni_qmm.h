@@ -133,7 +133,7 @@ int cogni_qmm_gemv_resident(int type, const void *d_w, const float *d_x, const f
  * does (src/ml/gguf/qwen35_cpu.cr:484-490), followed by qmatvec_many (qwen35_cpu.cr:1793, 1883:
  * attn_norm -> qkv / gate / alpha / beta, post_attention_norm -> ffn_gate / ffn_up); replaces the
  * reference's add_rmsnorm / rmsnorm probe kernels (deltanet_step_probe.ptx:1324) plus the GEMVs.
- * Where the tiled kernel takes the shapes (Q8_0 / Q4_K / Q5_K / Q6_K, in_dim a multiple of 256, at most 32
+ * Where the tiled kernel takes the shapes (in_dim a multiple of 256, at most 32
  * matrices) xn is never written; otherwise it goes to d_x_scratch (f32 [batch, in_dim],
  * COGNI_QMM_ERR_SCRATCH if NULL) and cogni_qmm_gemv_many runs on that.  norm_weight: f32 [in_dim]
  * on the device, 16-byte aligned.  Other arguments as cogni_qmm_gemv_many.
@@ -165,7 +165,7 @@ int cogni_qmm_embedding_lookup(int type, const void *d_table, int vocab, int n_e
  * per row, the norm as in cogni_qmm_gemv_many_rmsnorm.  This is the reference's
  * rmsnorm_project_top1_rows (src/ml/gguf/qwen35_metal.cr:9187) and the CUDA head runner's
  * rmsnorm -> lm_head -> top-1 chain (src/ml/cuda/qwen_output_head_runner.cr:884-947) as one launch
- * where the tiled kernel takes the shape (Q8_0 / Q4_K / Q5_K / Q6_K, in_dim a multiple of 256); otherwise the
+ * where the tiled kernel takes the shape (in_dim a multiple of 256); otherwise the
  * normalised rows go to d_x_scratch (f32 [batch, in_dim], COGNI_QMM_ERR_SCRATCH if NULL) first.
  * d_scratch / scratch_bytes as for cogni_qmm_gemv_top1.
  */
@@ -199,7 +199,7 @@ int cogni_qmm_gemv_top2(int type, const void *d_w, const float *d_x, int in_dim,
  * with silu(v) = v / (1 + exp(-v)) in f32 (src/ml/gguf/qwen35_cpu.cr:512-519, 1716-1718; the
  * reference's swiglu_probe kernel, src/ml/cuda/kernels/deltanet_step_probe.ptx:1076, followed by
  * the down-projection GEMV).  gate and up are f32 [batch, in_dim] device buffers, 16-byte aligned.
- * Where the tiled kernel takes the shape (Q8_0 / Q4_K / Q5_K / Q6_K, in_dim a multiple of 256) the product is
+ * Where the tiled kernel takes the shape (in_dim a multiple of 256) the product is
  * formed while the activations are quantised and never written to memory; otherwise it is
  * written to d_x_scratch (f32 [batch, in_dim], COGNI_QMM_ERR_SCRATCH if NULL) and the plain GEMV
  * runs on that.  `resident` as in cogni_qmm_gemv_resident.
