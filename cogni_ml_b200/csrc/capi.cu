@@ -290,7 +290,7 @@ int cogni_qmm_top1_unpack_keys(const int64_t *d_keys, int batch, int32_t *d_top_
 
 int cogni_qmm_gemm_bf16(int type, const void *d_w, const void *d_x_bf16, void *d_y, int out_type,
                         int m_rows, int n_out, int k_in, void *stream) {
-  if (type != kQ4_K && type != kQ5_K && type != kQ6_K && type != kQ8_0) return COGNI_QMM_ERR_TYPE;
+  if (!supported(type)) return COGNI_QMM_ERR_TYPE;
   if (!d_w || !d_x_bf16 || !d_y || m_rows <= 0 || n_out <= 0 || k_in <= 0 || k_in % 256 != 0)
     return COGNI_QMM_ERR_ARG;
   if (out_type != COGNI_QMM_OUT_F32 && out_type != COGNI_QMM_OUT_BF16) return COGNI_QMM_ERR_ARG;

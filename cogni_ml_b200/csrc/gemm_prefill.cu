@@ -288,6 +288,7 @@ template <> struct Raw<kQ4_K> { uint4 hdr, q0, q1; };
 template <> struct Raw<kQ5_K> { uint4 hdr, h0, h1, q0, q1; };
 template <> struct Raw<kQ6_K> { uint32_t ql[8], qh[8], sc; uint32_t d; };
 template <> struct Raw<kQ8_0> { uint32_t q[8]; uint32_t d; };  // one 34-byte block: half a k-step
+template <> struct Raw<kIQ4_NL> { uint32_t q[4]; uint32_t d; };  // one 18-byte block: half a k-step
 
 // `h`: which 32-element half of the k-step this thread expands (Q6_K fetches only that half's ql).
 // SHARED_TOO = false skips what both halves of a Q6_K k-step share (qh, d): a thread that expands
@@ -306,6 +307,45 @@ __device__ __forceinline__ void fetch_raw(const uint8_t *row, int ks, int h, Raw
     r.h1 = __ldg(reinterpret_cast<const uint4 *>(blk + 32));
     r.q0 = __ldg(reinterpret_cast<const uint4 *>(blk + 48 + 32 * j));
     r.q1 = __ldg(reinterpret_cast<const uint4 *>(blk + 64 + 32 * j));
+  } else if constexpr (TYPE == kIQ4_NL) {
+    // block 2j + h of the eight: fp16 d, then 16 bytes of nibble pairs, at an even address; two
+    // 16-byte vectors from the boundary below cover its 18 bytes
+    const uintptr_t a = reinterpret_cast<uintptr_t>(blk + 36 * j + 18 * h);
+    const uint4 *q = reinterpret_cast<const uint4 *>(a & ~(uintptr_t)15);
+    const uint4 v0 = __ldg(q), v1 = __ldg(q + 1);
+    const uint32_t w[9] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w, 0u};
+    const uint32_t o = (uint32_t)(a & 15);
+    const uint32_t sh = ((o + 2) & 2) * 8;
+    uint32_t dw = 0;
+    switch (o >> 2) {
+      case 0: dw = w[0]; break;
+      case 1: dw = w[1]; break;
+      case 2: dw = w[2]; break;
+      default: dw = w[3]; break;
+    }
+    r.d = (dw >> ((o & 2) * 8)) & 0xffffu;
+    switch ((o + 2) >> 2) {
+      case 0:
+#pragma unroll
+        for (int i = 0; i < 4; i++) r.q[i] = __funnelshift_r(w[i], w[i + 1], sh);
+        break;
+      case 1:
+#pragma unroll
+        for (int i = 0; i < 4; i++) r.q[i] = __funnelshift_r(w[i + 1], w[i + 2], sh);
+        break;
+      case 2:
+#pragma unroll
+        for (int i = 0; i < 4; i++) r.q[i] = __funnelshift_r(w[i + 2], w[i + 3], sh);
+        break;
+      case 3:
+#pragma unroll
+        for (int i = 0; i < 4; i++) r.q[i] = __funnelshift_r(w[i + 3], w[i + 4], sh);
+        break;
+      default:
+#pragma unroll
+        for (int i = 0; i < 4; i++) r.q[i] = __funnelshift_r(w[i + 4], w[i + 5], sh);
+        break;
+    }
   } else if constexpr (TYPE == kQ8_0) {
     // block 2j + h of the eight: fp16 d, then 32 int8, at an even address.  Three 16-byte vectors
     // from the boundary below cover its 34 bytes; the offset is the same for all rows of a tile.
@@ -433,7 +473,37 @@ __device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, int h
     return;
   }
   const int j = ks & 3;
-  if constexpr (TYPE == kQ8_0) {
+  if constexpr (TYPE == kIQ4_NL) {
+    // w = d * table[q] (dequant.cr IQ4_NL): element i is the low nibble of byte i, element 16 + i
+    // the high one.  Three byte permutes look four nibbles up (the table's halves by the low three
+    // bits, then a choice by the fourth); two more sort the results into element order.
+    const float d = __half2float(__ushort_as_half((unsigned short)raw.d));
+    const uint64_t d_2 = f2_pack(d, d), unbias2 = f2_pack(-8388736.f, -8388736.f);
+    auto lut4 = [](uint32_t hq) {
+      const uint32_t s7 = hq & 0x7777u;
+      const uint32_t lo = __byte_perm(0xBFAD9881u, 0xF6EADDCFu, s7);
+      const uint32_t hi = __byte_perm(0x26190D01u, 0x71594535u, s7);
+      return __byte_perm(lo, hi, 0x3210u | ((hq >> 1) & 0x4444u));
+    };
+    uint32_t lows[4], highs[4];  // elements 4i .. 4i+3 and 16+4i .. 16+4i+3 as int8
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const uint32_t a = lut4(raw.q[i]), b = lut4(raw.q[i] >> 16);
+      lows[i] = __byte_perm(a, b, 0x6420);
+      highs[i] = __byte_perm(a, b, 0x7531);
+    }
+#pragma unroll
+    for (int c4 = 0; c4 < 4; c4++) {
+      uint32_t out[4];
+#pragma unroll
+      for (int w2 = 0; w2 < 2; w2++) {
+        const uint32_t q = (c4 < 2 ? lows[2 * c4 + w2] : highs[2 * (c4 - 2) + w2]) ^ 0x80808080u;
+        out[2 * w2] = f2_to_bf16x2(f2_mul(d_2, f2_add(bytes2_biased(q, 0), unbias2)));
+        out[2 * w2 + 1] = f2_to_bf16x2(f2_mul(d_2, f2_add(bytes2_biased(q, 2), unbias2)));
+      }
+      store_chunk(tile, r, 4 * h + c4, make_uint4(out[0], out[1], out[2], out[3]));
+    }
+  } else if constexpr (TYPE == kQ8_0) {
     // w = d * q (dequant.cr Q8_0): int8 b as the float 2^23 + (b ^ 0x80), minus 2^23 + 128
     const float d = __half2float(__ushort_as_half((unsigned short)raw.d));
     const uint64_t d_2 = f2_pack(d, d), unbias2 = f2_pack(-8388736.f, -8388736.f);
@@ -848,7 +918,7 @@ int launch_typed(const void *d_w, const void *d_x, void *d_y, int out_type, int 
   // tile's rows are then staged through shared memory
   {
     const long long row_bytes = (long long)(k_in / 256) * Sb<TYPE>::bytes;
-    if (TYPE != kQ8_0 && row_bytes % 16 == 0 && n_out >= kBM && g_prefill_stage_raw) {
+    if (TYPE != kQ8_0 && TYPE != kIQ4_NL && row_bytes % 16 == 0 && n_out >= kBM && g_prefill_stage_raw) {
       if (bn == 512) return launch<TYPE, 512, true>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
       if (bn == 256) return launch<TYPE, 256, true>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
       return launch<TYPE, 128, true>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
@@ -868,6 +938,7 @@ int launch_gemm_prefill(int type, const void *d_w, const void *d_x_bf16, void *d
     case kQ5_K: return launch_typed<kQ5_K>(d_w, d_x_bf16, d_y, out_type, m_rows, n_out, k_in, s);
     case kQ6_K: return launch_typed<kQ6_K>(d_w, d_x_bf16, d_y, out_type, m_rows, n_out, k_in, s);
     case kQ8_0: return launch_typed<kQ8_0>(d_w, d_x_bf16, d_y, out_type, m_rows, n_out, k_in, s);
+    case kIQ4_NL: return launch_typed<kIQ4_NL>(d_w, d_x_bf16, d_y, out_type, m_rows, n_out, k_in, s);
     default: return COGNI_QMM_ERR_TYPE;
   }
 }

@@ -287,7 +287,7 @@ int cogni_qmm_top1_unpack_keys(const int64_t *d_keys, int batch, int32_t *d_top_
  *   d_w      raw GGUF blocks [n_out][k_in], 16-byte aligned
  *   d_x      bf16 [m_rows, k_in] row-major, 16-byte aligned
  *   d_y      [m_rows, n_out] row-major, f32 or bf16 per out_type
- * type: Q8_0, Q4_K, Q5_K or Q6_K.  k_in must be a multiple of 256.
+ * type: any of the five tensor types.  k_in must be a multiple of 256.
  */
 int cogni_qmm_gemm_bf16(int type, const void *d_w, const void *d_x_bf16, void *d_y,
                         int out_type, int m_rows, int n_out, int k_in, void *stream);

@@ -72,7 +72,7 @@ def test_argument_errors_come_before_any_cuda_call(engine):
     assert lib.cogni_qmm_gemv_resident(12, None, None, None, 0, None, 256, 1, 1, None) == 1002
     assert lib.cogni_qmm_dequantize(12, 16, 100, 16, None) == 1002
     assert lib.cogni_qmm_gemv_top1(14, 16, 16, 256, 8, 1, 0, 16, 1, 16, 16, None, None) == 1004
-    assert lib.cogni_qmm_gemm_bf16(20, 16, 16, 16, 0, 1, 1, 256, None) == 1001    # IQ4_NL has no GEMM
+    assert lib.cogni_qmm_gemm_bf16(2, 16, 16, 16, 0, 1, 1, 256, None) == 1001     # Q4_0: not a type of this engine
     assert lib.cogni_qmm_gemm_bf16(12, 16, 16, 16, 0, 1, 1, 100, None) == 1002
     assert lib.cogni_qmm_set_kernel_choice(7) == 1002
     assert lib.cogni_qmm_gemv_top1_scratch_bytes(0, 1) == 0

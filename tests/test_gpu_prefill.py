@@ -14,7 +14,7 @@ import torch
 from cogni_ml_b200 import DeviceQuantWeight, QuantWeight, synth
 
 pytestmark = pytest.mark.gpu
-Q4_K, Q5_K, Q6_K, Q8_0 = synth.Q4_K, synth.Q5_K, synth.Q6_K, synth.Q8_0
+Q4_K, Q5_K, Q6_K, Q8_0, IQ4_NL = synth.Q4_K, synth.Q5_K, synth.Q6_K, synth.Q8_0, synth.IQ4_NL
 
 
 def bf16_round(a: np.ndarray) -> np.ndarray:
@@ -32,7 +32,7 @@ def run_case(cuda, oracle, qtype, m, n, k, seed, out_dtype=torch.float32):
     return w, x, y, ref
 
 
-@pytest.mark.parametrize("qtype", [Q4_K, Q5_K, Q6_K, Q8_0])
+@pytest.mark.parametrize("qtype", [Q4_K, Q5_K, Q6_K, Q8_0, IQ4_NL])
 @pytest.mark.parametrize("m,n,k", [(128, 128, 256), (256, 256, 512), (200, 200, 768), (1, 37, 256),
                                    (300, 1000, 1024)])
 def test_gemm_matches_bf16_operand_reference(cuda, oracle, engine, qtype, m, n, k):
@@ -45,7 +45,7 @@ def test_gemm_matches_bf16_operand_reference(cuda, oracle, engine, qtype, m, n, 
 @pytest.mark.parametrize("tile", [128, 256, 512])
 @pytest.mark.parametrize("qtype,m,n,k", [(Q4_K, 700, 300, 512), (Q6_K, 513, 128, 1024),
                                          (Q5_K, 1100, 260, 256), (Q4_K, 40, 128, 2048),
-                                         (Q8_0, 530, 300, 768)])
+                                         (Q8_0, 530, 300, 768), (IQ4_NL, 260, 200, 512)])
 def test_gemm_every_token_tile_width(cuda, oracle, engine, tile, qtype, m, n, k):
     """The token-tile width (128 / 256 / 512 tokens per CTA) is normally chosen from the shape;
     here each width is forced, with token counts that leave ragged and empty tile halves."""
@@ -120,7 +120,8 @@ def test_gemm_split_along_k(cuda, oracle, engine, tile, qtype, m, n, k):
     assert engine.lib.cogni_qmm_wait_timeouts() == 0
 
 
-@pytest.mark.parametrize("qtype,n,k", [(Q4_K, 1024, 4096), (Q6_K, 512, 12288), (Q8_0, 512, 4096)])
+@pytest.mark.parametrize("qtype,n,k", [(Q4_K, 1024, 4096), (Q6_K, 512, 12288), (Q8_0, 512, 4096),
+                                       (IQ4_NL, 256, 2048)])
 def test_gemm_within_stated_tolerance_of_cpu_quant_matmul(cuda, oracle, qtype, n, k):
     m = 512
     w, x, y, ref = run_case(cuda, oracle, qtype, m, n, k, seed=5)
