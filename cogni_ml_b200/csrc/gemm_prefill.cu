@@ -46,7 +46,7 @@ constexpr int kBK = 64;       // k elements per stage: 128 bytes of bf16 = one s
 template <int TYPE> struct Sb { static constexpr int bytes = BlockGeom<TYPE>::bytes * (256 / BlockGeom<TYPE>::elems); };
 constexpr int kRawBox = 128 * 128;
 __host__ __device__ constexpr int raw_stage_bytes(int type) {
-  return type == kQ6_K ? 2 * kRawBox : 128 * (type == kQ4_K ? 144 : 176);
+  return type == kQ6_K ? 2 * kRawBox : 128 * (type == kQ5_K ? 176 : 144);  // Q4_K, IQ4_NL: 144
 }
 __host__ __device__ constexpr int raw_bytes(int type, bool staged) { return staged ? 2 * raw_stage_bytes(type) : 0; }
 // stages of the ring that fit beside the raw windows (227 KB per CTA)
@@ -416,8 +416,19 @@ __device__ __forceinline__ void scale_min_regs(const uint4 &h, int s, float &sc,
 
 // Q4_K / Q5_K, staged: the words of k-step j of the block at blk (shared memory, 16-byte aligned)
 template <int TYPE>
-__device__ __forceinline__ void fetch_raw_from(const uint8_t *blk, int j, Raw<TYPE> &r) {
-  if constexpr (TYPE == kQ4_K) {
+__device__ __forceinline__ void fetch_raw_from(const uint8_t *blk, int j, int h, Raw<TYPE> &r) {
+  if constexpr (TYPE == kIQ4_NL) {
+    // block 2j + h: d at 36j + 18h, the quants 2 bytes on (a word boundary only for odd blocks)
+    const uint8_t *b = blk + 36 * j + 18 * h;
+    r.d = *reinterpret_cast<const unsigned short *>(b);
+    const uint32_t *q = reinterpret_cast<const uint32_t *>(b + 2 - 2 * (1 - h));  // word at or below the quants
+    const uint32_t sh = (uint32_t)(1 - h) * 16;
+    uint32_t w[5];
+#pragma unroll
+    for (int i = 0; i < 5; i++) w[i] = q[i < 4 || h == 0 ? i : 3];
+#pragma unroll
+    for (int i = 0; i < 4; i++) r.q[i] = __funnelshift_r(w[i], w[i + 1], sh);
+  } else if constexpr (TYPE == kQ4_K) {
     r.hdr = *reinterpret_cast<const uint4 *>(blk);
     r.q0 = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * j);
     r.q1 = *reinterpret_cast<const uint4 *>(blk + 32 + 32 * j);
@@ -646,7 +657,7 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
           tma_load_2d(smem_u32(raw_win + (sbl & 1) * kRawStage + kRawBox), &tmap_w, x0 + 128, raw_n0, full);
         } else {  // 144- and 176-byte blocks start on 16-byte boundaries
           tma_load_2d(smem_u32(raw_win + (sbl & 1) * kRawStage), &tmap_w,
-                      BlockGeom<TYPE>::bytes * (sb0 + sbl), raw_n0, full);
+                      Sb<TYPE>::bytes * (sb0 + sbl), raw_n0, full);
         }
       };
       if constexpr (STAGED) issue_raw(0);
@@ -725,7 +736,7 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
                                    210 * (sb0 + sbl) - q6_window_start(sb0 + sbl, (int)p.row_bytes),
                                    (ks0 + ks) & 3, h0, cur);
         else  // the block of row r sits at r * block bytes: the global fetch code reads it as it is
-          fetch_raw_from<TYPE>(raw_win + buf * kRawStage + rr * BlockGeom<TYPE>::bytes, (ks0 + ks) & 3, cur[0]);
+          fetch_raw_from<TYPE>(raw_win + buf * kRawStage + rr * Sb<TYPE>::bytes, (ks0 + ks) & 3, h0, cur[0]);
         if ((ks & 3) == 3 || ks == nks - 1) {  // this warp has read all it needs of the window
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&raw_bars[2 + buf]));
@@ -825,7 +836,7 @@ int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows
     // the weights as a byte matrix [n_out, row_bytes]: boxes of 128 rows x 128 bytes
     const cuuint64_t wdims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)n_out};
     const cuuint64_t wstrides[1] = {(cuuint64_t)row_bytes};
-    const cuuint32_t wbox[2] = {TYPE == kQ6_K ? 128u : (cuuint32_t)BlockGeom<TYPE>::bytes, 128};
+    const cuuint32_t wbox[2] = {TYPE == kQ6_K ? 128u : (cuuint32_t)Sb<TYPE>::bytes, 128};
     const cuuint32_t westr[2] = {1, 1};
     CUresult wr = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(d_w), wdims,
                          wstrides, wbox, westr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -918,7 +929,7 @@ int launch_typed(const void *d_w, const void *d_x, void *d_y, int out_type, int 
   // tile's rows are then staged through shared memory
   {
     const long long row_bytes = (long long)(k_in / 256) * Sb<TYPE>::bytes;
-    if (TYPE != kQ8_0 && TYPE != kIQ4_NL && row_bytes % 16 == 0 && n_out >= kBM && g_prefill_stage_raw) {
+    if (TYPE != kQ8_0 && row_bytes % 16 == 0 && n_out >= kBM && g_prefill_stage_raw) {
       if (bn == 512) return launch<TYPE, 512, true>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
       if (bn == 256) return launch<TYPE, 256, true>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
       return launch<TYPE, 128, true>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);

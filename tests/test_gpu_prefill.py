@@ -62,7 +62,8 @@ def test_gemm_every_token_tile_width(cuda, oracle, engine, tile, qtype, m, n, k)
 @pytest.mark.parametrize("tile", [128, 256, 512])
 @pytest.mark.parametrize("qtype,m,n,k", [(Q6_K, 200, 200, 2048), (Q6_K, 300, 1000, 6144),
                                          (Q6_K, 64, 37, 4096), (Q4_K, 300, 1000, 1280),
-                                         (Q5_K, 130, 129, 768), (Q4_K, 600, 50, 256)])
+                                         (Q5_K, 130, 129, 768), (Q4_K, 600, 50, 256),
+                                         (IQ4_NL, 270, 300, 1024)])
 def test_gemm_staged_superblocks(cuda, oracle, engine, tile, qtype, m, n, k):
     """Rows that are multiples of 16 bytes (Q4_K / Q5_K always, Q6_K when in_dim is a multiple of
     2048) are fetched by TMA into shared memory and expanded from there; rows beyond out_dim are
