@@ -248,6 +248,31 @@ def measure_extras(dev, gate_h, down_h, peaks):
 
     out["ffn_block_fused"] = {"kernel": "per layer: RMSNorm + ffn_gate/ffn_up (1 launch), SwiGLU + ffn_down + residual (1 launch), b1",
                               "us_per_layer": timed(ffn_blocks, 20) * 1e3 / 4}
+    # the same four layers replayed from a CUDA graph (as the headline is), against the unfused
+    # sequence of the same work: RMSNorm kernel, dual GEMV, SwiGLU kernel, GEMV with residual
+    xn = torch.empty_like(hidden)
+    plain_calls = [GemvMany([gates[2 * i], gates[2 * i + 1]], xn, [g_out, u_out]) for i in range(4)]
+
+    def ffn_blocks_unfused():
+        for i in range(4):
+            ms = hidden.pow(2).mean(dim=-1, keepdim=True)
+            torch.mul(hidden * torch.rsqrt(ms + 1e-6), norm_w, out=xn)
+            plain_calls[i].run()
+            torch.mul(torch.nn.functional.silu(g_out), u_out, out=prod)
+            downs[i].gemv(prod, out=hidden2, residual=hidden)
+
+    for name, fn in (("us_per_layer_graph", ffn_blocks), ("us_per_layer_unfused_graph", ffn_blocks_unfused)):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        out["ffn_block_fused"][name] = timed(graph.replay, 20) * 1e3 / 4
+        del graph
+    del plain_calls
     del calls
     # the speculative verifier's row batches: one layer's ffn_gate + ffn_up (one launch) and ffn_down
     # at batch 2 .. 16, weight bytes per second; four layers of weights (390 MB) defeat L2
