@@ -885,10 +885,11 @@ int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows
 template <int TYPE>
 int launch_typed(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows, int n_out,
                  int k_in, cudaStream_t s) {
-  // Token-tile width: wider tiles do less dequant work per flop (a tile's time is about 1 : 1.27 :
-  // 1.97 for 128 / 256 / 512 tokens of Q4_K, whose dequant is cheap, and 1 : 1.1 : 1.3 for Q6_K,
-  // which is bound by it), narrower ones fill the SMs in fewer, fuller waves.  Pick the width
-  // with the least waves x tile time.
+  // Token-tile width: wider tiles do less dequant work per flop, narrower ones fill the SMs in
+  // fewer, fuller waves.  Measured time of a tile of 128 / 256 / 512 tokens (in_dim 4096, us):
+  // Q4_K 34 / 42 / 73, Q5_K 36 / 44 / 73, IQ4_NL 43 / 48 / 73, Q6_K 54 / 60 / 75, Q8_0 54 / 66 / 85
+  // (at 512 tokens the tensor pipe is what bounds every type).  Pick the width with the least
+  // waves x tile time.
   static int sms = 0;
   if (!sms) {
     int dev = 0;
@@ -897,15 +898,15 @@ int launch_typed(const void *d_w, const void *d_x, void *d_y, int out_type, int 
     if (sms <= 0) sms = 148;
   }
   const long long row_tiles = (n_out + kBM - 1) / kBM;
-  const double rel256 = TYPE == kQ4_K ? 1.27 : TYPE == kQ5_K ? 1.2 : 1.1;
-  const double rel512 = TYPE == kQ4_K ? 1.97 : TYPE == kQ5_K ? 1.6 : 1.3;
+  const double rel256 = TYPE == kQ4_K || TYPE == kQ5_K || TYPE == kQ8_0 ? 1.22 : 1.12;
+  const double rel512 = TYPE == kQ4_K || TYPE == kQ5_K ? 2.08 : TYPE == kIQ4_NL ? 1.72 : TYPE == kQ8_0 ? 1.57 : 1.39;
   // Few row tiles against many SMs (a down projection at a short prompt): two CTAs per tile take
   // half of K each and add their partial tiles onto a zeroed f32 y.  Two addends commute, so the
   // result stays independent of the order; more splits would not.  The price is the memset of y
   // and read-modify-write instead of plain stores: about 12 bytes of HBM traffic per output
   // element, weighed here against the measured time of a 128-token tile's k-step (microseconds).
   const bool may_split = out_type == COGNI_QMM_OUT_F32 && k_in / kBK >= 16 && g_prefill_force_split != 1;
-  const double us_per_kstep = TYPE == kQ4_K ? 0.58 : TYPE == kQ5_K ? 0.75 : 0.84;
+  const double us_per_kstep = TYPE == kQ4_K || TYPE == kQ5_K ? 0.55 : TYPE == kIQ4_NL ? 0.67 : 0.85;
   const double tile_us = us_per_kstep * (k_in / kBK);
   const double split_us = 12.0 * (double)m_rows * (double)n_out / 6.0e6;
   auto cost = [&](int bn, double rel, int splits) {
