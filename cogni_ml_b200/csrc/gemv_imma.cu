@@ -1363,7 +1363,7 @@ int g_imma_force_pair = 0;  // diagnostics: 0 = automatic, 1 / 2 = superblocks p
 int g_imma_min_splits = 1;  // diagnostics: at least this many column ranges per row
 
 template <int TYPE>
-bool make_plan_pair(int in_dim, int nb, int pair, Params &p, size_t &smem) {
+bool make_plan_pair(int in_dim, int nb, int pair, Params &p, size_t &smem, bool thin = false) {
   using C = Cfg<TYPE>;
   const int nblk = in_dim / 256;
   const int ngroups = in_dim / C::GROUP;
@@ -1379,7 +1379,13 @@ bool make_plan_pair(int in_dim, int nb, int pair, Params &p, size_t &smem) {
   const size_t off_xq = off;     off = al(off + (dense ? (size_t)in_dim * 2 * nb : (size_t)(in_dim / 64) * (4 * nb) * 64));
   const size_t off_stage = off;
   const size_t stage_bytes = al((size_t)kR * C::RS);
-  if (off_stage + 3 * stage_bytes > kDynSmemMax) return false;
+  // Three stages, or for the 4- and 8-row instances two that still keep 80 KB in flight (Q5_K
+  // at 8 rows: one launch over two 45 KB stages beat two column ranges, 30 against 37 us; two
+  // 27 KB Q6_K stages did not: 340 against 279 us).  `thin`: two stages of any size, for the
+  // fused top-1, which cannot use column ranges.
+  const size_t room = kDynSmemMax > off_stage ? kDynSmemMax - off_stage : 0;
+  const bool two_ok = nb > 2 && room >= 2 * stage_bytes && (thin || 2 * stage_bytes >= 80 * 1024);
+  if (room < 3 * stage_bytes && !two_ok) return false;
   int stages = (int)((kDynSmemMax - off_stage) / stage_bytes);
   if (stages > 8) stages = 8;  // 2*stages mbarriers in the first 128 bytes of shared memory
   p.in_dim = in_dim;
@@ -1397,8 +1403,8 @@ bool make_plan_pair(int in_dim, int nb, int pair, Params &p, size_t &smem) {
 // the items a CTA can hold in its stages halve too: pairs are used when the stages still hold
 // enough of them to keep the warps busy.
 template <int TYPE>
-bool make_plan(int in_dim, int nb, Params &p, size_t &smem) {
-  if (nb > 2) return make_plan_pair<TYPE>(in_dim, nb, 1, p, smem);
+bool make_plan(int in_dim, int nb, Params &p, size_t &smem, bool thin = false) {
+  if (nb > 2) return make_plan_pair<TYPE>(in_dim, nb, 1, p, smem, thin);
   if (g_imma_force_pair != 1 && make_plan_pair<TYPE>(in_dim, nb, 2, p, smem) &&
       (g_imma_force_pair == 2 || p.stages * Cfg<TYPE>::KB / 2 >= 20))
     return true;
@@ -1442,13 +1448,13 @@ int kernel_rows(int batch) {
 // the fewest equal ranges of whole superblocks whose plan fits.  Every weight byte is still read
 // once; the later ranges add onto y.  0 = none fits.
 template <int TYPE>
-int column_splits(int in_dim, int batch) {
+int column_splits(int in_dim, int batch, bool thin = false) {
   const int nb = kernel_rows<TYPE>(batch);
   const int nblk = in_dim / 256;
   for (int n = g_imma_min_splits < nblk ? g_imma_min_splits : nblk; n <= 8 && n <= nblk; n++) {
     Params p{};
     size_t smem = 0;
-    if (make_plan<TYPE>((nblk + n - 1) / n * 256, nb, p, smem)) return n;
+    if (make_plan<TYPE>((nblk + n - 1) / n * 256, nb, p, smem, thin)) return n;
   }
   return 0;
 }
@@ -1470,15 +1476,15 @@ int batch_pass_width(int in_dim, int batch) {
 // activations fit without column ranges; 0 = the fused kernel cannot take the shape.
 template <int TYPE>
 int top1_pass_width(int in_dim, int batch) {
-  if (batch <= 2) return column_splits<TYPE>(in_dim, batch) == 1 ? batch : 0;
+  if (batch <= 2) return column_splits<TYPE>(in_dim, batch, true) == 1 ? batch : 0;
   int width = 0;
-  if (batch > 4 && column_splits<TYPE>(in_dim, 8) == 1) width = 8;
-  else if (column_splits<TYPE>(in_dim, 4) == 1) width = 4;
+  if (batch > 4 && column_splits<TYPE>(in_dim, 8, true) == 1) width = 8;
+  else if (column_splits<TYPE>(in_dim, 4, true) == 1) width = 4;
   if (width == 0) return 0;
   const int tail = batch % width;
-  if (tail > 4 && column_splits<TYPE>(in_dim, 8) != 1) return 0;
-  if (tail > 2 && tail <= 4 && column_splits<TYPE>(in_dim, 4) != 1) return 0;
-  if ((tail == 1 || tail == 2) && column_splits<TYPE>(in_dim, tail) != 1) return 0;
+  if (tail > 4 && column_splits<TYPE>(in_dim, 8, true) != 1) return 0;
+  if (tail > 2 && tail <= 4 && column_splits<TYPE>(in_dim, 4, true) != 1) return 0;
+  if ((tail == 1 || tail == 2) && column_splits<TYPE>(in_dim, tail, true) != 1) return 0;
   return width;
 }
 
@@ -1491,14 +1497,15 @@ int run_pass(int nj, const void *const *d_w, const float *d_x, const float *cons
              const float *d_norm_w, float norm_eps) {
   using C = Cfg<TYPE>;
   const int nbk = kernel_rows<TYPE>(batch);
-  const int nsplit = column_splits<TYPE>(in_dim, nbk);
+  const bool thin = top1 != nullptr;
+  const int nsplit = column_splits<TYPE>(in_dim, nbk, thin);
   if (nsplit == 0 || (top1 && nsplit > 1)) return COGNI_QMM_ERR_LIMIT;
   const int nblk = in_dim / 256, per = (nblk + nsplit - 1) / nsplit;
   for (int b0 = 0; b0 < nblk; b0 += per) {
     const int nb_here = nblk - b0 < per ? nblk - b0 : per;
     Params p{};
     size_t smem = 0;
-    if (!make_plan<TYPE>(nb_here * 256, nbk, p, smem)) return COGNI_QMM_ERR_LIMIT;
+    if (!make_plan<TYPE>(nb_here * 256, nbk, p, smem, thin)) return COGNI_QMM_ERR_LIMIT;
     p.row_bytes = (long long)nblk * C::BB;  // the pitch of the whole rows
     p.x = d_x + b0 * 256;
     p.x_up = d_x_up ? d_x_up + b0 * 256 : nullptr;
