@@ -1313,7 +1313,8 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
   }
   consumer_sync<kNW>();
   const int nparts = gridDim.x;
-  if (ctid < NB) p.part_keys[(long long)ctid * nparts + blockIdx.x] = s_best[ctid];
+  // rows at or beyond the batch have no slots in the caller's scratch (it is sized for `batch` rows)
+  if (ctid < NB && ctid < p.batch) p.part_keys[(long long)ctid * nparts + blockIdx.x] = s_best[ctid];
   __threadfence();
   consumer_sync<kNW>();
   if (ctid == 0) {
