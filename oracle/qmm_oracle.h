@@ -7,13 +7,18 @@
  * the shipped product path.  Only tests, the smoke check and the CPU-baseline
  * legs of the benchmark may link or load it.
  *
- * PARITY PIN STATUS: the reference is written in Crystal, which cannot be built
- * where this oracle is developed, and the reference holds no golden vectors for
- * Q8_0/Q4_K/Q5_K/Q6_K.  The helpers shared by every type (fp16_to_f32, the
- * bias-seeded f64 accumulator, the nibble order) are pinned through the one
+ * PARITY PIN STATUS: pinned by the reference's own CUDA kernels.  The reference is written in
+ * Crystal, which cannot be built where this oracle is developed, and it holds no golden vectors
+ * for Q8_0/Q4_K/Q5_K/Q6_K; but it ships an independent implementation of the same arithmetic as
+ * PTX text (src/ml/cuda/kernels/q4k_gemv_probe.ptx, q5k_gemv_probe.ptx, q6k_gemv_probe.ptx,
+ * q4k_dual_gemv_probe.ptx, bin/cuda_q8_gemv_probe.cr:39-227,
+ * src/ml/cuda/qwen_output_head_runner.cr:14-625).  oracle/make_ref.py assembles that text,
+ * unmodified, into oracle/_ref/*.cubin and tests/test_gpu_reference_ptx.py runs it on the GPU
+ * against this oracle on the same seeded tensors, inside the reference probes' own thresholds
+ * (cos >= 0.99999, max_diff <= 1e-3; Q8_0: 0.999999, 1e-4), for the single-token, four-token,
+ * row-batched, residual-add, dual and fused top-1 kernels.  The helpers shared by every type
+ * (fp16_to_f32, the bias-seeded f64 accumulator, the nibble order) are also pinned through the one
  * synthetic known-answer spec the reference has (spec/iq4_nl_dequant_spec.cr:34-106).
- * For Q8_0/Q4_K/Q5_K/Q6_K the block arithmetic is "parity unpinned": it is checked
- * against an independent numpy restatement and hand-derived blocks only.
  */
 #ifndef QMM_ORACLE_H
 #define QMM_ORACLE_H
