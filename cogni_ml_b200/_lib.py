@@ -12,12 +12,12 @@ LIB_PATH = Path(__file__).resolve().parent / "libcogni_qmm.so"
 
 _vp, _i, _i64, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_size_t
 
-# symbol -> (restype, argtypes); kept in the order of include/cogni_qmm.h
+# symbol -> (restype, argtypes); kept in the order of include/cogni_qmm.h, then include/cogni_qmm_diag.h
 SIGNATURES = {
     "cogni_qmm_abi_version": (_i, []),
     "cogni_qmm_status_string": (C.c_char_p, [_i]),
-    "cogni_qmm_set_kernel_choice": (_i, [_i]),
     "cogni_qmm_wait_timeouts": (C.c_uint, []),
+    "cogni_qmm_reset_wait_timeouts": (_i, []),
     "cogni_qmm_block_bytes": (_i, [_i]),
     "cogni_qmm_block_elements": (_i, [_i]),
     "cogni_qmm_row_bytes": (_i64, [_i, _i]),
@@ -39,6 +39,9 @@ SIGNATURES = {
     "cogni_qmm_top1_unpack_keys": (_i, [_vp, _i, _vp, _vp, _vp]),
     "cogni_qmm_gemm_bf16": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "cogni_qmm_matmul_add_host": (_i, [_vp, _i, _i, _vp, _i64, _i, _i, _vp, _vp]),
+    # include/cogni_qmm_diag.h
+    "cogni_qmm_set_kernel_choice": (_i, [_i]),
+    "cogni_qmm_diag_expire_wait": (_i, [C.c_uint, _vp]),
 }
 
 

@@ -40,7 +40,7 @@ def needs_build() -> bool:
     if not LIB_PATH.exists():
         return True
     newest = max(p.stat().st_mtime for p in list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh"))
-                 + [PKG_DIR.parent / "include" / "cogni_qmm.h"])
+                 + [PKG_DIR.parent / "include" / "cogni_qmm.h", PKG_DIR.parent / "include" / "cogni_qmm_diag.h"])
     return newest > LIB_PATH.stat().st_mtime
 
 

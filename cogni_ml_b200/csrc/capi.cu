@@ -1,9 +1,11 @@
 // extern "C" entry points of libcogni_qmm.so: argument checks, kernel selection, and the
-// one-shot host-buffer form.  Declarations and per-function contracts: include/cogni_qmm.h.
+// one-shot host-buffer form.  Declarations and per-function contracts: include/cogni_qmm.h
+// (the product ABI) and include/cogni_qmm_diag.h (A/B switches for tests and measurements).
 #include <cstdio>
 #include <cstring>
 
 #include "qmm_common.cuh"
+#include "../../include/cogni_qmm_diag.h"
 
 using namespace cogni;
 
@@ -26,6 +28,21 @@ int check_gemv_args(int type, const void *w, const void *x, const void *y, int i
 
 }  // namespace
 
+namespace cogni {
+// Everything cogni_qmm_gemv_top1 checks before it touches the device (shared with the entry point
+// that keeps the scratch inside the library, which must not write to it for a call it rejects).
+int check_top1_args(int type, const void *d_w, const float *d_x, int in_dim, int out_dim, int batch,
+                    int32_t index_base, const void *d_scratch, size_t scratch_bytes,
+                    const int32_t *d_top_index, const float *d_top_value) {
+  int st = check_gemv_args(type, d_w, d_x, d_top_value, in_dim, out_dim, batch);
+  if (st) return st;
+  if (!d_top_index || !d_scratch || index_base < 0) return COGNI_QMM_ERR_ARG;
+  if (reinterpret_cast<uintptr_t>(d_scratch) & 7) return COGNI_QMM_ERR_ALIGN;
+  if (scratch_bytes < top1_scratch_bytes(out_dim, batch)) return COGNI_QMM_ERR_SCRATCH;
+  return COGNI_QMM_OK;
+}
+}  // namespace cogni
+
 extern "C" {
 
 int cogni_qmm_abi_version(void) { return COGNI_QMM_ABI_VERSION; }
@@ -39,6 +56,7 @@ const char *cogni_qmm_status_string(int status) {
     case COGNI_QMM_ERR_SCRATCH: return "scratch buffer too small";
     case COGNI_QMM_ERR_DEVICE: return "device is not compute capability 10.x";
     case COGNI_QMM_ERR_LIMIT: return "size beyond the entry point's fixed maximum";
+    case COGNI_QMM_ERR_TIMEOUT: return "a bounded device-side wait expired: results invalid until cogni_qmm_reset_wait_timeouts()";
     default: break;
   }
   if (status > 0 && status < 1000) return cudaGetErrorString(static_cast<cudaError_t>(status));
@@ -46,16 +64,17 @@ const char *cogni_qmm_status_string(int status) {
 }
 
 int cogni_qmm_set_kernel_choice(int choice) {
-  if (choice >= 16 && choice <= 21) {  // timing diagnostics of the tiled kernels (results invalid)
+#ifdef COGNI_QMM_DIAG_TIMING
+  if (choice >= 16 && choice <= 21) {  // timing diagnostics of the tiled GEMV (results invalid)
     // 16 normal, 17 stream only, 18 stream + scale decode; 19-21 the same without the copies
-    gemv_mma_set_debug(choice <= 18 ? choice - 16 : 0);
     gemv_imma_set_debug(choice <= 18 ? choice - 16 : 4 + (choice == 19 ? 0 : choice - 19));
     return COGNI_QMM_OK;
   }
-  if (choice >= 32 && choice < 48) {  // raw diagnostic bits of the tiled GEMV
+  if (choice >= 32 && choice < 48) {  // raw diagnostic bits of the tiled GEMV (results invalid)
     gemv_imma_set_debug(choice - 32);
     return COGNI_QMM_OK;
   }
+#endif
   if (choice >= 48 && choice <= 51) {  // prefill token-tile width: automatic / 128 / 256 / 512
     gemm_prefill_set_tile(choice == 48 ? 0 : 64 << (choice - 48));
     return COGNI_QMM_OK;
@@ -72,6 +91,10 @@ int cogni_qmm_set_kernel_choice(int choice) {
     gemv_imma_set_min_splits(choice - 26);
     return COGNI_QMM_OK;
   }
+  if (choice >= 60 && choice <= 68) {  // K slabs of the tiled GEMV: off / 1 .. 8 wherever a plan allows
+    gemv_imma_set_slabs(choice - 60);
+    return COGNI_QMM_OK;
+  }
   if (choice >= 24 && choice <= 26) {  // superblocks per work item of the tiled GEMV: automatic / 1 / 2
     gemv_imma_set_pair(choice - 24);
     return COGNI_QMM_OK;
@@ -81,7 +104,17 @@ int cogni_qmm_set_kernel_choice(int choice) {
   return COGNI_QMM_OK;
 }
 
-unsigned cogni_qmm_wait_timeouts(void) { return gemv_mma_timeouts() + gemv_imma_timeouts() + gemm_prefill_timeouts(); }
+int cogni_qmm_diag_expire_wait(unsigned limit_us, void *stream) {
+  return launch_expire_wait(limit_us, static_cast<cudaStream_t>(stream));
+}
+
+unsigned cogni_qmm_wait_timeouts(void) { return gemv_imma_timeouts() + gemm_prefill_timeouts(); }
+
+int cogni_qmm_reset_wait_timeouts(void) {
+  int st = gemv_imma_reset_timeouts();
+  if (st == COGNI_QMM_OK) st = gemm_prefill_reset_timeouts();
+  return st;
+}
 
 int cogni_qmm_block_bytes(int type) { return block_bytes(type); }
 int cogni_qmm_block_elements(int type) { return block_elems(type); }
@@ -229,11 +262,9 @@ int cogni_qmm_gemv_top1(int type, const void *d_w, const float *d_x, int in_dim,
                         int batch, int32_t index_base, void *d_scratch, size_t scratch_bytes,
                         int32_t *d_top_index, float *d_top_value, int64_t *d_top_key,
                         void *stream) {
-  int st = check_gemv_args(type, d_w, d_x, d_top_value, in_dim, out_dim, batch);
+  int st = check_top1_args(type, d_w, d_x, in_dim, out_dim, batch, index_base, d_scratch, scratch_bytes,
+                           d_top_index, d_top_value);
   if (st) return st;
-  if (!d_top_index || !d_scratch || index_base < 0) return COGNI_QMM_ERR_ARG;
-  if (reinterpret_cast<uintptr_t>(d_scratch) & 7) return COGNI_QMM_ERR_ALIGN;
-  if (scratch_bytes < top1_scratch_bytes(out_dim, batch)) return COGNI_QMM_ERR_SCRATCH;
   return launch_gemv_top1(type, d_w, d_x, in_dim, out_dim, batch, index_base, d_scratch,
                           d_top_index, d_top_value, reinterpret_cast<long long *>(d_top_key),
                           static_cast<cudaStream_t>(stream));
@@ -322,6 +353,7 @@ int cogni_qmm_matmul_add_host(const float *x, int rows, int in_dim, const void *
       (!bias || step(cudaMemcpy(d_b, bias, (size_t)out_dim * 4, cudaMemcpyHostToDevice)))) {
     st = cogni_qmm_gemv(type, d_w, d_x, d_b, 0, d_y, in_dim, out_dim, rows, nullptr);
     if (st == COGNI_QMM_OK) step(cudaMemcpy(y, d_y, yb, cudaMemcpyDeviceToHost));
+    if (st == COGNI_QMM_OK && cogni_qmm_wait_timeouts() != 0) st = COGNI_QMM_ERR_TIMEOUT;
   }
   cudaFree(d_w);
   cudaFree(d_x);

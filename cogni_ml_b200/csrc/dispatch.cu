@@ -26,8 +26,6 @@ int launch_gemv(int type, const void *d_w, const float *d_x, const float *d_adde
   if (g_force_rowwarp == 0 && gemv_imma_supports(type, d_w, d_x, in_dim, batch))
     return launch_gemv_imma(type, d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch,
                             resident, s);
-  if (g_force_rowwarp == 0 && gemv_mma_supports(type, d_w, d_x, in_dim))
-    return launch_gemv_mma(type, d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, s);
   return launch_gemv_rowwarp(type, d_w, d_x, d_addend, addend_stride, d_y, in_dim, out_dim, batch, s);
 }
 
@@ -37,9 +35,6 @@ int launch_gemv_top1(int type, const void *d_w, const float *d_x, int in_dim, in
   if (g_force_rowwarp == 0 && gemv_imma_supports(type, d_w, d_x, in_dim, batch, true))
     return launch_gemv_top1_imma(type, d_w, d_x, in_dim, out_dim, batch, index_base, d_scratch,
                                  d_idx, d_val, d_key, 0, s);
-  if (g_force_rowwarp == 0 && gemv_mma_supports(type, d_w, d_x, in_dim))
-    return launch_gemv_top1_mma(type, d_w, d_x, in_dim, out_dim, batch, index_base, d_scratch,
-                                d_idx, d_val, d_key, s);
   return launch_gemv_top1_rowwarp(type, d_w, d_x, in_dim, out_dim, batch, index_base, d_scratch,
                                   d_idx, d_val, d_key, s);
 }

@@ -965,4 +965,9 @@ unsigned gemm_prefill_timeouts() {
   return v;
 }
 
+int gemm_prefill_reset_timeouts() {
+  const unsigned zero = 0;
+  return (int)cudaMemcpyToSymbol(g_pipe_wait_timeouts, &zero, sizeof(zero));
+}
+
 }  // namespace cogni

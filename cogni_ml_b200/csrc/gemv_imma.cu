@@ -38,10 +38,19 @@
 // launching at once and itself waits for its predecessor only before it touches x or y.  With
 // `resident` weights the producer starts fetching weights before that wait.
 #include <climits>
+#include <mutex>
 #include <type_traits>
 
 #include "qmm_common.cuh"
 #include "tma_pipe.cuh"
+
+// Timing diagnostics (stream only / decode only / no copies / sleeping items) give invalid results
+// and exist only in builds made with -DCOGNI_QMM_DIAG_TIMING; the shipped kernels carry none.
+#ifdef COGNI_QMM_DIAG_TIMING
+#define COGNI_DIAG(x) (x)
+#else
+#define COGNI_DIAG(x) 0
+#endif
 
 namespace cogni {
 namespace {
@@ -104,6 +113,7 @@ template <> struct Cfg<kQ6_K> {
 };
 
 constexpr int kMaxJobs = 32;  // weight matrices one launch can take (they share x)
+constexpr int kMaxItems = 128;  // work items (superblocks or pairs) per row tile: in_dim <= 32768
 
 struct Job {
   const uint8_t *w;
@@ -132,6 +142,11 @@ struct Params {
   int pair;      // superblocks per work item (1 or 2)
   int resident;  // weights were complete before the preceding kernel started
   int debug;     // diagnostics: bits 0-1: 1 = no work on the stages, 2 = decode only; bit 2: no copies; bit 3: items sleep
+  // K slabs: nslabs CTAs share a row tile, each takes nblk superblocks of the row (slab s: the
+  // superblocks s*nblk ..); their partial sums meet in ws, the CTA that arrives last adds them up
+  int nslabs;            // 1: every CTA takes whole rows
+  float *ws;             // [tile][slab][batch row][16] partial sums
+  unsigned *ws_tickets;  // [tile] arrival counters, zero between launches
   long long *part_keys;  // fused top-1 (nullptr: plain GEMV)
   unsigned *counter;
   int32_t *top_idx;
@@ -140,20 +155,6 @@ struct Params {
   int index_base;
 };
 
-#ifdef COGNI_TRACE
-// timing diagnostics (never compiled into the shipped library): per-warp event log of CTA 0
-__device__ long long g_trace[1 << 16];
-__device__ __forceinline__ void trace(int warp, int lane, int &n, int ev) {
-  if (blockIdx.x == 0 && lane == 0 && n < 500) {
-    g_trace[(warp * 512 + n) * 2] = ev;
-    g_trace[(warp * 512 + n) * 2 + 1] = clock64();
-    n++;
-  }
-}
-#define TRACE(ev) trace(warp, lane, tr_n, ev)
-#else
-#define TRACE(ev)
-#endif
 
 template <int NW>
 __device__ __forceinline__ void consumer_sync() {
@@ -970,6 +971,185 @@ __device__ __forceinline__ void mma_dense(const uint8_t *blk, int pad_a, int pad
   }
 }
 
+// ---------------------------------------------------------------------------- Q6_K, batch 1-2
+// Q6_K at batch 1-2 keeps everything up to the end of a superblock in the integer domain.
+//  * Activations: ONE scale per superblock and batch row (x = sxb * n, |n| <= 16256, n = 128*hi + lo
+//    as above) instead of one per 16-element group, so the int8 group scales of the weights can be
+//    applied to the integer group sums and a row converts to float once per superblock.
+//  * The quants are never assembled.  ql bytes are split by two ANDs into L = b & 0x0F (elements
+//    32k + l, k = 0 / 1) and H = b & 0xF0 (16 x elements 32k + l, k = 2 / 3); the qh byte by four
+//    ANDs into its 2-bit fields in place (f0, 4*f1, 16*f2, 64*f3).  Per "unit" (half n of the
+//    superblock, 16-element run h: 64 weights of 4 scale groups k = 0..3 per row) four MMAs
+//        A = [L(ql run of k=0) | L(ql run of k=1)],  A = [H(k=2) | H(k=3)]   -> accumulator cq
+//        A = [f0 | 4 f1],                            A = [16 f2 | 64 f3]     -> accumulator ch
+//    whose eight columns are (group k, plane): column 2k + plane holds that group's activations in
+//    the k-slots of its own run and zeros in the other run's.  Lane (g, t) thus receives the exact
+//    sums of group k = t for rows g and g+8; 16 * sum(q * n) = mq * cq + mh * ch with
+//    (mq, mh) = (16, 256), (16, 64), (1, 16), (1, 4) for k = 0..3.
+//  * A lane keeps one activation word per unit (its column's 4 elements of its plane); the B
+//    fragments are that word or zero, selected by the lane's k: 2 bytes of shared memory per
+//    element and batch row.
+//  * The -32 of every quant is one integer term per group from the sums of n.
+// Integer ranges: |cq| <= 16 * 240 * 127, |ch| <= 16 * 192 * 127 per unit, times |sc| <= 128, four
+// units per lane and superblock, times at most 16 resp. 256 at the end: below 1.1e9.
+//
+// Quantises NBLK superblocks of x from kblk on.  Lane = 8 consecutive elements:
+// element 128 n + 32 k + 16 h + i  ->  unit u = 2 n + h, column 2 k + plane, MMA lane t = i / 4.
+template <int NB, int NBLK>
+__device__ __forceinline__ void quantise_q6v2(const float *x, const float *x_up, const float *norm_w,
+                                              const float *inv_rms, int K, int kblk, int lane,
+                                              uint8_t *xq, float *SXB, int *NG) {
+  const int e_in = lane * 8;
+  float4 v0[NBLK][NB], v1[NBLK][NB];
+#pragma unroll
+  for (int q = 0; q < NBLK; q++)
+#pragma unroll
+    for (int b = 0; b < NB; b++) {
+      const long long off = (long long)b * K + (kblk + q) * 256 + e_in;
+      v0[q][b] = __ldg(reinterpret_cast<const float4 *>(x + off));
+      v1[q][b] = __ldg(reinterpret_cast<const float4 *>(x + off + 4));
+      if (x_up) {  // SwiGLU: silu(gate) * up in f32 (qwen35_cpu.cr:512-519, 1716-1717)
+        const float4 u0 = __ldg(reinterpret_cast<const float4 *>(x_up + off));
+        const float4 u1 = __ldg(reinterpret_cast<const float4 *>(x_up + off + 4));
+        auto sw = [](float gte, float up) { return gte / (1.f + expf(-gte)) * up; };
+        v0[q][b] = make_float4(sw(v0[q][b].x, u0.x), sw(v0[q][b].y, u0.y), sw(v0[q][b].z, u0.z), sw(v0[q][b].w, u0.w));
+        v1[q][b] = make_float4(sw(v1[q][b].x, u1.x), sw(v1[q][b].y, u1.y), sw(v1[q][b].z, u1.z), sw(v1[q][b].w, u1.w));
+      }
+      if (norm_w) {  // RMSNorm: x * inv_rms * w in f32, left to right (qwen35_cpu.cr:484-490)
+        const float4 w0 = __ldg(reinterpret_cast<const float4 *>(norm_w + (kblk + q) * 256 + e_in));
+        const float4 w1 = __ldg(reinterpret_cast<const float4 *>(norm_w + (kblk + q) * 256 + e_in + 4));
+        const float r = inv_rms[b];
+        v0[q][b] = make_float4(v0[q][b].x * r * w0.x, v0[q][b].y * r * w0.y, v0[q][b].z * r * w0.z, v0[q][b].w * r * w0.w);
+        v1[q][b] = make_float4(v1[q][b].x * r * w1.x, v1[q][b].y * r * w1.y, v1[q][b].z * r * w1.z, v1[q][b].w * r * w1.w);
+      }
+    }
+  const int n = lane >> 4, k = (lane >> 2) & 3, h = (lane >> 1) & 1;
+  const int u = 2 * n + h, t0 = 2 * (lane & 1);
+#pragma unroll
+  for (int q = 0; q < NBLK; q++)
+#pragma unroll
+    for (int b = 0; b < NB; b++) {
+      const float v[8] = {v0[q][b].x, v0[q][b].y, v0[q][b].z, v0[q][b].w,
+                          v1[q][b].x, v1[q][b].y, v1[q][b].z, v1[q][b].w};
+      float mx = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; e++) mx = fmaxf(mx, fabsf(v[e]));
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      const bool live = mx > 1e-30f;  // a superblock below that contributes nothing
+      const float sxb = live ? mx * (1.f / kNMax) : 1.f;
+      const float inv = live ? (float)kNMax / mx : 0.f;
+      uint32_t bits[8], up[8];
+      int nsum = 0;
+#pragma unroll
+      for (int e = 0; e < 8; e++) {  // n in the low bits of x * inv + 1.5 * 2^23 (round to nearest)
+        bits[e] = __float_as_uint(fmaf(v[e], inv, 12582912.f));
+        up[e] = bits[e] << 1;
+        nsum += (int)(bits[e] - 0x4B400000u);
+      }
+      nsum += __shfl_xor_sync(0xffffffffu, nsum, 1);  // the group's 16 elements: this lane and its neighbour
+      const int sb = (kblk + q) * NB + b;
+      if ((lane & 1) == 0) NG[(sb * 4 + k) * 4 + u] = nsum;
+      if (lane == 0) SXB[sb] = sxb;
+      uint32_t *dst = reinterpret_cast<uint32_t *>(xq) + (sb * 4 + u) * 32 + 8 * k + t0;
+#pragma unroll
+      for (int w4 = 0; w4 < 2; w4++) {
+        const uint32_t lw = __byte_perm(__byte_perm(bits[4 * w4], bits[4 * w4 + 1], 0x0040),
+                                        __byte_perm(bits[4 * w4 + 2], bits[4 * w4 + 3], 0x0040),
+                                        0x5410) & 0x7f7f7f7fu;
+        const uint32_t hw = __byte_perm(__byte_perm(up[4 * w4], up[4 * w4 + 1], 0x0051),
+                                        __byte_perm(up[4 * w4 + 2], up[4 * w4 + 3], 0x0051), 0x5410);
+        dst[w4] = hw;      // column 2k:     hi plane
+        dst[4 + w4] = lw;  // column 2k + 1: lo plane
+      }
+    }
+}
+
+// One superblock of 16 rows against NB batch rows.  ra / rb: this superblock in rows g and g+8
+// (2-byte aligned); xw: the lane's activation word of unit 0, batch row 0; ng: the lane's four
+// group sums (units 0..3 of group k = t), batch row 0; sxb: the superblock's activation scales.
+template <int NB, bool ALIGNED>
+__device__ __forceinline__ void mma_q6v2(const uint8_t *ra, const uint8_t *rb, const uint32_t *xw,
+                                         const int4 *ng, const float *sxb, int lane,
+                                         float (&acc0)[NB], float (&acc1)[NB]) {
+  constexpr uint32_t ML = 0x0f0f0f0fu, MH = 0xf0f0f0f0u;
+  const int t = lane & 3, kcol = lane >> 3;
+  const uintptr_t aa = reinterpret_cast<uintptr_t>(ra) + 4 * t, ab = reinterpret_cast<uintptr_t>(rb) + 4 * t;
+  const uint8_t *base[2] = {reinterpret_cast<const uint8_t *>(aa & ~(uintptr_t)3),
+                            reinterpret_cast<const uint8_t *>(ab & ~(uintptr_t)3)};
+  const uint32_t sh[2] = {(uint32_t)(aa & 2) * 8, (uint32_t)(ab & 2) * 8};
+  auto ld = [&](int r, int off) {
+    const uint32_t *w32 = reinterpret_cast<const uint32_t *>(base[r] + off);
+    if constexpr (ALIGNED) return w32[0];
+    else return __funnelshift_r(w32[0], w32[1], sh[r]);
+  };
+  // the group scales of this lane's groups 8n + 2t + h, as (n, h) = unit order, rows g / g+8
+  int sc[2][4];
+#pragma unroll
+  for (int r = 0; r < 2; r++) {
+    const uint8_t *row = r ? rb : ra;
+    const uint32_t s01 = *reinterpret_cast<const unsigned short *>(row + 192 + 2 * t);
+    const uint32_t s23 = *reinterpret_cast<const unsigned short *>(row + 200 + 2 * t);
+    sc[r][0] = (int)(signed char)(s01 & 0xffu);
+    sc[r][1] = (int)(signed char)(s01 >> 8);
+    sc[r][2] = (int)(signed char)(s23 & 0xffu);
+    sc[r][3] = (int)(signed char)(s23 >> 8);
+  }
+  // B fragment selectors: the lane's word belongs to the k-slots of run k of its column's group
+  const uint32_t m0 = kcol == 0 ? 0xffffffffu : 0u, m1 = kcol == 1 ? 0xffffffffu : 0u;
+  const uint32_t m2 = kcol == 2 ? 0xffffffffu : 0u, m3 = kcol == 3 ? 0xffffffffu : 0u;
+  int aq[NB][4], ah[NB][4], corr[NB][2];
+#pragma unroll
+  for (int b = 0; b < NB; b++) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) aq[b][i] = ah[b][i] = 0;
+    corr[b][0] = corr[b][1] = 0;
+  }
+  int4 ngv[NB];
+#pragma unroll
+  for (int b = 0; b < NB; b++) ngv[b] = ng[b * 4];
+#pragma unroll
+  for (int u = 0; u < 4; u++) {
+    const int n = u >> 1, h = u & 1;
+    uint32_t q0[2], q1[2], qh[2];
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      q0[r] = ld(r, 64 * n + 16 * h);
+      q1[r] = ld(r, 64 * n + 32 + 16 * h);
+      qh[r] = ld(r, 128 + 32 * n + 16 * h);
+    }
+#pragma unroll
+    for (int b = 0; b < NB; b++) {
+      const uint32_t w = xw[(b * 4 + u) * 32];
+      const uint32_t b0 = w & m0, b1 = w & m1, b2 = w & m2, b3 = w & m3;
+      int cq[4], ch[4];
+      imma_zero(cq, q0[0] & ML, q0[1] & ML, q1[0] & ML, q1[1] & ML, b0, b1);
+      imma_acc(cq, q0[0] & MH, q0[1] & MH, q1[0] & MH, q1[1] & MH, b2, b3);
+      imma_zero(ch, qh[0] & 0x03030303u, qh[1] & 0x03030303u, qh[0] & 0x0c0c0c0cu, qh[1] & 0x0c0c0c0cu, b0, b1);
+      imma_acc(ch, qh[0] & 0x30303030u, qh[1] & 0x30303030u, qh[0] & 0xc0c0c0c0u, qh[1] & 0xc0c0c0c0u, b2, b3);
+      const int ngu = u == 0 ? ngv[b].x : u == 1 ? ngv[b].y : u == 2 ? ngv[b].z : ngv[b].w;
+      aq[b][0] += sc[0][u] * cq[0];  aq[b][1] += sc[0][u] * cq[1];
+      aq[b][2] += sc[1][u] * cq[2];  aq[b][3] += sc[1][u] * cq[3];
+      ah[b][0] += sc[0][u] * ch[0];  ah[b][1] += sc[0][u] * ch[1];
+      ah[b][2] += sc[1][u] * ch[2];  ah[b][3] += sc[1][u] * ch[3];
+      corr[b][0] += sc[0][u] * ngu;
+      corr[b][1] += sc[1][u] * ngu;
+    }
+  }
+  const int mq = t < 2 ? 16 : 1, mh = 256 >> (2 * t);
+  const float da = load_half_as_float(ra + 208), db = load_half_as_float(rb + 208);
+#pragma unroll
+  for (int b = 0; b < NB; b++) {
+    const float s16 = sxb[b] * 0.0625f;  // the integer sums are 16 x the true ones
+    const float fa = fmaf(-512.f, (float)corr[b][0],
+                          fmaf(128.f, (float)(mq * aq[b][0] + mh * ah[b][0]), (float)(mq * aq[b][1] + mh * ah[b][1])));
+    const float fb = fmaf(-512.f, (float)corr[b][1],
+                          fmaf(128.f, (float)(mq * aq[b][2] + mh * ah[b][2]), (float)(mq * aq[b][3] + mh * ah[b][3])));
+    acc0[b] = fmaf(da * s16, fa, acc0[b]);
+    acc1[b] = fmaf(db * s16, fb, acc1[b]);
+  }
+}
+
 // ---------------------------------------------------------------------------- the kernel
 template <int TYPE, int NB, int PAIR>
 __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1)
@@ -978,11 +1158,12 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
   using C = Cfg<TYPE>;
   using A = Area<TYPE>;
   constexpr bool DENSE = NB > 2;                 // batches 3 .. 8: one MMA column set per 4 batch rows
+  constexpr bool V2 = TYPE == kQ6_K && !DENSE;   // integer-domain group scales, no decode pass
   static_assert(!DENSE || (PAIR == 1 && NB % 4 == 0), "dense items are single superblocks");
   constexpr int kFoldBufs = fold_bufs(NB);
   constexpr int NCX = 4 * NB;                    // columns of the quantised-x layout
   constexpr int UNIT_BYTES = NCX * 64;
-  constexpr int AREA_FLOATS = DENSE ? 16 * dense_area_row(C::NG, NB) : PAIR * NB * A::BATCH;  // PAIR superblocks per item
+  constexpr int AREA_FLOATS = V2 ? 0 : DENSE ? 16 * dense_area_row(C::NG, NB) : PAIR * NB * A::BATCH;  // PAIR superblocks per item
   extern __shared__ __align__(128) uint8_t smem[];
   // mbarriers full[S] | empty[S] in the first 128 bytes; monotone counters from byte 192:
   // chunks armed by the producer | partial sums stored per tile buffer | folds done per tile buffer
@@ -992,16 +1173,17 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
   int *xready = reinterpret_cast<int *>(smem + p.off_flags);  // per superblock pair of x: quantised
   const int S = p.stages;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef COGNI_TRACE
-  int tr_n = 0;
-#endif
-  TRACE(1);
   pdl_launch_dependents();
 
   uint8_t *stages = smem + p.off_stage;
-  // The jobs' 16-row tiles form one global sequence (job-major); this CTA's tiles are
-  // blockIdx.x + i * gridDim.x, i < ntl.
-  const int ntl = (p.tcum[p.njobs] - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  // The jobs' 16-row tiles form one global sequence (job-major).  The grid is G row groups x
+  // nslabs K slabs: this CTA takes slab `slab` of the tiles rg + i * G, i < ntl.
+  const int nslabs = p.nslabs;
+  const int slab = nslabs > 1 ? (int)blockIdx.x % nslabs : 0;
+  const int rg = nslabs > 1 ? (int)blockIdx.x / nslabs : (int)blockIdx.x;
+  const int G = nslabs > 1 ? (int)gridDim.x / nslabs : (int)gridDim.x;
+  const long long slab_bytes = (long long)slab * p.nblk * C::BB;  // the slab's offset into a row
+  const int ntl = (p.tcum[p.njobs] - rg + G - 1) / G;
   auto locate = [&](int gt, int &j) {  // job of global tile gt, searched from the hint j
     while (gt >= p.tcum[j + 1]) j++;
     while (gt < p.tcum[j]) j--;
@@ -1016,8 +1198,8 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
       if (lane < S) mbar_init(smem_u32(&bars[lane]), kPW);
       else if (lane < 2 * S) mbar_init(smem_u32(&bars[lane]), C::KB);
       else if (lane < 2 * S + 1 + 2 * kFoldBufs) issued[lane - 2 * S] = 0;
-      xready[lane] = 0;
-      xready[lane + 32] = 0;
+#pragma unroll
+      for (int i = 0; i < kMaxItems / 32; i++) xready[lane + 32 * i] = 0;
       mbar_fence_init();
     }
     asm volatile("bar.sync 2, %0;" ::"n"(kPW * 32) : "memory");
@@ -1027,18 +1209,16 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
     // arrives once per chunk with the byte count of its own rows
     int s = 0, par = 1, pj = 0, cc = 0;  // stage, parity of its empty barrier, chunk number
     for (int li = 0; li < ntl; li++) {
-      const int gt = blockIdx.x + li * gridDim.x;
+      const int gt = rg + li * G;
       locate(gt, pj);
       const int row = (gt - p.tcum[pj]) * kR + lane;
       const bool rvalid = lane < kR && row < p.jobs[pj].out_dim;
-      const uint8_t *rsrc = p.jobs[pj].w + (long long)row * p.row_bytes;
+      const uint8_t *rsrc = p.jobs[pj].w + (long long)row * p.row_bytes + slab_bytes;
       for (int c = 0; c < p.nchunks; c++) {
-        TRACE(100 + li * p.nchunks + c);
         if (!mbar_wait(smem_u32(&bars[S + s]), par)) {  // broken pipeline: stop, let copies land
           drain_copies_in_flight();
           return;
         }
-        TRACE(200 + li * p.nchunks + c);
         const int nb = min(C::KB, p.nblk - c * C::KB);
         const uint8_t *src = rsrc + (long long)c * C::KB * C::BB;
         const uint32_t padb = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15);
@@ -1046,7 +1226,7 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
         const uint32_t full = smem_u32(&bars[s]);
         const bool mine = rvalid && (lane >> 2) == pw;
         const uint32_t my_bytes = __reduce_add_sync(0xffffffffu, mine ? bytes : 0u);
-        if (p.debug & 4) {  // the stage is declared full without any copy
+        if (COGNI_DIAG(p.debug & 4)) {  // the stage is declared full without any copy
           if (lane == 0) mbar_arrive(full);
         } else {
           if (lane == 0) mbar_arrive_expect_tx(full, my_bytes);
@@ -1073,11 +1253,13 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
   float *SX = reinterpret_cast<float *>(smem + p.off_sx);
   float *XX = reinterpret_cast<float *>(smem + p.off_xx);
   const int K = p.x_pitch;  // the quantisers only use it as the pitch of the batch rows
+  const int slab_el = slab * p.nblk * 256;  // the slab's first element of a row of x
+  const float *xs = p.x + slab_el;
+  const float *xs_up = p.x_up ? p.x_up + slab_el : nullptr;
+  const float *norm_ws = p.norm_w ? p.norm_w + slab_el : nullptr;
 
   asm volatile("bar.sync 3, %0;" ::"n"(kThreads) : "memory");  // mbarriers and counters ready
-  TRACE(3);
   pdl_wait_prior_grid();  // x (and y / the addend) may be produced by the preceding kernel
-  TRACE(4);
 
   // RMSNorm prologue: 1 / sqrt(mean(x^2) + eps) per batch row, the sum of squares in f64 as the
   // reference has it (qwen35_cpu.cr:484-490); per-warp partial sums are added in warp order, so
@@ -1148,10 +1330,10 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
       const int fill = (int)__umulhi((uint32_t)cc, s_inv), s = cc - fill * S, par = fill & 1;
       if (TYPE == kQ6_K && pad_li != li) {  // only Q6_K rows can start off a 16-byte boundary
         pad_li = li;
-        const int gt = blockIdx.x + li * gridDim.x;
+        const int gt = rg + li * G;
         locate(gt, cj);
         const int tile = gt - p.tcum[cj];
-        const uint32_t wlow = (uint32_t)reinterpret_cast<uintptr_t>(p.jobs[cj].w);
+        const uint32_t wlow = (uint32_t)reinterpret_cast<uintptr_t>(p.jobs[cj].w) + (uint32_t)slab_bytes;
         const uint32_t rb = (uint32_t)p.row_bytes;  // the low four bits are all that matter
         pad_a = (int)((wlow + (uint32_t)(tile * kR + g) * rb) & 15u);
         pad_b = (int)((wlow + (uint32_t)(tile * kR + g + 8) * rb) & 15u);
@@ -1160,18 +1342,19 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
       // The activations are quantised on the way: the warp that takes a superblock pair of the
       // CTA's first tile does x's two superblocks first; later tiles find them done.
       if (li == 0) {
-        if constexpr (DENSE) quantise_dense<TYPE, NB>(p.x, p.x_up, p.norm_w, s_inv_rms, K, p.batch, e0, lane, xq, SX, XX);
-        else if (PAIR == 2 && n2 == 2) quantise_superblocks<TYPE, NB, 2>(p.x, p.x_up, p.norm_w, s_inv_rms, K, e0, lane, xq, SX, XX);
-        else quantise_superblocks<TYPE, NB, 1>(p.x, p.x_up, p.norm_w, s_inv_rms, K, e0, lane, xq, SX, XX);
+        if constexpr (V2) {
+          if (PAIR == 2 && n2 == 2) quantise_q6v2<NB, 2>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, reinterpret_cast<int *>(XX));
+          else quantise_q6v2<NB, 1>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, reinterpret_cast<int *>(XX));
+        } else if constexpr (DENSE) quantise_dense<TYPE, NB>(xs, xs_up, norm_ws, s_inv_rms, K, p.batch, e0, lane, xq, SX, XX);
+        else if (PAIR == 2 && n2 == 2) quantise_superblocks<TYPE, NB, 2>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, XX);
+        else quantise_superblocks<TYPE, NB, 1>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, XX);
         __syncwarp();
         if (lane == 0) st_release_shared(&xready[e], 1);
       } else {
         spin_until_ge(&xready[e], 1);
       }
-      TRACE(1000 + li * per_tile + e);
       spin_until_ge(issued, cc + 1);
       mbar_wait(bar0 + 8 * s, par);
-      TRACE(2000 + li * per_tile + e);
       const int tb = li & (kFoldBufs - 1);
       const uint8_t *blk = stages + (size_t)s * p.stage_bytes + bi * C::BB;
       if constexpr (DENSE) {
@@ -1186,10 +1369,37 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
 #pragma unroll
         for (int j = 0; j < J; j++)
           red[tb * red_tile + (e * 8 + g) * NB + 4 * j + t] = make_float2(acc0[j], acc1[j]);
+      } else if constexpr (V2) {
+        float acc0[NB], acc1[NB];  // rows g and g+8, this lane's scale groups (k = t) of every unit
+#pragma unroll
+        for (int b = 0; b < NB; b++) acc0[b] = acc1[b] = 0.f;
+#pragma unroll 1
+        for (int q = 0; q < n2; q++) {
+          const uint8_t *ra = blk + q * C::BB + g * C::RS + pad_a;
+          const uint8_t *rb = blk + q * C::BB + (g + 8) * C::RS + pad_b;
+          const uint32_t *xw = reinterpret_cast<const uint32_t *>(xq) + (size_t)(e0 + q) * NB * 128 + lane;
+          const int4 *ng = reinterpret_cast<const int4 *>(XX) + ((size_t)(e0 + q) * NB * 4 + t);
+          const float *sxb = SX + (size_t)(e0 + q) * NB;
+          const uint32_t two = (uint32_t)((reinterpret_cast<uintptr_t>(ra) | reinterpret_cast<uintptr_t>(rb)) & 2);
+          if (__all_sync(0xffffffffu, two == 0)) mma_q6v2<NB, true>(ra, rb, xw, ng, sxb, lane, acc0, acc1);
+          else mma_q6v2<NB, false>(ra, rb, xw, ng, sxb, lane, acc0, acc1);
+        }
+#pragma unroll
+        for (int b = 0; b < NB; b++) {  // the four group lanes of a row pair
+          acc0[b] += __shfl_xor_sync(0xffffffffu, acc0[b], 1);
+          acc1[b] += __shfl_xor_sync(0xffffffffu, acc1[b], 1);
+          acc0[b] += __shfl_xor_sync(0xffffffffu, acc0[b], 2);
+          acc1[b] += __shfl_xor_sync(0xffffffffu, acc1[b], 2);
+        }
+        spin_until_ge(&folded[tb], li / kFoldBufs);  // the buffer's previous tile has been folded
+        if (t == 0) {
+#pragma unroll
+          for (int b = 0; b < NB; b++) red[tb * red_tile + (e * 8 + g) * NB + b] = make_float2(acc0[b], acc1[b]);
+        }
       } else {
       float acc0 = 0.f, acc1 = 0.f;  // rows g and g+8 of (group slot sub, batch row bt)
-      if (p.debug & 8) __nanosleep(1500);  // diagnostics: keep the consumers the bottleneck
-      if ((p.debug & 3) != 1) {
+      if (COGNI_DIAG(p.debug & 8)) __nanosleep(1500);  // diagnostics: keep the consumers the bottleneck
+      if (COGNI_DIAG(p.debug & 3) != 1) {
         const int which = lane >> 4;
         if constexpr (PAIR == 1) {
           decode_scales_half<TYPE, NB>(blk + (lane & 15) * C::RS + pad_d, lane, e0, SX, XX, area);
@@ -1198,7 +1408,7 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
                                   e0 + which, SX, XX, area);
         }
         __syncwarp();
-        if ((p.debug & 3) != 2) {
+        if (COGNI_DIAG(p.debug & 3) != 2) {
           mma_block<TYPE, UNIT_BYTES>(blk, pad_a, pad_b, xlane + (size_t)e0 * 4 * UNIT_BYTES,
                                       area_b, g, t, sub, acc0, acc1);
           if (PAIR == 2 && n2 == 2)
@@ -1222,17 +1432,27 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
         mbar_arrive_n(bar0 + 8 * (S + s), e == npairs - 1 ? n2 + tail_missing : n2);
         add_release_shared(&arrivals[tb], 1);
       }
-      TRACE(3000 + li * per_tile + e);
     } else if (li > 0) {
       // ------------------------------------------------ fold tile li - 1
       const int fl = li - 1;
       const int tb = fl & (kFoldBufs - 1);
-      TRACE(4000 + li * per_tile + e);
       spin_until_ge(&arrivals[tb], (fl / kFoldBufs + 1) * npairs);  // all partials of tile fl stored
-      TRACE(5000 + li * per_tile + e);
       // lane = (batch row, row of the tile): a fixed-order sum over the superblock pairs
       const int r16 = lane & 15;
-      const int gt = blockIdx.x + fl * gridDim.x;
+      const int gt = rg + fl * G;
+      // K slabs: the tile's slabs leave their partial sums in ws; the one that draws the last
+      // ticket adds them up in slab order (so the result does not depend on who was last) and
+      // carries on as if it had summed the whole rows itself.
+      bool last_slab = true;
+      auto slab_ticket = [&]() {
+        __threadfence();
+        __syncwarp();
+        unsigned ticket = 0;
+        if (lane == 0) ticket = atomicAdd(&p.ws_tickets[gt], 1u);
+        ticket = __shfl_sync(0xffffffffu, ticket, 0);
+        last_slab = ticket == (unsigned)nslabs - 1u;
+        if (last_slab) __threadfence();
+      };
       if constexpr (DENSE) {
         float v[NB / 2];  // batch rows 2i + (lane >> 4)
 #pragma unroll
@@ -1246,13 +1466,29 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
         }
         __syncwarp();
         if (lane == 0) st_release_shared(&folded[tb], fl / kFoldBufs + 1);
+        if (nslabs > 1) {
+          float *part = p.ws + (((long long)gt * nslabs + slab) * NB + (lane >> 4)) * 16 + r16;
+#pragma unroll
+          for (int i = 0; i < NB / 2; i++) part[2 * i * 16] = v[i];
+          slab_ticket();
+          if (last_slab) {
+            const float *all = p.ws + ((long long)gt * nslabs * NB + (lane >> 4)) * 16 + r16;
+#pragma unroll
+            for (int i = 0; i < NB / 2; i++) {
+              float a = 0.f;
+              for (int sl = 0; sl < nslabs; sl++) a += __ldcg(all + (sl * NB + 2 * i) * 16);
+              v[i] = a;
+            }
+            if (lane == 0) p.ws_tickets[gt] = 0u;  // ready for the next launch on this workspace
+          }
+        }
         locate(gt, cj);
         const Job &job = p.jobs[cj];
         const int row = (gt - p.tcum[cj]) * kR + r16;
 #pragma unroll
         for (int i = 0; i < NB / 2; i++) {
           const int b = 2 * i + (lane >> 4);
-          if (b < p.batch && row < job.out_dim) {
+          if (last_slab && b < p.batch && row < job.out_dim) {
             if (p.part_keys) {
               const long long key = top1_key(v[i], (uint32_t)(p.index_base + row));
               bestd[i] = key > bestd[i] ? key : bestd[i];
@@ -1271,10 +1507,23 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
       for (int k = 0; k < npairs; k++) v += src[k * 16 * NB];
       __syncwarp();
       if (lane == 0) st_release_shared(&folded[tb], fl / kFoldBufs + 1);
+      if (nslabs > 1) {
+        if (b < NB) p.ws[(((long long)gt * nslabs + slab) * NB + b) * 16 + r16] = v;
+        slab_ticket();
+        if (last_slab) {
+          if (b < NB) {
+            const float *all = p.ws + ((long long)gt * nslabs * NB + b) * 16 + r16;
+            float a = 0.f;
+            for (int sl = 0; sl < nslabs; sl++) a += __ldcg(all + sl * NB * 16);
+            v = a;
+          }
+          if (lane == 0) p.ws_tickets[gt] = 0u;  // ready for the next launch on this workspace
+        }
+      }
       locate(gt, cj);
       const Job &job = p.jobs[cj];
       const int row = (gt - p.tcum[cj]) * kR + r16;
-      if (b < NB && row < job.out_dim) {
+      if (last_slab && b < NB && row < job.out_dim) {
         if (p.part_keys) {
           const long long key = top1_key(v, (uint32_t)(p.index_base + row));
           if (b == 0) best = key > best ? key : best;
@@ -1370,14 +1619,15 @@ bool make_plan_pair(int in_dim, int nb, int pair, Params &p, size_t &smem, bool 
   const int ngroups = in_dim / C::GROUP;
   auto al = [](size_t v) { return (v + 127) & ~(size_t)127; };
   size_t off = 256;  // mbarriers and counters
-  const size_t off_flags = off;  off += 256;  // one flag per superblock of x (in_dim <= 16384)
+  const size_t off_flags = off;  off += kMaxItems * 4;  // one flag per work item of a row of x
   const bool dense = nb > 2;  // nb = 4 or 8 then: single-superblock items, 2 bytes of x per element and batch row
-  const size_t area_floats = dense ? (size_t)16 * dense_area_row(C::NG, nb) : (size_t)pair * nb * Area<TYPE>::BATCH;
+  const bool v2 = TYPE == kQ6_K && !dense;  // Q6_K batch 1-2: no decode areas, 2 bytes of x per element and batch row
+  const size_t area_floats = v2 ? 0 : dense ? (size_t)16 * dense_area_row(C::NG, nb) : (size_t)pair * nb * Area<TYPE>::BATCH;
   const size_t off_red = off;    off = al(off + (size_t)fold_bufs(nb) * ((nblk + pair - 1) / pair) * 8 * nb * 8);  // [tile buffer][item][g][batch] float2
   const size_t off_area = off;   off = al(off + (size_t)consumer_warps(TYPE, pair, nb) * area_floats * 4);
   const size_t off_sx = off;     off = al(off + (size_t)ngroups * nb * 4);
   const size_t off_xx = off;     off = al(off + (size_t)ngroups * nb * 4);
-  const size_t off_xq = off;     off = al(off + (dense ? (size_t)in_dim * 2 * nb : (size_t)(in_dim / 64) * (4 * nb) * 64));
+  const size_t off_xq = off;     off = al(off + (dense || v2 ? (size_t)in_dim * 2 * nb : (size_t)(in_dim / 64) * (4 * nb) * 64));
   const size_t off_stage = off;
   const size_t stage_bytes = al((size_t)kR * C::RS);
   // Three stages, or for the 4- and 8-row instances two that still keep 80 KB in flight (Q5_K
@@ -1489,6 +1739,93 @@ int top1_pass_width(int in_dim, int batch) {
   return width;
 }
 
+// ---------------------------------------------------------------------------- K slabs
+// When a matrix has few row tiles per SM (ffn_down 4096 x 12288: 256 tiles for 148 SMs, the k / v
+// projections: 64), whole-row tiles leave SMs idle or give some of them twice the work of others.
+// The launch then runs as G row groups x S slabs of the K dimension: every CTA takes nblk / S
+// superblocks of its tiles' rows (and quantises only that part of x), the slabs' partial sums
+// meet in a workspace and the CTA that arrives last at a tile adds them in slab order.
+//
+// The workspace is a fixed device array (nothing is ever allocated): kWsSlots regions, one per
+// stream that has used the engine, so that launches which may overlap on the device (different
+// streams) never share a region; launches of one stream are ordered by the stream (a dependent
+// launch touches the workspace only after its predecessor has completed).  A ninth stream, or
+// a shape whose partial sums do not fit a region, runs without slabs.
+constexpr int kWsSlots = 8;
+constexpr int kWsFloats = 1 << 17;  // 512 KB of partial sums per region
+constexpr int kWsTickets = 4096;    // tiles per launch that can be split
+static __device__ __align__(256) float g_slab_ws[kWsSlots][kWsFloats];
+static __device__ unsigned g_slab_tickets[kWsSlots][kWsTickets];
+
+struct SlabRegion {
+  float *ws;
+  unsigned *tickets;
+};
+std::mutex g_slab_mutex;
+float *g_slab_ws_base[64];
+unsigned *g_slab_tickets_base[64];
+cudaStream_t g_slab_streams[64][kWsSlots];
+int g_slab_nstreams[64];
+
+bool slab_region(cudaStream_t s, SlabRegion &out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  std::lock_guard<std::mutex> lock(g_slab_mutex);
+  if (!g_slab_ws_base[dev]) {  // the arrays' device addresses, once per device, that device current
+    void *a = nullptr, *b = nullptr;
+    if (cudaGetSymbolAddress(&a, g_slab_ws) != cudaSuccess || !a) return false;
+    if (cudaGetSymbolAddress(&b, g_slab_tickets) != cudaSuccess || !b) return false;
+    g_slab_ws_base[dev] = static_cast<float *>(a);
+    g_slab_tickets_base[dev] = static_cast<unsigned *>(b);
+  }
+  int slot = -1;
+  for (int i = 0; i < g_slab_nstreams[dev]; i++)
+    if (g_slab_streams[dev][i] == s) slot = i;
+  if (slot < 0) {
+    if (g_slab_nstreams[dev] == kWsSlots) return false;
+    slot = g_slab_nstreams[dev]++;
+    g_slab_streams[dev][slot] = s;
+  }
+  out.ws = g_slab_ws_base[dev] + (size_t)slot * kWsFloats;
+  out.tickets = g_slab_tickets_base[dev] + (size_t)slot * kWsTickets;
+  return true;
+}
+
+int g_imma_force_slabs = 0;  // diagnostics: 0 = automatic, n = n slabs wherever a plan allows it
+
+// Slabs for a launch of `tiles` row tiles: the count that minimises the work of the busiest CTA,
+//   tiles per CTA x (superblocks per slab + the fixed cost of a tile part) + the slab's share of
+//   the activation pass,
+// in units of one 16-row superblock.  0 = no single-launch plan fits (not even whole rows).
+template <int TYPE>
+int choose_slabs(int in_dim, int nbk, int tiles, bool thin, bool workspace_ok) {
+  const int nblk = in_dim / 256, sms = sm_count();
+  int best = 0;
+  float best_cost = 0.f;
+  for (int S = 1; S <= 8; S++) {
+    if (nblk % S != 0 || nblk / S < 4) continue;
+    // Slabs are correct but not yet faster: the fence and the ticket of every tile part sit in a
+    // consumer warp's path (measured on the 9B FFN: 15.1 against 13.2 us for ffn_down with four
+    // slabs), so a launch only uses them when asked to.
+    if (S != 1 && S != g_imma_force_slabs) continue;
+    if (S > 1 && (!workspace_ok || tiles > kWsTickets || (long long)tiles * S * nbk * 16 > kWsFloats ||
+                  sms / S < 1))
+      continue;
+    Params q{};
+    size_t smem = 0;
+    if (!make_plan<TYPE>(nblk / S * 256, nbk, q, smem, thin)) continue;
+    const int G = tiles < sms / S ? tiles : sms / S;
+    const int per_cta = (tiles + G - 1) / G, len = nblk / S;
+    float cost = per_cta * (len + 1.5f) + 0.3f * (nbk > 2 ? nbk / 2 : 1) * len;
+    if (g_imma_force_slabs > 0 && S == g_imma_force_slabs) cost = -1.f;
+    if (best == 0 || cost < best_cost) {
+      best = S;
+      best_cost = cost;
+    }
+  }
+  return best;
+}
+
 // One pass: up to kMaxJobs weight matrices against `batch` rows of x (1, 2, or 3 .. 8), as one
 // launch per column range.
 template <int TYPE>
@@ -1499,14 +1836,26 @@ int run_pass(int nj, const void *const *d_w, const float *d_x, const float *cons
   using C = Cfg<TYPE>;
   const int nbk = kernel_rows<TYPE>(batch);
   const bool thin = top1 != nullptr;
-  const int nsplit = column_splits<TYPE>(in_dim, nbk, thin);
+  const int nblk = in_dim / 256;
+  int tiles = 0;
+  for (int j = 0; j < nj; j++) tiles += (out_dims[j] + kR - 1) / kR;
+  // One launch over K slabs where a plan allows it; else (a row of activations too long for
+  // shared memory and not divisible into equal slabs) one launch per column range.
+  SlabRegion region{nullptr, nullptr};
+  const bool have_ws = slab_region(s, region);
+  const int nslabs = choose_slabs<TYPE>(in_dim, nbk, tiles, thin, have_ws);
+  const int nsplit = nslabs > 0 ? 1 : column_splits<TYPE>(in_dim, nbk, thin);
   if (nsplit == 0 || (top1 && nsplit > 1)) return COGNI_QMM_ERR_LIMIT;
-  const int nblk = in_dim / 256, per = (nblk + nsplit - 1) / nsplit;
+  const int per = (nblk + nsplit - 1) / nsplit;
   for (int b0 = 0; b0 < nblk; b0 += per) {
     const int nb_here = nblk - b0 < per ? nblk - b0 : per;
     Params p{};
     size_t smem = 0;
-    if (!make_plan<TYPE>(nb_here * 256, nbk, p, smem, thin)) return COGNI_QMM_ERR_LIMIT;
+    const int S = nslabs > 0 ? nslabs : 1;
+    if (!make_plan<TYPE>(nb_here / S * 256, nbk, p, smem, thin)) return COGNI_QMM_ERR_LIMIT;
+    p.nslabs = S;
+    p.ws = region.ws;
+    p.ws_tickets = region.tickets;
     p.row_bytes = (long long)nblk * C::BB;  // the pitch of the whole rows
     p.x = d_x + b0 * 256;
     p.x_up = d_x_up ? d_x_up + b0 * 256 : nullptr;
@@ -1532,7 +1881,8 @@ int run_pass(int nj, const void *const *d_w, const float *d_x, const float *cons
     }
     p.addend_stride = b0 == 0 ? addend_stride : -1;  // -1: the stride of y (per job)
     const int sms = sm_count();
-    const int grid = p.tcum[nj] < sms ? p.tcum[nj] : sms;
+    const int groups = p.tcum[nj] < sms / S ? p.tcum[nj] : sms / S;
+    const int grid = groups * S;
     if (top1) {
       p.part_keys = top1->part_keys;
       p.counter = top1->counter;
@@ -1600,12 +1950,13 @@ int gemv_typed(int njobs, const void *const *d_w, const float *d_x, const float 
 void gemv_imma_set_debug(int mode) { g_imma_debug = mode; }
 void gemv_imma_set_pair(int pair) { g_imma_force_pair = pair; }
 void gemv_imma_set_min_splits(int n) { g_imma_min_splits = n < 1 ? 1 : n; }
+void gemv_imma_set_slabs(int n) { g_imma_force_slabs = n < 0 ? 0 : n; }
 
 bool gemv_imma_supports(int type, const void *d_w, const float *d_x, int in_dim, int batch, bool top1) {
   if (type != kQ8_0 && type != kQ4_K && type != kQ5_K && type != kQ6_K && type != kIQ4_NL) return false;
   if (batch < 1 || batch > 64) return false;
   if ((reinterpret_cast<uintptr_t>(d_w) & 15) || (reinterpret_cast<uintptr_t>(d_x) & 15)) return false;
-  if (in_dim % 256 != 0 || in_dim > 16384) return false;
+  if (in_dim % 256 != 0 || in_dim > kMaxItems * 256) return false;
   // the activations (of a column range of the rows, if need be), the warps' areas and at least
   // three stages must fit into shared memory; the fused top-1 needs whole rows in one launch
   auto ok = [&](auto tag) {
@@ -1695,18 +2046,44 @@ int launch_gemv_top1_imma(int type, const void *d_w, const float *d_x, int in_di
   }
 }
 
-#ifdef COGNI_TRACE
-}  // namespace cogni
-extern "C" int cogni_qmm_debug_trace(long long *out, int n) {
-  return (int)cudaMemcpyFromSymbol(out, cogni::g_trace, (size_t)n * 8);
-}
-namespace cogni {
-#endif
 
 unsigned gemv_imma_timeouts() {
   unsigned v = 0;
   cudaMemcpyFromSymbol(&v, g_pipe_wait_timeouts, sizeof(v));
   return v;
+}
+
+// After an expired wait: clears this file's counter and the K-slab tickets (a launch that gave up
+// may have left some drawn).  Synchronises the device.
+int gemv_imma_reset_timeouts() {
+  cudaError_t e = cudaDeviceSynchronize();
+  const unsigned zero = 0;
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_pipe_wait_timeouts, &zero, sizeof(zero));
+  void *tickets = nullptr;
+  if (e == cudaSuccess) e = cudaGetSymbolAddress(&tickets, g_slab_tickets);
+  if (e == cudaSuccess) e = cudaMemset(tickets, 0, sizeof(unsigned) * kWsSlots * kWsTickets);
+  return (int)e;
+}
+
+namespace {
+// One warp waits on an mbarrier that nothing ever arrives at, with the given limit: the wait runs
+// out, is counted, and the kernel returns.  Exercises the give-up path of every bounded wait.
+__global__ void expire_wait_kernel(unsigned long long limit_ns, int *gave_up) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  const bool ok = mbar_wait(smem_u32(&bar), 0, limit_ns);
+  if (threadIdx.x == 0 && gave_up) *gave_up = ok ? 0 : 1;
+}
+}  // namespace
+
+int launch_expire_wait(unsigned limit_us, cudaStream_t s) {
+  if (limit_us == 0 || limit_us > 100000) return COGNI_QMM_ERR_ARG;  // at most 0.1 s
+  expire_wait_kernel<<<1, 32, 0, s>>>((unsigned long long)limit_us * 1000ull, nullptr);
+  return (int)cudaGetLastError();
 }
 
 }  // namespace cogni

@@ -116,21 +116,13 @@ int launch_gemv_top1_rowwarp(int type, const void *d_w, const float *d_x, int in
                              int out_dim, int batch, int32_t index_base, void *d_scratch,
                              int32_t *d_idx, float *d_val, long long *d_key, cudaStream_t s);
 size_t top1_scratch_bytes(int out_dim, int batch);
+int check_top1_args(int type, const void *d_w, const float *d_x, int in_dim, int out_dim, int batch,
+                    int32_t index_base, const void *d_scratch, size_t scratch_bytes,
+                    const int32_t *d_top_index, const float *d_top_value);
 size_t top2_scratch_bytes(int out_dim, int batch);
 int launch_gemv_top2(int type, const void *d_w, const float *d_x, int in_dim, int out_dim, int batch,
                      int32_t index_base, void *d_scratch, int32_t *d_idx, float *d_val,
                      long long *d_key, int resident, cudaStream_t s);
-
-// Tiled tensor-core GEMV (gemv_mma.cu): Q4_K / Q5_K / Q6_K, 16-byte aligned w and x.
-bool gemv_mma_supports(int type, const void *d_w, const float *d_x, int in_dim);
-int launch_gemv_mma(int type, const void *d_w, const float *d_x, const float *d_addend,
-                    int64_t addend_stride, float *d_y, int in_dim, int out_dim, int batch,
-                    cudaStream_t s);
-int launch_gemv_top1_mma(int type, const void *d_w, const float *d_x, int in_dim, int out_dim,
-                         int batch, int32_t index_base, void *d_scratch, int32_t *d_idx,
-                         float *d_val, long long *d_key, cudaStream_t s);
-unsigned gemv_mma_timeouts();
-void gemv_mma_set_debug(int mode);
 
 // Integer tensor-core GEMV (gemv_imma.cu): Q8_0 / Q4_K / Q5_K / Q6_K; the fused top-1 for batch 1-2.
 bool gemv_imma_supports(int type, const void *d_w, const float *d_x, int in_dim, int batch,
@@ -159,9 +151,13 @@ int launch_gemv_imma_many(int type, int njobs, const void *const *d_w, const flo
                           const int *out_dims, int in_dim, int batch, int resident, cudaStream_t s);
 unsigned gemv_imma_timeouts();
 unsigned gemm_prefill_timeouts();
+int gemv_imma_reset_timeouts();   // also clears the K-slab tickets of every workspace region
+int gemm_prefill_reset_timeouts();
+int launch_expire_wait(unsigned limit_us, cudaStream_t s);
 void gemv_imma_set_debug(int mode);
 void gemv_imma_set_pair(int pair);
 void gemv_imma_set_min_splits(int n);
+void gemv_imma_set_slabs(int n);
 void gemm_prefill_set_tile(int bn);
 void gemm_prefill_set_split(int mode);
 void gemm_prefill_set_stage_raw(int on);

@@ -2,7 +2,8 @@
 //
 // Every wait on an mbarrier is bounded by a wall-clock limit: on expiry the waiter records the
 // event in a device counter, treats the wait as satisfied and carries on, so a kernel always runs
-// to completion (its results are then invalid; cogni::pipe_wait_timeouts() reports it).
+// to completion (its results are then invalid; cogni_qmm_wait_timeouts() reports it and
+// cogni_qmm_reset_wait_timeouts() clears the counters once the host has dealt with it).
 #pragma once
 
 #include <cuda_runtime.h>
@@ -67,7 +68,8 @@ __device__ __forceinline__ unsigned long long global_ns() {
 // the process has expired, later waits give up at their first slow-path check, so a broken
 // pipeline costs one time limit in total rather than one per wait.  Returns false when it gave
 // up: a consumer may carry on with invalid data, a producer must stop issuing copies.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
+                                          unsigned long long limit_ns = kPipeWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_ns();
   for (unsigned spin = 1;; spin++) {
@@ -75,7 +77,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     __nanosleep(spin < 4 ? 32 : 256);
     if ((spin & 15u) == 0) {
       if (*reinterpret_cast<volatile unsigned int *>(&g_pipe_wait_timeouts) != 0u) return false;
-      if (global_ns() - t0 > kPipeWaitLimitNs) {
+      if (global_ns() - t0 > limit_ns) {
         atomicAdd(&g_pipe_wait_timeouts, 1u);
         return false;
       }

@@ -9,8 +9,6 @@
 //
 // The array lives in every GPU context that loads the library, from load until exit, whether or
 // not the entry point is ever called.  Its size is the fixed maximum below.
-#include <mutex>
-
 #include "qmm_common.cuh"
 
 namespace {
@@ -19,28 +17,16 @@ namespace {
 constexpr size_t kStaticScratchBytes = 1u << 20;
 static __device__ __align__(256) unsigned char g_top1_static_scratch[kStaticScratchBytes];
 
-constexpr int kMaxDevices = 64;
-std::mutex g_setup_mutex;
-void *g_scratch_ptr[kMaxDevices];  // device address of the array, per device ordinal
-bool g_scratch_ready[kMaxDevices];
-
 // In host code the array's name is only a handle for the runtime, not an address a kernel can
-// use: the device address has to be asked for, once per device, with that device current.
+// use: the device address has to be asked for with the device current.  The lookup is a cheap host
+// call, so it is made on every call rather than cached: a cached address would go stale when the
+// host destroys and re-creates the device's context (cudaDeviceReset).
 int static_scratch_for_current_device(void **out) {
-  int dev = -1;
-  cudaError_t e = cudaGetDevice(&dev);
+  void *ptr = nullptr;
+  const cudaError_t e = cudaGetSymbolAddress(&ptr, g_top1_static_scratch);
   if (e != cudaSuccess) return (int)e;
-  if (dev < 0 || dev >= kMaxDevices) return COGNI_QMM_ERR_LIMIT;
-  std::lock_guard<std::mutex> lock(g_setup_mutex);
-  if (!g_scratch_ready[dev]) {
-    void *ptr = nullptr;
-    e = cudaGetSymbolAddress(&ptr, g_top1_static_scratch);
-    if (e != cudaSuccess) return (int)e;
-    if (!ptr) return COGNI_QMM_ERR_ARG;
-    g_scratch_ptr[dev] = ptr;
-    g_scratch_ready[dev] = true;
-  }
-  *out = g_scratch_ptr[dev];
+  if (!ptr) return COGNI_QMM_ERR_ARG;
+  *out = ptr;
   return COGNI_QMM_OK;
 }
 
@@ -59,6 +45,10 @@ int cogni_qmm_gemv_top1_noalloc(int type, const void *d_w, const float *d_x, int
   if (need > kStaticScratchBytes) return COGNI_QMM_ERR_LIMIT;  // vocabulary x batch too large
   void *scratch = nullptr;
   int st = static_scratch_for_current_device(&scratch);
+  if (st != COGNI_QMM_OK) return st;
+  // every argument check of cogni_qmm_gemv_top1 first: a rejected call must not touch the array
+  st = cogni::check_top1_args(type, d_w, d_x, in_dim, out_dim, batch, index_base, scratch,
+                              kStaticScratchBytes, d_top_index, d_top_value);
   if (st != COGNI_QMM_OK) return st;
   // The array keeps whatever the previous call (or a call that failed half-way) left in it; the
   // ticket counters at its start are the only part the kernel needs at zero.

@@ -34,7 +34,7 @@ extern "C" {
 #define COGNI_QMM_TYPE_Q4_K 12
 #define COGNI_QMM_TYPE_Q5_K 13
 #define COGNI_QMM_TYPE_Q6_K 14
-#define COGNI_QMM_TYPE_IQ4_NL 20 /* dequantize, embedding lookup and the general GEMV; no tiled kernel yet */
+#define COGNI_QMM_TYPE_IQ4_NL 20
 
 #define COGNI_QMM_OK 0
 #define COGNI_QMM_ERR_TYPE 1001      /* tensor type not supported by this engine           */
@@ -43,6 +43,7 @@ extern "C" {
 #define COGNI_QMM_ERR_SCRATCH 1004   /* scratch buffer too small                           */
 #define COGNI_QMM_ERR_DEVICE 1005    /* device is not compute capability 10.x             */
 #define COGNI_QMM_ERR_LIMIT 1006     /* size beyond a documented fixed maximum             */
+#define COGNI_QMM_ERR_TIMEOUT 1007   /* a bounded device-side wait expired (results invalid) */
 
 /* Output element types of the prefill GEMM. */
 #define COGNI_QMM_OUT_F32 0
@@ -54,21 +55,22 @@ int cogni_qmm_abi_version(void);
 /* Human-readable name of a status returned by any entry point. Never NULL. */
 const char *cogni_qmm_status_string(int status);
 
-/* Diagnostics (no counterpart in the reference).
- * cogni_qmm_set_kernel_choice: 0 = automatic (tiled tensor-core GEMV where the shape allows it,
- * the default), 1 = always the general row-per-warp GEMV; process-wide, for A/B checks.
- * Further codes select timing modes and tile shapes of the tiled kernels: 16-21 (16 = normal,
- * others stream / decode only, with or without the weight copies: results invalid), 24-26
- * superblocks per GEMV work item (automatic / 1 / 2), 27-30 at least 1 .. 4 column ranges per
- * row of the tiled GEMV (27 = the default), 32-47 raw diagnostic bits (results
- * invalid), 48-51 prefill token-tile width (automatic / 128 / 256 / 512),
- * 52-54 prefill split along K (automatic / never / wherever it is allowed), 55-56 prefill raw
- * superblocks staged by TMA (default) / read directly by the dequant threads.
- * cogni_qmm_wait_timeouts: how many bounded device-side waits have expired since the library
- * was loaded (0 in a healthy process; a non-zero value means the results of some launch are
- * invalid).  Synchronises the device. */
-int cogni_qmm_set_kernel_choice(int choice);
+/*
+ * Bounded waits.  Every device-side wait of the tiled kernels (on a copy, a stage, a counter) has
+ * a wall-clock limit of one second; a wait that runs out is counted, the kernel carries on to its
+ * end with invalid results, and from then on every wait of every launch gives up at once, so a
+ * broken pipeline can never hang the GPU.  (No counterpart in the reference, whose kernels do not
+ * wait on anything.)
+ *   cogni_qmm_wait_timeouts        how many waits have expired since the library was loaded or the
+ *                                  counters were last reset; 0 in a healthy process.  Synchronises
+ *                                  the device.  cogni_qmm_matmul_add_host checks it itself and
+ *                                  returns COGNI_QMM_ERR_TIMEOUT.
+ *   cogni_qmm_reset_wait_timeouts  clears the counters and the kernels' cross-CTA tickets after the
+ *                                  host has dealt with an expiry; launches are valid again.
+ *                                  Synchronises the device.
+ */
 unsigned cogni_qmm_wait_timeouts(void);
+int cogni_qmm_reset_wait_timeouts(void);
 
 /* Block geometry: TensorType#block_bytes / #block_elements (reader.cr:53-80).
  * Return -1 for a type this engine does not handle. */
@@ -262,8 +264,10 @@ int cogni_qmm_gemv_top1(int type, const void *d_w, const float *d_x, int in_dim,
  *     loads the library holds it until the process exits, used or not.
  *   - Shapes whose scratch need (cogni_qmm_gemv_top1_scratch_bytes) exceeds that size are
  *     rejected with COGNI_QMM_ERR_LIMIT; a 262144-row vocabulary at batch 16 fits.
- *   - The first call on each device looks up the array's device address (with that device
- *     current).  Make that first call outside any stream capture.
+ *   - Every call looks up the array's device address for the device that is current (a host
+ *     lookup, no device work), so the library survives a host that destroys and re-creates its
+ *     context.  Make the first call on a device outside any stream capture.
+ *   - A call that is rejected for its arguments does not touch the array.
  *   - All calls on a device share the one array: calls that can overlap on the GPU (different
  *     streams without an ordering between them) race and give wrong answers.  Keep them on one
  *     stream or order them with events.

@@ -1,4 +1,4 @@
-"""The C-ABI library without a GPU: it loads, exports every symbol include/cogni_qmm.h declares,
+"""The C-ABI library without a GPU: it loads, exports every symbol include/cogni_qmm.h and include/cogni_qmm_diag.h declare,
 answers the geometry queries, names its statuses and rejects bad arguments before touching CUDA."""
 import ctypes as C
 import re
@@ -7,7 +7,7 @@ from pathlib import Path
 import pytest
 
 ROOT = Path(__file__).resolve().parent.parent
-HEADER = (ROOT / "include" / "cogni_qmm.h").read_text()
+HEADER = (ROOT / "include" / "cogni_qmm.h").read_text() + (ROOT / "include" / "cogni_qmm_diag.h").read_text()
 
 
 def declared_symbols():
@@ -75,6 +75,8 @@ def test_argument_errors_come_before_any_cuda_call(engine):
     assert lib.cogni_qmm_gemm_bf16(2, 16, 16, 16, 0, 1, 1, 256, None) == 1001     # Q4_0: not a type of this engine
     assert lib.cogni_qmm_gemm_bf16(12, 16, 16, 16, 0, 1, 1, 100, None) == 1002
     assert lib.cogni_qmm_set_kernel_choice(7) == 1002
+    assert lib.cogni_qmm_set_kernel_choice(17) == 1002   # timing modes are not in the shipped build
+    assert lib.cogni_qmm_diag_expire_wait(0, None) == 1002
     assert lib.cogni_qmm_gemv_top1_scratch_bytes(0, 1) == 0
     assert lib.cogni_qmm_gemv_top1_scratch_bytes(151936, 1) >= 8 + 8 * (151936 // 64)
 

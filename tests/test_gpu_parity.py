@@ -449,3 +449,92 @@ def test_runner_lifecycle_matches_oracle(cuda, oracle):
         assert_close(out["ffn_down"][t], ref, "runner down+residual")
     runner.close()
     runner.close()  # idempotent, as every close in the reference's driver binding
+
+
+@pytest.mark.parametrize("qtype,in_dim,slabs", [
+    (Q4_K, 4096, 2), (Q4_K, 4096, 4), (Q5_K, 2048, 2), (Q6_K, 12288, 4), (Q6_K, 12288, 3),
+    (Q6_K, 5120, 5), (Q8_0, 2048, 2), (IQ4_NL, 2048, 2), (Q6_K, 3072, 3),
+])
+@pytest.mark.parametrize("batch", [1, 2, 4, 8])
+def test_gemv_k_slabs(cuda, oracle, engine, kernel_choice, qtype, in_dim, slabs, batch):
+    """The tiled GEMV with the K dimension of every row tile split over `slabs` CTAs whose partial
+    sums meet in the workspace: same results as whole rows per CTA, bit-identical from launch to
+    launch (the slabs are summed in slab order whoever arrives last), residual added once, ragged
+    last tile, and the fused top-1 on the completed rows."""
+    if kernel_choice == "rowwarp":
+        pytest.skip("slabs exist only in the tiled kernel")
+    out_dim = 16 * 37 + 5
+    engine.lib.cogni_qmm_set_kernel_choice(60 + slabs)
+    try:
+        w, x, y, add = run_gemv(cuda, qtype, out_dim, in_dim, batch, seed=61, addend="residual")
+        dw = DeviceQuantWeight.upload(QuantWeight(w, qtype, out_dim, in_dim), cuda)
+        xd = torch.from_numpy(x).to(cuda)
+        res = torch.from_numpy(add["residual"]).to(cuda)
+        again = [dw.gemv(xd, residual=res).cpu().numpy() for _ in range(3)]
+        idx, val = dw.gemv_top1(xd)
+    finally:
+        engine.lib.cogni_qmm_set_kernel_choice(60)
+    ref = np.stack([oracle.matmul_add(x[b], 1, in_dim, w, qtype, out_dim, add["residual"][b],
+                                      threads=oracle.max_threads()) for b in range(batch)])
+    assert not np.isnan(y).any()
+    assert_close(y, ref, f"slabs {slabs} type {qtype} {out_dim}x{in_dim} batch {batch}")
+    for a in again:
+        assert np.array_equal(a.view(np.uint32), y.view(np.uint32)), "slab sums depend on arrival order"
+    logits = oracle.matmul_add(x, batch, in_dim, w, qtype, out_dim, np.zeros(out_dim, np.float32),
+                               threads=oracle.max_threads()).reshape(batch, out_dim)
+    for b in range(batch):
+        assert int(idx[b]) == oracle.top1(logits[b])[0]
+
+
+@pytest.mark.parametrize("qtype,batch,out_dim", [(IQ4_NL, 1, 2000), (IQ4_NL, 2, 5000), (IQ4_NL, 1, 300),
+                                                 (Q4_K, 3, 4000), (Q6_K, 5, 2500), (Q8_0, 1, 1000)])
+def test_fused_top1_stays_inside_an_exactly_sized_scratch(cuda, engine, oracle, kernel_choice, qtype, batch, out_dim):
+    """The fused top-1 instances run 4 or 8 batch rows per launch whatever the batch; only the
+    caller's `batch` rows have slots in the scratch.  A sentinel-filled guard region right behind a
+    scratch buffer of exactly cogni_qmm_gemv_top1_scratch_bytes() must come back untouched."""
+    in_dim = 1024
+    w = synth.make_weight(qtype, out_dim, in_dim, seed=71, tensor_id=qtype)
+    x = synth.make_activation(batch, in_dim, seed=71)
+    dw = DeviceQuantWeight.upload(QuantWeight(w, qtype, out_dim, in_dim), cuda)
+    need = engine.lib.cogni_qmm_gemv_top1_scratch_bytes(out_dim, batch)
+    guard = 64 * 1024
+    buf = torch.zeros(need + guard, dtype=torch.uint8, device=cuda)
+    buf[need:] = 0xA5
+    xd = torch.from_numpy(x).to(cuda)
+    idx = torch.empty(batch, dtype=torch.int32, device=cuda)
+    val = torch.empty(batch, dtype=torch.float32, device=cuda)
+    for _ in range(2):
+        st = engine.lib.cogni_qmm_gemv_top1(qtype, dw.raw.data_ptr(), xd.data_ptr(), in_dim, out_dim, batch, 0,
+                                            buf.data_ptr(), need, idx.data_ptr(), val.data_ptr(), None, None)
+        assert st == 0
+    torch.cuda.synchronize()
+    assert bool((buf[need:] == 0xA5).all()), "the kernel wrote behind the caller's scratch buffer"
+    logits = oracle.matmul_add(x, batch, in_dim, w, qtype, out_dim, np.zeros(out_dim, np.float32)).reshape(batch, out_dim)
+    for b in range(batch):
+        assert int(idx[b]) == oracle.top1(logits[b])[0]
+
+
+def test_expired_wait_is_counted_reported_and_reset(cuda, engine, oracle):
+    """A bounded device-side wait that runs out: the kernel returns, cogni_qmm_wait_timeouts()
+    reads 1, the host-buffer entry point reports COGNI_QMM_ERR_TIMEOUT instead of handing back a
+    result, and after cogni_qmm_reset_wait_timeouts() launches are valid again.  The wait is made
+    to run out by a one-warp kernel that waits 2 ms on a barrier nothing arrives at."""
+    lib = engine.lib
+    assert lib.cogni_qmm_wait_timeouts() == 0
+    out_dim, in_dim = 256, 1024
+    w = synth.make_weight(Q4_K, out_dim, in_dim, seed=81, tensor_id=Q4_K)
+    x = synth.make_activation(1, in_dim, seed=81)
+    ref = oracle.matmul_add(x, 1, in_dim, w, Q4_K, out_dim, np.zeros(out_dim, np.float32))
+    try:
+        assert lib.cogni_qmm_diag_expire_wait(2000, None) == 0
+        torch.cuda.synchronize()
+        assert lib.cogni_qmm_wait_timeouts() == 1
+        y = np.zeros(out_dim, np.float32)
+        st = lib.cogni_qmm_matmul_add_host(x.ctypes.data, 1, in_dim, w.ctypes.data, w.nbytes, Q4_K, out_dim,
+                                           None, y.ctypes.data)
+        assert st == 1007 and b"wait expired" in lib.cogni_qmm_status_string(st)
+    finally:
+        assert lib.cogni_qmm_reset_wait_timeouts() == 0
+    assert lib.cogni_qmm_wait_timeouts() == 0
+    y = QuantMatmul.matmul_add(x, 1, in_dim, w, Q4_K, out_dim, np.zeros(out_dim, np.float32))
+    assert_close(y.ravel(), ref, "after the reset")

@@ -30,7 +30,7 @@ def _noalloc_top1(dw, x):
     return idx, val, key
 
 
-def test_noalloc_top1_matches_scratch_entry_point_twice(cuda):
+def test_noalloc_top1_matches_scratch_entry_point_twice(cuda, oracle):
     out_dim, in_dim = 9000, 1024
     w = synth.make_weight(synth.Q6_K, out_dim, in_dim, seed=91)
     dw = DeviceQuantWeight.upload(QuantWeight(w, synth.Q6_K, out_dim, in_dim), cuda)
@@ -45,6 +45,14 @@ def test_noalloc_top1_matches_scratch_entry_point_twice(cuda):
         # same kernel, same reduction order: the values agree to the last bit, well inside the
         # 1e-3 * |y|inf tolerance the parity tests allow
         assert torch.equal(val, ref_val), f"call {call}"
+        # and against the CPU oracle: QuantMatmul, then the first maximum (shard offset added)
+        xh = x.cpu().numpy()
+        logits = oracle.matmul_add(xh, batch, in_dim, w, synth.Q6_K, out_dim,
+                                   np.zeros(out_dim, np.float32)).reshape(batch, out_dim)
+        for b in range(batch):
+            oi, ov = oracle.top1(logits[b])
+            assert int(idx[b]) == oi + 123, f"call {call} row {b}"
+            assert abs(float(val[b]) - float(ov)) <= 1e-3 * abs(float(ov))
 
 
 def test_noalloc_top1_rejects_shapes_beyond_the_fixed_array(cuda):
