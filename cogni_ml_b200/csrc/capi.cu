@@ -226,6 +226,39 @@ int cogni_qmm_gemv_many(int type, int n_weights, const void *const *d_w, const f
   return COGNI_QMM_OK;
 }
 
+int cogni_qmm_gemv_many_exchange(int type, int n_weights, const void *const *d_w, const float *d_x,
+                                 const float *const *d_addend, int64_t addend_stride,
+                                 float *const *d_y, const int *out_dims, int in_dim, int batch,
+                                 int resident, const cogni_qmm_exchange *ex, int wait_previous,
+                                 void *stream) {
+  if (!supported(type)) return COGNI_QMM_ERR_TYPE;
+  if (n_weights <= 0 || !d_w || !d_y || !out_dims || !ex) return COGNI_QMM_ERR_ARG;
+  if (ex->world < 1 || ex->world > 8 || ex->rank < 0 || ex->rank >= ex->world || !ex->flags ||
+      !ex->epoch || !ex->ticket)
+    return COGNI_QMM_ERR_ARG;
+  for (int g = 0; g < ex->world; g++)
+    if (!ex->peer_flag[g] || (g != ex->rank && (ex->peer_offset[g] & 3))) return COGNI_QMM_ERR_ARG;
+  for (int j = 0; j < n_weights; j++) {
+    int st = check_gemv_args(type, d_w[j], d_x, d_y[j], in_dim, out_dims[j], batch);
+    if (st) return st;
+    if (d_addend && d_addend[j] && addend_stride != 0 && addend_stride != out_dims[j])
+      return COGNI_QMM_ERR_ARG;
+    if (g_force_rowwarp != 0 || !gemv_imma_supports(type, d_w[j], d_x, in_dim, batch)) return COGNI_QMM_ERR_LIMIT;
+  }
+  return launch_gemv_imma_many_exchange(type, n_weights, d_w, d_x, d_addend, addend_stride, d_y, out_dims,
+                                        in_dim, batch, resident, ex, wait_previous,
+                                        static_cast<cudaStream_t>(stream));
+}
+
+int cogni_qmm_enable_peer_access(int peer_device) {
+  const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    cudaGetLastError();  // not an error for the caller: clear the sticky code
+    return COGNI_QMM_OK;
+  }
+  return (int)e;
+}
+
 int cogni_qmm_gemv_many_rmsnorm(int type, int n_weights, const void *const *d_w, const float *d_x,
                                 const float *d_norm_weight, float eps,
                                 const float *const *d_addend, int64_t addend_stride,

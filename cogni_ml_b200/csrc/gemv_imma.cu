@@ -113,6 +113,7 @@ template <> struct Cfg<kQ6_K> {
 };
 
 constexpr int kMaxJobs = 32;  // weight matrices one launch can take (they share x)
+constexpr int kMaxRanks = 8;   // GPUs of one box
 constexpr int kMaxItems = 128;  // work items (superblocks or pairs) per row tile: in_dim <= 32768
 
 struct Job {
@@ -120,6 +121,15 @@ struct Job {
   const float *addend;
   float *y;
   int out_dim;
+};
+
+struct Exchange {
+  int world, rank;               // world <= 1: no exchange
+  long long peer_delta[kMaxRanks];   // bytes from an address in this GPU's buffer to the same place in GPU g's, as mapped here
+  unsigned *peer_flag[kMaxRanks];    // GPU g's flag word for this rank, as mapped here ([rank]: the local one)
+  const unsigned *flags;         // this GPU's flag words, one per rank, written by the peers
+  unsigned *epoch;               // exchanges this GPU has completed on this buffer set
+  unsigned *ticket;              // CTA arrivals of the running launch, zero between launches
 };
 
 struct Params {
@@ -147,6 +157,11 @@ struct Params {
   int nslabs;            // 1: every CTA takes whole rows
   float *ws;             // [tile][slab][batch row][16] partial sums
   unsigned *ws_tickets;  // [tile] arrival counters, zero between launches
+  // Exchange of the outputs with the other GPUs of the box, fused into the kernel: every y value is
+  // also stored into the same place of each peer's gather buffer (peer-mapped memory, ordinary
+  // stores over NVLink), and the last CTA raises this rank's flag on every GPU.
+  Exchange ex;
+  int ex_wait;           // before touching x: wait until every rank's flag has reached this GPU's epoch
   long long *part_keys;  // fused top-1 (nullptr: plain GEMV)
   unsigned *counter;
   int32_t *top_idx;
@@ -1260,6 +1275,29 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
 
   asm volatile("bar.sync 3, %0;" ::"n"(kThreads) : "memory");  // mbarriers and counters ready
   pdl_wait_prior_grid();  // x (and y / the addend) may be produced by the preceding kernel
+  if (p.ex_wait) {
+    // x comes out of an exchange: every rank's stores into this GPU's buffer are complete once its
+    // flag has reached the number of exchanges this GPU has itself completed (all ranks run the
+    // same sequence).  Bounded like every wait; an expiry is counted and the launch carries on.
+    if (warp == 0 && lane < p.ex.world) {
+      const unsigned want = *reinterpret_cast<volatile const unsigned *>(p.ex.epoch);
+      const unsigned long long t0 = global_ns();
+      for (unsigned spin = 0;; spin++) {
+        unsigned have;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(have) : "l"(p.ex.flags + lane) : "memory");
+        if ((int)(have - want) >= 0) break;
+        __nanosleep(64);
+        if ((spin & 63u) == 63u) {
+          if (pipe_broken()) break;
+          if (global_ns() - t0 > kPipeWaitLimitNs) {
+            atomicAdd(&g_pipe_wait_timeouts, 1u);
+            break;
+          }
+        }
+      }
+    }
+    consumer_sync<kNW>();
+  }
 
   // RMSNorm prologue: 1 / sqrt(mean(x^2) + eps) per batch row, the sum of squares in f64 as the
   // reference has it (qwen35_cpu.cr:484-490); per-warp partial sums are added in warp order, so
@@ -1495,7 +1533,11 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
             } else {
               const long long as = p.addend_stride < 0 ? job.out_dim : p.addend_stride;
               const float a = job.addend ? job.addend[(long long)b * as + row] : 0.f;
-              job.y[(long long)b * job.out_dim + row] = a + v[i];
+              float *dst = job.y + (long long)b * job.out_dim + row;
+              *dst = a + v[i];
+              for (int gpu = 0; gpu < p.ex.world; gpu++)
+                if (gpu != p.ex.rank)
+                  *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + p.ex.peer_delta[gpu]) = a + v[i];
             }
           }
         }
@@ -1531,7 +1573,11 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
         } else {
           const long long as = p.addend_stride < 0 ? job.out_dim : p.addend_stride;
           const float a = job.addend ? job.addend[(long long)b * as + row] : 0.f;
-          job.y[(long long)b * job.out_dim + row] = a + v;
+          float *dst = job.y + (long long)b * job.out_dim + row;
+          *dst = a + v;
+          for (int gpu = 0; gpu < p.ex.world; gpu++)
+            if (gpu != p.ex.rank)
+              *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + p.ex.peer_delta[gpu]) = a + v;
         }
       }
       }
@@ -1545,6 +1591,23 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
     }
   }
 
+  if (p.ex.world > 1) {
+    // every thread that stored into peer memory makes its stores visible system-wide, then the
+    // CTA draws a ticket; the last CTA of the launch raises this rank's flag on every GPU.
+    __threadfence_system();
+    consumer_sync<kNW>();
+    if (ctid == 0) {
+      const unsigned ticket = atomicAdd(p.ex.ticket, 1u);
+      if (ticket == gridDim.x - 1u) {
+        __threadfence_system();
+        const unsigned e = *reinterpret_cast<volatile unsigned *>(p.ex.epoch) + 1u;
+        for (int gpu = 0; gpu < p.ex.world; gpu++)
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.ex.peer_flag[gpu]), "r"(e) : "memory");
+        *reinterpret_cast<volatile unsigned *>(p.ex.epoch) = e;
+        *p.ex.ticket = 0u;
+      }
+    }
+  }
   if (p.part_keys == nullptr) return;
 
   // ------------------------------------------------------------ fused top-1 epilogue
@@ -1832,7 +1895,7 @@ template <int TYPE>
 int run_pass(int nj, const void *const *d_w, const float *d_x, const float *const *d_addend,
              int64_t addend_stride, float *const *d_y, const int *out_dims, int in_dim, int batch,
              int resident, const Params *top1, cudaStream_t s, const float *d_x_up,
-             const float *d_norm_w, float norm_eps) {
+             const float *d_norm_w, float norm_eps, const Exchange *ex = nullptr, int ex_wait = 0) {
   using C = Cfg<TYPE>;
   const int nbk = kernel_rows<TYPE>(batch);
   const bool thin = top1 != nullptr;
@@ -1846,6 +1909,7 @@ int run_pass(int nj, const void *const *d_w, const float *d_x, const float *cons
   const int nslabs = choose_slabs<TYPE>(in_dim, nbk, tiles, thin, have_ws);
   const int nsplit = nslabs > 0 ? 1 : column_splits<TYPE>(in_dim, nbk, thin);
   if (nsplit == 0 || (top1 && nsplit > 1)) return COGNI_QMM_ERR_LIMIT;
+  if (ex && nsplit > 1) return COGNI_QMM_ERR_LIMIT;  // the fused exchange needs the rows complete in one launch
   const int per = (nblk + nsplit - 1) / nsplit;
   for (int b0 = 0; b0 < nblk; b0 += per) {
     const int nb_here = nblk - b0 < per ? nblk - b0 : per;
@@ -1856,6 +1920,8 @@ int run_pass(int nj, const void *const *d_w, const float *d_x, const float *cons
     p.nslabs = S;
     p.ws = region.ws;
     p.ws_tickets = region.tickets;
+    if (ex) p.ex = *ex;
+    p.ex_wait = ex_wait;
     p.row_bytes = (long long)nblk * C::BB;  // the pitch of the whole rows
     p.x = d_x + b0 * 256;
     p.x_up = d_x_up ? d_x_up + b0 * 256 : nullptr;
@@ -1912,10 +1978,14 @@ template <int TYPE>
 int gemv_typed(int njobs, const void *const *d_w, const float *d_x, const float *const *d_addend,
                int64_t addend_stride, float *const *d_y, const int *out_dims, int in_dim, int batch,
                int resident, const Params *top1, cudaStream_t s, const float *d_x_up = nullptr,
-               const float *d_norm_w = nullptr, float norm_eps = 0.f) {
+               const float *d_norm_w = nullptr, float norm_eps = 0.f, const Exchange *ex = nullptr,
+               int ex_wait = 0) {
+
   const int width = top1 ? top1_pass_width<TYPE>(in_dim, batch)
                          : (batch <= 2 ? batch : batch_pass_width<TYPE>(in_dim, batch));
   if (width == 0) return COGNI_QMM_ERR_LIMIT;
+  // the fused exchange raises its flags once: the call has to be one launch
+  if (ex && (njobs > kMaxJobs || batch > width)) return COGNI_QMM_ERR_LIMIT;
   for (int b0 = 0; b0 < batch; b0 += width) {
     const int nbat = batch - b0 < width ? batch - b0 : width;
     Params t1{};  // this pass's rows of the top-1 outputs and scratch slots
@@ -1938,7 +2008,7 @@ int gemv_typed(int njobs, const void *const *d_w, const float *d_x, const float 
       const int st = run_pass<TYPE>(nj, d_w + j0, d_x + (long long)b0 * in_dim, d_addend ? add : nullptr,
                                     addend_stride, d_y ? ys : nullptr, out_dims + j0, in_dim, nbat, resident,
                                     top1 ? &t1 : nullptr, s, d_x_up ? d_x_up + (long long)b0 * in_dim : nullptr, d_norm_w,
-                                    norm_eps);
+                                    norm_eps, ex, ex_wait);
       if (st) return st;
     }
   }
@@ -1983,6 +2053,33 @@ int launch_gemv_imma_many(int type, int njobs, const void *const *d_w, const flo
     case kQ8_0: return gemv_typed<kQ8_0>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s);
     case kIQ4_NL: return gemv_typed<kIQ4_NL>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s);
     case kQ6_K: return gemv_typed<kQ6_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s);
+    default: return COGNI_QMM_ERR_TYPE;
+  }
+}
+
+// The same with the outputs exchanged between the GPUs of the box inside the launch (ex) and,
+// optionally, the wait for the preceding exchange before x is read.
+int launch_gemv_imma_many_exchange(int type, int njobs, const void *const *d_w, const float *d_x,
+                                   const float *const *d_addend, int64_t addend_stride,
+                                   float *const *d_y, const int *out_dims, int in_dim, int batch,
+                                   int resident, const cogni_qmm_exchange *cex, int wait_previous,
+                                   cudaStream_t s) {
+  Exchange ex{};
+  ex.world = cex->world;
+  ex.rank = cex->rank;
+  for (int g = 0; g < cex->world && g < kMaxRanks; g++) {
+    ex.peer_delta[g] = cex->peer_offset[g];
+    ex.peer_flag[g] = cex->peer_flag[g];
+  }
+  ex.flags = cex->flags;
+  ex.epoch = cex->epoch;
+  ex.ticket = cex->ticket;
+  switch (type) {
+    case kQ4_K: return gemv_typed<kQ4_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, nullptr, 0.f, &ex, wait_previous);
+    case kQ5_K: return gemv_typed<kQ5_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, nullptr, 0.f, &ex, wait_previous);
+    case kQ8_0: return gemv_typed<kQ8_0>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, nullptr, 0.f, &ex, wait_previous);
+    case kIQ4_NL: return gemv_typed<kIQ4_NL>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, nullptr, 0.f, &ex, wait_previous);
+    case kQ6_K: return gemv_typed<kQ6_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, nullptr, 0.f, &ex, wait_previous);
     default: return COGNI_QMM_ERR_TYPE;
   }
 }
@@ -2075,8 +2172,10 @@ __global__ void expire_wait_kernel(unsigned long long limit_ns, int *gave_up) {
     mbar_fence_init();
   }
   __syncwarp();
-  const bool ok = mbar_wait(smem_u32(&bar), 0, limit_ns);
-  if (threadIdx.x == 0 && gave_up) *gave_up = ok ? 0 : 1;
+  if (threadIdx.x == 0) {  // one waiter, one count
+    const bool ok = mbar_wait(smem_u32(&bar), 0, limit_ns);
+    if (gave_up) *gave_up = ok ? 0 : 1;
+  }
 }
 }  // namespace
 

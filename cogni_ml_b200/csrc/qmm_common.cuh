@@ -149,6 +149,11 @@ int launch_gemv_top1_imma(int type, const void *d_w, const float *d_x, int in_di
 int launch_gemv_imma_many(int type, int njobs, const void *const *d_w, const float *d_x,
                           const float *const *d_addend, int64_t addend_stride, float *const *d_y,
                           const int *out_dims, int in_dim, int batch, int resident, cudaStream_t s);
+int launch_gemv_imma_many_exchange(int type, int njobs, const void *const *d_w, const float *d_x,
+                                   const float *const *d_addend, int64_t addend_stride,
+                                   float *const *d_y, const int *out_dims, int in_dim, int batch,
+                                   int resident, const cogni_qmm_exchange *ex, int wait_previous,
+                                   cudaStream_t s);
 unsigned gemv_imma_timeouts();
 unsigned gemm_prefill_timeouts();
 int gemv_imma_reset_timeouts();   // also clears the K-slab tickets of every workspace region

@@ -137,3 +137,125 @@ class ShardedLmHead:
             return unpack_top1_keys(key)
         idx, val = unpack_top1_key(key.numpy())
         return torch.from_numpy(idx.copy()), torch.from_numpy(val.copy())
+
+
+# ----------------------------------------------------------------------------------------------
+# The exchange fused into the GEMV launch (cogni_qmm_gemv_many_exchange): peer-mapped buffers.
+
+class PeerExchange:
+    """One arena per rank, laid out identically on every rank and mapped into every process of the
+    box (torch symmetric memory: the same physical allocation of rank g appears at buffer_ptrs[g] in
+    every process, accessible from the local GPU): 256 bytes of state (the flag word of every rank,
+    this rank's epoch and ticket) followed by the gather buffers.  `buffer(name, shape)` hands out
+    the same region on every rank, so an address offset inside the local arena is the offset
+    inside every peer's."""
+
+    STATE_BYTES = 256
+
+    def __init__(self, nbytes: int, device, group: Optional[dist.ProcessGroup] = None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if self.world > 8:
+            raise ValueError("at most 8 ranks (the GPUs of one box)")
+        self.device = torch.device(device)
+        total = self.STATE_BYTES + ((nbytes + 255) // 256) * 256
+        self._cursor = self.STATE_BYTES
+        self._named = {}
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.arena = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
+            self.arena.zero_()
+            torch.cuda.synchronize(self.device)
+            self._handle = symm_mem.rendezvous(self.arena, group if group is not None else dist.group.WORLD)
+            ptrs = [int(v) for v in self._handle.buffer_ptrs]
+            if ptrs[self.rank] != self.arena.data_ptr():
+                raise RuntimeError("symmetric memory: the local buffer is not where the handle says")
+            # every peer's arena through a torch view first: the same access path the kernels use
+            for g in range(self.world):
+                view = self._handle.get_buffer(g, (self.STATE_BYTES,), torch.uint8, 0)
+                if int(view[128:192].sum().item()) != 0:
+                    raise RuntimeError("symmetric memory: a peer's arena is not readable from here")
+            self._handle.barrier()
+        else:
+            self.arena = torch.zeros(total, dtype=torch.uint8, device=self.device)
+            torch.cuda.synchronize(self.device)
+            ptrs = [self.arena.data_ptr()]
+        ex = _ExchangeStruct()
+        ex.world, ex.rank = self.world, self.rank
+        base = ptrs[self.rank]
+        for g in range(self.world):
+            ex.peer_offset[g] = ptrs[g] - base
+            ex.peer_flag[g] = ptrs[g] + 4 * self.rank      # rank g's flags[self.rank]
+        ex.flags = base
+        ex.epoch = base + 64
+        ex.ticket = base + 68
+        self.struct = ex
+
+    def buffer(self, name: str, shape, dtype=torch.float32) -> torch.Tensor:
+        """The region `name` of the local arena (allocated on first use; every rank must ask for the
+        same names, shapes and order)."""
+        if name not in self._named:
+            n = int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()
+            n = (n + 255) // 256 * 256
+            if self._cursor + n > self.arena.numel():
+                raise ValueError("exchange arena too small")
+            self._named[name] = (self._cursor, tuple(shape), dtype)
+            self._cursor += n
+        off, shp, dt = self._named[name]
+        count = int(np.prod(shp))
+        return self.arena[off:off + count * torch.empty((), dtype=dt).element_size()].view(dt).view(*shp)
+
+    def epoch(self) -> int:
+        return int(self.arena[64:68].view(torch.int32).item())
+
+
+def _make_exchange_struct():
+    import ctypes as C
+
+    class Exchange(C.Structure):   # struct cogni_qmm_exchange (include/cogni_qmm.h)
+        _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("peer_offset", C.c_int64 * 8),
+                    ("peer_flag", C.c_void_p * 8), ("flags", C.c_void_p), ("epoch", C.c_void_p),
+                    ("ticket", C.c_void_p)]
+    return Exchange
+
+
+_ExchangeStruct = _make_exchange_struct()
+
+
+class ExchangingGemv:
+    """A prepared row-sharded qmatvec_many whose outputs reach every GPU inside the launch.
+
+    weights: this rank's row shards (DeviceQuantWeight) of matrices that share x; outs: for each,
+    a [world, batch, rows] region of the exchange arena (PeerExchange.buffer): the launch writes
+    slot `rank` locally and on every peer.  wait_previous: do not read x before the exchange that
+    precedes this launch on the arena has arrived from every rank."""
+
+    def __init__(self, exchange: PeerExchange, weights, x: torch.Tensor, outs, wait_previous: bool):
+        import ctypes as C
+        self.ex, self.weights, self.x, self.outs = exchange, list(weights), x, list(outs)
+        w0 = self.weights[0]
+        if len({(w.type, w.in_dim) for w in self.weights}) != 1:
+            raise ValueError("weights must share type and in_dim")
+        self.batch = x.numel() // w0.in_dim
+        n = len(self.weights)
+        for w, o in zip(self.weights, self.outs):
+            if tuple(o.shape) != (exchange.world, self.batch, w.out_dim) or not o.is_contiguous():
+                raise ValueError("each output must be a contiguous [world, batch, rows] arena region")
+        self._w = (C.c_void_p * n)(*[w.raw.data_ptr() for w in self.weights])
+        self._y = (C.c_void_p * n)(*[o[exchange.rank].data_ptr() for o in self.outs])
+        self._n = (C.c_int * n)(*[w.out_dim for w in self.weights])
+        self._resident = int(all(w.resident for w in self.weights))
+        self._wait = int(bool(wait_previous))
+
+    def run(self, stream=None):
+        import ctypes as C
+
+        from ._lib import check, lib
+        from .quant_matmul import _stream_ptr
+        w0 = self.weights[0]
+        check(lib.cogni_qmm_gemv_many_exchange(w0.type, len(self.weights), self._w, self.x.data_ptr(),
+                                               None, 0, self._y, self._n, w0.in_dim, self.batch,
+                                               self._resident, C.byref(self.ex.struct), self._wait,
+                                               _stream_ptr(stream)), "cogni_qmm_gemv_many_exchange")
+        return self.outs

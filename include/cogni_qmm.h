@@ -228,6 +228,52 @@ int cogni_qmm_gemv_many(int type, int n_weights, const void *const *d_w, const f
                         const int *out_dims, int in_dim, int batch, int resident, void *stream);
 
 /*
+ * Row-sharded decode over the GPUs of one box with the exchange fused into the GEMV launch.
+ * (No counterpart in the reference, which is single-GPU; the partition is the one its layout
+ * suggests: output rows are independent and stored back to back, src/ml/gguf/qwen35_weights.cr:209-212.)
+ *
+ * Every rank holds the rows [rank * N / G, (rank + 1) * N / G) of each matrix and a gather buffer
+ * laid out identically on all ranks; d_y[j] points INTO this rank's buffer, at the place of this
+ * rank's shard.  The kernel stores every output value there and, with ordinary stores over NVLink,
+ * at the same place of every peer's buffer (peer-mapped: cuIpcOpenMemHandle / cuMemMap by the
+ * host); when the last CTA has finished it raises this rank's flag on every GPU.  A later launch
+ * that reads the gathered buffer passes wait_previous = 1 and does not touch its activations
+ * before every rank's flag has arrived.  No NCCL call, no extra launch, no multicast load.
+ *
+ *   world, rank     ranks of the box (world <= 8) and this one
+ *   peer_offset[g]  BYTES from an address in this rank's gather buffer to the same place in rank
+ *                   g's buffer as mapped into this process (entry [rank] is ignored)
+ *   peer_flag[g]    rank g's flag word FOR this rank (&flags_of_g[rank], as mapped here); entry
+ *                   [rank] is this rank's own &flags[rank]
+ *   flags           this rank's `world` flag words (device memory the peers write)
+ *   epoch, ticket   two device words of this rank, zero-initialised together with the flags
+ * All ranks must issue the same sequence of exchanging launches on one buffer set; a buffer may
+ * be reused by the launch after next (two buffers alternating are enough for a chain in which
+ * every launch waits for the exchange before it).  The wait is bounded like every device-side
+ * wait of this library (cogni_qmm_wait_timeouts).  Shapes the tiled kernel does not take in one
+ * launch (batch > 8, in_dim not a multiple of 256, ...) return COGNI_QMM_ERR_LIMIT: run
+ * cogni_qmm_gemv_many and an all-gather instead.
+ */
+typedef struct cogni_qmm_exchange {
+  int32_t world, rank;
+  int64_t peer_offset[8];
+  uint32_t *peer_flag[8];
+  const uint32_t *flags;
+  uint32_t *epoch;
+  uint32_t *ticket;
+} cogni_qmm_exchange;
+
+int cogni_qmm_gemv_many_exchange(int type, int n_weights, const void *const *d_w, const float *d_x,
+                                 const float *const *d_addend, int64_t addend_stride,
+                                 float *const *d_y, const int *out_dims, int in_dim, int batch,
+                                 int resident, const cogni_qmm_exchange *exchange, int wait_previous,
+                                 void *stream);
+
+/* Lets kernels of the current device store into memory of `peer_device` (cudaDeviceEnablePeerAccess;
+ * already-enabled is not an error).  The host needs it once per peer before the first exchange. */
+int cogni_qmm_enable_peer_access(int peer_device);
+
+/*
  * Fused lm_head: GEMV over `out_dim` vocabulary rows plus top-1 per batch row, without
  * writing the logits.  Replaces q6_k_gemv_top1_partial_f32 + output_top1_values_reduce_probe
  * (q6k_gemv_probe.ptx:1331; src/ml/cuda/qwen_output_head_runner.cr:530-624, 884-947).

@@ -50,6 +50,80 @@ def _worker(rank, world, port):
         dist.destroy_process_group()
 
 
+def _exchange_worker(rank, world, port):
+    """The exchange fused into the GEMV launch: launch A leaves y1 = W1 x on every GPU (peer
+    stores + flags), launch B waits for that exchange and computes W2 y1 from the gathered buffer,
+    again exchanging; repeated so that flags, epochs and the two buffers are reused many times."""
+    import torch.distributed as dist
+
+    from cogni_ml_b200 import DeviceQuantWeight, QuantWeight, lib, synth
+    from cogni_ml_b200.sharded import ExchangingGemv, PeerExchange, shard_rows
+    from oracle import loader
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        n1, k1, n2 = 2048, 1024, 1024
+        raw1 = synth.make_weight(synth.Q4_K, n1, k1, seed=27, tensor_id=1)
+        raw2 = synth.make_weight(synth.Q6_K, n2, n1, seed=27, tensor_id=2)
+        x = synth.make_activation(1, k1, seed=27)
+        zero = lambda n: np.zeros(n, np.float32)
+        y1_ref = loader.matmul_add(x, 1, k1, raw1, synth.Q4_K, n1, zero(n1))
+        y2_ref = loader.matmul_add(y1_ref, 1, n1, raw2, synth.Q6_K, n2, zero(n2))
+        ex = PeerExchange(1 << 20, dev)
+        r0, r1 = shard_rows(n1, rank, world)
+        w1 = DeviceQuantWeight.upload(QuantWeight(raw1, synth.Q4_K, n1, k1), dev, r0, r1)
+        r0, r1 = shard_rows(n2, rank, world)
+        w2 = DeviceQuantWeight.upload(QuantWeight(raw2, synth.Q6_K, n2, n1), dev, r0, r1)
+        buf1 = ex.buffer("y1", (world, 1, n1 // world))
+        buf2 = ex.buffer("y2", (world, 1, n2 // world))
+        xd = torch.from_numpy(x).to(dev)
+        first = ExchangingGemv(ex, [w1], xd, [buf1], wait_previous=False)
+        a = ExchangingGemv(ex, [w1], xd, [buf1], wait_previous=True)
+        b = ExchangingGemv(ex, [w2], buf1.view(1, n1), [buf2], wait_previous=True)
+        tail = torch.zeros(1, device=dev)
+        for it in range(40):
+            (first if it == 0 else a).run()
+            b.run()
+        # a last launch that only waits for b's exchange, so that buf2 is complete when it is read
+        probe = ExchangingGemv(ex, [w1], xd, [ex.buffer("y3", (world, 1, n1 // world))], wait_previous=True)
+        probe.run()
+        torch.cuda.synchronize()
+        assert ex.epoch() == 81
+        y1 = buf1.cpu().numpy().reshape(-1)
+        y2 = buf2.cpu().numpy().reshape(-1)
+        assert np.abs(y1 - y1_ref).max() <= 1e-3 * np.abs(y1_ref).max()
+        assert np.abs(y2 - y2_ref).max() <= 2e-3 * np.abs(y2_ref).max()   # two chained GEMVs
+        assert lib.cogni_qmm_wait_timeouts() == 0
+        # batch 4, two matrices in one launch (ffn_gate + ffn_up shape of use)
+        xb = synth.make_activation(4, k1, seed=28)
+        rawu = synth.make_weight(synth.Q4_K, n1, k1, seed=28, tensor_id=3)
+        r0, r1 = shard_rows(n1, rank, world)
+        wu = DeviceQuantWeight.upload(QuantWeight(rawu, synth.Q4_K, n1, k1), dev, r0, r1)
+        g_buf = ex.buffer("g4", (world, 4, n1 // world))
+        u_buf = ex.buffer("u4", (world, 4, n1 // world))
+        ExchangingGemv(ex, [w1, wu], torch.from_numpy(xb).to(dev), [g_buf, u_buf], wait_previous=True).run()
+        probe.run()
+        torch.cuda.synchronize()
+        for raw, buf in ((raw1, g_buf), (rawu, u_buf)):
+            ref = loader.matmul_add(xb, 4, k1, raw, synth.Q4_K, n1, zero(n1)).reshape(4, n1)
+            got = buf.permute(1, 0, 2).reshape(4, n1).cpu().numpy()
+            assert np.abs(got - ref).max() <= 1e-3 * np.abs(ref).max()
+        assert lib.cogni_qmm_wait_timeouts() == 0
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_exchange_fused_into_the_gemv(cuda):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_exchange_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
 def test_two_rank_row_sharded_gemv_and_vocab_sharded_top1(cuda):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
