@@ -50,7 +50,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     cmd = [_nvcc(), *NVCC_FLAGS]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", str(LIB_PATH), *map(str, sources())]
+    cmd += ["-o", str(LIB_PATH), *map(str, sources()), "-ldl"]
     env = dict(os.environ)
     # the image exports CC/CXX pointing at a compiler wrapper nvcc cannot drive; use PATH's g++
     env.pop("CC", None)

@@ -56,10 +56,12 @@ const char *cogni_qmm_status_string(int status) {
     case COGNI_QMM_ERR_SCRATCH: return "scratch buffer too small";
     case COGNI_QMM_ERR_DEVICE: return "device is not compute capability 10.x";
     case COGNI_QMM_ERR_LIMIT: return "size beyond the entry point's fixed maximum";
+    case COGNI_QMM_ERR_NCCL_MISSING: return "libnccl.so.2 could not be loaded";
     case COGNI_QMM_ERR_TIMEOUT: return "a bounded device-side wait expired: results invalid until cogni_qmm_reset_wait_timeouts()";
     default: break;
   }
   if (status > 0 && status < 1000) return cudaGetErrorString(static_cast<cudaError_t>(status));
+  if (status > COGNI_QMM_ERR_NCCL_BASE && status < COGNI_QMM_ERR_NCCL_BASE + 100) return "an NCCL call failed (status - 2000 is its ncclResult_t)";
   return "unknown status";
 }
 

@@ -150,6 +150,7 @@ struct Params {
   long long row_bytes;
   int off_flags, off_red, off_area, off_sx, off_xx, off_xq, off_stage, stage_bytes;
   int pair;      // superblocks per work item (1 or 2)
+  int nflags;    // words of the per-item flags of x
   int resident;  // weights were complete before the preceding kernel started
   int debug;     // diagnostics: bits 0-1: 1 = no work on the stages, 2 = decode only; bit 2: no copies; bit 3: items sleep
   // K slabs: nslabs CTAs share a row tile, each takes nblk superblocks of the row (slab s: the
@@ -1166,7 +1167,9 @@ __device__ __forceinline__ void mma_q6v2(const uint8_t *ra, const uint8_t *rb, c
 }
 
 // ---------------------------------------------------------------------------- the kernel
-template <int TYPE, int NB, int PAIR>
+// XT: the instance that can split row tiles over K slabs and exchange its outputs with the other
+// GPUs; the plain instance carries none of that code.
+template <int TYPE, int NB, int PAIR, bool XT>
 __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1)
     gemv_imma_kernel(const Params p) {
   constexpr int kNW = consumer_warps(TYPE, PAIR, NB), kThreads = (kNW + kPW) * 32;
@@ -1193,7 +1196,7 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
   uint8_t *stages = smem + p.off_stage;
   // The jobs' 16-row tiles form one global sequence (job-major).  The grid is G row groups x
   // nslabs K slabs: this CTA takes slab `slab` of the tiles rg + i * G, i < ntl.
-  const int nslabs = p.nslabs;
+  const int nslabs = XT ? p.nslabs : 1;
   const int slab = nslabs > 1 ? (int)blockIdx.x % nslabs : 0;
   const int rg = nslabs > 1 ? (int)blockIdx.x / nslabs : (int)blockIdx.x;
   const int G = nslabs > 1 ? (int)gridDim.x / nslabs : (int)gridDim.x;
@@ -1213,8 +1216,7 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
       if (lane < S) mbar_init(smem_u32(&bars[lane]), kPW);
       else if (lane < 2 * S) mbar_init(smem_u32(&bars[lane]), C::KB);
       else if (lane < 2 * S + 1 + 2 * kFoldBufs) issued[lane - 2 * S] = 0;
-#pragma unroll
-      for (int i = 0; i < kMaxItems / 32; i++) xready[lane + 32 * i] = 0;
+      for (int i = lane; i < p.nflags; i += 32) xready[i] = 0;
       mbar_fence_init();
     }
     asm volatile("bar.sync 2, %0;" ::"n"(kPW * 32) : "memory");
@@ -1275,7 +1277,7 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
 
   asm volatile("bar.sync 3, %0;" ::"n"(kThreads) : "memory");  // mbarriers and counters ready
   pdl_wait_prior_grid();  // x (and y / the addend) may be produced by the preceding kernel
-  if (p.ex_wait) {
+  if (XT && p.ex_wait) {
     // x comes out of an exchange: every rank's stores into this GPU's buffer are complete once its
     // flag has reached the number of exchanges this GPU has itself completed (all ranks run the
     // same sequence).  Bounded like every wait; an expiry is counted and the launch carries on.
@@ -1483,10 +1485,14 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
       // carries on as if it had summed the whole rows itself.
       bool last_slab = true;
       auto slab_ticket = [&]() {
-        __threadfence();
+        // one fence for the warp: the lanes' stores are ordered before lane 0's fence by the warp
+        // barrier, and the fence is cumulative
         __syncwarp();
         unsigned ticket = 0;
-        if (lane == 0) ticket = atomicAdd(&p.ws_tickets[gt], 1u);
+        if (lane == 0) {
+          __threadfence();
+          ticket = atomicAdd(&p.ws_tickets[gt], 1u);
+        }
         ticket = __shfl_sync(0xffffffffu, ticket, 0);
         last_slab = ticket == (unsigned)nslabs - 1u;
         if (last_slab) __threadfence();
@@ -1504,7 +1510,7 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
         }
         __syncwarp();
         if (lane == 0) st_release_shared(&folded[tb], fl / kFoldBufs + 1);
-        if (nslabs > 1) {
+        if (XT && nslabs > 1) {
           float *part = p.ws + (((long long)gt * nslabs + slab) * NB + (lane >> 4)) * 16 + r16;
 #pragma unroll
           for (int i = 0; i < NB / 2; i++) part[2 * i * 16] = v[i];
@@ -1535,9 +1541,10 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
               const float a = job.addend ? job.addend[(long long)b * as + row] : 0.f;
               float *dst = job.y + (long long)b * job.out_dim + row;
               *dst = a + v[i];
-              for (int gpu = 0; gpu < p.ex.world; gpu++)
-                if (gpu != p.ex.rank)
-                  *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + p.ex.peer_delta[gpu]) = a + v[i];
+              if constexpr (XT)
+                for (int gpu = 0; gpu < p.ex.world; gpu++)
+                  if (gpu != p.ex.rank)
+                    *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + p.ex.peer_delta[gpu]) = a + v[i];
             }
           }
         }
@@ -1549,7 +1556,7 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
       for (int k = 0; k < npairs; k++) v += src[k * 16 * NB];
       __syncwarp();
       if (lane == 0) st_release_shared(&folded[tb], fl / kFoldBufs + 1);
-      if (nslabs > 1) {
+      if (XT && nslabs > 1) {
         if (b < NB) p.ws[(((long long)gt * nslabs + slab) * NB + b) * 16 + r16] = v;
         slab_ticket();
         if (last_slab) {
@@ -1575,9 +1582,10 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
           const float a = job.addend ? job.addend[(long long)b * as + row] : 0.f;
           float *dst = job.y + (long long)b * job.out_dim + row;
           *dst = a + v;
-          for (int gpu = 0; gpu < p.ex.world; gpu++)
-            if (gpu != p.ex.rank)
-              *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + p.ex.peer_delta[gpu]) = a + v;
+          if constexpr (XT)
+            for (int gpu = 0; gpu < p.ex.world; gpu++)
+              if (gpu != p.ex.rank)
+                *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + p.ex.peer_delta[gpu]) = a + v;
         }
       }
       }
@@ -1591,12 +1599,13 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
     }
   }
 
-  if (p.ex.world > 1) {
-    // every thread that stored into peer memory makes its stores visible system-wide, then the
-    // CTA draws a ticket; the last CTA of the launch raises this rank's flag on every GPU.
-    __threadfence_system();
+  if (XT && p.ex.world > 1) {
+    // The CTA's stores into peer memory are ordered before thread 0's system-scope fence by the
+    // barrier (one fence per CTA: a system-scope fence in every thread cost ~10 us per launch),
+    // then the CTA draws a ticket; the last CTA of the launch raises this rank's flag on every GPU.
     consumer_sync<kNW>();
     if (ctid == 0) {
+      __threadfence_system();
       const unsigned ticket = atomicAdd(p.ex.ticket, 1u);
       if (ticket == gridDim.x - 1u) {
         __threadfence_system();
@@ -1682,7 +1691,10 @@ bool make_plan_pair(int in_dim, int nb, int pair, Params &p, size_t &smem, bool 
   const int ngroups = in_dim / C::GROUP;
   auto al = [](size_t v) { return (v + 127) & ~(size_t)127; };
   size_t off = 256;  // mbarriers and counters
-  const size_t off_flags = off;  off += kMaxItems * 4;  // one flag per work item of a row of x
+  // one flag per work item of a row of x: 64 for rows of up to 16384 columns (more would cost the
+  // Q4_K plan at 4096 columns its fifth stage, which fits to the byte), 128 beyond
+  const int nflags = (nblk + pair - 1) / pair <= 64 ? 64 : kMaxItems;
+  const size_t off_flags = off;  off += (size_t)nflags * 4;
   const bool dense = nb > 2;  // nb = 4 or 8 then: single-superblock items, 2 bytes of x per element and batch row
   const bool v2 = TYPE == kQ6_K && !dense;  // Q6_K batch 1-2: no decode areas, 2 bytes of x per element and batch row
   const size_t area_floats = v2 ? 0 : dense ? (size_t)16 * dense_area_row(C::NG, nb) : (size_t)pair * nb * Area<TYPE>::BATCH;
@@ -1709,6 +1721,7 @@ bool make_plan_pair(int in_dim, int nb, int pair, Params &p, size_t &smem, bool 
   p.off_xx = (int)off_xx; p.off_xq = (int)off_xq; p.off_stage = (int)off_stage;
   p.stage_bytes = (int)stage_bytes;
   p.pair = pair;
+  p.nflags = nflags;
   smem = off_stage + (size_t)stages * stage_bytes;
   return true;
 }
@@ -1725,13 +1738,13 @@ bool make_plan(int in_dim, int nb, Params &p, size_t &smem, bool thin = false) {
   return make_plan_pair<TYPE>(in_dim, nb, 1, p, smem);
 }
 
-template <int TYPE, int NB, int PAIR>
-int launch_instance(const Params &p, size_t smem, int grid, cudaStream_t s) {
+template <int TYPE, int NB, int PAIR, bool XT>
+int launch_instance_x(const Params &p, size_t smem, int grid, cudaStream_t s) {
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_imma_kernel<TYPE, NB, PAIR>,
+    cudaError_t e = cudaFuncSetAttribute(gemv_imma_kernel<TYPE, NB, PAIR, XT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)kDynSmemMax);
     if (e != cudaSuccess) return (int)e;
@@ -1747,7 +1760,12 @@ int launch_instance(const Params &p, size_t smem, int grid, cudaStream_t s) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return (int)cudaLaunchKernelEx(&cfg, gemv_imma_kernel<TYPE, NB, PAIR>, p);
+  return (int)cudaLaunchKernelEx(&cfg, gemv_imma_kernel<TYPE, NB, PAIR, XT>, p);
+}
+template <int TYPE, int NB, int PAIR>
+int launch_instance(const Params &p, size_t smem, int grid, cudaStream_t s) {
+  if (p.nslabs > 1 || p.ex.world > 1 || p.ex_wait) return launch_instance_x<TYPE, NB, PAIR, true>(p, smem, grid, s);
+  return launch_instance_x<TYPE, NB, PAIR, false>(p, smem, grid, s);
 }
 
 // Batch rows of the kernel instance that takes `batch` (<= 8) rows: 1, 2, 4 or 8; IQ4_NL has only
@@ -1815,7 +1833,7 @@ int top1_pass_width(int in_dim, int batch) {
 // launch touches the workspace only after its predecessor has completed).  A ninth stream, or
 // a shape whose partial sums do not fit a region, runs without slabs.
 constexpr int kWsSlots = 8;
-constexpr int kWsFloats = 1 << 17;  // 512 KB of partial sums per region
+constexpr int kWsFloats = 1 << 19;  // 2 MB of partial sums per region
 constexpr int kWsTickets = 4096;    // tiles per launch that can be split
 static __device__ __align__(256) float g_slab_ws[kWsSlots][kWsFloats];
 static __device__ unsigned g_slab_tickets[kWsSlots][kWsTickets];
@@ -1865,12 +1883,16 @@ int choose_slabs(int in_dim, int nbk, int tiles, bool thin, bool workspace_ok) {
   const int nblk = in_dim / 256, sms = sm_count();
   int best = 0;
   float best_cost = 0.f;
+  // Where whole rows fit, slabs are correct but not faster: the fence and the ticket of every tile
+  // part sit in a consumer warp's path (measured on the 9B FFN: 15.1 against 13.2 us for ffn_down
+  // with four slabs), so such a launch only uses them when asked to.  Where a row of activations
+  // does not fit shared memory, slabs replace the column ranges (one launch instead of several).
+  Params whole{};
+  size_t whole_smem = 0;
+  const bool whole_fits = make_plan<TYPE>(in_dim, nbk, whole, whole_smem, thin);
   for (int S = 1; S <= 8; S++) {
     if (nblk % S != 0 || nblk / S < 4) continue;
-    // Slabs are correct but not yet faster: the fence and the ticket of every tile part sit in a
-    // consumer warp's path (measured on the 9B FFN: 15.1 against 13.2 us for ffn_down with four
-    // slabs), so a launch only uses them when asked to.
-    if (S != 1 && S != g_imma_force_slabs) continue;
+    if (S != 1 && S != g_imma_force_slabs && (whole_fits || g_imma_force_slabs == 1)) continue;
     if (S > 1 && (!workspace_ok || tiles > kWsTickets || (long long)tiles * S * nbk * 16 > kWsFloats ||
                   sms / S < 1))
       continue;

@@ -44,6 +44,8 @@ extern "C" {
 #define COGNI_QMM_ERR_DEVICE 1005    /* device is not compute capability 10.x             */
 #define COGNI_QMM_ERR_LIMIT 1006     /* size beyond a documented fixed maximum             */
 #define COGNI_QMM_ERR_TIMEOUT 1007   /* a bounded device-side wait expired (results invalid) */
+#define COGNI_QMM_ERR_NCCL_MISSING 1008 /* libnccl.so.2 could not be loaded                    */
+#define COGNI_QMM_ERR_NCCL_BASE 2000 /* 2000 + ncclResult_t of a failed NCCL call           */
 
 /* Output element types of the prefill GEMM. */
 #define COGNI_QMM_OUT_F32 0
@@ -268,6 +270,31 @@ int cogni_qmm_gemv_many_exchange(int type, int n_weights, const void *const *d_w
                                  float *const *d_y, const int *out_dims, int in_dim, int batch,
                                  int resident, const cogni_qmm_exchange *exchange, int wait_previous,
                                  void *stream);
+
+/*
+ * The same two sharded operations with NCCL as the exchange step, on a communicator the host owns
+ * (ncclCommInitRank / ncclCommInitAll in the host's binding; this library neither creates nor
+ * destroys communicators).  (No counterpart in the reference, which has no collective call.)
+ *
+ * cogni_qmm_sharded_gemv_nccl: rank's row shard (rows = N / world rows of the matrix) against the
+ * replicated x, written into block `rank` of d_gather ([world][batch][rows] f32), then one
+ * in-place ncclAllGather: every rank ends with all blocks.
+ *
+ * cogni_qmm_sharded_top1_nccl: the fused lm_head on rank's vocabulary shard (index_base = its first
+ * row), then ncclAllReduce(ncclMax) on the int64 keys (highest value, lowest index: the tie rule of
+ * cogni_qmm_gemv_top1) and the unpacking of the winning keys: d_top_index / d_top_value / d_keys
+ * hold the global answer on every rank.
+ *
+ * NCCL is bound at run time (dlopen of libnccl.so.2): COGNI_QMM_ERR_NCCL_MISSING without it; a
+ * failed NCCL call returns COGNI_QMM_ERR_NCCL_BASE + its ncclResult_t.
+ */
+int cogni_qmm_sharded_gemv_nccl(void *nccl_comm, int world, int rank, int type, const void *d_w_shard,
+                                const float *d_x, float *d_gather, int in_dim, int rows, int batch,
+                                int resident, void *stream);
+int cogni_qmm_sharded_top1_nccl(void *nccl_comm, int world, int type, const void *d_w_shard,
+                                const float *d_x, int in_dim, int rows, int batch, int32_t index_base,
+                                void *d_scratch, size_t scratch_bytes, int64_t *d_keys,
+                                int32_t *d_top_index, float *d_top_value, void *stream);
 
 /* Lets kernels of the current device store into memory of `peer_device` (cudaDeviceEnablePeerAccess;
  * already-enabled is not an error).  The host needs it once per peer before the first exchange. */

@@ -117,6 +117,80 @@ def _exchange_worker(rank, world, port):
         dist.destroy_process_group()
 
 
+def _nccl_capi_worker(rank, world, port):
+    """The C-ABI entries that take the host's ncclComm_t: the communicator is made here the way a
+    host binding would (ncclGetUniqueId on rank 0, ncclCommInitRank everywhere, through ctypes on
+    libnccl), the sharded GEMV + all-gather and the sharded fused top-1 + MAX all-reduce run inside
+    libcogni_qmm, and every rank must hold the CPU oracle's unsharded answer."""
+    import ctypes as C
+
+    import torch.distributed as dist
+
+    from cogni_ml_b200 import DeviceQuantWeight, QuantWeight, lib, synth
+    from cogni_ml_b200._lib import check
+    from cogni_ml_b200.sharded import shard_rows
+    from oracle import loader
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    nccl = C.CDLL("libnccl.so.2")
+
+    class UniqueId(C.Structure):
+        _fields_ = [("internal", C.c_byte * 128)]
+
+    uid = UniqueId()
+    if rank == 0:
+        assert nccl.ncclGetUniqueId(C.byref(uid)) == 0
+    box = [bytes(uid)]
+    dist.broadcast_object_list(box, src=0)
+    C.memmove(C.byref(uid), box[0], 128)
+    comm = C.c_void_p()
+    nccl.ncclCommInitRank.argtypes = [C.POINTER(C.c_void_p), C.c_int, UniqueId, C.c_int]
+    assert nccl.ncclCommInitRank(C.byref(comm), world, uid, rank) == 0
+    try:
+        stream = torch.cuda.current_stream().cuda_stream
+        for qtype, out_dim, in_dim, batch in [(synth.Q4_K, 2048, 1024, 1), (synth.Q6_K, 4096, 2560, 8)]:
+            raw = synth.make_weight(qtype, out_dim, in_dim, seed=19, tensor_id=qtype)
+            x = synth.make_activation(batch, in_dim, seed=19)
+            ref = loader.matmul_add(x, batch, in_dim, raw, qtype, out_dim,
+                                    np.zeros(out_dim, np.float32)).reshape(batch, out_dim)
+            r0, r1 = shard_rows(out_dim, rank, world)
+            rows = r1 - r0
+            dw = DeviceQuantWeight.upload(QuantWeight(raw, qtype, out_dim, in_dim), dev, r0, r1)
+            xd = torch.from_numpy(x).to(dev)
+            gather = torch.full((world, batch, rows), float("nan"), dtype=torch.float32, device=dev)
+            check(lib.cogni_qmm_sharded_gemv_nccl(comm, world, rank, qtype, dw.raw.data_ptr(), xd.data_ptr(),
+                                                  gather.data_ptr(), in_dim, rows, batch, 1, stream),
+                  "cogni_qmm_sharded_gemv_nccl")
+            y = gather.permute(1, 0, 2).reshape(batch, out_dim).cpu().numpy()
+            assert np.abs(y - ref).max() <= 1e-3 * np.abs(ref).max()
+            scratch = dw.top1_scratch(batch)
+            keys = torch.zeros(batch, dtype=torch.int64, device=dev)
+            idx = torch.zeros(batch, dtype=torch.int32, device=dev)
+            val = torch.zeros(batch, dtype=torch.float32, device=dev)
+            check(lib.cogni_qmm_sharded_top1_nccl(comm, world, qtype, dw.raw.data_ptr(), xd.data_ptr(), in_dim,
+                                                  rows, batch, r0, scratch.data_ptr(), scratch.numel(),
+                                                  keys.data_ptr(), idx.data_ptr(), val.data_ptr(), stream),
+                  "cogni_qmm_sharded_top1_nccl")
+            torch.cuda.synchronize()
+            for b in range(batch):
+                assert int(idx[b]) == loader.top1(ref[b])[0]
+        dist.barrier()
+    finally:
+        nccl.ncclCommDestroy.argtypes = [C.c_void_p]
+        nccl.ncclCommDestroy(comm)
+        dist.destroy_process_group()
+
+
+def test_two_rank_sharded_entries_on_the_hosts_nccl_communicator(cuda):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_nccl_capi_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
 def test_two_rank_exchange_fused_into_the_gemv(cuda):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
