@@ -630,70 +630,84 @@ class _HeadShape:
 
 def sharded_27b(dev, world, rank, exchange, peaks):
     """Config 5, strong scaling: the fixed 27B matrices split by rows over the ranks, batch 1 and 8.
-    Per (matrix, batch): kernel-only us (the shard's GEMV, no exchange), kernel + exchange us with
-    the exchange fused into the launch, and with an NCCL all-gather after the launch; for the
-    lm_head the per-shard fused top-1 plus the MAX all-reduce of the keys.  Max over ranks."""
+    Per batch: kernel-only us of the shard GEMVs (no exchange); the decode chain ffn_gate + ffn_up
+    (one launch) -> ffn_down with every launch exchanging its outputs inside the kernel and the
+    next one reading the gathered (value, epoch) words; the same chain with an NCCL all-gather
+    after each launch.  us per launch, max over ranks; aggregate weight GB/s of the whole box."""
     import torch
     import torch.distributed as dist
 
-    from cogni_ml_b200 import synth
+    from cogni_ml_b200 import CogniQmmError, GemvMany, synth
     from cogni_ml_b200.sharded import ExchangingGemv
+    hid, ffn = 5120, 17408
     rows = []
-    shapes = [("27b_ffn_gate_up", Q4_K, 17408, 5120, 2), ("27b_ffn_down", Q6_K, 5120, 17408, 1)]
-    for name, qtype, n, k, nmat in shapes:
-        local = n // world
-        raw = synth.make_weight(qtype, local, k, seed=rank, tensor_id=qtype)
-        ring = weight_ring(raw, qtype, local, k, dev, min_bytes=200e6 / max(1, nmat), max_copies=24)
-        if nmat == 2:
-            ring2 = weight_ring(raw, qtype, local, k, dev, min_bytes=200e6 / nmat, max_copies=24)
-        for batch in (1, 8):
-            x = torch.from_numpy(synth.make_activation(batch, k, seed=1, tensor_id=70 + batch)).to(dev)
-            from cogni_ml_b200 import GemvMany
-            y_local = [torch.empty(batch, local, dtype=torch.float32, device=dev) for _ in range(nmat)]
-            plain = [GemvMany([ring[i]] + ([ring2[i]] if nmat == 2 else []), x, y_local) for i in range(len(ring))]
+    g_rows, d_rows = ffn // world, hid // world
+    gate_raw = synth.make_weight(Q4_K, g_rows, hid, seed=rank, tensor_id=Q4_K)
+    down_raw = synth.make_weight(Q6_K, d_rows, ffn, seed=rank, tensor_id=Q6_K)
+    copies = int(max(2, min(24, 250e6 // (2 * gate_raw.nbytes + down_raw.nbytes) + 1)))
+    from cogni_ml_b200 import DeviceQuantWeight, QuantWeight
+    g0 = DeviceQuantWeight.upload(QuantWeight(gate_raw, Q4_K, g_rows, hid), dev)
+    d0 = DeviceQuantWeight.upload(QuantWeight(down_raw, Q6_K, d_rows, ffn), dev)
+    gates = [g0] + [DeviceQuantWeight(g0.raw.clone(), Q4_K, g_rows, hid) for _ in range(copies - 1)]
+    ups = [DeviceQuantWeight(g0.raw.clone(), Q4_K, g_rows, hid) for _ in range(copies)]
+    downs = [d0] + [DeviceQuantWeight(d0.raw.clone(), Q6_K, d_rows, ffn) for _ in range(copies - 1)]
+    torch.cuda.synchronize()
+    for w in gates + ups + downs:
+        w.resident = True
+    layer_bytes = 2 * ffn * (hid // 256) * 144 + hid * (ffn // 256) * 210
+    for batch in (1, 8):
+        xh = torch.from_numpy(synth.make_activation(batch, hid, seed=1, tensor_id=70 + batch)).to(dev)
+        xf = torch.from_numpy(synth.make_activation(batch, ffn, seed=1, tensor_id=80 + batch)).to(dev)
+        yg = torch.empty(world, batch, g_rows, dtype=torch.float32, device=dev)
+        yu = torch.empty_like(yg)
+        yd = torch.empty(world, batch, d_rows, dtype=torch.float32, device=dev)
+        plain_gu = [GemvMany([gates[i], ups[i]], xh, [yg[rank], yu[rank]]) for i in range(copies)]
 
-            def kernel_only():
-                for c in plain:
-                    c.run()
-            us_kernel = timed(graphed(kernel_only).replay, 10) * 1e3 / len(ring)
-            row = {"name": name, "type": TYPE_NAME[qtype], "out_dim": n, "in_dim": k, "matrices": nmat,
-                   "batch": batch, "kernel_us": reduce_max(us_kernel, dev) if world > 1 else us_kernel}
-            if world > 1:
-                bufs = [exchange.buffer(f"{name}_{batch}_{j}", (world, batch, local)) for j in range(nmat)]
-                fused = [ExchangingGemv(exchange, [ring[i]] + ([ring2[i]] if nmat == 2 else []), x, bufs, True)
-                         for i in range(len(ring))]
+        def kernel_only():
+            for i in range(copies):
+                plain_gu[i].run()
+                downs[i].gemv(xf, out=yd[rank])
+        us_kernel = timed(graphed(kernel_only).replay, 10) * 1e3 / (2 * copies)
+        row = {"batch": batch, "layers_in_ring": copies,
+               "per_layer": "ffn_gate+ffn_up Q4_K 17408x5120 (one launch), ffn_down Q6_K 5120x17408, rows / n_gpus per rank",
+               "kernel_us_per_launch": reduce_max(us_kernel, dev) if world > 1 else us_kernel}
+        best = row["kernel_us_per_launch"]
+        if world > 1:
+            bg = exchange.buffer(f"g27_{batch}", batch, ffn)
+            bu = exchange.buffer(f"u27_{batch}", batch, ffn)
+            bd = exchange.buffer(f"d27_{batch}", batch, hid)
+            try:
+                # the chain: gate/up read the gathered words of the previous down projection, down
+                # reads the gathered words of gate (standing in for silu(gate) * up)
+                fgu = [ExchangingGemv(exchange, [gates[i], ups[i]], bd, [bg, bu], True) for i in range(copies)]
+                fdn = [ExchangingGemv(exchange, [downs[i]], bg, [bd], True) for i in range(copies)]
+                ExchangingGemv(exchange, [downs[0]], xf, [bd], False).run()   # the first input of the chain
 
-                def with_fused():
-                    for c in fused:
-                        c.run()
+                def chain():
+                    for i in range(copies):
+                        fgu[i].run()
+                        fdn[i].run()
                 dist.barrier()
-                from cogni_ml_b200 import CogniQmmError
-                try:
-                    us = timed(graphed(with_fused).replay, 10) * 1e3 / len(ring)
-                    row["kernel_plus_fused_exchange_us"] = reduce_max(us, dev)
-                except CogniQmmError as exc:   # same answer on every rank: the shape decides
-                    row["kernel_plus_fused_exchange_us"] = None
-                    row["fused_exchange_note"] = f"not offered for this shape (status {exc.status})"
-                gath = [torch.empty(world, batch, local, dtype=torch.float32, device=dev) for _ in range(nmat)]
-                nccl_calls = [GemvMany([ring[i]] + ([ring2[i]] if nmat == 2 else []), x,
-                                       [gb[rank] for gb in gath]) for i in range(len(ring))]
+                us = timed(graphed(chain).replay, 10) * 1e3 / (2 * copies)
+                row["chain_fused_exchange_us_per_launch"] = best = reduce_max(us, dev)
+            except CogniQmmError as exc:   # same answer on every rank: the shape decides
+                row["chain_fused_exchange_us_per_launch"] = None
+                row["fused_exchange_note"] = f"not offered for this shape (status {exc.status})"
 
-                def with_nccl():
-                    for c in nccl_calls:
-                        c.run()
-                        for gb in gath:
-                            dist.all_gather_into_tensor(gb.view(-1), gb[rank].reshape(-1))
-                dist.barrier()
-                us = timed(with_nccl, 5) * 1e3 / len(ring)
-                row["kernel_plus_nccl_allgather_us"] = reduce_max(us, dev)
-            total_bytes = nmat * n * (k // 256) * (144 if qtype == Q4_K else 210)
-            best = row.get("kernel_plus_fused_exchange_us") or row.get("kernel_plus_nccl_allgather_us") or row["kernel_us"]
-            row["aggregate_weight_gbs"] = total_bytes / best / 1e3
-            rows.append(row)
-        del ring
-        if nmat == 2:
-            del ring2
-        torch.cuda.empty_cache()
+            def chain_nccl():
+                for i in range(copies):
+                    plain_gu[i].run()
+                    dist.all_gather_into_tensor(yg.view(-1), yg[rank].reshape(-1))
+                    dist.all_gather_into_tensor(yu.view(-1), yu[rank].reshape(-1))
+                    downs[i].gemv(xf, out=yd[rank])
+                    dist.all_gather_into_tensor(yd.view(-1), yd[rank].reshape(-1))
+            dist.barrier()
+            us = timed(chain_nccl, 5) * 1e3 / (2 * copies)
+            row["chain_nccl_allgather_us_per_launch"] = reduce_max(us, dev)
+            if row.get("chain_fused_exchange_us_per_launch") is None:
+                best = row["chain_nccl_allgather_us_per_launch"]
+        row["aggregate_weight_gbs"] = layer_bytes / (2 * best) / 1e3
+        rows.append(row)
     return rows
 
 
@@ -780,14 +794,13 @@ def run_ours(args):
     if world > 1:
         from cogni_ml_b200.sharded import ExchangingGemv, PeerExchange
         exchange = PeerExchange(64 << 20, dev)
-    if fused:
-        y_gate = exchange.buffer("y_gate", (world, B, FFN))
-        y_up = exchange.buffer("y_up", (world, B, FFN))
-        y_down = exchange.buffer("y_down", (world, B, HIDDEN))
-    else:
-        y_gate = torch.empty(world, B, FFN, dtype=torch.float32, device=dev)
-        y_up = torch.empty(world, B, FFN, dtype=torch.float32, device=dev)
-        y_down = torch.empty(world, B, HIDDEN, dtype=torch.float32, device=dev)
+    y_gate = torch.empty(world, B, FFN, dtype=torch.float32, device=dev)
+    y_up = torch.empty(world, B, FFN, dtype=torch.float32, device=dev)
+    y_down = torch.empty(world, B, HIDDEN, dtype=torch.float32, device=dev)
+    if fused:   # gather buffers of (value, epoch) words, [B][world * rows]
+        x_gate = exchange.buffer("y_gate", B, world * FFN)
+        x_up = exchange.buffer("y_up", B, world * FFN)
+        x_down = exchange.buffer("y_down", B, world * HIDDEN)
     out_host = [torch.empty(B, n, dtype=torch.float32).pin_memory() for n in (FFN, FFN, HIDDEN)]
 
     def gather(buf):
@@ -826,8 +839,10 @@ def run_ours(args):
                 marks[2].record()
     elif fused:
         # every launch exchanges its outputs and waits for the exchange before it, layer by layer
-        ex_gu = [ExchangingGemv(exchange, [gates[l], ups[l]], xh, [y_gate, y_up], True) for l in range(L)]
-        ex_dn = [ExchangingGemv(exchange, [downs[l]], xf, [y_down], True) for l in range(L)]
+        # (the activations stay the static xh / xf so that every rank streams the same bytes as at
+        # N = 1; a consumer that reads the gathered words instead is timed in extras.sharded_27b)
+        ex_gu = [ExchangingGemv(exchange, [gates[l], ups[l]], xh, [x_gate, x_up], False) for l in range(L)]
+        ex_dn = [ExchangingGemv(exchange, [downs[l]], xf, [x_down], False) for l in range(L)]
 
         def launch_exchanging(layers=range(L)):
             for l in layers:
@@ -857,7 +872,12 @@ def run_ours(args):
     check = None
     if world > 1 and not args.no_check:
         if fused:
-            layer0 = lambda: launch_exchanging(range(1))
+            def layer0():
+                launch_exchanging(range(1))
+                torch.cuda.synchronize()
+                dist.barrier()     # every rank's stores have landed: read the words' values
+                for dst, src, n in ((y_gate, x_gate, FFN), (y_up, x_up, FFN), (y_down, x_down, HIDDEN)):
+                    dst.copy_(src[..., 0].reshape(B, world, n).permute(1, 0, 2))
         else:
             def layer0():
                 gate_up[0].run()
@@ -893,9 +913,14 @@ def run_ours(args):
         xh.copy_(xh_host, non_blocking=True)
         xf.copy_(xf_host, non_blocking=True)
         step()
-        out_host[0].copy_(y_gate[rank], non_blocking=True)
-        out_host[1].copy_(y_up[rank], non_blocking=True)
-        out_host[2].copy_(y_down[rank], non_blocking=True)
+        if fused:   # this rank's columns of the gathered words
+            out_host[0].copy_(x_gate[:, rank * FFN:(rank + 1) * FFN, 0], non_blocking=True)
+            out_host[1].copy_(x_up[:, rank * FFN:(rank + 1) * FFN, 0], non_blocking=True)
+            out_host[2].copy_(x_down[:, rank * HIDDEN:(rank + 1) * HIDDEN, 0], non_blocking=True)
+        else:
+            out_host[0].copy_(y_gate[rank], non_blocking=True)
+            out_host[1].copy_(y_up[rank], non_blocking=True)
+            out_host[2].copy_(y_down[rank], non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     for _ in range(args.warmup):

@@ -29,7 +29,8 @@ SIGNATURES = {
     "cogni_qmm_gemv_many_rmsnorm": (_i, [_i, _i, _vp, _vp, _vp, C.c_float, _vp, _i64, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "cogni_qmm_embedding_lookup": (_i, [_i, _vp, _i, _i, _vp, _i, _vp, _vp, _vp]),
     "cogni_qmm_gemv_swiglu": (_i, [_i, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i, _i, _i, _i, _vp]),
-    "cogni_qmm_gemv_many_exchange": (_i, [_i, _i, _vp, _vp, _vp, _i64, _vp, _vp, _i, _i, _i, _vp, _i, _vp]),
+    "cogni_qmm_gemv_many_exchange": (_i, [_i, _i, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _i, _i, _i, _vp, _i, _vp]),
+    "cogni_qmm_exchange_unpack": (_i, [_vp, _i64, C.c_uint32, _vp, _vp]),
     "cogni_qmm_sharded_gemv_nccl": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "cogni_qmm_sharded_top1_nccl": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, C.c_int32, _vp, _sz, _vp, _vp, _vp, _vp]),
     "cogni_qmm_enable_peer_access": (_i, [_i]),

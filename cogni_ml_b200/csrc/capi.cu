@@ -230,26 +230,32 @@ int cogni_qmm_gemv_many(int type, int n_weights, const void *const *d_w, const f
 
 int cogni_qmm_gemv_many_exchange(int type, int n_weights, const void *const *d_w, const float *d_x,
                                  const float *const *d_addend, int64_t addend_stride,
-                                 float *const *d_y, const int *out_dims, int in_dim, int batch,
-                                 int resident, const cogni_qmm_exchange *ex, int wait_previous,
-                                 void *stream) {
+                                 float *const *d_y, int64_t y_pitch, const int *out_dims, int in_dim,
+                                 int batch, int resident, const cogni_qmm_exchange *ex,
+                                 int wait_previous, void *stream) {
   if (!supported(type)) return COGNI_QMM_ERR_TYPE;
-  if (n_weights <= 0 || !d_w || !d_y || !out_dims || !ex) return COGNI_QMM_ERR_ARG;
-  if (ex->world < 1 || ex->world > 8 || ex->rank < 0 || ex->rank >= ex->world || !ex->flags ||
-      !ex->epoch || !ex->ticket)
+  if (n_weights <= 0 || !d_w || !d_y || !out_dims || !ex || y_pitch < 0) return COGNI_QMM_ERR_ARG;
+  if (ex->world < 1 || ex->world > 8 || ex->rank < 0 || ex->rank >= ex->world || !ex->epoch || !ex->ticket)
     return COGNI_QMM_ERR_ARG;
   for (int g = 0; g < ex->world; g++)
-    if (!ex->peer_flag[g] || (g != ex->rank && (ex->peer_offset[g] & 3))) return COGNI_QMM_ERR_ARG;
+    if (g != ex->rank && (ex->peer_offset[g] & 7)) return COGNI_QMM_ERR_ARG;
   for (int j = 0; j < n_weights; j++) {
     int st = check_gemv_args(type, d_w[j], d_x, d_y[j], in_dim, out_dims[j], batch);
     if (st) return st;
+    if (reinterpret_cast<uintptr_t>(d_y[j]) & 7) return COGNI_QMM_ERR_ALIGN;   // 8-byte words
     if (d_addend && d_addend[j] && addend_stride != 0 && addend_stride != out_dims[j])
       return COGNI_QMM_ERR_ARG;
     if (g_force_rowwarp != 0 || !gemv_imma_supports(type, d_w[j], d_x, in_dim, batch)) return COGNI_QMM_ERR_LIMIT;
   }
   return launch_gemv_imma_many_exchange(type, n_weights, d_w, d_x, d_addend, addend_stride, d_y, out_dims,
-                                        in_dim, batch, resident, ex, wait_previous,
+                                        in_dim, batch, resident, ex, wait_previous, y_pitch,
                                         static_cast<cudaStream_t>(stream));
+}
+
+int cogni_qmm_exchange_unpack(const void *d_words, int64_t n, uint32_t epoch, float *d_out, void *stream) {
+  if (!d_words || !d_out || n <= 0) return COGNI_QMM_ERR_ARG;
+  if (reinterpret_cast<uintptr_t>(d_words) & 7) return COGNI_QMM_ERR_ALIGN;
+  return launch_exchange_unpack(d_words, n, epoch, d_out, static_cast<cudaStream_t>(stream));
 }
 
 int cogni_qmm_enable_peer_access(int peer_device) {

@@ -124,13 +124,53 @@ struct Job {
 };
 
 struct Exchange {
-  int world, rank;               // world <= 1: no exchange
-  long long peer_delta[kMaxRanks];   // bytes from an address in this GPU's buffer to the same place in GPU g's, as mapped here
-  unsigned *peer_flag[kMaxRanks];    // GPU g's flag word for this rank, as mapped here ([rank]: the local one)
-  const unsigned *flags;         // this GPU's flag words, one per rank, written by the peers
-  unsigned *epoch;               // exchanges this GPU has completed on this buffer set
-  unsigned *ticket;              // CTA arrivals of the running launch, zero between launches
+  int world, rank;                  // world <= 1: no exchange
+  long long peer_delta[kMaxRanks];  // bytes from an address in this GPU's buffer to the same place in GPU g's, as mapped here ([rank]: 0)
+  unsigned *epoch;                  // exchanges this GPU has completed on this buffer set
+  unsigned *ticket;                 // CTA arrivals of the running launch, zero between launches
 };
+
+// Where a kernel's activations come from: plain f32, or the 8-byte (value, epoch) words an
+// exchanging launch leaves in the gather buffer of every GPU.  Such a word is written by ONE
+// 8-byte store, so value and epoch arrive together: the reader polls the word until it carries the
+// epoch it expects and needs no fence, flag or barrier (the "LL" scheme of collective libraries).
+struct XSrc {
+  int ll;
+  unsigned epoch;
+};
+// Four consecutive activations from element `off` on.
+__device__ __forceinline__ float4 ld4x(const float *x, long long off, const XSrc &src) {
+  if (!src.ll) return __ldg(reinterpret_cast<const float4 *>(x + off));
+  const uint2 *w = reinterpret_cast<const uint2 *>(x) + off;  // 16-byte aligned: off is a multiple of 4
+  uint4 a, b;
+  const unsigned long long t0 = global_ns();
+  for (unsigned spin = 0;; spin++) {
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(w) : "memory");
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(w + 2) : "memory");
+    if (a.y == src.epoch && a.w == src.epoch && b.y == src.epoch && b.w == src.epoch) break;
+    if ((spin & 255u) == 255u) {  // bounded like every wait: count the expiry and carry on
+      if (pipe_broken()) break;
+      if (global_ns() - t0 > kPipeWaitLimitNs) {
+        atomicAdd(&g_pipe_wait_timeouts, 1u);
+        break;
+      }
+    }
+  }
+  return make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
+}
+// One output value: plain, or as a (value, epoch) word here and at the same place on every peer.
+__device__ __forceinline__ void store_y(float *y, long long idx, float v, const Exchange &ex, unsigned e_out) {
+  if (ex.world <= 1) {
+    y[idx] = v;
+    return;
+  }
+  char *w = reinterpret_cast<char *>(reinterpret_cast<uint2 *>(y) + idx);
+  for (int gpu = 0; gpu < ex.world; gpu++)
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(w + ex.peer_delta[gpu]),
+                 "r"(__float_as_uint(v)), "r"(e_out) : "memory");
+}
 
 struct Params {
   const float *x;
@@ -158,11 +198,12 @@ struct Params {
   int nslabs;            // 1: every CTA takes whole rows
   float *ws;             // [tile][slab][batch row][16] partial sums
   unsigned *ws_tickets;  // [tile] arrival counters, zero between launches
-  // Exchange of the outputs with the other GPUs of the box, fused into the kernel: every y value is
-  // also stored into the same place of each peer's gather buffer (peer-mapped memory, ordinary
-  // stores over NVLink), and the last CTA raises this rank's flag on every GPU.
+  // Exchange of the outputs with the other GPUs of the box, fused into the kernel: every y value
+  // goes, as a (value, epoch) word, into this GPU's gather buffer and into the same place of each
+  // peer's (peer-mapped memory, ordinary 8-byte stores over NVLink).
   Exchange ex;
-  int ex_wait;           // before touching x: wait until every rank's flag has reached this GPU's epoch
+  int ex_wait;           // the activations are the (value, epoch) words of the exchange before this launch
+  long long y_pitch;     // elements between the batch rows of y; 0: the job's out_dim
   long long *part_keys;  // fused top-1 (nullptr: plain GEMV)
   unsigned *counter;
   int32_t *top_idx;
@@ -588,7 +629,7 @@ template <int TYPE, int NB, int NBLK>
 __device__ __forceinline__ void quantise_superblocks(const float *x, const float *x_up,
                                                      const float *norm_w, const float *inv_rms,
                                                      int K, int kblk, int lane, uint8_t *xq,
-                                                     float *SX, float *XX) {
+                                                     float *SX, float *XX, const XSrc &src) {
   using C = Cfg<TYPE>;
   constexpr int NCX = 4 * NB, UNIT_BYTES = NCX * 64;
   constexpr int LPG = C::GROUP / 8;  // lanes per scale group
@@ -603,11 +644,11 @@ __device__ __forceinline__ void quantise_superblocks(const float *x, const float
 #pragma unroll
     for (int b = 0; b < NB; b++) {
       const long long off = (long long)b * K + (kblk + q) * 256 + e_in;
-      v0[q][b] = __ldg(reinterpret_cast<const float4 *>(x + off));
-      v1[q][b] = __ldg(reinterpret_cast<const float4 *>(x + off + 4));
+      v0[q][b] = ld4x(x, off, src);
+      v1[q][b] = ld4x(x, off + 4, src);
       if (x_up) {  // SwiGLU: silu(gate) * up in f32, silu(v) = v / (1 + exp(-v)) (qwen35_cpu.cr:512-519, 1716-1717)
-        const float4 u0 = __ldg(reinterpret_cast<const float4 *>(x_up + off));
-        const float4 u1 = __ldg(reinterpret_cast<const float4 *>(x_up + off + 4));
+        const float4 u0 = ld4x(x_up, off, src);
+        const float4 u1 = ld4x(x_up, off + 4, src);
         auto sw = [](float gte, float up) { return gte / (1.f + expf(-gte)) * up; };
         v0[q][b] = make_float4(sw(v0[q][b].x, u0.x), sw(v0[q][b].y, u0.y), sw(v0[q][b].z, u0.z), sw(v0[q][b].w, u0.w));
         v1[q][b] = make_float4(sw(v1[q][b].x, u1.x), sw(v1[q][b].y, u1.y), sw(v1[q][b].z, u1.z), sw(v1[q][b].w, u1.w));
@@ -698,7 +739,7 @@ template <int TYPE, int NB>
 __device__ __forceinline__ void quantise_dense(const float *x, const float *x_up,
                                                const float *norm_w, const float *inv_rms, int K,
                                                int batch, int kblk, int lane, uint8_t *xq,
-                                               float *SX, float *XX) {
+                                               float *SX, float *XX, const XSrc &src) {
   using C = Cfg<TYPE>;
   constexpr int J = NB / 4, W = Dense<TYPE>::W;
   constexpr int LPG = C::GROUP / 8;  // lanes per scale group
@@ -718,11 +759,11 @@ __device__ __forceinline__ void quantise_dense(const float *x, const float *x_up
     for (int i = 0; i < 4; i++) {
       const int br = min(b4 + i, batch - 1);
       const long long off = (long long)br * K + k;
-      v0[i] = __ldg(reinterpret_cast<const float4 *>(x + off));
-      v1[i] = __ldg(reinterpret_cast<const float4 *>(x + off + 4));
+      v0[i] = ld4x(x, off, src);
+      v1[i] = ld4x(x, off + 4, src);
       if (x_up) {  // SwiGLU: silu(gate) * up in f32, silu(v) = v / (1 + exp(-v)) (qwen35_cpu.cr:512-519, 1716-1717)
-        const float4 u0 = __ldg(reinterpret_cast<const float4 *>(x_up + off));
-        const float4 u1 = __ldg(reinterpret_cast<const float4 *>(x_up + off + 4));
+        const float4 u0 = ld4x(x_up, off, src);
+        const float4 u1 = ld4x(x_up, off + 4, src);
         auto sw = [](float gte, float up) { return gte / (1.f + expf(-gte)) * up; };
         v0[i] = make_float4(sw(v0[i].x, u0.x), sw(v0[i].y, u0.y), sw(v0[i].z, u0.z), sw(v0[i].w, u0.w));
         v1[i] = make_float4(sw(v1[i].x, u1.x), sw(v1[i].y, u1.y), sw(v1[i].z, u1.z), sw(v1[i].w, u1.w));
@@ -1014,7 +1055,7 @@ __device__ __forceinline__ void mma_dense(const uint8_t *blk, int pad_a, int pad
 template <int NB, int NBLK>
 __device__ __forceinline__ void quantise_q6v2(const float *x, const float *x_up, const float *norm_w,
                                               const float *inv_rms, int K, int kblk, int lane,
-                                              uint8_t *xq, float *SXB, int *NG) {
+                                              uint8_t *xq, float *SXB, int *NG, const XSrc &src) {
   const int e_in = lane * 8;
   float4 v0[NBLK][NB], v1[NBLK][NB];
 #pragma unroll
@@ -1022,11 +1063,11 @@ __device__ __forceinline__ void quantise_q6v2(const float *x, const float *x_up,
 #pragma unroll
     for (int b = 0; b < NB; b++) {
       const long long off = (long long)b * K + (kblk + q) * 256 + e_in;
-      v0[q][b] = __ldg(reinterpret_cast<const float4 *>(x + off));
-      v1[q][b] = __ldg(reinterpret_cast<const float4 *>(x + off + 4));
+      v0[q][b] = ld4x(x, off, src);
+      v1[q][b] = ld4x(x, off + 4, src);
       if (x_up) {  // SwiGLU: silu(gate) * up in f32 (qwen35_cpu.cr:512-519, 1716-1717)
-        const float4 u0 = __ldg(reinterpret_cast<const float4 *>(x_up + off));
-        const float4 u1 = __ldg(reinterpret_cast<const float4 *>(x_up + off + 4));
+        const float4 u0 = ld4x(x_up, off, src);
+        const float4 u1 = ld4x(x_up, off + 4, src);
         auto sw = [](float gte, float up) { return gte / (1.f + expf(-gte)) * up; };
         v0[q][b] = make_float4(sw(v0[q][b].x, u0.x), sw(v0[q][b].y, u0.y), sw(v0[q][b].z, u0.z), sw(v0[q][b].w, u0.w));
         v1[q][b] = make_float4(sw(v1[q][b].x, u1.x), sw(v1[q][b].y, u1.y), sw(v1[q][b].z, u1.z), sw(v1[q][b].w, u1.w));
@@ -1277,29 +1318,11 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
 
   asm volatile("bar.sync 3, %0;" ::"n"(kThreads) : "memory");  // mbarriers and counters ready
   pdl_wait_prior_grid();  // x (and y / the addend) may be produced by the preceding kernel
-  if (XT && p.ex_wait) {
-    // x comes out of an exchange: every rank's stores into this GPU's buffer are complete once its
-    // flag has reached the number of exchanges this GPU has itself completed (all ranks run the
-    // same sequence).  Bounded like every wait; an expiry is counted and the launch carries on.
-    if (warp == 0 && lane < p.ex.world) {
-      const unsigned want = *reinterpret_cast<volatile const unsigned *>(p.ex.epoch);
-      const unsigned long long t0 = global_ns();
-      for (unsigned spin = 0;; spin++) {
-        unsigned have;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(have) : "l"(p.ex.flags + lane) : "memory");
-        if ((int)(have - want) >= 0) break;
-        __nanosleep(64);
-        if ((spin & 63u) == 63u) {
-          if (pipe_broken()) break;
-          if (global_ns() - t0 > kPipeWaitLimitNs) {
-            atomicAdd(&g_pipe_wait_timeouts, 1u);
-            break;
-          }
-        }
-      }
-    }
-    consumer_sync<kNW>();
-  }
+  // exchanges completed on this GPU before this launch: the epoch its inputs carry (if they come
+  // out of an exchange) and, plus one, the epoch its outputs get
+  unsigned ex_epoch = 0;
+  if (XT && p.ex.epoch) ex_epoch = *reinterpret_cast<volatile const unsigned *>(p.ex.epoch);
+  const XSrc xsrc{XT ? p.ex_wait : 0, ex_epoch};
 
   // RMSNorm prologue: 1 / sqrt(mean(x^2) + eps) per batch row, the sum of squares in f64 as the
   // reference has it (qwen35_cpu.cr:484-490); per-warp partial sums are added in warp order, so
@@ -1315,7 +1338,7 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
       const int br = DENSE ? min(b, p.batch - 1) : b;
       double ss = 0.0;
       for (int k = ctid * 4; k < p.norm_dim; k += kNW * 32 * 4) {
-        const float4 v = __ldg(reinterpret_cast<const float4 *>(p.norm_x + (long long)br * K + k));
+        const float4 v = ld4x(p.norm_x, (long long)br * K + k, xsrc);
         ss += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
       }
 #pragma unroll
@@ -1383,11 +1406,11 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
       // CTA's first tile does x's two superblocks first; later tiles find them done.
       if (li == 0) {
         if constexpr (V2) {
-          if (PAIR == 2 && n2 == 2) quantise_q6v2<NB, 2>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, reinterpret_cast<int *>(XX));
-          else quantise_q6v2<NB, 1>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, reinterpret_cast<int *>(XX));
-        } else if constexpr (DENSE) quantise_dense<TYPE, NB>(xs, xs_up, norm_ws, s_inv_rms, K, p.batch, e0, lane, xq, SX, XX);
-        else if (PAIR == 2 && n2 == 2) quantise_superblocks<TYPE, NB, 2>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, XX);
-        else quantise_superblocks<TYPE, NB, 1>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, XX);
+          if (PAIR == 2 && n2 == 2) quantise_q6v2<NB, 2>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, reinterpret_cast<int *>(XX), xsrc);
+          else quantise_q6v2<NB, 1>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, reinterpret_cast<int *>(XX), xsrc);
+        } else if constexpr (DENSE) quantise_dense<TYPE, NB>(xs, xs_up, norm_ws, s_inv_rms, K, p.batch, e0, lane, xq, SX, XX, xsrc);
+        else if (PAIR == 2 && n2 == 2) quantise_superblocks<TYPE, NB, 2>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, XX, xsrc);
+        else quantise_superblocks<TYPE, NB, 1>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, XX, xsrc);
         __syncwarp();
         if (lane == 0) st_release_shared(&xready[e], 1);
       } else {
@@ -1539,12 +1562,9 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
             } else {
               const long long as = p.addend_stride < 0 ? job.out_dim : p.addend_stride;
               const float a = job.addend ? job.addend[(long long)b * as + row] : 0.f;
-              float *dst = job.y + (long long)b * job.out_dim + row;
-              *dst = a + v[i];
-              if constexpr (XT)
-                for (int gpu = 0; gpu < p.ex.world; gpu++)
-                  if (gpu != p.ex.rank)
-                    *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + p.ex.peer_delta[gpu]) = a + v[i];
+              const long long idx = (long long)b * (XT && p.y_pitch ? p.y_pitch : job.out_dim) + row;
+              if constexpr (XT) store_y(job.y, idx, a + v[i], p.ex, ex_epoch + 1u);
+              else job.y[idx] = a + v[i];
             }
           }
         }
@@ -1580,12 +1600,9 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
         } else {
           const long long as = p.addend_stride < 0 ? job.out_dim : p.addend_stride;
           const float a = job.addend ? job.addend[(long long)b * as + row] : 0.f;
-          float *dst = job.y + (long long)b * job.out_dim + row;
-          *dst = a + v;
-          if constexpr (XT)
-            for (int gpu = 0; gpu < p.ex.world; gpu++)
-              if (gpu != p.ex.rank)
-                *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + p.ex.peer_delta[gpu]) = a + v;
+          const long long idx = (long long)b * (XT && p.y_pitch ? p.y_pitch : job.out_dim) + row;
+          if constexpr (XT) store_y(job.y, idx, a + v, p.ex, ex_epoch + 1u);
+          else job.y[idx] = a + v;
         }
       }
       }
@@ -1600,19 +1617,13 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
   }
 
   if (XT && p.ex.world > 1) {
-    // The CTA's stores into peer memory are ordered before thread 0's system-scope fence by the
-    // barrier (one fence per CTA: a system-scope fence in every thread cost ~10 us per launch),
-    // then the CTA draws a ticket; the last CTA of the launch raises this rank's flag on every GPU.
+    // the last CTA of the launch counts the exchange (the next launch on this GPU reads the word
+    // after this grid has completed: no fence is needed for it)
     consumer_sync<kNW>();
     if (ctid == 0) {
-      __threadfence_system();
       const unsigned ticket = atomicAdd(p.ex.ticket, 1u);
       if (ticket == gridDim.x - 1u) {
-        __threadfence_system();
-        const unsigned e = *reinterpret_cast<volatile unsigned *>(p.ex.epoch) + 1u;
-        for (int gpu = 0; gpu < p.ex.world; gpu++)
-          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.ex.peer_flag[gpu]), "r"(e) : "memory");
-        *reinterpret_cast<volatile unsigned *>(p.ex.epoch) = e;
+        *reinterpret_cast<volatile unsigned *>(p.ex.epoch) = ex_epoch + 1u;
         *p.ex.ticket = 0u;
       }
     }
@@ -1917,7 +1928,8 @@ template <int TYPE>
 int run_pass(int nj, const void *const *d_w, const float *d_x, const float *const *d_addend,
              int64_t addend_stride, float *const *d_y, const int *out_dims, int in_dim, int batch,
              int resident, const Params *top1, cudaStream_t s, const float *d_x_up,
-             const float *d_norm_w, float norm_eps, const Exchange *ex = nullptr, int ex_wait = 0) {
+             const float *d_norm_w, float norm_eps, const Exchange *ex = nullptr, int ex_wait = 0,
+             long long y_pitch = 0) {
   using C = Cfg<TYPE>;
   const int nbk = kernel_rows<TYPE>(batch);
   const bool thin = top1 != nullptr;
@@ -1944,6 +1956,7 @@ int run_pass(int nj, const void *const *d_w, const float *d_x, const float *cons
     p.ws_tickets = region.tickets;
     if (ex) p.ex = *ex;
     p.ex_wait = ex_wait;
+    p.y_pitch = y_pitch;
     p.row_bytes = (long long)nblk * C::BB;  // the pitch of the whole rows
     p.x = d_x + b0 * 256;
     p.x_up = d_x_up ? d_x_up + b0 * 256 : nullptr;
@@ -2001,7 +2014,7 @@ int gemv_typed(int njobs, const void *const *d_w, const float *d_x, const float 
                int64_t addend_stride, float *const *d_y, const int *out_dims, int in_dim, int batch,
                int resident, const Params *top1, cudaStream_t s, const float *d_x_up = nullptr,
                const float *d_norm_w = nullptr, float norm_eps = 0.f, const Exchange *ex = nullptr,
-               int ex_wait = 0) {
+               int ex_wait = 0, long long y_pitch = 0) {
 
   const int width = top1 ? top1_pass_width<TYPE>(in_dim, batch)
                          : (batch <= 2 ? batch : batch_pass_width<TYPE>(in_dim, batch));
@@ -2030,7 +2043,7 @@ int gemv_typed(int njobs, const void *const *d_w, const float *d_x, const float 
       const int st = run_pass<TYPE>(nj, d_w + j0, d_x + (long long)b0 * in_dim, d_addend ? add : nullptr,
                                     addend_stride, d_y ? ys : nullptr, out_dims + j0, in_dim, nbat, resident,
                                     top1 ? &t1 : nullptr, s, d_x_up ? d_x_up + (long long)b0 * in_dim : nullptr, d_norm_w,
-                                    norm_eps, ex, ex_wait);
+                                    norm_eps, ex, ex_wait, y_pitch);
       if (st) return st;
     }
   }
@@ -2085,23 +2098,19 @@ int launch_gemv_imma_many_exchange(int type, int njobs, const void *const *d_w, 
                                    const float *const *d_addend, int64_t addend_stride,
                                    float *const *d_y, const int *out_dims, int in_dim, int batch,
                                    int resident, const cogni_qmm_exchange *cex, int wait_previous,
-                                   cudaStream_t s) {
+                                   int64_t y_pitch, cudaStream_t s) {
   Exchange ex{};
   ex.world = cex->world;
   ex.rank = cex->rank;
-  for (int g = 0; g < cex->world && g < kMaxRanks; g++) {
-    ex.peer_delta[g] = cex->peer_offset[g];
-    ex.peer_flag[g] = cex->peer_flag[g];
-  }
-  ex.flags = cex->flags;
+  for (int g = 0; g < cex->world && g < kMaxRanks; g++) ex.peer_delta[g] = g == cex->rank ? 0 : cex->peer_offset[g];
   ex.epoch = cex->epoch;
   ex.ticket = cex->ticket;
   switch (type) {
-    case kQ4_K: return gemv_typed<kQ4_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, nullptr, 0.f, &ex, wait_previous);
-    case kQ5_K: return gemv_typed<kQ5_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, nullptr, 0.f, &ex, wait_previous);
-    case kQ8_0: return gemv_typed<kQ8_0>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, nullptr, 0.f, &ex, wait_previous);
-    case kIQ4_NL: return gemv_typed<kIQ4_NL>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, nullptr, 0.f, &ex, wait_previous);
-    case kQ6_K: return gemv_typed<kQ6_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, nullptr, 0.f, &ex, wait_previous);
+    case kQ4_K: return gemv_typed<kQ4_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, nullptr, 0.f, &ex, wait_previous, y_pitch);
+    case kQ5_K: return gemv_typed<kQ5_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, nullptr, 0.f, &ex, wait_previous, y_pitch);
+    case kQ8_0: return gemv_typed<kQ8_0>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, nullptr, 0.f, &ex, wait_previous, y_pitch);
+    case kIQ4_NL: return gemv_typed<kIQ4_NL>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, nullptr, 0.f, &ex, wait_previous, y_pitch);
+    case kQ6_K: return gemv_typed<kQ6_K>(njobs, d_w, d_x, d_addend, addend_stride, d_y, out_dims, in_dim, batch, resident, nullptr, s, nullptr, nullptr, 0.f, &ex, wait_previous, y_pitch);
     default: return COGNI_QMM_ERR_TYPE;
   }
 }
@@ -2200,6 +2209,32 @@ __global__ void expire_wait_kernel(unsigned long long limit_ns, int *gave_up) {
   }
 }
 }  // namespace
+
+namespace {
+__global__ void exchange_unpack_kernel(const uint2 *words, long long n, unsigned epoch, float *out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  uint2 w;
+  const unsigned long long t0 = global_ns();
+  for (unsigned spin = 0;; spin++) {
+    asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(words + i) : "memory");
+    if (w.y == epoch) break;
+    if ((spin & 255u) == 255u) {
+      if (pipe_broken()) break;
+      if (global_ns() - t0 > kPipeWaitLimitNs) {
+        atomicAdd(&g_pipe_wait_timeouts, 1u);
+        break;
+      }
+    }
+  }
+  out[i] = __uint_as_float(w.x);
+}
+}  // namespace
+
+int launch_exchange_unpack(const void *d_words, int64_t n, unsigned epoch, float *d_out, cudaStream_t s) {
+  exchange_unpack_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(static_cast<const uint2 *>(d_words), n, epoch, d_out);
+  return (int)cudaGetLastError();
+}
 
 int launch_expire_wait(unsigned limit_us, cudaStream_t s) {
   if (limit_us == 0 || limit_us > 100000) return COGNI_QMM_ERR_ARG;  // at most 0.1 s

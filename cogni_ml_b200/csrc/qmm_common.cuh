@@ -153,12 +153,13 @@ int launch_gemv_imma_many_exchange(int type, int njobs, const void *const *d_w, 
                                    const float *const *d_addend, int64_t addend_stride,
                                    float *const *d_y, const int *out_dims, int in_dim, int batch,
                                    int resident, const cogni_qmm_exchange *ex, int wait_previous,
-                                   cudaStream_t s);
+                                   int64_t y_pitch, cudaStream_t s);
 unsigned gemv_imma_timeouts();
 unsigned gemm_prefill_timeouts();
 int gemv_imma_reset_timeouts();   // also clears the K-slab tickets of every workspace region
 int gemm_prefill_reset_timeouts();
 int launch_expire_wait(unsigned limit_us, cudaStream_t s);
+int launch_exchange_unpack(const void *d_words, int64_t n, unsigned epoch, float *d_out, cudaStream_t s);
 void gemv_imma_set_debug(int mode);
 void gemv_imma_set_pair(int pair);
 void gemv_imma_set_min_splits(int n);

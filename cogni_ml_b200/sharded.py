@@ -142,13 +142,28 @@ class ShardedLmHead:
 # ----------------------------------------------------------------------------------------------
 # The exchange fused into the GEMV launch (cogni_qmm_gemv_many_exchange): peer-mapped buffers.
 
+def _make_exchange_struct():
+    import ctypes as C
+
+    class Exchange(C.Structure):   # struct cogni_qmm_exchange (include/cogni_qmm.h)
+        _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("peer_offset", C.c_int64 * 8),
+                    ("epoch", C.c_void_p), ("ticket", C.c_void_p)]
+    return Exchange
+
+
+_ExchangeStruct = _make_exchange_struct()
+
+
 class PeerExchange:
     """One arena per rank, laid out identically on every rank and mapped into every process of the
     box (torch symmetric memory: the same physical allocation of rank g appears at buffer_ptrs[g] in
-    every process, accessible from the local GPU): 256 bytes of state (the flag word of every rank,
-    this rank's epoch and ticket) followed by the gather buffers.  `buffer(name, shape)` hands out
-    the same region on every rank, so an address offset inside the local arena is the offset
-    inside every peer's."""
+    every process, accessible from the local GPU): 256 bytes of state (this rank's epoch and
+    ticket) followed by the gather buffers.  `buffer(name, batch, n)` hands out the same region on
+    every rank, so an address offset inside the local arena is the offset inside every peer's.
+
+    A gather buffer holds [batch][n] words of 8 bytes, (f32 value, u32 epoch): an exchanging launch
+    writes each output as one such word on every GPU, and its consumer polls the words it reads for
+    the epoch it expects (no fence, flag or barrier in between)."""
 
     STATE_BYTES = 256
 
@@ -186,50 +201,51 @@ class PeerExchange:
         base = ptrs[self.rank]
         for g in range(self.world):
             ex.peer_offset[g] = ptrs[g] - base
-            ex.peer_flag[g] = ptrs[g] + 4 * self.rank      # rank g's flags[self.rank]
-        ex.flags = base
         ex.epoch = base + 64
         ex.ticket = base + 68
         self.struct = ex
 
-    def buffer(self, name: str, shape, dtype=torch.float32) -> torch.Tensor:
-        """The region `name` of the local arena (allocated on first use; every rank must ask for the
-        same names, shapes and order)."""
+    def buffer(self, name: str, batch: int, n: int) -> torch.Tensor:
+        """The gather buffer `name` of the local arena as f32 [batch, n, 2]: [..., 0] the values,
+        [..., 1] the epoch bits (allocated on first use; every rank must ask for the same names,
+        shapes and order)."""
         if name not in self._named:
-            n = int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()
-            n = (n + 255) // 256 * 256
-            if self._cursor + n > self.arena.numel():
+            nbytes = (batch * n * 8 + 255) // 256 * 256
+            if self._cursor + nbytes > self.arena.numel():
                 raise ValueError("exchange arena too small")
-            self._named[name] = (self._cursor, tuple(shape), dtype)
-            self._cursor += n
-        off, shp, dt = self._named[name]
-        count = int(np.prod(shp))
-        return self.arena[off:off + count * torch.empty((), dtype=dt).element_size()].view(dt).view(*shp)
+            self._named[name] = (self._cursor, batch, n)
+            self._cursor += nbytes
+        off, b, nn = self._named[name]
+        return self.arena[off:off + b * nn * 8].view(torch.float32).view(b, nn, 2)
 
     def epoch(self) -> int:
         return int(self.arena[64:68].view(torch.int32).item())
 
-
-def _make_exchange_struct():
-    import ctypes as C
-
-    class Exchange(C.Structure):   # struct cogni_qmm_exchange (include/cogni_qmm.h)
-        _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("peer_offset", C.c_int64 * 8),
-                    ("peer_flag", C.c_void_p * 8), ("flags", C.c_void_p), ("epoch", C.c_void_p),
-                    ("ticket", C.c_void_p)]
-    return Exchange
-
-
-_ExchangeStruct = _make_exchange_struct()
+    def unpack(self, buf: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        """f32 [batch, n] values of a gather buffer written by the exchanging launch issued last on
+        this exchange, on the stream's order (the unpacking kernel waits for the words itself)."""
+        from ._lib import check, lib
+        from .quant_matmul import _stream_ptr
+        b, n, _ = buf.shape
+        if out is None:
+            out = torch.empty(b, n, dtype=torch.float32, device=buf.device)
+        # the epoch of the exchange before this point of the stream is only known on the device;
+        # read it in stream order
+        epoch = torch.empty(1, dtype=torch.int32, device=buf.device)
+        epoch.copy_(self.arena[64:68].view(torch.int32))
+        check(lib.cogni_qmm_exchange_unpack(buf.data_ptr(), b * n, int(epoch.item()) & 0xFFFFFFFF,
+                                            out.data_ptr(), _stream_ptr(stream)), "cogni_qmm_exchange_unpack")
+        return out
 
 
 class ExchangingGemv:
     """A prepared row-sharded qmatvec_many whose outputs reach every GPU inside the launch.
 
-    weights: this rank's row shards (DeviceQuantWeight) of matrices that share x; outs: for each,
-    a [world, batch, rows] region of the exchange arena (PeerExchange.buffer): the launch writes
-    slot `rank` locally and on every peer.  wait_previous: do not read x before the exchange that
-    precedes this launch on the arena has arrived from every rank."""
+    weights: this rank's row shards (DeviceQuantWeight) of matrices that share x; outs: for each, a
+    gather buffer (PeerExchange.buffer(name, batch, world * rows)): the launch writes this rank's
+    columns [rank * rows, (rank + 1) * rows) of every batch row, locally and on every peer.
+    x: plain f32 [batch, in_dim], or -- wait_previous -- the gather buffer [batch, in_dim, 2] that
+    the exchanging launch issued just before this one wrote."""
 
     def __init__(self, exchange: PeerExchange, weights, x: torch.Tensor, outs, wait_previous: bool):
         import ctypes as C
@@ -237,14 +253,18 @@ class ExchangingGemv:
         w0 = self.weights[0]
         if len({(w.type, w.in_dim) for w in self.weights}) != 1:
             raise ValueError("weights must share type and in_dim")
-        self.batch = x.numel() // w0.in_dim
+        if len({w.out_dim for w in self.weights}) != 1:
+            raise ValueError("the exchanged matrices of one launch must have equal row counts")
+        self.batch = x.numel() // (w0.in_dim * (2 if wait_previous else 1))
         n = len(self.weights)
-        for w, o in zip(self.weights, self.outs):
-            if tuple(o.shape) != (exchange.world, self.batch, w.out_dim) or not o.is_contiguous():
-                raise ValueError("each output must be a contiguous [world, batch, rows] arena region")
+        total = exchange.world * w0.out_dim
+        for o in self.outs:
+            if tuple(o.shape) != (self.batch, total, 2) or not o.is_contiguous():
+                raise ValueError("each output must be a gather buffer [batch, world * rows, 2]")
         self._w = (C.c_void_p * n)(*[w.raw.data_ptr() for w in self.weights])
-        self._y = (C.c_void_p * n)(*[o[exchange.rank].data_ptr() for o in self.outs])
+        self._y = (C.c_void_p * n)(*[o[0, exchange.rank * w0.out_dim].data_ptr() for o in self.outs])
         self._n = (C.c_int * n)(*[w.out_dim for w in self.weights])
+        self._pitch = total
         self._resident = int(all(w.resident for w in self.weights))
         self._wait = int(bool(wait_previous))
 
@@ -255,7 +275,8 @@ class ExchangingGemv:
         from .quant_matmul import _stream_ptr
         w0 = self.weights[0]
         check(lib.cogni_qmm_gemv_many_exchange(w0.type, len(self.weights), self._w, self.x.data_ptr(),
-                                               None, 0, self._y, self._n, w0.in_dim, self.batch,
-                                               self._resident, C.byref(self.ex.struct), self._wait,
-                                               _stream_ptr(stream)), "cogni_qmm_gemv_many_exchange")
+                                               None, 0, self._y, self._pitch, self._n, w0.in_dim,
+                                               self.batch, self._resident, C.byref(self.ex.struct),
+                                               self._wait, _stream_ptr(stream)),
+              "cogni_qmm_gemv_many_exchange")
         return self.outs

@@ -235,41 +235,45 @@ int cogni_qmm_gemv_many(int type, int n_weights, const void *const *d_w, const f
  * suggests: output rows are independent and stored back to back, src/ml/gguf/qwen35_weights.cr:209-212.)
  *
  * Every rank holds the rows [rank * N / G, (rank + 1) * N / G) of each matrix and a gather buffer
- * laid out identically on all ranks; d_y[j] points INTO this rank's buffer, at the place of this
- * rank's shard.  The kernel stores every output value there and, with ordinary stores over NVLink,
- * at the same place of every peer's buffer (peer-mapped: cuIpcOpenMemHandle / cuMemMap by the
- * host); when the last CTA has finished it raises this rank's flag on every GPU.  A later launch
- * that reads the gathered buffer passes wait_previous = 1 and does not touch its activations
- * before every rank's flag has arrived.  No NCCL call, no extra launch, no multicast load.
+ * laid out identically on all ranks: [batch][N] WORDS of 8 bytes, (f32 value, u32 epoch).  d_y[j]
+ * points INTO this rank's buffer at the word of its first row (column rank * N / G of batch row 0),
+ * y_pitch = N.  The kernel writes every output value as one 8-byte store (value, epoch) there and,
+ * with ordinary stores over NVLink, at the same place of every peer's buffer (peer-mapped memory:
+ * cuIpcOpenMemHandle / cuMemMap by the host).  Value and epoch arrive together, so there is no
+ * fence, no flag and no barrier: a later launch whose activations are such a buffer passes
+ * wait_previous = 1 and polls every word it reads until it carries the epoch of the exchange
+ * before it (a bounded wait, cogni_qmm_wait_timeouts).  No NCCL call, no extra launch, no
+ * multicast load.
  *
  *   world, rank     ranks of the box (world <= 8) and this one
  *   peer_offset[g]  BYTES from an address in this rank's gather buffer to the same place in rank
  *                   g's buffer as mapped into this process (entry [rank] is ignored)
- *   peer_flag[g]    rank g's flag word FOR this rank (&flags_of_g[rank], as mapped here); entry
- *                   [rank] is this rank's own &flags[rank]
- *   flags           this rank's `world` flag words (device memory the peers write)
- *   epoch, ticket   two device words of this rank, zero-initialised together with the flags
- * All ranks must issue the same sequence of exchanging launches on one buffer set; a buffer may
- * be reused by the launch after next (two buffers alternating are enough for a chain in which
- * every launch waits for the exchange before it).  The wait is bounded like every device-side
- * wait of this library (cogni_qmm_wait_timeouts).  Shapes the tiled kernel does not take in one
- * launch (batch > 8, in_dim not a multiple of 256, ...) return COGNI_QMM_ERR_LIMIT: run
- * cogni_qmm_gemv_many and an all-gather instead.
+ *   epoch, ticket   two device words of this rank, zero-initialised before the first exchange:
+ *                   the count of exchanges this rank has completed, and the arrivals of the
+ *                   running launch
+ * All ranks must issue the same sequence of exchanging launches on one exchange (epoch / ticket
+ * pair).  wait_previous = 1 means: d_x is the gather buffer written by the exchanging launch
+ * issued immediately before this one on the same exchange (in_dim = its N).  A buffer may be
+ * rewritten by the launch after next: two buffers alternating are enough for a chain.  Shapes the
+ * tiled kernel does not take in one launch (batch > 8, in_dim not a multiple of 256, ...) return
+ * COGNI_QMM_ERR_LIMIT: run cogni_qmm_gemv_many and an all-gather instead.
+ * cogni_qmm_exchange_unpack strips the epochs for a reader that is not a GEMV of this library:
+ * out[i] = value of word i, after waiting (bounded) until the word carries `epoch`.
  */
 typedef struct cogni_qmm_exchange {
   int32_t world, rank;
   int64_t peer_offset[8];
-  uint32_t *peer_flag[8];
-  const uint32_t *flags;
   uint32_t *epoch;
   uint32_t *ticket;
 } cogni_qmm_exchange;
 
 int cogni_qmm_gemv_many_exchange(int type, int n_weights, const void *const *d_w, const float *d_x,
                                  const float *const *d_addend, int64_t addend_stride,
-                                 float *const *d_y, const int *out_dims, int in_dim, int batch,
-                                 int resident, const cogni_qmm_exchange *exchange, int wait_previous,
-                                 void *stream);
+                                 float *const *d_y, int64_t y_pitch, const int *out_dims, int in_dim,
+                                 int batch, int resident, const cogni_qmm_exchange *exchange,
+                                 int wait_previous, void *stream);
+int cogni_qmm_exchange_unpack(const void *d_words, int64_t n, uint32_t epoch, float *d_out,
+                              void *stream);
 
 /*
  * The same two sharded operations with NCCL as the exchange step, on a communicator the host owns

@@ -51,9 +51,10 @@ def _worker(rank, world, port):
 
 
 def _exchange_worker(rank, world, port):
-    """The exchange fused into the GEMV launch: launch A leaves y1 = W1 x on every GPU (peer
-    stores + flags), launch B waits for that exchange and computes W2 y1 from the gathered buffer,
-    again exchanging; repeated so that flags, epochs and the two buffers are reused many times."""
+    """The exchange fused into the GEMV launch: launch A leaves y1 = W1 x on every GPU as
+    (value, epoch) words (8-byte peer stores), launch B computes W2 y1 straight from those words,
+    polling each for A's epoch, and exchanges again; repeated so that epochs and buffers are reused
+    many times.  Then two matrices at batch 4 in one launch."""
     import torch.distributed as dist
 
     from cogni_ml_b200 import DeviceQuantWeight, QuantWeight, lib, synth
@@ -70,47 +71,59 @@ def _exchange_worker(rank, world, port):
         raw2 = synth.make_weight(synth.Q6_K, n2, n1, seed=27, tensor_id=2)
         x = synth.make_activation(1, k1, seed=27)
         zero = lambda n: np.zeros(n, np.float32)
-        y1_ref = loader.matmul_add(x, 1, k1, raw1, synth.Q4_K, n1, zero(n1))
-        y2_ref = loader.matmul_add(y1_ref, 1, n1, raw2, synth.Q6_K, n2, zero(n2))
+        # the chain y1 = W1 x, y2 = W2 y1, y1' = W1 y2, ... : every launch reads the gathered words of
+        # the launch before it, so no rank can run ahead of a reader; six GEMVs keep the values
+        # (which grow by two orders of magnitude per step) inside the f32 range
+        steps = 3
+        ref, refs = x, []
+        for it in range(steps):
+            y1_ref = loader.matmul_add(ref, 1, k1, raw1, synth.Q4_K, n1, zero(n1))
+            y2_ref = loader.matmul_add(y1_ref, 1, n1, raw2, synth.Q6_K, n2, zero(n2))
+            ref = y2_ref
         ex = PeerExchange(1 << 20, dev)
         r0, r1 = shard_rows(n1, rank, world)
         w1 = DeviceQuantWeight.upload(QuantWeight(raw1, synth.Q4_K, n1, k1), dev, r0, r1)
         r0, r1 = shard_rows(n2, rank, world)
         w2 = DeviceQuantWeight.upload(QuantWeight(raw2, synth.Q6_K, n2, n1), dev, r0, r1)
-        buf1 = ex.buffer("y1", (world, 1, n1 // world))
-        buf2 = ex.buffer("y2", (world, 1, n2 // world))
+        buf1 = ex.buffer("y1", 1, n1)
+        buf2 = ex.buffer("y2", 1, n2)
         xd = torch.from_numpy(x).to(dev)
         first = ExchangingGemv(ex, [w1], xd, [buf1], wait_previous=False)
-        a = ExchangingGemv(ex, [w1], xd, [buf1], wait_previous=True)
-        b = ExchangingGemv(ex, [w2], buf1.view(1, n1), [buf2], wait_previous=True)
-        tail = torch.zeros(1, device=dev)
-        for it in range(40):
-            (first if it == 0 else a).run()
-            b.run()
-        # a last launch that only waits for b's exchange, so that buf2 is complete when it is read
-        probe = ExchangingGemv(ex, [w1], xd, [ex.buffer("y3", (world, 1, n1 // world))], wait_previous=True)
-        probe.run()
-        torch.cuda.synchronize()
-        assert ex.epoch() == 81
-        y1 = buf1.cpu().numpy().reshape(-1)
-        y2 = buf2.cpu().numpy().reshape(-1)
-        assert np.abs(y1 - y1_ref).max() <= 1e-3 * np.abs(y1_ref).max()
-        assert np.abs(y2 - y2_ref).max() <= 2e-3 * np.abs(y2_ref).max()   # two chained GEMVs
+        a = ExchangingGemv(ex, [w1], buf2, [buf1], wait_previous=True)     # k1 == n2
+        b = ExchangingGemv(ex, [w2], buf1, [buf2], wait_previous=True)
+        for rounds in range(12):         # the same three-step chain again and again: epochs 1 .. 72
+            for it in range(steps):
+                (first if it == 0 else a).run()
+                b.run()
+            y2 = ex.unpack(buf2).cpu().numpy().reshape(-1)   # waits for the words of the last exchange
+            torch.cuda.synchronize()
+            dist.barrier()                                    # every rank's launches have completed
+            assert np.abs(y2 - y2_ref).max() <= 5e-3 * np.abs(y2_ref).max(), rounds   # six chained GEMVs
+        assert ex.epoch() == 72
+        y1 = buf1[..., 0].cpu().numpy().reshape(-1)
+        assert np.abs(y1 - y1_ref).max() <= 5e-3 * np.abs(y1_ref).max()
         assert lib.cogni_qmm_wait_timeouts() == 0
-        # batch 4, two matrices in one launch (ffn_gate + ffn_up shape of use)
+        # batch 4, two matrices in one launch (the ffn_gate + ffn_up way of use), then a consumer
+        # of batch 4 reading the gathered words
         xb = synth.make_activation(4, k1, seed=28)
         rawu = synth.make_weight(synth.Q4_K, n1, k1, seed=28, tensor_id=3)
         r0, r1 = shard_rows(n1, rank, world)
         wu = DeviceQuantWeight.upload(QuantWeight(rawu, synth.Q4_K, n1, k1), dev, r0, r1)
-        g_buf = ex.buffer("g4", (world, 4, n1 // world))
-        u_buf = ex.buffer("u4", (world, 4, n1 // world))
-        ExchangingGemv(ex, [w1, wu], torch.from_numpy(xb).to(dev), [g_buf, u_buf], wait_previous=True).run()
-        probe.run()
+        g_buf = ex.buffer("g4", 4, n1)
+        u_buf = ex.buffer("u4", 4, n1)
+        d_buf = ex.buffer("d4", 4, n2)
+        ExchangingGemv(ex, [w1, wu], torch.from_numpy(xb).to(dev), [g_buf, u_buf], wait_previous=False).run()
+        ExchangingGemv(ex, [w2], g_buf, [d_buf], wait_previous=True).run()
+        d4 = ex.unpack(d_buf).cpu().numpy()
         torch.cuda.synchronize()
-        for raw, buf in ((raw1, g_buf), (rawu, u_buf)):
-            ref = loader.matmul_add(xb, 4, k1, raw, synth.Q4_K, n1, zero(n1)).reshape(4, n1)
-            got = buf.permute(1, 0, 2).reshape(4, n1).cpu().numpy()
+        dist.barrier()
+        g_ref = loader.matmul_add(xb, 4, k1, raw1, synth.Q4_K, n1, zero(n1)).reshape(4, n1)
+        u_ref = loader.matmul_add(xb, 4, k1, rawu, synth.Q4_K, n1, zero(n1)).reshape(4, n1)
+        for ref, buf in ((g_ref, g_buf), (u_ref, u_buf)):
+            got = buf[..., 0].cpu().numpy()
             assert np.abs(got - ref).max() <= 1e-3 * np.abs(ref).max()
+        d_ref = loader.matmul_add(g_ref, 4, n1, raw2, synth.Q6_K, n2, zero(n2)).reshape(4, n2)
+        assert np.abs(d4 - d_ref).max() <= 2e-3 * np.abs(d_ref).max()
         assert lib.cogni_qmm_wait_timeouts() == 0
         dist.barrier()
     finally:
