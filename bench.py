@@ -237,10 +237,17 @@ def timed(fn, reps, warm=3):
     return e0.elapsed_time(e1) / reps
 
 
+_side_stream = None
+
+
 def graphed(fn):
-    """fn captured into a CUDA graph (after one eager run on a side stream)."""
+    """fn captured into a CUDA graph (after one eager run on a side stream; one side stream for
+    the whole run: the engine keeps a workspace region per stream it has seen)."""
     import torch
-    side = torch.cuda.Stream()
+    global _side_stream
+    if _side_stream is None:
+        _side_stream = torch.cuda.Stream()
+    side = _side_stream
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
         fn()
@@ -1013,6 +1020,44 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_probe(args):
+    """--probe type,out_dim,in_dim,batch[;...]: one GEMV shape at a time on one GPU, weights rotated
+    through copies > L2; prints one key=value line per shape (the profiling summaries under
+    profiles/ name this command).  With --no-graph the launches are eager, so that a profiler sees
+    them one by one."""
+    import torch
+
+    from cogni_ml_b200 import lib, synth
+    dev = torch.device("cuda", 0)
+    peaks, _ = measured_peaks()
+    if args.kernel_choice:
+        lib.cogni_qmm_set_kernel_choice(args.kernel_choice)
+    out = []
+    for spec in args.probe.split(";"):
+        qtype, out_dim, in_dim, batch = (int(v) for v in spec.split(","))
+        raw = synth.make_weight(qtype, out_dim, in_dim, seed=1, tensor_id=qtype)
+        ring = weight_ring(raw, qtype, out_dim, in_dim, dev)
+        x = torch.from_numpy(synth.make_activation(batch, in_dim, seed=1)).to(dev)
+        if args.no_graph:
+            y = torch.empty(batch, out_dim, dtype=torch.float32, device=dev)
+
+            def go():
+                for w in ring:
+                    w.gemv(x, out=y)
+            us = timed(go, 3) * 1e3 / len(ring)
+        else:
+            us = gemv_us(ring, x, batch)
+        alg = algorithmic_bytes(raw.nbytes, in_dim, out_dim, batch)
+        row = {"type": TYPE_NAME[qtype], "out_dim": out_dim, "in_dim": in_dim, "batch": batch,
+               "cuda_us": us, "weight_gbs": raw.nbytes / us / 1e3,
+               "hbm_frac_measured": alg / us / 1e3 / peaks["hbm_gbs"], "copies": len(ring)}
+        out.append(row)
+        log(" ".join(f"{k}={v:.3f}" if isinstance(v, float) else f"{k}={v}" for k, v in row.items()))
+        del ring
+        torch.cuda.empty_cache()
+    print(json.dumps({"probe": out, "wait_timeouts": lib.cogni_qmm_wait_timeouts()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1033,8 +1078,11 @@ def main():
     ap.add_argument("--separate", action="store_true",
                     help="launch ffn_gate and ffn_up separately instead of one qmatvec_many launch")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of graph replay")
+    ap.add_argument("--probe", default="", help="type,out_dim,in_dim,batch[;...]: time single GEMV shapes instead of the step")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.probe:
+        run_probe(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

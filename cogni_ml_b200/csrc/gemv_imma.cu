@@ -916,7 +916,7 @@ __device__ __forceinline__ void mma_dense(const uint8_t *blk, int pad_a, int pad
       const uint32_t hi = __byte_perm(0x26190D01u, 0x71594535u, s7);   // entries 8 .. 15
       return __byte_perm(lo, hi, 0x3210u | ((h >> 1) & 0x4444u));
     };
-#pragma unroll
+#pragma unroll 1  // rolled: the unrolled body of eight groups x two sets overflowed the instruction cache
     for (int g4 = 0; g4 < 4; g4++) {
       const float2 sa = *reinterpret_cast<const float2 *>(rowa + 2 * g4);
       const float2 sb = *reinterpret_cast<const float2 *>(rowb + 2 * g4);
@@ -935,7 +935,7 @@ __device__ __forceinline__ void mma_dense(const uint8_t *blk, int pad_a, int pad
       w0 = __funnelshift_r(a, b, 16);
       w1 = __funnelshift_r(b, c, 16);
     };
-#pragma unroll
+#pragma unroll 1  // rolled: the unrolled body of eight groups x two sets overflowed the instruction cache
     for (int g4 = 0; g4 < 4; g4++) {
       const float2 sa = *reinterpret_cast<const float2 *>(rowa + 2 * g4);
       const float2 sb = *reinterpret_cast<const float2 *>(rowb + 2 * g4);
@@ -958,7 +958,7 @@ __device__ __forceinline__ void mma_dense(const uint8_t *blk, int pad_a, int pad
       qha = *reinterpret_cast<const uint2 *>(ra + 16);
       qhb = *reinterpret_cast<const uint2 *>(rb + 16);
     }
-#pragma unroll
+#pragma unroll 1  // rolled: the unrolled body of eight groups x two sets overflowed the instruction cache
     for (int g4 = 0; g4 < 4; g4++) {
       const float2 sa = *reinterpret_cast<const float2 *>(rowa + 2 * g4);
       const float2 sb = *reinterpret_cast<const float2 *>(rowb + 2 * g4);
@@ -1841,9 +1841,9 @@ int top1_pass_width(int in_dim, int batch) {
 // The workspace is a fixed device array (nothing is ever allocated): kWsSlots regions, one per
 // stream that has used the engine, so that launches which may overlap on the device (different
 // streams) never share a region; launches of one stream are ordered by the stream (a dependent
-// launch touches the workspace only after its predecessor has completed).  A ninth stream, or
+// launch touches the workspace only after its predecessor has completed).  A seventeenth stream, or
 // a shape whose partial sums do not fit a region, runs without slabs.
-constexpr int kWsSlots = 8;
+constexpr int kWsSlots = 16;
 constexpr int kWsFloats = 1 << 19;  // 2 MB of partial sums per region
 constexpr int kWsTickets = 4096;    // tiles per launch that can be split
 static __device__ __align__(256) float g_slab_ws[kWsSlots][kWsFloats];
