@@ -138,9 +138,12 @@ struct XSrc {
   int ll;
   unsigned epoch;
 };
-// Four consecutive activations from element `off` on.
+// Four consecutive activations from element `off` on.  LL is a template parameter so that the
+// plain path stays a bare load: a run-time branch in front of every load would keep the compiler
+// from issuing a lane's loads together (measured: +2 us per launch).
+template <bool LL>
 __device__ __forceinline__ float4 ld4x(const float *x, long long off, const XSrc &src) {
-  if (!src.ll) return __ldg(reinterpret_cast<const float4 *>(x + off));
+  if constexpr (!LL) return __ldg(reinterpret_cast<const float4 *>(x + off));
   const uint2 *w = reinterpret_cast<const uint2 *>(x) + off;  // 16-byte aligned: off is a multiple of 4
   uint4 a, b;
   const unsigned long long t0 = global_ns();
@@ -625,7 +628,7 @@ __device__ __forceinline__ void mma_block(const uint8_t *blk, int pad_a, int pad
 // n = rint(x / sx) = 128*hi + lo with hi = n >> 7 in [-127, 127] and lo = n & 127.  One warp,
 // lane = 8 consecutive elements.  The superblocks' areas are zeroed first: their unused words are
 // the structural zeros of the layout.  All loads are issued before the first use.
-template <int TYPE, int NB, int NBLK>
+template <int TYPE, int NB, int NBLK, bool LL>
 __device__ __forceinline__ void quantise_superblocks(const float *x, const float *x_up,
                                                      const float *norm_w, const float *inv_rms,
                                                      int K, int kblk, int lane, uint8_t *xq,
@@ -644,11 +647,11 @@ __device__ __forceinline__ void quantise_superblocks(const float *x, const float
 #pragma unroll
     for (int b = 0; b < NB; b++) {
       const long long off = (long long)b * K + (kblk + q) * 256 + e_in;
-      v0[q][b] = ld4x(x, off, src);
-      v1[q][b] = ld4x(x, off + 4, src);
+      v0[q][b] = ld4x<LL>(x, off, src);
+      v1[q][b] = ld4x<LL>(x, off + 4, src);
       if (x_up) {  // SwiGLU: silu(gate) * up in f32, silu(v) = v / (1 + exp(-v)) (qwen35_cpu.cr:512-519, 1716-1717)
-        const float4 u0 = ld4x(x_up, off, src);
-        const float4 u1 = ld4x(x_up, off + 4, src);
+        const float4 u0 = ld4x<LL>(x_up, off, src);
+        const float4 u1 = ld4x<LL>(x_up, off + 4, src);
         auto sw = [](float gte, float up) { return gte / (1.f + expf(-gte)) * up; };
         v0[q][b] = make_float4(sw(v0[q][b].x, u0.x), sw(v0[q][b].y, u0.y), sw(v0[q][b].z, u0.z), sw(v0[q][b].w, u0.w));
         v1[q][b] = make_float4(sw(v1[q][b].x, u1.x), sw(v1[q][b].y, u1.y), sw(v1[q][b].z, u1.z), sw(v1[q][b].w, u1.w));
@@ -735,7 +738,7 @@ __host__ __device__ constexpr int dense_area_row(int ng, int nb) {
 
 // Quantises superblock kblk of x for NB batch rows (rows beyond `batch` repeat the last one) into
 // the dense fragment order: byte offset ((group * J + set) * 32 + column * 4 + t) * W.
-template <int TYPE, int NB>
+template <int TYPE, int NB, bool LL>
 __device__ __forceinline__ void quantise_dense(const float *x, const float *x_up,
                                                const float *norm_w, const float *inv_rms, int K,
                                                int batch, int kblk, int lane, uint8_t *xq,
@@ -759,11 +762,11 @@ __device__ __forceinline__ void quantise_dense(const float *x, const float *x_up
     for (int i = 0; i < 4; i++) {
       const int br = min(b4 + i, batch - 1);
       const long long off = (long long)br * K + k;
-      v0[i] = ld4x(x, off, src);
-      v1[i] = ld4x(x, off + 4, src);
+      v0[i] = ld4x<LL>(x, off, src);
+      v1[i] = ld4x<LL>(x, off + 4, src);
       if (x_up) {  // SwiGLU: silu(gate) * up in f32, silu(v) = v / (1 + exp(-v)) (qwen35_cpu.cr:512-519, 1716-1717)
-        const float4 u0 = ld4x(x_up, off, src);
-        const float4 u1 = ld4x(x_up, off + 4, src);
+        const float4 u0 = ld4x<LL>(x_up, off, src);
+        const float4 u1 = ld4x<LL>(x_up, off + 4, src);
         auto sw = [](float gte, float up) { return gte / (1.f + expf(-gte)) * up; };
         v0[i] = make_float4(sw(v0[i].x, u0.x), sw(v0[i].y, u0.y), sw(v0[i].z, u0.z), sw(v0[i].w, u0.w));
         v1[i] = make_float4(sw(v1[i].x, u1.x), sw(v1[i].y, u1.y), sw(v1[i].z, u1.z), sw(v1[i].w, u1.w));
@@ -1052,7 +1055,7 @@ __device__ __forceinline__ void mma_dense(const uint8_t *blk, int pad_a, int pad
 //
 // Quantises NBLK superblocks of x from kblk on.  Lane = 8 consecutive elements:
 // element 128 n + 32 k + 16 h + i  ->  unit u = 2 n + h, column 2 k + plane, MMA lane t = i / 4.
-template <int NB, int NBLK>
+template <int NB, int NBLK, bool LL>
 __device__ __forceinline__ void quantise_q6v2(const float *x, const float *x_up, const float *norm_w,
                                               const float *inv_rms, int K, int kblk, int lane,
                                               uint8_t *xq, float *SXB, int *NG, const XSrc &src) {
@@ -1063,11 +1066,11 @@ __device__ __forceinline__ void quantise_q6v2(const float *x, const float *x_up,
 #pragma unroll
     for (int b = 0; b < NB; b++) {
       const long long off = (long long)b * K + (kblk + q) * 256 + e_in;
-      v0[q][b] = ld4x(x, off, src);
-      v1[q][b] = ld4x(x, off + 4, src);
+      v0[q][b] = ld4x<LL>(x, off, src);
+      v1[q][b] = ld4x<LL>(x, off + 4, src);
       if (x_up) {  // SwiGLU: silu(gate) * up in f32 (qwen35_cpu.cr:512-519, 1716-1717)
-        const float4 u0 = ld4x(x_up, off, src);
-        const float4 u1 = ld4x(x_up, off + 4, src);
+        const float4 u0 = ld4x<LL>(x_up, off, src);
+        const float4 u1 = ld4x<LL>(x_up, off + 4, src);
         auto sw = [](float gte, float up) { return gte / (1.f + expf(-gte)) * up; };
         v0[q][b] = make_float4(sw(v0[q][b].x, u0.x), sw(v0[q][b].y, u0.y), sw(v0[q][b].z, u0.z), sw(v0[q][b].w, u0.w));
         v1[q][b] = make_float4(sw(v1[q][b].x, u1.x), sw(v1[q][b].y, u1.y), sw(v1[q][b].z, u1.z), sw(v1[q][b].w, u1.w));
@@ -1321,7 +1324,20 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
   // exchanges completed on this GPU before this launch: the epoch its inputs carry (if they come
   // out of an exchange) and, plus one, the epoch its outputs get
   unsigned ex_epoch = 0;
-  if (XT && p.ex.epoch) ex_epoch = *reinterpret_cast<volatile const unsigned *>(p.ex.epoch);
+  if (XT && p.ex.epoch) {
+    // (acquire: the ticket below must not be drawn before this load has been performed)
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(ex_epoch) : "l"(p.ex.epoch) : "memory");
+    // The exchange is counted by the CTA that draws the last ticket: by then every CTA of this
+    // launch has read the epoch, and the next launch reads it only after this grid has completed.
+    // Drawn here, at the start, the atomic's round trip hides behind the launch's work.
+    if (p.ex.world > 1 && ctid == 0) {
+      const unsigned ticket = atomicAdd(p.ex.ticket, 1u);
+      if (ticket == gridDim.x - 1u) {
+        *p.ex.ticket = 0u;
+        *reinterpret_cast<volatile unsigned *>(p.ex.epoch) = ex_epoch + 1u;
+      }
+    }
+  }
   const XSrc xsrc{XT ? p.ex_wait : 0, ex_epoch};
 
   // RMSNorm prologue: 1 / sqrt(mean(x^2) + eps) per batch row, the sum of squares in f64 as the
@@ -1338,7 +1354,8 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
       const int br = DENSE ? min(b, p.batch - 1) : b;
       double ss = 0.0;
       for (int k = ctid * 4; k < p.norm_dim; k += kNW * 32 * 4) {
-        const float4 v = ld4x(p.norm_x, (long long)br * K + k, xsrc);
+        const float4 v = XT && xsrc.ll ? ld4x<true>(p.norm_x, (long long)br * K + k, xsrc)
+                                       : ld4x<false>(p.norm_x, (long long)br * K + k, xsrc);
         ss += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
       }
 #pragma unroll
@@ -1405,12 +1422,24 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
       // The activations are quantised on the way: the warp that takes a superblock pair of the
       // CTA's first tile does x's two superblocks first; later tiles find them done.
       if (li == 0) {
-        if constexpr (V2) {
-          if (PAIR == 2 && n2 == 2) quantise_q6v2<NB, 2>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, reinterpret_cast<int *>(XX), xsrc);
-          else quantise_q6v2<NB, 1>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, reinterpret_cast<int *>(XX), xsrc);
-        } else if constexpr (DENSE) quantise_dense<TYPE, NB>(xs, xs_up, norm_ws, s_inv_rms, K, p.batch, e0, lane, xq, SX, XX, xsrc);
-        else if (PAIR == 2 && n2 == 2) quantise_superblocks<TYPE, NB, 2>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, XX, xsrc);
-        else quantise_superblocks<TYPE, NB, 1>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, XX, xsrc);
+        auto quantise = [&](auto ll_tag) {
+          constexpr bool LL = decltype(ll_tag)::value;
+          if constexpr (V2) {
+            if (PAIR == 2 && n2 == 2) quantise_q6v2<NB, 2, LL>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, reinterpret_cast<int *>(XX), xsrc);
+            else quantise_q6v2<NB, 1, LL>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, reinterpret_cast<int *>(XX), xsrc);
+          } else if constexpr (DENSE) {
+            quantise_dense<TYPE, NB, LL>(xs, xs_up, norm_ws, s_inv_rms, K, p.batch, e0, lane, xq, SX, XX, xsrc);
+          } else {
+            if (PAIR == 2 && n2 == 2) quantise_superblocks<TYPE, NB, 2, LL>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, XX, xsrc);
+            else quantise_superblocks<TYPE, NB, 1, LL>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, XX, xsrc);
+          }
+        };
+        if constexpr (XT) {
+          if (xsrc.ll) quantise(std::true_type{});
+          else quantise(std::false_type{});
+        } else {
+          quantise(std::false_type{});
+        }
         __syncwarp();
         if (lane == 0) st_release_shared(&xready[e], 1);
       } else {
@@ -1616,18 +1645,6 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
     }
   }
 
-  if (XT && p.ex.world > 1) {
-    // the last CTA of the launch counts the exchange (the next launch on this GPU reads the word
-    // after this grid has completed: no fence is needed for it)
-    consumer_sync<kNW>();
-    if (ctid == 0) {
-      const unsigned ticket = atomicAdd(p.ex.ticket, 1u);
-      if (ticket == gridDim.x - 1u) {
-        *reinterpret_cast<volatile unsigned *>(p.ex.epoch) = ex_epoch + 1u;
-        *p.ex.ticket = 0u;
-      }
-    }
-  }
   if (p.part_keys == nullptr) return;
 
   // ------------------------------------------------------------ fused top-1 epilogue
