@@ -1211,11 +1211,13 @@ __device__ __forceinline__ void mma_q6v2(const uint8_t *ra, const uint8_t *rb, c
 }
 
 // ---------------------------------------------------------------------------- the kernel
-// XT: the instance that can split row tiles over K slabs and exchange its outputs with the other
-// GPUs; the plain instance carries none of that code.
-template <int TYPE, int NB, int PAIR, bool XT>
+// VAR picks how much the instance carries: 0 the plain GEMV; 1 adds the fused prologues (RMSNorm,
+// SwiGLU) to the activation quantisers; 2 also splits row tiles over K slabs and exchanges its
+// outputs with the other GPUs.  The plain instance carries none of that code.
+template <int TYPE, int NB, int PAIR, int VAR>
 __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1)
     gemv_imma_kernel(const Params p) {
+  constexpr bool XT = VAR == 2, PRO = VAR >= 1;
   constexpr int kNW = consumer_warps(TYPE, PAIR, NB), kThreads = (kNW + kPW) * 32;
   using C = Cfg<TYPE>;
   using A = Area<TYPE>;
@@ -1316,8 +1318,8 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
   const int K = p.x_pitch;  // the quantisers only use it as the pitch of the batch rows
   const int slab_el = slab * p.nblk * 256;  // the slab's first element of a row of x
   const float *xs = p.x + slab_el;
-  const float *xs_up = p.x_up ? p.x_up + slab_el : nullptr;
-  const float *norm_ws = p.norm_w ? p.norm_w + slab_el : nullptr;
+  const float *xs_up = PRO && p.x_up ? p.x_up + slab_el : nullptr;
+  const float *norm_ws = PRO && p.norm_w ? p.norm_w + slab_el : nullptr;
 
   asm volatile("bar.sync 3, %0;" ::"n"(kThreads) : "memory");  // mbarriers and counters ready
   pdl_wait_prior_grid();  // x (and y / the addend) may be produced by the preceding kernel
@@ -1345,7 +1347,7 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
   // every warp (and every CTA) arrives at the same value.
   __shared__ double s_ss2[24 * 2];
   __shared__ float s_inv_rms[DENSE ? NB : 2];
-  if (p.norm_w) {
+  if (PRO && p.norm_w) {
     // batches above 2 borrow the (still unused) partial-sum buffer for the warps' sums
     constexpr int NBS = DENSE ? NB : 2;
     double *s_ss = DENSE ? reinterpret_cast<double *>(smem + p.off_red) : s_ss2;
@@ -1766,13 +1768,13 @@ bool make_plan(int in_dim, int nb, Params &p, size_t &smem, bool thin = false) {
   return make_plan_pair<TYPE>(in_dim, nb, 1, p, smem);
 }
 
-template <int TYPE, int NB, int PAIR, bool XT>
+template <int TYPE, int NB, int PAIR, int VAR>
 int launch_instance_x(const Params &p, size_t smem, int grid, cudaStream_t s) {
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_imma_kernel<TYPE, NB, PAIR, XT>,
+    cudaError_t e = cudaFuncSetAttribute(gemv_imma_kernel<TYPE, NB, PAIR, VAR>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)kDynSmemMax);
     if (e != cudaSuccess) return (int)e;
@@ -1788,12 +1790,13 @@ int launch_instance_x(const Params &p, size_t smem, int grid, cudaStream_t s) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return (int)cudaLaunchKernelEx(&cfg, gemv_imma_kernel<TYPE, NB, PAIR, XT>, p);
+  return (int)cudaLaunchKernelEx(&cfg, gemv_imma_kernel<TYPE, NB, PAIR, VAR>, p);
 }
 template <int TYPE, int NB, int PAIR>
 int launch_instance(const Params &p, size_t smem, int grid, cudaStream_t s) {
-  if (p.nslabs > 1 || p.ex.world > 1 || p.ex_wait) return launch_instance_x<TYPE, NB, PAIR, true>(p, smem, grid, s);
-  return launch_instance_x<TYPE, NB, PAIR, false>(p, smem, grid, s);
+  if (p.nslabs > 1 || p.ex.world > 1 || p.ex_wait) return launch_instance_x<TYPE, NB, PAIR, 2>(p, smem, grid, s);
+  if (p.x_up || p.norm_w) return launch_instance_x<TYPE, NB, PAIR, 1>(p, smem, grid, s);
+  return launch_instance_x<TYPE, NB, PAIR, 0>(p, smem, grid, s);
 }
 
 // Batch rows of the kernel instance that takes `batch` (<= 8) rows: 1, 2, 4 or 8; IQ4_NL has only
