@@ -890,12 +890,14 @@ int launch_typed(const void *d_w, const void *d_x, void *d_y, int out_type, int 
   // Q4_K 34 / 42 / 73, Q5_K 36 / 44 / 73, IQ4_NL 43 / 48 / 73, Q6_K 54 / 60 / 75, Q8_0 54 / 66 / 85
   // (at 512 tokens the tensor pipe is what bounds every type).  Pick the width with the least
   // waves x tile time.
-  static int sms = 0;
+  static int sms_of[64] = {0};  // per device: a process may drive GPUs of different sizes
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int sms = dev >= 0 && dev < 64 ? sms_of[dev] : 0;
   if (!sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms <= 0) sms = 148;
+    if (dev >= 0 && dev < 64) sms_of[dev] = sms;
   }
   const long long row_tiles = (n_out + kBM - 1) / kBM;
   const double rel256 = TYPE == kQ4_K || TYPE == kQ5_K || TYPE == kQ8_0 ? 1.22 : 1.12;

@@ -738,7 +738,9 @@ __host__ __device__ constexpr int dense_area_row(int ng, int nb) {
 
 // Quantises superblock kblk of x for NB batch rows (rows beyond `batch` repeat the last one) into
 // the dense fragment order: byte offset ((group * J + set) * 32 + column * 4 + t) * W.
-template <int TYPE, int NB, bool LL>
+// SB: one scale per superblock and batch row (SX[kblk * NB + b]) and the groups' integer sums of n
+// in XX, for the integer-domain loop of the K-quants; otherwise one scale per group.
+template <int TYPE, int NB, bool LL, bool SB>
 __device__ __forceinline__ void quantise_dense(const float *x, const float *x_up,
                                                const float *norm_w, const float *inv_rms, int K,
                                                int batch, int kblk, int lane, uint8_t *xq,
@@ -785,7 +787,7 @@ __device__ __forceinline__ void quantise_dense(const float *x, const float *x_up
 #pragma unroll
       for (int e = 0; e < 8; e++) mx = fmaxf(mx, fabsf(v[e]));
 #pragma unroll
-      for (int off = 1; off < LPG; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      for (int off = 1; off < (SB ? 32 : LPG); off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
       const bool live = mx > 1e-30f;  // as in quantise_superblocks
       const float sx = live ? mx * (1.f / kNMax) : 1.f;
       const float inv = live ? (float)kNMax / mx : 0.f;
@@ -799,7 +801,10 @@ __device__ __forceinline__ void quantise_dense(const float *x, const float *x_up
       }
 #pragma unroll
       for (int off = 1; off < LPG; off <<= 1) nsum += __shfl_xor_sync(0xffffffffu, nsum, off);
-      if ((lane & (LPG - 1)) == 0) {
+      if constexpr (SB) {
+        if (lane == 0) SX[kblk * NB + b] = sx;
+        if ((lane & (LPG - 1)) == 0) reinterpret_cast<int *>(XX)[grp * NB + b] = nsum;
+      } else if ((lane & (LPG - 1)) == 0) {
         SX[grp * NB + b] = sx;
         XX[grp * NB + b] = sx * (float)nsum;
       }
@@ -1028,6 +1033,199 @@ __device__ __forceinline__ void mma_dense(const uint8_t *blk, int pad_a, int pad
         }
       }
     }
+  }
+}
+
+// ---------------------------------------------------------------------------- batches 3 .. 8, K-quants
+// Q4_K, Q5_K and Q6_K keep a superblock in the integer domain, like Q6_K at batch 1-2: one
+// activation scale per superblock and batch row, the weights' 6-bit (int8) group scales multiplied
+// onto the integer group sums, one conversion per (row, batch row) and superblock.  Per (group, set
+// of four batch rows) a lane issues one B-fragment load, one MMA and four integer multiply-adds
+// (rows g / g+8 x planes hi / lo).  The planes stay apart until the conversion (hi * 128 + lo in
+// float), which keeps the sums in range: per group |sum| <= 32 * 240 * 127 (Q4_K's high nibbles in
+// place), times a scale <= 63 (the low-nibble groups' scales come times 16 instead), eight groups:
+// below 5e8; Q5_K 32 * 31 * 127 * 63 * 8 < 7e7; Q6_K 16 * 63 * 127 * 128 * 16 < 2.7e8.  The
+// offsets (-dmin * m, -32) are integer sums of (min or scale) x (group sum of n), below 5.4e8.
+template <int TYPE> constexpr bool kDenseInt = TYPE == kQ4_K || TYPE == kQ5_K || TYPE == kQ6_K;
+
+// Lanes (r = lane & 15, half = lane >> 4) write the integer scales of one half of row r's groups
+// into the warp's area; the offsets of the NB batch rows follow at index NG + b as floats.
+template <int TYPE, int NB>
+__device__ __forceinline__ void decode_dense_int(const uint8_t *blk_row, int lane, int kblk,
+                                                 const float *SX, const int *XN, float *area) {
+  using C = Cfg<TYPE>;
+  constexpr int NH = C::NG / 2, ROW = dense_area_row(C::NG, NB);
+  const int r = lane & 15, half = lane >> 4;
+  int sc[NH], mn[NH];
+  float dneg;  // the factor of the offset sum: -dmin, or -32 d
+  if constexpr (C::HAS_MIN) {
+    const uint4 h = *reinterpret_cast<const uint4 *>(blk_row);
+    dneg = -__high2float(*reinterpret_cast<const __half2 *>(&h.x));
+    const uint32_t u0 = h.y, u1 = h.z, u2 = h.w;
+    // four 6-bit scales / mins of this half as bytes (dequant.cr:240-249, four at a time)
+    const uint32_t scw = half ? ((u2 & 0x0f0f0f0fu) | ((u0 >> 2) & 0x30303030u)) : (u0 & 0x3f3f3f3fu);
+    const uint32_t mnw = half ? (((u2 >> 4) & 0x0f0f0f0fu) | ((u1 >> 2) & 0x30303030u)) : (u1 & 0x3f3f3f3fu);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      sc[i] = (int)((scw >> (8 * i)) & 0xffu);
+      // Q4_K: the odd groups' sums arrive times 16 (nibbles in place), so the even ones' scales do
+      if (TYPE == kQ4_K && !(i & 1)) sc[i] <<= 4;
+      mn[i] = (int)((mnw >> (8 * i)) & 0xffu);
+    }
+  } else {
+    dneg = -32.f * load_half_as_float(blk_row + 208);
+    const int8_t *s8 = reinterpret_cast<const int8_t *>(blk_row + 192 + 8 * half);
+#pragma unroll
+    for (int i = 0; i < 8; i++) sc[i] = mn[i] = (int)s8[i];
+  }
+  int *row = reinterpret_cast<int *>(area + r * ROW);
+#pragma unroll
+  for (int i = 0; i < NH; i += 4)
+    *reinterpret_cast<int4 *>(row + NH * half + i) = make_int4(sc[i], sc[i + 1], sc[i + 2], sc[i + 3]);
+  int cs[NB];
+#pragma unroll
+  for (int b = 0; b < NB; b++) cs[b] = 0;
+  const int4 *xn = reinterpret_cast<const int4 *>(XN + (size_t)(kblk * C::NG + NH * half) * NB);
+#pragma unroll
+  for (int i = 0; i < NH; i++)
+#pragma unroll
+    for (int b4 = 0; b4 < NB / 4; b4++) {
+      const int4 c = xn[i * (NB / 4) + b4];
+      cs[4 * b4] += mn[i] * c.x;
+      cs[4 * b4 + 1] += mn[i] * c.y;
+      cs[4 * b4 + 2] += mn[i] * c.z;
+      cs[4 * b4 + 3] += mn[i] * c.w;
+    }
+#pragma unroll
+  for (int b = 0; b < NB; b++) cs[b] += __shfl_xor_sync(0xffffffffu, cs[b], 16);
+  // the halves store alternate fours of the batch rows
+#pragma unroll
+  for (int b4 = 0; b4 < NB / 4; b4++)
+    if (half == (b4 & 1)) {
+      const float4 sx = *reinterpret_cast<const float4 *>(SX + (size_t)kblk * NB + 4 * b4);
+      *reinterpret_cast<float4 *>(area + r * ROW + C::NG + 4 * b4) =
+          make_float4(dneg * sx.x * (float)cs[4 * b4], dneg * sx.y * (float)cs[4 * b4 + 1],
+                      dneg * sx.z * (float)cs[4 * b4 + 2], dneg * sx.w * (float)cs[4 * b4 + 3]);
+    }
+}
+
+// MMAs of one superblock for all NB batch rows.  xg: this lane's B fragment of the superblock's
+// first (group, set); sxb: the superblock's activation scales (one per batch row).
+template <int TYPE, int NB>
+__device__ __forceinline__ void mma_dense_int(const uint8_t *blk, int pad_a, int pad_b,
+                                              const uint8_t *xg, const float *area, const float *sxb,
+                                              int g, int t, float (&acc0)[NB / 4], float (&acc1)[NB / 4]) {
+  using C = Cfg<TYPE>;
+  constexpr int J = NB / 4, GB = Dense<TYPE>::GB, ROW = dense_area_row(C::NG, NB);
+  constexpr uint32_t M4 = 0x0f0f0f0fu;
+  const int *rowa = reinterpret_cast<const int *>(area + g * ROW);
+  const int *rowb = reinterpret_cast<const int *>(area + (g + 8) * ROW);
+  int h0[J], l0[J], h1[J], l1[J];  // rows g / g+8, planes hi / lo, batch row 4j + t
+#pragma unroll
+  for (int j = 0; j < J; j++) h0[j] = l0[j] = h1[j] = l1[j] = 0;
+  float da, db;
+  if constexpr (C::HAS_MIN) {
+    constexpr bool Q5 = TYPE == kQ5_K;
+    constexpr int QOFF = Q5 ? 48 : 16;
+    constexpr uint32_t M1 = 0x10101010u, MH = 0xf0f0f0f0u;
+    const uint8_t *ra = blk + g * C::RS + pad_a, *rb = blk + (g + 8) * C::RS + pad_b;
+    da = load_half_as_float(ra) * (Q5 ? 1.f : 0.0625f);
+    db = load_half_as_float(rb) * (Q5 ? 1.f : 0.0625f);
+    ra += 8 * t;
+    rb += 8 * t;
+    uint2 qha = make_uint2(0, 0), qhb = make_uint2(0, 0);
+    if constexpr (Q5) {
+      qha = *reinterpret_cast<const uint2 *>(ra + 16);
+      qhb = *reinterpret_cast<const uint2 *>(rb + 16);
+    }
+    auto group32 = [&](int gi, int sa, int sb, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
+#pragma unroll
+      for (int j = 0; j < J; j++) {
+        const uint2 bv = *reinterpret_cast<const uint2 *>(xg + (gi * J + j) * GB);
+        int cc[4];
+        imma_zero(cc, a0, a1, a2, a3, bv.x, bv.y);
+        h0[j] += sa * cc[0];
+        l0[j] += sa * cc[1];
+        h1[j] += sb * cc[2];
+        l1[j] += sb * cc[3];
+      }
+    };
+#pragma unroll 1  // unrolling by 2 or 4 measured the same
+    for (int g4 = 0; g4 < 4; g4++) {
+      const int2 sa = *reinterpret_cast<const int2 *>(rowa + 2 * g4);
+      const int2 sb = *reinterpret_cast<const int2 *>(rowb + 2 * g4);
+      const uint2 qa = *reinterpret_cast<const uint2 *>(ra + QOFF + 32 * g4);
+      const uint2 qb = *reinterpret_cast<const uint2 *>(rb + QOFF + 32 * g4);
+      uint32_t la0 = qa.x & M4, la1 = qa.y & M4, lb0 = qb.x & M4, lb1 = qb.y & M4;
+      uint32_t ha0, ha1, hb0, hb1;
+      if constexpr (!Q5) {  // high nibbles stay in place: 16 * q
+        ha0 = qa.x & MH; ha1 = qa.y & MH; hb0 = qb.x & MH; hb1 = qb.y & MH;
+      } else {
+        ha0 = (qa.x >> 4) & M4; ha1 = (qa.y >> 4) & M4; hb0 = (qb.x >> 4) & M4; hb1 = (qb.y >> 4) & M4;
+        // fifth bit: bit 2*g4 of qh for the low-nibble elements, bit 2*g4+1 for the high ones
+        auto bit = [&](uint32_t q, int b) { return b <= 4 ? ((q << (4 - b)) & M1) : ((q >> (b - 4)) & M1); };
+        la0 |= bit(qha.x, 2 * g4);     la1 |= bit(qha.y, 2 * g4);
+        lb0 |= bit(qhb.x, 2 * g4);     lb1 |= bit(qhb.y, 2 * g4);
+        ha0 |= bit(qha.x, 2 * g4 + 1); ha1 |= bit(qha.y, 2 * g4 + 1);
+        hb0 |= bit(qhb.x, 2 * g4 + 1); hb1 |= bit(qhb.y, 2 * g4 + 1);
+      }
+      group32(2 * g4, sa.x, sb.x, la0, lb0, la1, lb1);
+      group32(2 * g4 + 1, sa.y, sb.y, ha0, hb0, ha1, hb1);
+    }
+  } else {
+    constexpr uint32_t M2 = 0x30303030u;
+    da = load_half_as_float(blk + g * C::RS + pad_a + 208);
+    db = load_half_as_float(blk + (g + 8) * C::RS + pad_b + 208);
+    const uintptr_t aa = reinterpret_cast<uintptr_t>(blk + g * C::RS + pad_a + 4 * t);
+    const uintptr_t ab8 = reinterpret_cast<uintptr_t>(blk + (g + 8) * C::RS + pad_b + 4 * t);
+    const uint8_t *base[2] = {reinterpret_cast<const uint8_t *>(aa & ~(uintptr_t)3),
+                              reinterpret_cast<const uint8_t *>(ab8 & ~(uintptr_t)3)};
+    const uint32_t sh[2] = {(uint32_t)(aa & 2) * 8, (uint32_t)(ab8 & 2) * 8};
+#pragma unroll
+    for (int n = 0; n < 2; n++) {
+      const int4 sa0 = *reinterpret_cast<const int4 *>(rowa + 8 * n), sa1 = *reinterpret_cast<const int4 *>(rowa + 8 * n + 4);
+      const int4 sb0 = *reinterpret_cast<const int4 *>(rowb + 8 * n), sb1 = *reinterpret_cast<const int4 *>(rowb + 8 * n + 4);
+      const int sa[8] = {sa0.x, sa0.y, sa0.z, sa0.w, sa1.x, sa1.y, sa1.z, sa1.w};
+      const int sb[8] = {sb0.x, sb0.y, sb0.z, sb0.w, sb1.x, sb1.y, sb1.z, sb1.w};
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        uint32_t q[2][4];
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+          auto ld = [&](int off) {  // rows may start 2 bytes off a word: two loads and a funnel shift
+            const uint32_t *w32 = reinterpret_cast<const uint32_t *>(base[r] + off);
+            return __funnelshift_r(w32[0], w32[1], sh[r]);
+          };
+          const uint32_t ql0 = ld(64 * n + 16 * h), ql1 = ld(64 * n + 32 + 16 * h);
+          const uint32_t qhw = ld(128 + 32 * n + 16 * h);
+          q[r][0] = (ql0 & M4) | ((qhw << 4) & M2);
+          q[r][1] = (ql1 & M4) | ((qhw << 2) & M2);
+          q[r][2] = ((ql0 >> 4) & M4) | (qhw & M2);
+          q[r][3] = ((ql1 >> 4) & M4) | ((qhw >> 2) & M2);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++) {  // elements 128n + 32k + 16h + (0..15): scale group 8n + 2k + h
+          const int gi = 8 * n + 2 * k + h;
+#pragma unroll
+          for (int j = 0; j < J; j++) {
+            const uint32_t bw = *reinterpret_cast<const uint32_t *>(xg + (gi * J + j) * GB);
+            int cc[4];
+            imma16_zero(cc, q[0][k], q[1][k], bw);
+            h0[j] += sa[2 * k + h] * cc[0];
+            l0[j] += sa[2 * k + h] * cc[1];
+            h1[j] += sb[2 * k + h] * cc[2];
+            l1[j] += sb[2 * k + h] * cc[3];
+          }
+        }
+      }
+    }
+  }
+  const float *rowfa = area + g * ROW + C::NG, *rowfb = area + (g + 8) * ROW + C::NG;
+#pragma unroll
+  for (int j = 0; j < J; j++) {
+    const float sx = sxb[4 * j + t];
+    acc0[j] = fmaf(da * sx, fmaf((float)h0[j], 128.f, (float)l0[j]), rowfa[4 * j + t]);
+    acc1[j] = fmaf(db * sx, fmaf((float)h1[j], 128.f, (float)l1[j]), rowfb[4 * j + t]);
   }
 }
 
@@ -1430,7 +1628,7 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
             if (PAIR == 2 && n2 == 2) quantise_q6v2<NB, 2, LL>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, reinterpret_cast<int *>(XX), xsrc);
             else quantise_q6v2<NB, 1, LL>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, reinterpret_cast<int *>(XX), xsrc);
           } else if constexpr (DENSE) {
-            quantise_dense<TYPE, NB, LL>(xs, xs_up, norm_ws, s_inv_rms, K, p.batch, e0, lane, xq, SX, XX, xsrc);
+            quantise_dense<TYPE, NB, LL, kDenseInt<TYPE>>(xs, xs_up, norm_ws, s_inv_rms, K, p.batch, e0, lane, xq, SX, XX, xsrc);
           } else {
             if (PAIR == 2 && n2 == 2) quantise_superblocks<TYPE, NB, 2, LL>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, XX, xsrc);
             else quantise_superblocks<TYPE, NB, 1, LL>(xs, xs_up, norm_ws, s_inv_rms, K, e0, lane, xq, SX, XX, xsrc);
@@ -1454,10 +1652,18 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
       if constexpr (DENSE) {
         constexpr int J = NB / 4;
         float acc0[J], acc1[J];  // rows g and g+8 of batch rows 4j + t
-        decode_dense<TYPE, NB>(blk + (lane & 15) * C::RS + pad_d, lane, e0, XX, area);
-        __syncwarp();
-        mma_dense<TYPE, NB>(blk, pad_a, pad_b, xlane + (size_t)e0 * C::NG * J * Dense<TYPE>::GB, area,
-                            SX + (size_t)e0 * C::NG * NB + t, g, t, acc0, acc1);
+        if constexpr (kDenseInt<TYPE>) {
+          decode_dense_int<TYPE, NB>(blk + (lane & 15) * C::RS + pad_d, lane, e0, SX,
+                                     reinterpret_cast<const int *>(XX), area);
+          __syncwarp();
+          mma_dense_int<TYPE, NB>(blk, pad_a, pad_b, xlane + (size_t)e0 * C::NG * J * Dense<TYPE>::GB,
+                                  area, SX + (size_t)e0 * NB, g, t, acc0, acc1);
+        } else {
+          decode_dense<TYPE, NB>(blk + (lane & 15) * C::RS + pad_d, lane, e0, XX, area);
+          __syncwarp();
+          mma_dense<TYPE, NB>(blk, pad_a, pad_b, xlane + (size_t)e0 * C::NG * J * Dense<TYPE>::GB, area,
+                              SX + (size_t)e0 * C::NG * NB + t, g, t, acc0, acc1);
+        }
         __syncwarp();  // the area is rewritten by this warp's next decode
         spin_until_ge(&folded[tb], li / kFoldBufs);  // the buffer's previous tile has been folded
 #pragma unroll

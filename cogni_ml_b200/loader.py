@@ -48,6 +48,10 @@ class WeightUploader:
         rb = row_bytes(qw.type, qw.in_dim)
         src = qw.raw[row_begin * rb:row_end * rb]
         dev = torch.empty(src.size, dtype=torch.uint8, device=self.device)
+        # the allocation may reuse a block whose last user is still queued on the current stream,
+        # and the caching allocator must not hand it out again while the copies are in flight
+        self.stream.wait_stream(torch.cuda.current_stream(self.device))
+        dev.record_stream(self.stream)
         for off, size in plan_chunks(src.size, self.chunk_bytes):
             i = self._next
             self._next = (i + 1) % len(self._staging)
