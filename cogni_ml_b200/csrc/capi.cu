@@ -85,6 +85,10 @@ int cogni_qmm_set_kernel_choice(int choice) {
     gemm_prefill_set_stage_raw(choice == 55);
     return COGNI_QMM_OK;
   }
+  if (choice == 57 || choice == 58) {  // prefill, 512-token tiles: CTA pairs (57, default) or single CTAs (58)
+    gemm_prefill_set_pair(choice == 57);
+    return COGNI_QMM_OK;
+  }
   if (choice >= 52 && choice <= 54) {  // prefill split along K: automatic / never / wherever allowed
     gemm_prefill_set_split(choice - 52);
     return COGNI_QMM_OK;

@@ -55,15 +55,42 @@ __host__ __device__ constexpr int stages_for(int bn, int raw = 0) {
   const int fit = (227 * 1024 - 1024 - 256 - raw) / (128 * 64 * 2 + bn * 64 * 2);
   return fit < want ? fit : want;
 }
-// Dequant warps: eight (two threads per tile row, one per 32-element half of a k-step); four (one
-// thread per row, both halves) for Q6_K read directly from global memory, whose two halves share
-// the qh bytes and whose loads are the bound there (measured both ways).
+// Dequant warps: sixteen for Q4_K / Q5_K staged by TMA (four threads per tile row, one per
+// 16-element quarter of a k-step: the expansion is a chain of dependent conversions, and two warps
+// per scheduler could not hide its latencies; Q6_K, whose quarters would share the qh bytes and
+// repeat the funnel shifts of its unaligned block, measured slower that way); eight (two threads
+// per tile row, one per 32-element half of a k-step); four (one thread per row, both halves) for
+// Q6_K read directly from global memory, whose loads are the bound there.
 __host__ __device__ constexpr int dequant_warps(int type, bool staged = false) {
+  if (staged && (type == kQ4_K || type == kQ5_K)) return 16;
   return type == kQ6_K && !staged ? 4 : 8;
 }
+// Warp roles.  A warp scheduler serves the warps w with the same w % 4, and the thread that issues
+// the MMAs must not queue behind dequant warps for an issue slot: the tensor pipe idles whenever it
+// is late (measured on the 2-CTA kernel, Q4_K 12288 x 4096, 4096 tokens: 972 TFLOP/s with four
+// dequant warps on its scheduler, 945 with two, 1131 with none).  With sixteen dequant warps,
+// scheduler 1 therefore hosts only the MMA warp (1), the TMA warp (5) and four warps (9, 13, 17,
+// 21) that sleep until the epilogue, where they read the TMEM lane quarter 1 that only warps of
+// their residue can; the dequant warps are the other warps up to 20.  With eight or four dequant
+// warps: warp 0 TMA, warp 1 MMA, the rest dequant.
+constexpr int kIsoWarps = 22;
 __host__ __device__ constexpr int threads_for(int type, bool staged = false) {
-  return 64 + 32 * dequant_warps(type, staged);  // warp 0: TMA, warp 1: MMA + TMEM
+  return dequant_warps(type, staged) == 16 ? 32 * kIsoWarps : 64 + 32 * dequant_warps(type, staged);
 }
+template <bool ISO> struct Roles {
+  static constexpr int tma_warp = ISO ? 5 : 0;
+  __device__ static bool is_dequant(int warp) { return ISO ? (warp & 3) != 1 && warp <= 20 : warp >= 2; }
+  // dense index over the dequant warps
+  __device__ static int dequant_index(int warp) { return ISO ? warp - ((warp + 2) >> 2) : warp - 2; }
+  // the epilogue: four warps (ISO; else all dequant warps) per TMEM lane quarter warp % 4, each
+  // taking an equal chunk of the token columns
+  __device__ static bool in_epilogue(int warp) {
+    return ISO ? ((warp & 3) == 1 ? warp >= 9 : warp < 16) : warp >= 2;
+  }
+  __device__ static int epilogue_chunk(int warp) {
+    return ISO ? ((warp & 3) == 1 ? (warp >> 2) - 2 : warp >> 2) : (warp - 2) >> 2;
+  }
+};
 constexpr int kATile = kBM * kBK * 2;  // 16 KB
 
 struct GemmParams {
@@ -102,6 +129,40 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The four K = 16 MMAs of a 64-element k-step as one block of instructions.  The thread that
+// issues the MMAs shares its warp scheduler with other warps and the tensor pipe idles whenever
+// it is late, so its instruction count per k-step matters: descriptors are formed here from their
+// 32-bit halves (a step of 16 bf16 along K is 32 bytes = 2 in the descriptor's address field),
+// one predicate decides whether the first MMA accumulates, the others always do.
+// a_lo / b_lo: low descriptor words of the operand tiles (smem_desc_lo), desc_hi: kDescHi.
+constexpr uint32_t kDescHi = 64u | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr) {
+  return ((smem_addr & 0x3FFFF) >> 4) | (1u << 16);
+}
+#define COGNI_UMMA4(GROUP)                                                                      \
+  asm volatile(                                                                                  \
+      "{\n\t.reg .pred p0, p1;\n\t.reg .b64 da, db;\n\t.reg .b32 al, bl;\n\t"                      \
+      "setp.ne.b32 p0, %5, 0;\n\t"                                                               \
+      "setp.eq.b32 p1, %4, %4;\n\t"                                                              \
+      "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"                                       \
+      "tcgen05.mma.cta_group::" GROUP ".kind::f16 [%0], da, db, %4, p0;\n\t"                      \
+      "add.u32 al, %1, 2;\n\tadd.u32 bl, %2, 2;\n\tmov.b64 da, {al, %3};\n\tmov.b64 db, {bl, %3};\n\t" \
+      "tcgen05.mma.cta_group::" GROUP ".kind::f16 [%0], da, db, %4, p1;\n\t"                      \
+      "add.u32 al, %1, 4;\n\tadd.u32 bl, %2, 4;\n\tmov.b64 da, {al, %3};\n\tmov.b64 db, {bl, %3};\n\t" \
+      "tcgen05.mma.cta_group::" GROUP ".kind::f16 [%0], da, db, %4, p1;\n\t"                      \
+      "add.u32 al, %1, 6;\n\tadd.u32 bl, %2, 6;\n\tmov.b64 da, {al, %3};\n\tmov.b64 db, {bl, %3};\n\t" \
+      "tcgen05.mma.cta_group::" GROUP ".kind::f16 [%0], da, db, %4, p1;\n\t}"                     \
+      ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(accumulate_first)         \
+      : "memory")
+__device__ __forceinline__ void umma4_bf16(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                           uint32_t accumulate_first) {
+  COGNI_UMMA4("1");
+}
+__device__ __forceinline__ void umma4_bf16_pair(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo,
+                                                uint32_t idesc, uint32_t accumulate_first) {
+  COGNI_UMMA4("2");
+}
+#undef COGNI_UMMA4
 // Arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
@@ -415,6 +476,20 @@ __device__ __forceinline__ void scale_min_regs(const uint4 &h, int s, float &sc,
 }
 
 // Q4_K / Q5_K, staged: the words of k-step j of the block at blk (shared memory, 16-byte aligned)
+// Q4_K / Q5_K, staged, one thread per quarter: the header and the 16 bytes (q0, h0) that hold the
+// quarter's nibbles and fifth bits.
+template <int TYPE>
+__device__ __forceinline__ void fetch_quarter_from(const uint8_t *blk, int j, int q2, Raw<TYPE> &r) {
+  static_assert(TYPE == kQ4_K || TYPE == kQ5_K, "K-quants with 32-element groups");
+  r.hdr = *reinterpret_cast<const uint4 *>(blk);
+  if constexpr (TYPE == kQ4_K) {
+    r.q0 = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * j + 16 * q2);
+  } else {
+    r.h0 = *reinterpret_cast<const uint4 *>(blk + 16 + 16 * q2);
+    r.q0 = *reinterpret_cast<const uint4 *>(blk + 48 + 32 * j + 16 * q2);
+  }
+}
+
 template <int TYPE>
 __device__ __forceinline__ void fetch_raw_from(const uint8_t *blk, int j, int h, Raw<TYPE> &r) {
   if constexpr (TYPE == kIQ4_NL) {
@@ -474,13 +549,16 @@ __device__ __forceinline__ void fetch_staged_q6(const uint8_t *win, int r, int p
 }
 
 // Rebuilds half h (32 weights: chunks 4h .. 4h+3) of k-step ks of tile row r as bf16 and stores
-// them swizzled.
-template <int TYPE>
+// them swizzled.  QUARTER: only quarter q2 of the half (chunks 4h + 2 q2, + 1), whose raw words
+// are the first ones of `raw` (fetch_quarter_from).
+template <int TYPE, bool QUARTER = false>
 __device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, int h, uint8_t *tile,
-                                             int r, bool valid) {
+                                             int r, bool valid, int q2 = 0) {
+  constexpr int NC = QUARTER ? 2 : 4;  // chunks of 8 weights this thread writes
+  const int cbase = 4 * h + (QUARTER ? 2 * q2 : 0);
   if (!valid) {
 #pragma unroll
-    for (int c4 = 0; c4 < 4; c4++) store_chunk(tile, r, 4 * h + c4, make_uint4(0, 0, 0, 0));
+    for (int c4 = 0; c4 < NC; c4++) store_chunk(tile, r, cbase + c4, make_uint4(0, 0, 0, 0));
     return;
   }
   const int j = ks & 3;
@@ -546,7 +624,7 @@ __device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, int h
     const uint64_t d1_2 = f2_pack(d1, d1), nm1_2 = f2_pack(-m1, -m1);
     const uint64_t unbias2 = f2_pack(-8388608.f, -8388608.f);
 #pragma unroll
-    for (int c4 = 0; c4 < 4; c4++) {           // 8 elements: bytes 8*c4 .. 8*c4+7
+    for (int c4 = 0; c4 < NC; c4++) {          // 8 elements: bytes 8*c4 .. 8*c4+7 (of the quarter)
       uint32_t out[4];
 #pragma unroll
       for (int w2 = 0; w2 < 2; w2++) {
@@ -557,7 +635,7 @@ __device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, int h
         out[2 * w2] = f2_to_bf16x2(f2_fma(d1_2, f2_add(bytes2_biased(q, 0), unbias2), nm1_2));
         out[2 * w2 + 1] = f2_to_bf16x2(f2_fma(d1_2, f2_add(bytes2_biased(q, 2), unbias2), nm1_2));
       }
-      store_chunk(tile, r, 4 * h + c4, make_uint4(out[0], out[1], out[2], out[3]));
+      store_chunk(tile, r, cbase + c4, make_uint4(out[0], out[1], out[2], out[3]));
     }
   } else {
     // the k-step is elements 64*hi .. 64*hi+63 of the superblock's half n = j >> 1: two runs of 32,
@@ -566,8 +644,8 @@ __device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, int h
     const float d = __half2float(__ushort_as_half((unsigned short)raw.d));
     const int hi = j & 1, kk = 2 * hi + h;
 #pragma unroll
-    for (int c4 = 0; c4 < 4; c4++) {
-      const int scb = (int)(int8_t)((raw.sc >> (8 * ((c4 >> 1) + 2 * h))) & 0xff);
+    for (int c4 = 0; c4 < NC; c4++) {
+      const int scb = (int)(int8_t)((raw.sc >> (8 * ((QUARTER ? q2 : (c4 >> 1)) + 2 * h))) & 0xff);
       const float dsc = __fmul_rn(d, (float)scb);
       const uint64_t dsc_2 = f2_pack(dsc, dsc), unbias2 = f2_pack(-8388640.f, -8388640.f);
       uint32_t out[4];
@@ -580,7 +658,7 @@ __device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, int h
         out[2 * w2] = f2_to_bf16x2(f2_mul(dsc_2, f2_add(bytes2_biased(q, 0), unbias2)));
         out[2 * w2 + 1] = f2_to_bf16x2(f2_mul(dsc_2, f2_add(bytes2_biased(q, 2), unbias2)));
       }
-      store_chunk(tile, r, 4 * h + c4, make_uint4(out[0], out[1], out[2], out[3]));
+      store_chunk(tile, r, cbase + c4, make_uint4(out[0], out[1], out[2], out[3]));
     }
   }
 }
@@ -593,7 +671,9 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
   constexpr int kRawStage = raw_stage_bytes(TYPE);
   constexpr int kStages = stages_for(BN, raw_bytes(TYPE, STAGED));
   static_assert(kStages >= 2, "at least two stages");
-  constexpr int kDequantWarps = dequant_warps(TYPE, STAGED), kHalves = 8 / kDequantWarps;  // halves per thread
+  constexpr int kDequantWarps = dequant_warps(TYPE, STAGED);
+  constexpr int kHalves = kDequantWarps >= 8 ? 1 : 2;   // halves of a k-step per thread
+  constexpr bool kQuarter = kDequantWarps == 16;        // a thread expands one quarter of a k-step
   constexpr int kBTile = BN * kBK * 2;
   constexpr int kStageBytes = kATile + kBTile;
   // UMMA N is at most 256: a 512-token tile is two accumulators of 256 TMEM columns, fed by the
@@ -604,9 +684,15 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
   uint8_t *smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
   uint8_t *raw_win = smem + kStages * kStageBytes;  // STAGED: two raw stages of two boxes each
   uint64_t *bars = reinterpret_cast<uint64_t *>(raw_win + raw_bytes(TYPE, STAGED));
-  // bars: full_a[S] | full_b[S] | empty[S] | acc_full | raw_full[2] | raw_empty[2]; then the TMEM
-  // base address slot
-  uint64_t *raw_bars = bars + 3 * kStages + 1;
+  // bars: full_a[S] | full_b[S][kNSub] | empty_a[S] | empty_b[S][kNSub] | acc_full | raw_full[2] |
+  // raw_empty[2]; then the TMEM base address slot.  The B tile of a stage is kNSub boxes of 256
+  // tokens, each with its own full / empty barrier: a box is reloaded as soon as the MMAs that read
+  // it are done, half a k-step before the stage's other box, which is what lets a 32 KB load hide
+  // behind the MMAs with only two stages.
+  constexpr int kFullB = kStages, kEmptyA = kFullB + kStages * kNSub, kEmptyB = kEmptyA + kStages;
+  constexpr int kAccBar = kEmptyB + kStages * kNSub;
+  static_assert((kAccBar + 5) * 8 + 4 <= 256, "barriers fit their 256 bytes");
+  uint64_t *raw_bars = bars + kAccBar + 1;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(raw_bars + 4);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * kBM, m0 = blockIdx.y * BN;
@@ -620,10 +706,13 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; s++) {
       mbar_init(smem_u32(&bars[s]), kDequantWarps);        // full_a: one arrive per dequant warp
-      mbar_init(smem_u32(&bars[kStages + s]), 1);          // full_b: the TMA thread
-      mbar_init(smem_u32(&bars[2 * kStages + s]), 1);      // empty: tcgen05.commit
+      mbar_init(smem_u32(&bars[kEmptyA + s]), 1);          // empty_a: tcgen05.commit
+      for (int h = 0; h < kNSub; h++) {
+        mbar_init(smem_u32(&bars[kFullB + s * kNSub + h]), 1);   // full_b: the TMA thread + bytes
+        mbar_init(smem_u32(&bars[kEmptyB + s * kNSub + h]), 1);  // empty_b: tcgen05.commit
+      }
     }
-    mbar_init(smem_u32(&bars[3 * kStages]), 1);            // accumulator complete
+    mbar_init(smem_u32(&bars[kAccBar]), 1);                // accumulator complete
     if constexpr (STAGED) {
       mbar_init(smem_u32(&raw_bars[0]), 1);                // raw_full: the issuing thread + bytes
       mbar_init(smem_u32(&raw_bars[1]), 1);
@@ -641,7 +730,8 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  using R = Roles<kQuarter>;
+  if (warp == R::tma_warp) {
     // ---------------------------------------------------------------- activations via TMA
     if (lane == 0) {
       // STAGED: the same thread keeps the next superblock column's raw windows in flight.
@@ -660,7 +750,9 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
                       Sb<TYPE>::bytes * (sb0 + sbl), raw_n0, full);
         }
       };
+      {
       if constexpr (STAGED) issue_raw(0);
+      }
       for (int ks = 0; ks < nks; ks++) {
         const int s = ks % kStages;
         if constexpr (STAGED) {
@@ -672,41 +764,48 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
             issue_raw(sbl + 1);
           }
         }
-        mbar_wait(smem_u32(&bars[2 * kStages + s]), ((ks / kStages) & 1) ^ 1);
-        const uint32_t full = smem_u32(&bars[kStages + s]);
-        mbar_arrive_expect_tx(full, kBTile);
 #pragma unroll
-        for (int h = 0; h < kNSub; h++)
+        for (int h = 0; h < kNSub; h++) {
+          mbar_wait(smem_u32(&bars[kEmptyB + s * kNSub + h]), ((ks / kStages) & 1) ^ 1);
+          const uint32_t full = smem_u32(&bars[kFullB + s * kNSub + h]);
+          mbar_arrive_expect_tx(full, kBTile / kNSub);
           tma_load_2d(smem_u32(smem + s * kStageBytes + kATile + h * kNMma * kBK * 2), &tmap_x,
                       (ks0 + ks) * kBK, m0 + h * kNMma, full);
+        }
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issue
     if (lane == 0) {
       constexpr uint32_t idesc = idesc_bf16(kBM, kNMma);
+      const uint32_t bar0 = smem_u32(&bars[0]);
+      const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem));
+      uint32_t s = 0, ph = 0;
       for (int ks = 0; ks < nks; ks++) {
-        const int s = ks % kStages;
-        const uint32_t ph = (ks / kStages) & 1;
-        mbar_wait(smem_u32(&bars[s]), ph);
-        mbar_wait(smem_u32(&bars[kStages + s]), ph);
-        tc_fence_after();
-        const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
-        const uint32_t b_addr = a_addr + kATile;
+        mbar_wait(bar0 + 8 * s, ph);
+        const uint32_t a_lo = a_lo0 + s * (kStageBytes >> 4);
 #pragma unroll
-        for (int k = 0; k < kBK / 16; k++)   // 16 bf16 = 32 bytes further along the swizzled row
-#pragma unroll
-          for (int h = 0; h < kNSub; h++)
-            umma_bf16(tmem_base + h * kNMma, smem_desc_sw128(a_addr + 32 * k),
-                      smem_desc_sw128(b_addr + h * kNMma * kBK * 2 + 32 * k), idesc, (ks | k) != 0);
-        umma_commit(smem_u32(&bars[2 * kStages + s]));     // frees the stage when the MMAs are done
+        for (int h = 0; h < kNSub; h++) {
+          mbar_wait(bar0 + 8 * (kFullB + s * kNSub + h), ph);
+          tc_fence_after();
+          umma4_bf16(tmem_base + h * kNMma, a_lo, a_lo + ((kATile + h * kNMma * kBK * 2) >> 4), idesc, ks != 0);
+          umma_commit(bar0 + 8 * (kEmptyB + s * kNSub + h));  // frees this box of tokens
+        }
+        umma_commit(bar0 + 8 * (kEmptyA + s));             // frees the weight tile when the MMAs are done
+        if (++s == kStages) {
+          s = 0;
+          ph ^= 1;
+        }
       }
-      umma_commit(smem_u32(&bars[3 * kStages]));           // accumulator ready
+      umma_commit(smem_u32(&bars[kAccBar]));               // accumulator ready
     }
-  } else {
+  } else if (R::is_dequant(warp)) {
     // ---------------------------------------------------------------- dequant producers
-    const int r = (threadIdx.x - 64) & 127;                // tile row 0..127
-    const int h0 = (threadIdx.x - 64) >> 7;                // first (or only) half of every k-step
+    const int dt = R::dequant_index(warp) * 32 + lane;
+    const int r = dt & 127;                                // tile row 0..127
+    const int part = dt >> 7;
+    const int h0 = kQuarter ? part >> 1 : part;            // first (or only) half of every k-step
+    const int q2 = kQuarter ? part & 1 : 0;                // the half's quarter
     const bool valid = n0 + r < p.n_out;
     const uint8_t *row = p.w + (long long)(valid ? n0 + r : 0) * p.row_bytes;
     Raw<TYPE> cur[kHalves], nxt[kHalves];
@@ -731,7 +830,9 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
         const int s = ks % kStages;
         const int sbl = ks >> 2, buf = sbl & 1;
         if ((ks & 3) == 0) mbar_wait(smem_u32(&raw_bars[buf]), (sbl >> 1) & 1);
-        if constexpr (TYPE == kQ6_K)
+        if constexpr (kQuarter)
+          fetch_quarter_from<TYPE>(raw_win + buf * kRawStage + rr * Sb<TYPE>::bytes, (ks0 + ks) & 3, q2, cur[0]);
+        else if constexpr (TYPE == kQ6_K)
           fetch_staged_q6<kHalves>(raw_win + buf * kRawStage, rr,
                                    210 * (sb0 + sbl) - q6_window_start(sb0 + sbl, (int)p.row_bytes),
                                    (ks0 + ks) & 3, h0, cur);
@@ -741,10 +842,10 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&raw_bars[2 + buf]));
         }
-        mbar_wait(smem_u32(&bars[2 * kStages + s]), ((ks / kStages) & 1) ^ 1);
+        mbar_wait(smem_u32(&bars[kEmptyA + s]), ((ks / kStages) & 1) ^ 1);
 #pragma unroll
         for (int i = 0; i < kHalves; i++)
-          expand_kstep<TYPE>(cur[i], ks0 + ks, h0 + i, smem + s * kStageBytes, r, valid);
+          expand_kstep<TYPE, kQuarter>(cur[i], ks0 + ks, h0 + i, smem + s * kStageBytes, r, valid, q2);
         fence_async_smem();                                   // generic-proxy writes -> tensor core
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bars[s]));
@@ -754,7 +855,7 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
       for (int ks = 0; ks < nks; ks++) {
         const int s = ks % kStages;
         if (ks + 1 < nks) fetch_all(ks + 1, nxt);             // in flight while this k-step expands
-        mbar_wait(smem_u32(&bars[2 * kStages + s]), ((ks / kStages) & 1) ^ 1);
+        mbar_wait(smem_u32(&bars[kEmptyA + s]), ((ks / kStages) & 1) ^ 1);
 #pragma unroll
         for (int i = 0; i < kHalves; i++)
           expand_kstep<TYPE>(cur[i], ks0 + ks, h0 + i, smem + s * kStageBytes, r, valid);
@@ -765,16 +866,17 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
         for (int i = 0; i < kHalves; i++) cur[i] = nxt[i];
       }
     }
-
-    // ---------------------------------------------------------------- epilogue
-    mbar_wait(smem_u32(&bars[3 * kStages]), 0);
+  }
+  // ---------------------------------------------------------------- epilogue
+  if (R::in_epilogue(warp)) {
+    mbar_wait(smem_u32(&bars[kAccBar]), 0);
     tc_fence_after();
     const int q = warp & 3;                                // TMEM lane quarter this warp may read
     const int n = n0 + 32 * q + lane;
     const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16);
-    // with eight warps the two of a lane quarter take one half of the token columns each
-    constexpr int kCols = BN / (kDequantWarps / 4);
-    const int cbeg = ((warp - 2) >> 2) * kCols;
+    // the warps of a lane quarter take an equal share of the token columns each
+    constexpr int kCols = BN / (kQuarter ? 4 : kDequantWarps / 4);
+    const int cbeg = R::epilogue_chunk(warp) * kCols;
 #pragma unroll 1
     for (int c0 = cbeg; c0 < cbeg + kCols; c0 += 32) {
       uint32_t v[32];
@@ -801,6 +903,285 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, BN);
+}
+
+// ---------------------------------------------------------------------------- the 2-CTA kernel
+// A pair of CTAs (a cluster of two SMs) computes 256 weight rows x 512 tokens with
+// tcgen05.mma.cta_group::2: each CTA dequantises its own 128 rows (the A operand of its half of
+// M = 256) and loads only 128 of the 256 tokens of every B box; the tensor cores of both SMs read
+// both halves.  Per k-step a CTA's shared memory then takes 32 KB of activations instead of 64 KB
+// and the MMAs read 64 KB instead of 96 KB, which is what bounds the one-CTA kernel (shared-memory
+// bandwidth: 185 KB of traffic per k-step against 1024 cycles of MMAs), and three 48 KB stages
+// fit where the one-CTA tile had two of 80 KB.
+//   * CTA 0 of the pair issues the MMAs.  Its full barriers collect the arrivals of both CTAs'
+//     dequant warps (remote mbarrier arrives) and the bytes of both CTAs' TMA loads (the loads name
+//     CTA 0's barrier); the empty and accumulator barriers exist in both CTAs and are signalled by
+//     one tcgen05.commit each.
+//   * No load of this kernel is multicast.
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// the address of `addr` (shared memory of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_in_cluster(uint32_t cluster_addr) {
+  // default semantics (release at CTA scope): what the arrive has to order is this warp's
+  // fence.proxy.async before it; a cluster-scope release costs a memory barrier per k-step and
+  // warp (measured: the leading stall of the kernel)
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the mbarrier at `cluster_addr` (any CTA of the pair) once every MMA issued so far
+// by this thread has completed in both CTAs.
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+// 2-D TMA tile load into this CTA's shared memory whose bytes are counted on a barrier of either
+// CTA of the pair (cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *tmap, int c0, int c1,
+                                                 uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], "
+      "[%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(tmap), "r"(c0), "r"(c1), "r"(bar_cluster_addr)
+      : "memory");
+}
+
+constexpr int kPairBN = 512;                 // tokens per pair tile: two accumulators of 256 columns
+constexpr int kPairThreads = 32 * kIsoWarps;
+constexpr int kPairBHalf = 128 * kBK * 2;    // this CTA's 128 tokens of a 256-token box: 16 KB
+// Two rings: the dequantised weight tiles (16 KB per k-step) and the token boxes (2 x 16 KB per
+// k-step and CTA).  They are decoupled because what a weight tile costs is latency, not work:
+// from the commit that frees a slot over the expansion, the proxy fence and the (remote) arrive to
+// the MMA thread's wake-up is more than two k-steps of MMAs, so the weight ring has to be deeper
+// than the three token stages that fit.
+constexpr int kPairBStages = 3;
+constexpr int kPairBStage = 2 * kPairBHalf;  // 32 KB
+__host__ __device__ constexpr int pair_a_stages(int type) {
+  const int fit = (227 * 1024 - 1024 - 256 - raw_bytes(type, true) - kPairBStages * kPairBStage) / kATile;
+  return fit < 6 ? fit : 6;
+}
+
+template <int TYPE>
+__global__ void __launch_bounds__(kPairThreads, 1)
+    gemm_prefill_pair_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                             const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) {
+  constexpr int kRawStage = raw_stage_bytes(TYPE);
+  constexpr int kSA = pair_a_stages(TYPE), kSB = kPairBStages;
+  static_assert(kSA >= 2, "at least two weight stages");
+  constexpr int kDequantWarps = dequant_warps(TYPE, true);
+  constexpr int kHalves = kDequantWarps >= 8 ? 1 : 2;
+  static_assert(kDequantWarps == 16, "the warp roles below assume sixteen dequant warps");
+  constexpr bool kQuarter = kDequantWarps == 16;
+  constexpr int kNSub = 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
+  uint8_t *smem_b = smem + kSA * kATile;
+  uint8_t *raw_win = smem_b + kSB * kPairBStage;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(raw_win + raw_bytes(TYPE, true));
+  // bars: full_a[SA] | full_b[SB][2] | empty_a[SA] | empty_b[SB][2] | acc_full | raw_full[2] |
+  // raw_empty[2]; the full barriers are used in CTA 0 only
+  constexpr int kFullB = kSA, kEmptyA = kFullB + kSB * kNSub, kEmptyB = kEmptyA + kSA;
+  constexpr int kAccBar = kEmptyB + kSB * kNSub;
+  static_assert((kAccBar + 5) * 8 + 4 <= 256, "barriers fit their 256 bytes");
+  uint64_t *raw_bars = bars + kAccBar + 1;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(raw_bars + 4);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();  // 0 issues the MMAs
+  const int n0 = blockIdx.x * kBM, m0 = blockIdx.y * kPairBN;
+  const int raw_n0 = min(n0, p.n_out - kBM);
+  const int nks = p.k_in / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kSA; s++) {
+      mbar_init(smem_u32(&bars[s]), 2 * kDequantWarps);    // full_a: the dequant warps of both CTAs
+      mbar_init(smem_u32(&bars[kEmptyA + s]), 1);          // empty_a: tcgen05.commit
+    }
+    for (int s = 0; s < kSB; s++) {
+      for (int h = 0; h < kNSub; h++) {
+        mbar_init(smem_u32(&bars[kFullB + s * kNSub + h]), 1);   // full_b: CTA 0's TMA thread + both CTAs' bytes
+        mbar_init(smem_u32(&bars[kEmptyB + s * kNSub + h]), 1);  // empty_b: tcgen05.commit
+      }
+    }
+    mbar_init(smem_u32(&bars[kAccBar]), 1);                // accumulator complete
+    mbar_init(smem_u32(&raw_bars[0]), 1);
+    mbar_init(smem_u32(&raw_bars[1]), 1);
+    mbar_init(smem_u32(&raw_bars[2]), kDequantWarps);
+    mbar_init(smem_u32(&raw_bars[3]), kDequantWarps);
+    mbar_fence_init();
+  }
+  if (warp == 1) {  // the same warp of both CTAs takes part in the pair's allocation
+    tmem_alloc_pair(smem_u32(tmem_slot), kPairBN);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();  // barriers initialised and TMEM allocated in both CTAs
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  using R = Roles<true>;
+  if (warp == R::tma_warp) {
+    // ---------------------------------------------------------------- activations and raw weights via TMA
+    if (lane == 0) {
+      const int nsb = (nks + 3) >> 2;
+      auto issue_raw = [&](int sbl) {
+        const uint32_t full = smem_u32(&raw_bars[sbl & 1]);
+        mbar_arrive_expect_tx(full, kRawStage);
+        if constexpr (TYPE == kQ6_K) {
+          const int x0 = q6_window_start(sbl, (int)p.row_bytes);
+          tma_load_2d(smem_u32(raw_win + (sbl & 1) * kRawStage), &tmap_w, x0, raw_n0, full);
+          tma_load_2d(smem_u32(raw_win + (sbl & 1) * kRawStage + kRawBox), &tmap_w, x0 + 128, raw_n0, full);
+        } else {
+          tma_load_2d(smem_u32(raw_win + (sbl & 1) * kRawStage), &tmap_w, Sb<TYPE>::bytes * sbl, raw_n0, full);
+        }
+      };
+      issue_raw(0);
+      for (int ks = 0; ks < nks; ks++) {
+        const int s = ks % kSB;
+        const int sbl = ks >> 2;
+        if ((ks & 3) == 0 && sbl + 1 < nsb) {
+          if (sbl >= 1) mbar_wait(smem_u32(&raw_bars[2 + ((sbl & 1) ^ 1)]), ((sbl - 1) >> 1) & 1);
+          issue_raw(sbl + 1);
+        }
+#pragma unroll
+        for (int h = 0; h < kNSub; h++) {
+          mbar_wait(smem_u32(&bars[kEmptyB + s * kNSub + h]), ((ks / kSB) & 1) ^ 1);
+          const uint32_t full = smem_u32(&bars[kFullB + s * kNSub + h]);
+          if (rank == 0) mbar_arrive_expect_tx(full, 2 * kPairBHalf);  // both CTAs' halves of the box
+          tma_load_2d_pair(smem_u32(smem_b + s * kPairBStage + h * kPairBHalf), &tmap_x, ks * kBK,
+                           m0 + h * 256 + (int)rank * 128, map_to_cta(full, 0));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issue (CTA 0)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = idesc_bf16(256, 256);
+      // the barriers' addresses in both CTAs, as cluster addresses (linear in the barrier index)
+      const uint32_t bars0 = map_to_cta(smem_u32(&bars[0]), 0), bars1 = map_to_cta(smem_u32(&bars[0]), 1);
+      const uint32_t bar0 = smem_u32(&bars[0]);
+      const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem)), b_lo0 = smem_desc_lo(smem_u32(smem_b));
+      uint32_t sa = 0, pa = 0, s = 0, ph = 0;
+      for (int ks = 0; ks < nks; ks++) {
+        mbar_wait(bar0 + 8 * sa, pa);
+#pragma unroll
+        for (int h = 0; h < kNSub; h++) {
+          mbar_wait(bar0 + 8 * (kFullB + s * kNSub + h), ph);
+          tc_fence_after();
+          umma4_bf16_pair(tmem_base + h * 256, a_lo0 + sa * (kATile >> 4),
+                          b_lo0 + ((s * kPairBStage + h * kPairBHalf) >> 4), idesc, ks != 0);
+          umma_commit_pair(bars0 + 8 * (kEmptyB + s * kNSub + h));
+          umma_commit_pair(bars1 + 8 * (kEmptyB + s * kNSub + h));
+        }
+        umma_commit_pair(bars0 + 8 * (kEmptyA + sa));
+        umma_commit_pair(bars1 + 8 * (kEmptyA + sa));
+        if (++sa == kSA) {
+          sa = 0;
+          pa ^= 1;
+        }
+        if (++s == kSB) {
+          s = 0;
+          ph ^= 1;
+        }
+      }
+      umma_commit_pair(bars0 + 8 * kAccBar);
+      umma_commit_pair(bars1 + 8 * kAccBar);
+    }
+  } else if (R::is_dequant(warp)) {
+    // ---------------------------------------------------------------- dequant producers
+    const int dt = R::dequant_index(warp) * 32 + lane;
+    const int r = dt & 127;
+    const int part = dt >> 7;
+    const int h0 = kQuarter ? part >> 1 : part;
+    const int q2 = kQuarter ? part & 1 : 0;
+    const bool valid = n0 + r < p.n_out;
+    Raw<TYPE> cur[kHalves];
+    const int rr = max(0, min(r + n0 - raw_n0, kBM - 1));  // this thread's row of the raw box
+    for (int ks = 0; ks < nks; ks++) {
+      const int s = ks % kSA;
+      const int sbl = ks >> 2, buf = sbl & 1;
+      if ((ks & 3) == 0) mbar_wait(smem_u32(&raw_bars[buf]), (sbl >> 1) & 1);
+      if constexpr (kQuarter)
+        fetch_quarter_from<TYPE>(raw_win + buf * kRawStage + rr * Sb<TYPE>::bytes, ks & 3, q2, cur[0]);
+      else if constexpr (TYPE == kQ6_K)
+        fetch_staged_q6<kHalves>(raw_win + buf * kRawStage, rr,
+                                 210 * sbl - q6_window_start(sbl, (int)p.row_bytes), ks & 3, h0, cur);
+      else
+        fetch_raw_from<TYPE>(raw_win + buf * kRawStage + rr * Sb<TYPE>::bytes, ks & 3, h0, cur[0]);
+      if ((ks & 3) == 3 || ks == nks - 1) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&raw_bars[2 + buf]));
+      }
+      mbar_wait(smem_u32(&bars[kEmptyA + s]), ((ks / kSA) & 1) ^ 1);
+#pragma unroll
+      for (int i = 0; i < kHalves; i++)
+        expand_kstep<TYPE, kQuarter>(cur[i], ks, h0 + i, smem + s * kATile, r, valid, q2);
+      fence_async_smem();  // generic-proxy writes -> tensor core
+      __syncwarp();
+      if (lane == 0) mbar_arrive_in_cluster(map_to_cta(smem_u32(&bars[s]), 0));
+    }
+  }
+  // ---------------------------------------------------------------- epilogue (own 128 rows)
+  if (R::in_epilogue(warp)) {
+    mbar_wait(smem_u32(&bars[kAccBar]), 0);
+    tc_fence_after();
+    const int q = warp & 3;
+    const int n = n0 + 32 * q + lane;
+    const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16);
+    constexpr int kCols = kPairBN / 4;
+    const int cbeg = R::epilogue_chunk(warp) * kCols;
+#pragma unroll 1
+    for (int c0 = cbeg; c0 < cbeg + kCols; c0 += 32) {
+      uint32_t v[32];
+      tmem_ld32(taddr + c0, v);
+      tmem_ld_wait();
+      if (n < p.n_out) {
+#pragma unroll
+        for (int jj = 0; jj < 32; jj++) {
+          const int m = m0 + c0 + jj;
+          if (m < p.m_rows) {
+            const float f = __uint_as_float(v[jj]);
+            if (p.out_bf16)
+              reinterpret_cast<__nv_bfloat16 *>(p.y)[(long long)m * p.n_out + n] = __float2bfloat16_rn(f);
+            else
+              reinterpret_cast<float *>(p.y)[(long long)m * p.n_out + n] = f;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  cluster_sync_all();  // both epilogues done: neither CTA's TMEM or shared memory is in use any more
+  if (warp == 1) tmem_dealloc_pair(tmem_base, kPairBN);
 }
 
 // ---------------------------------------------------------------------------- host side
@@ -882,6 +1263,69 @@ int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows
   return (int)cudaGetLastError();
 }
 
+int g_prefill_pair = 1;  // diagnostics: 0 = the one-CTA kernel for 512-token tiles too
+
+// The 2-CTA kernel: 256 weight rows x 512 tokens per cluster of two CTAs.
+template <int TYPE>
+int launch_pair(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows, int n_out,
+                int k_in, cudaStream_t s) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (!encode) return COGNI_QMM_ERR_DEVICE;
+  const long long row_bytes = (long long)(k_in / 256) * Sb<TYPE>::bytes;
+  CUtensorMap tmap, tmap_w;
+  {
+    const cuuint64_t wdims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)n_out};
+    const cuuint64_t wstrides[1] = {(cuuint64_t)row_bytes};
+    const cuuint32_t wbox[2] = {TYPE == kQ6_K ? 128u : (cuuint32_t)Sb<TYPE>::bytes, 128};
+    const cuuint32_t westr[2] = {1, 1};
+    CUresult wr = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(d_w), wdims,
+                         wstrides, wbox, westr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         TYPE == kQ6_K ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (wr != CUDA_SUCCESS) return (int)wr;
+  }
+  const cuuint64_t dims[2] = {(cuuint64_t)k_in, (cuuint64_t)m_rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)k_in * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kBK, 128};  // a CTA's 128 tokens of a 256-token box
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult cr = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(d_x), dims,
+                       strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (cr != CUDA_SUCCESS) return (int)cr;
+  constexpr int smem = pair_a_stages(TYPE) * kATile + kPairBStages * kPairBStage + raw_bytes(TYPE, true) +
+                       1024 /*alignment*/ + 256 /*barriers*/;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_prefill_pair_kernel<TYPE>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured[dev] = true;
+  }
+  GemmParams p;
+  p.w = static_cast<const uint8_t *>(d_w);
+  p.y = d_y;
+  p.m_rows = m_rows; p.n_out = n_out; p.k_in = k_in;
+  p.out_bf16 = out_type == COGNI_QMM_OUT_BF16;
+  p.row_bytes = row_bytes;
+  p.splits = 1;
+  p.ks_per_split = k_in / kBK;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * ((n_out + 2 * kBM - 1) / (2 * kBM)), (m_rows + kPairBN - 1) / kPairBN, 1);
+  cfg.blockDim = dim3(kPairThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, gemm_prefill_pair_kernel<TYPE>, tmap, tmap_w, p);
+}
+
 template <int TYPE>
 int launch_typed(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows, int n_out,
                  int k_in, cudaStream_t s) {
@@ -933,6 +1377,10 @@ int launch_typed(const void *d_w, const void *d_x, void *d_y, int out_type, int 
   {
     const long long row_bytes = (long long)(k_in / 256) * Sb<TYPE>::bytes;
     if (TYPE != kQ8_0 && row_bytes % 16 == 0 && n_out >= kBM && g_prefill_stage_raw) {
+      if constexpr (TYPE == kQ4_K || TYPE == kQ5_K) {
+        if (bn == 512 && splits == 1 && g_prefill_pair)
+          return launch_pair<TYPE>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, s);
+      }
       if (bn == 512) return launch<TYPE, 512, true>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
       if (bn == 256) return launch<TYPE, 256, true>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
       return launch<TYPE, 128, true>(d_w, d_x, d_y, out_type, m_rows, n_out, k_in, splits, s);
@@ -960,6 +1408,7 @@ int launch_gemm_prefill(int type, const void *d_w, const void *d_x_bf16, void *d
 void gemm_prefill_set_tile(int bn) { g_prefill_force_bn = bn; }
 void gemm_prefill_set_split(int mode) { g_prefill_force_split = mode; }
 void gemm_prefill_set_stage_raw(int on) { g_prefill_stage_raw = on; }
+void gemm_prefill_set_pair(int on) { g_prefill_pair = on; }
 
 unsigned gemm_prefill_timeouts() {
   unsigned v = 0;

@@ -167,6 +167,7 @@ void gemv_imma_set_slabs(int n);
 void gemm_prefill_set_tile(int bn);
 void gemm_prefill_set_split(int mode);
 void gemm_prefill_set_stage_raw(int on);
+void gemm_prefill_set_pair(int on);
 
 // Kernel selection (dispatch.cu): picks the tiled kernel when the shape allows it, else the
 // general row-per-warp kernel.

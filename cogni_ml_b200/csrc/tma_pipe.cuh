@@ -84,6 +84,35 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
     }
   }
 }
+// The same wait with cluster-scope acquire: for a barrier that threads of the peer CTA of a
+// cluster arrive on after writing their own shared memory.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
+                                                  unsigned long long limit_ns = kPipeWaitLimitNs) {
+  if (mbar_try_wait_cluster(bar, parity, 0u)) return true;
+  const unsigned long long t0 = global_ns();
+  for (unsigned spin = 1;; spin++) {
+    if (mbar_try_wait_cluster(bar, parity, 20000u)) return true;
+    __nanosleep(spin < 4 ? 32 : 256);
+    if ((spin & 15u) == 0) {
+      if (*reinterpret_cast<volatile unsigned int *>(&g_pipe_wait_timeouts) != 0u) return false;
+      if (global_ns() - t0 > limit_ns) {
+        atomicAdd(&g_pipe_wait_timeouts, 1u);
+        return false;
+      }
+    }
+  }
+}
 // Acquire / release accesses to counters and flags in shared memory at CTA scope: the data they
 // publish is ordinary shared memory written before the release and read after the acquire.
 __device__ __forceinline__ int ld_acquire_shared(const int *p) {
