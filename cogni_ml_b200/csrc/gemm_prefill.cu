@@ -2,28 +2,28 @@
 //
 //     y[m, n] = sum_k bf16(x[m, k]) * bf16(dequant(W[n, k]))        fp32 accumulation in TMEM
 //
-// One CTA computes a 128 (weight rows n) x BN (tokens m) tile of y^T, BN = 128, 256 or 512:
+// One CTA computes a 128 (weight rows n) x BN (tokens m) tile of y^T, BN = 128, 256 or 512; for
+// Q4_K / Q5_K a 512-token tile is computed by a pair of CTAs over 256 weight rows (the 2-CTA
+// kernel further down, tcgen05 cta_group::2):
 //   * A operand = weights.  The raw GGUF superblocks of the tile's 128 rows reach shared memory by
 //     TMA, one superblock column at a time (the weights as a byte matrix [rows, row bytes]; double
 //     buffered), so the fetch is one instruction per column instead of one uncoalesced load per
-//     row and word.  Eight dequant warps (two threads per row, one per 32-element half of a
-//     k-step) read their row's block from there, rebuild the f32 weight with the reference's
-//     operation order (src/ml/gguf/dequant.cr), round it to bf16 and write a 128 x 64 K-major
-//     tile into shared memory in the 128-byte-swizzled canonical layout.  Q6_K rows that are not
-//     multiples of 16 bytes (in_dim not a multiple of 2048) cannot be described to TMA: their
-//     threads read global memory directly (four warps, one thread per row).
+//     row and word.  Dequant warps (sixteen for Q4_K / Q5_K: four threads per row, one per
+//     16-element quarter of a k-step; eight otherwise: two threads per row) read their row's block
+//     from there, rebuild the f32 weight (src/ml/gguf/dequant.cr), round it to bf16 and write a
+//     128 x 64 K-major tile into shared memory in the 128-byte-swizzled canonical layout.  Q6_K
+//     rows that are not multiples of 16 bytes (in_dim not a multiple of 2048) cannot be described
+//     to TMA: their threads read global memory directly (four warps, one thread per row).
 //   * B operand = activations.  One thread issues TMA tile loads (bf16 [<= 256 x 64] boxes,
-//     128-byte swizzle) per k-step.
+//     128-byte swizzle) per k-step; every box has its own full and empty barrier.
 //   * One thread issues tcgen05.mma (kind::f16, M = 128, N = min(BN, 256), K = 16) four times per
-//     k-step (eight for BN = 512: two accumulators of 256 columns fill the tensor memory), and
-//     tcgen05.commit releases the stage.
-//   * After the last k-step the dequant warps read the accumulator back with tcgen05.ld (each
-//     warp may read 32 TMEM lanes = 32 weight rows; the two warps of a lane quarter take half
-//     of the columns each) and store y[m, n]: for a fixed token a warp's 32 lanes write 32
-//     consecutive n, one 128-byte segment.
-// An mbarrier ring (up to four 48 KB stages, two 80 KB stages for BN = 512, as many as fit beside
-// the raw windows) decouples the three roles.  The dequant warps bound the kernel: wider token
-// tiles do less dequant work per flop.  Every wait is bounded (tma_pipe.cuh).
+//     k-step and box (a 512-token tile: two accumulators of 256 columns fill the tensor memory);
+//     tcgen05.commit releases the boxes and the weight tile.
+//   * After the last k-step warps read the accumulator back with tcgen05.ld (each warp may read
+//     the 32 TMEM lanes = 32 weight rows of its residue mod 4; the warps of a lane quarter share
+//     the columns) and store y[m, n]: for a fixed token a warp's 32 lanes write 32 consecutive n,
+//     one 128-byte segment.
+// mbarrier rings decouple the three roles.  Every wait is bounded (tma_pipe.cuh).
 #include <cuda.h>
 #include <cuda_bf16.h>
 
@@ -910,14 +910,14 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
 // tcgen05.mma.cta_group::2: each CTA dequantises its own 128 rows (the A operand of its half of
 // M = 256) and loads only 128 of the 256 tokens of every B box; the tensor cores of both SMs read
 // both halves.  Per k-step a CTA's shared memory then takes 32 KB of activations instead of 64 KB
-// and the MMAs read 64 KB instead of 96 KB, which is what bounds the one-CTA kernel (shared-memory
-// bandwidth: 185 KB of traffic per k-step against 1024 cycles of MMAs), and three 48 KB stages
-// fit where the one-CTA tile had two of 80 KB.
+// (half the L2 -> SM traffic of the one-CTA tile), which leaves room for five weight stages and
+// three token stages where the one-CTA tile has two stages of 80 KB.
 //   * CTA 0 of the pair issues the MMAs.  Its full barriers collect the arrivals of both CTAs'
 //     dequant warps (remote mbarrier arrives) and the bytes of both CTAs' TMA loads (the loads name
 //     CTA 0's barrier); the empty and accumulator barriers exist in both CTAs and are signalled by
 //     one tcgen05.commit each.
 //   * No load of this kernel is multicast.
+//   * The accumulation order is the one-CTA kernel's: the results are equal bit for bit.
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));

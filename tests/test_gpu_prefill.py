@@ -83,6 +83,40 @@ def test_gemm_staged_superblocks(cuda, oracle, engine, tile, qtype, m, n, k):
     assert engine.lib.cogni_qmm_wait_timeouts() == 0
 
 
+@pytest.mark.parametrize("qtype,m,n,k", [(Q4_K, 512, 512, 1024), (Q5_K, 700, 384, 2048),
+                                         (Q4_K, 1300, 260, 4352), (Q5_K, 37, 132, 512),
+                                         (Q4_K, 2048, 1280, 4096)])
+def test_gemm_cta_pairs_match_single_ctas(cuda, oracle, engine, qtype, m, n, k):
+    """512-token tiles of Q4_K / Q5_K run on clusters of two CTAs (tcgen05 cta_group::2: each CTA
+    dequantises 128 of the 256 weight rows and loads 128 of every 256 tokens).  The accumulation
+    order is the one-CTA kernel's, so the outputs must be equal bit for bit, launch after launch;
+    the shapes leave a pair whose second CTA has no valid row, ragged token boxes and a K that is
+    no multiple of the ring depths."""
+    w = synth.make_weight(qtype, n, k, seed=29, tensor_id=qtype)
+    dw = DeviceQuantWeight.upload(QuantWeight(w, qtype, n, k), cuda)
+    x = bf16_round(synth.make_activation(m, k, seed=29))
+    xd = torch.from_numpy(x).to(cuda).bfloat16()
+    lib = engine.lib
+    lib.cogni_qmm_set_kernel_choice(51)   # 512-token tiles
+    lib.cogni_qmm_set_kernel_choice(53)   # no split along K: the pair kernel takes whole rows
+    try:
+        lib.cogni_qmm_set_kernel_choice(58)
+        single = dw.gemm(xd).clone()
+        lib.cogni_qmm_set_kernel_choice(57)
+        for _ in range(20):
+            assert torch.equal(dw.gemm(xd), single)
+    finally:
+        lib.cogni_qmm_set_kernel_choice(57)
+        lib.cogni_qmm_set_kernel_choice(52)
+        lib.cogni_qmm_set_kernel_choice(48)
+    rb = len(w) // n
+    wq = np.stack([bf16_round(oracle.dequantize(qtype, w[c * rb:(c + 1) * rb], k)) for c in range(n)])
+    ref = x.astype(np.float64) @ wq.astype(np.float64).T
+    y = single.float().cpu().numpy()
+    assert np.abs(y - ref).max() <= 1e-4 * np.abs(ref).max()
+    assert lib.cogni_qmm_wait_timeouts() == 0
+
+
 @pytest.mark.parametrize("qtype,m,n,k", [(Q4_K, 300, 260, 4352), (Q6_K, 100, 132, 2048)])
 def test_gemm_last_row_tile_is_reproducible(cuda, engine, qtype, m, n, k):
     """A last row tile with four valid rows, launched many times: every launch must give the same
