@@ -1410,12 +1410,15 @@ __device__ __forceinline__ void mma_q6v2(const uint8_t *ra, const uint8_t *rb, c
 
 // ---------------------------------------------------------------------------- the kernel
 // VAR picks how much the instance carries: 0 the plain GEMV; 1 adds the fused prologues (RMSNorm,
-// SwiGLU) to the activation quantisers; 2 also splits row tiles over K slabs and exchanges its
-// outputs with the other GPUs.  The plain instance carries none of that code.
+// SwiGLU) to the activation quantisers; 2 also splits row tiles over K slabs, exchanges its outputs
+// with the other GPUs and reads activations that come out of an exchange; 3 is the plain GEMV that
+// only sends its outputs (whole rows, plain activations).  The plain instance carries none of
+// that code.
 template <int TYPE, int NB, int PAIR, int VAR>
 __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1)
     gemv_imma_kernel(const Params p) {
-  constexpr bool XT = VAR == 2, PRO = VAR >= 1;
+  // XT: K slabs and exchanged activations; XO: outputs go to the other GPUs
+  constexpr bool XT = VAR == 2, XO = VAR >= 2, PRO = VAR == 1 || VAR == 2;
   constexpr int kNW = consumer_warps(TYPE, PAIR, NB), kThreads = (kNW + kPW) * 32;
   using C = Cfg<TYPE>;
   using A = Area<TYPE>;
@@ -1524,7 +1527,7 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
   // exchanges completed on this GPU before this launch: the epoch its inputs carry (if they come
   // out of an exchange) and, plus one, the epoch its outputs get
   unsigned ex_epoch = 0;
-  if (XT && p.ex.epoch) {
+  if (XO && p.ex.epoch) {
     // (acquire: the ticket below must not be drawn before this load has been performed)
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(ex_epoch) : "l"(p.ex.epoch) : "memory");
     // The exchange is counted by the CTA that draws the last ticket: by then every CTA of this
@@ -1799,8 +1802,8 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
             } else {
               const long long as = p.addend_stride < 0 ? job.out_dim : p.addend_stride;
               const float a = job.addend ? job.addend[(long long)b * as + row] : 0.f;
-              const long long idx = (long long)b * (XT && p.y_pitch ? p.y_pitch : job.out_dim) + row;
-              if constexpr (XT) store_y(job.y, idx, a + v[i], p.ex, ex_epoch + 1u);
+              const long long idx = (long long)b * (XO && p.y_pitch ? p.y_pitch : job.out_dim) + row;
+              if constexpr (XO) store_y(job.y, idx, a + v[i], p.ex, ex_epoch + 1u);
               else job.y[idx] = a + v[i];
             }
           }
@@ -1837,8 +1840,8 @@ __global__ void __launch_bounds__((consumer_warps(TYPE, PAIR, NB) + kPW) * 32, 1
         } else {
           const long long as = p.addend_stride < 0 ? job.out_dim : p.addend_stride;
           const float a = job.addend ? job.addend[(long long)b * as + row] : 0.f;
-          const long long idx = (long long)b * (XT && p.y_pitch ? p.y_pitch : job.out_dim) + row;
-          if constexpr (XT) store_y(job.y, idx, a + v, p.ex, ex_epoch + 1u);
+          const long long idx = (long long)b * (XO && p.y_pitch ? p.y_pitch : job.out_dim) + row;
+          if constexpr (XO) store_y(job.y, idx, a + v, p.ex, ex_epoch + 1u);
           else job.y[idx] = a + v;
         }
       }
@@ -2000,7 +2003,9 @@ int launch_instance_x(const Params &p, size_t smem, int grid, cudaStream_t s) {
 }
 template <int TYPE, int NB, int PAIR>
 int launch_instance(const Params &p, size_t smem, int grid, cudaStream_t s) {
-  if (p.nslabs > 1 || p.ex.world > 1 || p.ex_wait) return launch_instance_x<TYPE, NB, PAIR, 2>(p, smem, grid, s);
+  if (p.nslabs > 1 || p.ex_wait || (p.ex.world > 1 && (p.x_up || p.norm_w)))
+    return launch_instance_x<TYPE, NB, PAIR, 2>(p, smem, grid, s);
+  if (p.ex.world > 1) return launch_instance_x<TYPE, NB, PAIR, 3>(p, smem, grid, s);
   if (p.x_up || p.norm_w) return launch_instance_x<TYPE, NB, PAIR, 1>(p, smem, grid, s);
   return launch_instance_x<TYPE, NB, PAIR, 0>(p, smem, grid, s);
 }
