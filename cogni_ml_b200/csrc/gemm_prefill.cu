@@ -73,9 +73,15 @@ __host__ __device__ constexpr int dequant_warps(int type, bool staged = false) {
 // 21) that sleep until the epilogue, where they read the TMEM lane quarter 1 that only warps of
 // their residue can; the dequant warps are the other warps up to 20.  With eight or four dequant
 // warps: warp 0 TMA, warp 1 MMA, the rest dequant.
+// Tiles narrower than 512 tokens are bound by the expansion, not by the MMAs: there the sixteen
+// dequant warps use all four schedulers (measured tile times at in_dim 4096, Q4_K, 128 / 256
+// tokens: 44.1 / 48.4 us with the isolated layout against 39.1 / 44.5 us without).
 constexpr int kIsoWarps = 22;
-__host__ __device__ constexpr int threads_for(int type, bool staged = false) {
-  return dequant_warps(type, staged) == 16 ? 32 * kIsoWarps : 64 + 32 * dequant_warps(type, staged);
+__host__ __device__ constexpr bool isolate_mma_warp(int type, bool staged, int bn) {
+  return dequant_warps(type, staged) == 16 && bn == 512;
+}
+__host__ __device__ constexpr int threads_for(int type, bool staged = false, int bn = 512) {
+  return isolate_mma_warp(type, staged, bn) ? 32 * kIsoWarps : 64 + 32 * dequant_warps(type, staged);
 }
 template <bool ISO> struct Roles {
   static constexpr int tma_warp = ISO ? 5 : 0;
@@ -665,7 +671,7 @@ __device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, int h
 
 // ---------------------------------------------------------------------------- the kernel
 template <int TYPE, int BN, bool STAGED>
-__global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
+__global__ void __launch_bounds__(threads_for(TYPE, STAGED, BN), 1)
     gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
                         const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) {
   constexpr int kRawStage = raw_stage_bytes(TYPE);
@@ -730,7 +736,7 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  using R = Roles<kQuarter>;
+  using R = Roles<isolate_mma_warp(TYPE, STAGED, BN)>;
   if (warp == R::tma_warp) {
     // ---------------------------------------------------------------- activations via TMA
     if (lane == 0) {
@@ -875,7 +881,7 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED), 1)
     const int n = n0 + 32 * q + lane;
     const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16);
     // the warps of a lane quarter take an equal share of the token columns each
-    constexpr int kCols = BN / (kQuarter ? 4 : kDequantWarps / 4);
+    constexpr int kCols = BN / (isolate_mma_warp(TYPE, STAGED, BN) ? 4 : kDequantWarps / 4);
     const int cbeg = R::epilogue_chunk(warp) * kCols;
 #pragma unroll 1
     for (int c0 = cbeg; c0 < cbeg + kCols; c0 += 32) {
@@ -1259,7 +1265,7 @@ int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid((n_out + kBM - 1) / kBM, (m_rows + BN - 1) / BN, splits);
-  gemm_prefill_kernel<TYPE, BN, STAGED><<<grid, threads_for(TYPE, STAGED), smem, s>>>(tmap, tmap_w, p);
+  gemm_prefill_kernel<TYPE, BN, STAGED><<<grid, threads_for(TYPE, STAGED, BN), smem, s>>>(tmap, tmap_w, p);
   return (int)cudaGetLastError();
 }
 
@@ -1330,9 +1336,9 @@ template <int TYPE>
 int launch_typed(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows, int n_out,
                  int k_in, cudaStream_t s) {
   // Token-tile width: wider tiles do less dequant work per flop, narrower ones fill the SMs in
-  // fewer, fuller waves.  Measured time of a tile of 128 / 256 / 512 tokens (in_dim 4096, us):
-  // Q4_K 34 / 42 / 73, Q5_K 36 / 44 / 73, IQ4_NL 43 / 48 / 73, Q6_K 54 / 60 / 75, Q8_0 54 / 66 / 85
-  // (at 512 tokens the tensor pipe is what bounds every type).  Pick the width with the least
+  // fewer, fuller waves.  Measured time of a tile of 128 / 256 / 512 tokens (in_dim 4096, one wave,
+  // us): Q4_K 39 / 45 / 61 (the 512-token tile on a CTA pair; 63 on one CTA), Q5_K 40 / 45 / 60,
+  // IQ4_NL 49 / 52 / 66, Q6_K 60 / 66 / 79, Q8_0 58 / 67 / 81.  Pick the width with the least
   // waves x tile time.
   static int sms_of[64] = {0};  // per device: a process may drive GPUs of different sizes
   int dev = 0;
@@ -1344,15 +1350,15 @@ int launch_typed(const void *d_w, const void *d_x, void *d_y, int out_type, int 
     if (dev >= 0 && dev < 64) sms_of[dev] = sms;
   }
   const long long row_tiles = (n_out + kBM - 1) / kBM;
-  const double rel256 = TYPE == kQ4_K || TYPE == kQ5_K || TYPE == kQ8_0 ? 1.22 : 1.12;
-  const double rel512 = TYPE == kQ4_K || TYPE == kQ5_K ? 2.08 : TYPE == kIQ4_NL ? 1.72 : TYPE == kQ8_0 ? 1.57 : 1.39;
+  const double rel256 = TYPE == kQ4_K || TYPE == kQ5_K || TYPE == kQ8_0 ? 1.15 : 1.10;
+  const double rel512 = TYPE == kQ4_K || TYPE == kQ5_K ? 1.55 : TYPE == kIQ4_NL ? 1.37 : TYPE == kQ8_0 ? 1.41 : 1.31;
   // Few row tiles against many SMs (a down projection at a short prompt): two CTAs per tile take
   // half of K each and add their partial tiles onto a zeroed f32 y.  Two addends commute, so the
   // result stays independent of the order; more splits would not.  The price is the memset of y
   // and read-modify-write instead of plain stores: about 12 bytes of HBM traffic per output
   // element, weighed here against the measured time of a 128-token tile's k-step (microseconds).
   const bool may_split = out_type == COGNI_QMM_OUT_F32 && k_in / kBK >= 16 && g_prefill_force_split != 1;
-  const double us_per_kstep = TYPE == kQ4_K || TYPE == kQ5_K ? 0.55 : TYPE == kIQ4_NL ? 0.67 : 0.85;
+  const double us_per_kstep = TYPE == kQ4_K || TYPE == kQ5_K ? 0.61 : TYPE == kIQ4_NL ? 0.76 : 0.92;
   const double tile_us = us_per_kstep * (k_in / kBK);
   const double split_us = 12.0 * (double)m_rows * (double)n_out / 6.0e6;
   auto cost = [&](int bn, double rel, int splits) {
