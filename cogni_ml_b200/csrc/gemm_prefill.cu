@@ -536,22 +536,26 @@ template <int NH>
 __device__ __forceinline__ void fetch_staged_q6(const uint8_t *win, int r, int pad, int j, int h0,
                                                 Raw<kQ6_K> (&dst)[NH]) {
   const int n = j >> 1;
-  lds_words<8>(win, r, pad + 64 * n + 32 * h0, dst[0].ql);
-  if constexpr (NH == 2) lds_words<8>(win, r, pad + 64 * n + 32, dst[1].ql);
-  lds_words<8>(win, r, pad + 128 + 32 * n, dst[0].qh);
+  // The two k-steps of a half n of the superblock (j = 2n, 2n + 1) use the same ql bytes (low /
+  // high nibbles) and the same qh bytes (bit pairs 2 kk): they are fetched at the even k-step and
+  // stay in `dst` for the odd one (a CTA's first k-step is a multiple of four).
+  if ((j & 1) == 0) {
+    lds_words<8>(win, r, pad + 64 * n + 32 * h0, dst[0].ql);
+    if constexpr (NH == 2) lds_words<8>(win, r, pad + 64 * n + 32, dst[1].ql);
+    lds_words<8>(win, r, pad + 128 + 32 * n, dst[0].qh);
+    const int doff = pad + 208;
+    dst[0].d = *reinterpret_cast<const unsigned short *>(
+        win + (doff >> 7) * kRawBox + r * 128 + ((((doff >> 4) & 7) ^ (r & 7)) << 4) + (doff & 15));
+    if constexpr (NH == 2) {
+#pragma unroll
+      for (int w = 0; w < 8; w++) dst[1].qh[w] = dst[0].qh[w];
+      dst[1].d = dst[0].d;
+    }
+  }
   uint32_t scw[1];
   lds_words<1>(win, r, pad + 192 + 8 * n + 4 * (j & 1), scw);
-  const int doff = pad + 208;
-  const uint32_t d = *reinterpret_cast<const unsigned short *>(
-      win + (doff >> 7) * kRawBox + r * 128 + ((((doff >> 4) & 7) ^ (r & 7)) << 4) + (doff & 15));
   dst[0].sc = scw[0];
-  dst[0].d = d;
-  if constexpr (NH == 2) {
-#pragma unroll
-    for (int w = 0; w < 8; w++) dst[1].qh[w] = dst[0].qh[w];
-    dst[1].sc = scw[0];
-    dst[1].d = d;
-  }
+  if constexpr (NH == 2) dst[1].sc = scw[0];
 }
 
 // Rebuilds half h (32 weights: chunks 4h .. 4h+3) of k-step ks of tile row r as bf16 and stores
