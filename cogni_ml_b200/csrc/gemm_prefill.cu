@@ -57,8 +57,8 @@ __host__ __device__ constexpr int stages_for(int bn, int raw = 0) {
 }
 // Dequant warps: sixteen for Q4_K / Q5_K staged by TMA (four threads per tile row, one per
 // 16-element quarter of a k-step: the expansion is a chain of dependent conversions, and two warps
-// per scheduler could not hide its latencies; Q6_K, whose quarters would share the qh bytes and
-// repeat the funnel shifts of its unaligned block, measured slower that way); eight (two threads
+// per scheduler could not hide its latencies; Q6_K measured slower that way on one CTA, 1144
+// against 1216 TFLOP/s, and the same on a CTA pair); eight (two threads
 // per tile row, one per 32-element half of a k-step); four (one thread per row, both halves) for
 // Q6_K read directly from global memory, whose loads are the bound there.
 __host__ __device__ constexpr int dequant_warps(int type, bool staged = false) {
@@ -353,7 +353,7 @@ __device__ __forceinline__ void lds_words(const uint8_t *win, int r, int off, ui
 template <int TYPE> struct Raw;
 template <> struct Raw<kQ4_K> { uint4 hdr, q0, q1; };
 template <> struct Raw<kQ5_K> { uint4 hdr, h0, h1, q0, q1; };
-template <> struct Raw<kQ6_K> { uint32_t ql[8], qh[8], sc; uint32_t d; };
+template <> struct Raw<kQ6_K> { uint32_t ql[8], qh[8], sc; uint32_t d; uint32_t scw[4]; };  // scw: the superblock's 16 scales (staged path)
 template <> struct Raw<kQ8_0> { uint32_t q[8]; uint32_t d; };  // one 34-byte block: half a k-step
 template <> struct Raw<kIQ4_NL> { uint32_t q[4]; uint32_t d; };  // one 18-byte block: half a k-step
 
@@ -552,10 +552,10 @@ __device__ __forceinline__ void fetch_staged_q6(const uint8_t *win, int r, int p
       dst[1].d = dst[0].d;
     }
   }
-  uint32_t scw[1];
-  lds_words<1>(win, r, pad + 192 + 8 * n + 4 * (j & 1), scw);
-  dst[0].sc = scw[0];
-  if constexpr (NH == 2) dst[1].sc = scw[0];
+  // the 16 scales of the superblock: fetched with its first k-step; k-step j uses word j
+  if (j == 0) lds_words<4>(win, r, pad + 192, dst[0].scw);
+  dst[0].sc = j == 0 ? dst[0].scw[0] : j == 1 ? dst[0].scw[1] : j == 2 ? dst[0].scw[2] : dst[0].scw[3];
+  if constexpr (NH == 2) dst[1].sc = dst[0].sc;
 }
 
 // Rebuilds half h (32 weights: chunks 4h .. 4h+3) of k-step ks of tile row r as bf16 and stores
@@ -1342,7 +1342,7 @@ int launch_typed(const void *d_w, const void *d_x, void *d_y, int out_type, int 
   // Token-tile width: wider tiles do less dequant work per flop, narrower ones fill the SMs in
   // fewer, fuller waves.  Measured time of a tile of 128 / 256 / 512 tokens (in_dim 4096, one wave,
   // us): Q4_K 39 / 45 / 61 (the 512-token tile on a CTA pair; 63 on one CTA), Q5_K 40 / 45 / 60,
-  // IQ4_NL 49 / 52 / 66, Q6_K 60 / 66 / 79, Q8_0 58 / 67 / 81.  Pick the width with the least
+  // IQ4_NL 49 / 52 / 66, Q6_K 53 / 59 / 69, Q8_0 58 / 67 / 81.  Pick the width with the least
   // waves x tile time.
   static int sms_of[64] = {0};  // per device: a process may drive GPUs of different sizes
   int dev = 0;
@@ -1362,7 +1362,7 @@ int launch_typed(const void *d_w, const void *d_x, void *d_y, int out_type, int 
   // and read-modify-write instead of plain stores: about 12 bytes of HBM traffic per output
   // element, weighed here against the measured time of a 128-token tile's k-step (microseconds).
   const bool may_split = out_type == COGNI_QMM_OUT_F32 && k_in / kBK >= 16 && g_prefill_force_split != 1;
-  const double us_per_kstep = TYPE == kQ4_K || TYPE == kQ5_K ? 0.61 : TYPE == kIQ4_NL ? 0.76 : 0.92;
+  const double us_per_kstep = TYPE == kQ4_K || TYPE == kQ5_K ? 0.61 : TYPE == kIQ4_NL ? 0.76 : TYPE == kQ6_K ? 0.83 : 0.92;
   const double tile_us = us_per_kstep * (k_in / kBK);
   const double split_us = 12.0 * (double)m_rows * (double)n_out / 6.0e6;
   auto cost = [&](int bn, double rel, int splits) {
