@@ -486,6 +486,22 @@ def test_gemv_k_slabs(cuda, oracle, engine, kernel_choice, qtype, in_dim, slabs,
         assert int(idx[b]) == oracle.top1(logits[b])[0]
 
 
+@pytest.mark.parametrize("qtype", [Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL])
+@pytest.mark.parametrize("in_dim", [32768, 32768 + 256])
+@pytest.mark.parametrize("batch", [1, 8])
+def test_gemv_longest_rows(cuda, oracle, engine, kernel_choice, qtype, in_dim, batch):
+    """Rows of 32768 columns are the longest the tiled kernel takes (128 work items per row tile);
+    one superblock more goes to the row-per-warp kernel.  Either way the call must succeed and
+    agree with the oracle, with the residual added once."""
+    out_dim = 16 * 5 + 3
+    w, x, y, add = run_gemv(cuda, qtype, out_dim, in_dim, batch, seed=71, addend="residual")
+    ref = np.stack([oracle.matmul_add(x[b], 1, in_dim, w, qtype, out_dim, add["residual"][b],
+                                      threads=oracle.max_threads()) for b in range(batch)])
+    assert not np.isnan(y).any()
+    assert_close(y, ref, f"type {qtype} {out_dim}x{in_dim} batch {batch}")
+    assert engine.lib.cogni_qmm_wait_timeouts() == 0
+
+
 @pytest.mark.parametrize("qtype,batch,out_dim", [(IQ4_NL, 1, 2000), (IQ4_NL, 2, 5000), (IQ4_NL, 1, 300),
                                                  (Q4_K, 3, 4000), (Q6_K, 5, 2500), (Q8_0, 1, 1000)])
 def test_fused_top1_stays_inside_an_exactly_sized_scratch(cuda, engine, oracle, kernel_choice, qtype, batch, out_dim):
