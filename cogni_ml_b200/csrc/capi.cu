@@ -89,8 +89,12 @@ int cogni_qmm_set_kernel_choice(int choice) {
     gemm_prefill_set_pair(choice == 57);
     return COGNI_QMM_OK;
   }
-  if (choice >= 52 && choice <= 54) {  // prefill split along K: automatic / never / wherever allowed
+  if (choice >= 52 && choice <= 54) {  // prefill split along K: automatic / never / two splits wherever allowed
     gemm_prefill_set_split(choice - 52);
+    return COGNI_QMM_OK;
+  }
+  if (choice == 59) {  // prefill split along K: four ordered splits wherever allowed
+    gemm_prefill_set_split(3);
     return COGNI_QMM_OK;
   }
   if (choice >= 27 && choice <= 30) {  // at least 1 .. 4 column ranges per row of the tiled GEMV

@@ -25,6 +25,7 @@
 //     one 128-byte segment.
 // mbarrier rings decouple the three roles.  Every wait is bounded (tma_pipe.cuh).
 #include <cuda.h>
+#include <mutex>
 #include <cuda_bf16.h>
 
 #include "qmm_common.cuh"
@@ -105,6 +106,7 @@ struct GemmParams {
   int m_rows, n_out, k_in, out_bf16;
   int ks_per_split;  // k-steps per blockIdx.z; with two splits the partial tiles are added onto a zeroed y
   int splits;
+  unsigned *turns;   // four splits: [tile][4] turn counters that order the partial tiles' additions (else nullptr)
   long long row_bytes;
 };
 
@@ -673,6 +675,32 @@ __device__ __forceinline__ void expand_kstep(const Raw<TYPE> &raw, int ks, int h
   }
 }
 
+// Ordered split along K.  Four CTAs of a tile take a quarter of K each and add their partial tiles
+// into y (the first part of every group is stored, so y is not zeroed).  Float addition does not commute over four addends, so the order is fixed: the
+// tile's columns form four groups, split z adds its part of group (z + t) mod 4 at step t, and a
+// turn counter per (tile, group) admits the steps in order; in every step the four splits work on
+// different groups.  The order depends on the group only, so every launch gives the same bits.
+// The four CTAs of a tile must run at the same time: the host uses this only for grids of at most
+// one CTA per SM.  The wait is bounded like every wait.
+__device__ unsigned g_prefill_turns[8][64 * 4];  // [stream slot][tile][group], zero between launches
+
+__device__ __forceinline__ void wait_turn(const unsigned *turn, unsigned want) {
+  const unsigned long long t0 = global_ns();
+  for (unsigned spin = 0;; spin++) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(turn) : "memory");
+    if (v == want) return;
+    __nanosleep(64);
+    if ((spin & 63u) == 63u) {
+      if (pipe_broken()) return;
+      if (global_ns() - t0 > kPipeWaitLimitNs) {
+        atomicAdd(&g_pipe_wait_timeouts, 1u);
+        return;
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------- the kernel
 template <int TYPE, int BN, bool STAGED>
 __global__ void __launch_bounds__(threads_for(TYPE, STAGED, BN), 1)
@@ -887,8 +915,45 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED, BN), 1)
     // the warps of a lane quarter take an equal share of the token columns each
     constexpr int kCols = BN / (isolate_mma_warp(TYPE, STAGED, BN) ? 4 : kDequantWarps / 4);
     const int cbeg = R::epilogue_chunk(warp) * kCols;
+    if constexpr ((kCols / 4) % 32 == 0) {
+      if (p.turns) {  // four splits: the groups of this warp's columns in the order of the turns
+        constexpr int kEpiThreads = 32 * (isolate_mma_warp(TYPE, STAGED, BN) ? 16 : kDequantWarps);
+        constexpr int kG = kCols / 4;
+        unsigned *turn = p.turns + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 4;
+        const bool leader = threadIdx.x == (isolate_mma_warp(TYPE, STAGED, BN) ? 0 : 64);
 #pragma unroll 1
-    for (int c0 = cbeg; c0 < cbeg + kCols; c0 += 32) {
+        for (int t = 0; t < 4; t++) {
+          const int g = ((int)blockIdx.z + t) & 3;
+          if (leader) wait_turn(turn + g, (unsigned)t);
+          asm volatile("bar.sync 2, %0;" ::"n"(kEpiThreads) : "memory");
+#pragma unroll 1
+          for (int c0 = cbeg + g * kG; c0 < cbeg + (g + 1) * kG; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(taddr + c0, v);
+            tmem_ld_wait();
+            if (n < p.n_out) {
+#pragma unroll
+              for (int jj = 0; jj < 32; jj++) {
+                const int m = m0 + c0 + jj;
+                if (m < p.m_rows) {
+                  float *dst = reinterpret_cast<float *>(p.y) + (long long)m * p.n_out + n;
+                  if (t == 0) *dst = __uint_as_float(v[jj]);  // the group's first part: y needs no zeroing
+                  else atomicAdd(dst, __uint_as_float(v[jj]));
+                }
+              }
+            }
+          }
+          __threadfence();  // this split's additions are performed before the next split's turn
+          asm volatile("bar.sync 2, %0;" ::"n"(kEpiThreads) : "memory");
+          if (leader)
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(turn + g), "r"(t == 3 ? 0u : (unsigned)(t + 1))
+                         : "memory");
+        }
+      }
+    }
+    const bool plain_epilogue = !((kCols / 4) % 32 == 0 && p.turns);
+#pragma unroll 1
+    for (int c0 = cbeg; plain_epilogue && c0 < cbeg + kCols; c0 += 32) {
       uint32_t v[32];
       tmem_ld32(taddr + c0, v);
       tmem_ld_wait();
@@ -1212,9 +1277,36 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// The turn counters of the ordered four-way split: one region of the static device array per
+// (device, stream) that has used it, so that launches on different streams do not share counters.
+constexpr int kTurnSlots = 8, kTurnTiles = 64;
+std::mutex g_turn_mutex;
+unsigned *g_turn_base[64] = {nullptr};
+cudaStream_t g_turn_streams[64][kTurnSlots];
+int g_turn_nstreams[64] = {0};
+unsigned *turn_region(cudaStream_t s) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(g_turn_mutex);
+  if (!g_turn_base[dev]) {
+    void *a = nullptr;
+    if (cudaGetSymbolAddress(&a, g_prefill_turns) != cudaSuccess || !a) return nullptr;
+    g_turn_base[dev] = static_cast<unsigned *>(a);
+  }
+  int slot = -1;
+  for (int i = 0; i < g_turn_nstreams[dev]; i++)
+    if (g_turn_streams[dev][i] == s) slot = i;
+  if (slot < 0) {
+    if (g_turn_nstreams[dev] == kTurnSlots) return nullptr;
+    slot = g_turn_nstreams[dev]++;
+    g_turn_streams[dev][slot] = s;
+  }
+  return g_turn_base[dev] + (size_t)slot * kTurnTiles * 4;
+}
+
 int g_prefill_force_bn = 0;  // diagnostics: 0 = automatic, else the token-tile width to use
 int g_prefill_stage_raw = 1;    // diagnostics: 0 = dequant threads read global memory directly
-int g_prefill_force_split = 0;  // diagnostics: 0 = automatic, 1 = never split along K, 2 = split where allowed
+int g_prefill_force_split = 0;  // diagnostics: 0 = automatic, 1 = never split along K, 2 = two splits where allowed, 3 = four
 
 template <int TYPE, int BN, bool STAGED>
 int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows, int n_out,
@@ -1264,7 +1356,12 @@ int launch(const void *d_w, const void *d_x, void *d_y, int out_type, int m_rows
   const int nks = k_in / kBK;
   p.splits = splits;
   p.ks_per_split = splits > 1 ? ((nks + splits - 1) / splits + 3) / 4 * 4 : nks;  // whole superblocks
-  if (splits > 1) {
+  p.turns = nullptr;
+  if (splits == 4) {  // the caller has checked that the tiles fit the region and the SMs
+    p.turns = turn_region(s);
+    if (!p.turns) return COGNI_QMM_ERR_LIMIT;
+  }
+  if (splits == 2) {  // (four ordered splits store their first part)
     cudaError_t e = cudaMemsetAsync(d_y, 0, (size_t)m_rows * n_out * sizeof(float), s);
     if (e != cudaSuccess) return (int)e;
   }
@@ -1321,6 +1418,7 @@ int launch_pair(const void *d_w, const void *d_x, void *d_y, int out_type, int m
   p.row_bytes = row_bytes;
   p.splits = 1;
   p.ks_per_split = k_in / kBK;
+  p.turns = nullptr;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * ((n_out + 2 * kBM - 1) / (2 * kBM)), (m_rows + kPairBN - 1) / kPairBN, 1);
   cfg.blockDim = dim3(kPairThreads);
@@ -1376,9 +1474,21 @@ int launch_typed(const void *d_w, const void *d_x, void *d_y, int out_type, int 
   for (int i = 0; i < 3; i++) {
     if (g_prefill_force_bn && g_prefill_force_bn != widths[i]) continue;
     for (int sp = 1; sp <= (may_split ? 2 : 1); sp++) {
-      if (g_prefill_force_split == 2 && may_split && sp != 2) continue;
+      if (g_prefill_force_split >= 2 && may_split && sp != 2) continue;
       const double c = cost(widths[i], rels[i], sp);
       if (c <= best) { best = c; bn = widths[i]; splits = sp; }
+    }
+  }
+  // Four splits in a fixed order of addition (see wait_turn): 512-token tiles only (the groups of
+  // the epilogue), all CTAs resident at once, a quarter of K of at least 16 k-steps each; costs
+  // the two-split price plus four rounds of turn-taking (about 3 us).
+  {
+    const long long tiles4 = row_tiles * ((m_rows + 511) / 512);
+    const bool can4 = may_split && k_in / kBK >= 64 && tiles4 * 4 <= sms && tiles4 <= kTurnTiles &&
+                      (!g_prefill_force_bn || g_prefill_force_bn == 512);
+    if (can4 && g_prefill_force_split != 2) {
+      const double c4 = rel512 * tile_us / 4 + split_us + 3.0;
+      if (c4 < best || g_prefill_force_split == 3) { best = c4; bn = 512; splits = 4; }
     }
   }
   // Rows that are multiples of 16 bytes (always for Q4_K / Q5_K; Q6_K: in_dim a multiple of 2048)
@@ -1428,7 +1538,12 @@ unsigned gemm_prefill_timeouts() {
 
 int gemm_prefill_reset_timeouts() {
   const unsigned zero = 0;
-  return (int)cudaMemcpyToSymbol(g_pipe_wait_timeouts, &zero, sizeof(zero));
+  cudaError_t e = cudaMemcpyToSymbol(g_pipe_wait_timeouts, &zero, sizeof(zero));
+  if (e != cudaSuccess) return (int)e;
+  void *turns = nullptr;  // an expired wait can leave turn counters of the ordered split non-zero
+  e = cudaGetSymbolAddress(&turns, g_prefill_turns);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaMemset(turns, 0, sizeof(unsigned) * 8 * 64 * 4);
 }
 
 }  // namespace cogni

@@ -23,6 +23,7 @@ extern "C" {
  *   52-54     prefill split along K: automatic / never / wherever it is allowed
  *   55-56     prefill raw superblocks staged by TMA (default) / read directly by the dequant threads
  *   57-58     prefill 512-token tiles of Q4_K / Q5_K on CTA pairs (default) / on single CTAs
+ *   59        prefill split along K: four ordered splits wherever allowed (52 returns to automatic)
  *   60-68     K slabs of the tiled GEMV (several CTAs share a row tile, partial sums meet in a
  *             workspace): 60 = off (default), 61-68 = 1 .. 8 slabs wherever a plan allows it
  * Returns COGNI_QMM_ERR_ARG for any other value.  (A library built with -DCOGNI_QMM_DIAG_TIMING

@@ -68,14 +68,17 @@ def test_gemm_staged_superblocks(cuda, oracle, engine, tile, qtype, m, n, k):
     """Rows that are multiples of 16 bytes (Q4_K / Q5_K always, Q6_K when in_dim is a multiple of
     2048) are fetched by TMA into shared memory and expanded from there; rows beyond out_dim are
     zero-filled boxes.  The result must equal the direct-read path bit for bit (same expansion,
-    same MMA order)."""
+    same MMA order; without a split along K, whose four-way form adds the partial tiles in an
+    order that depends on the number of dequant warps, which differs between the two paths)."""
     engine.lib.cogni_qmm_set_kernel_choice({128: 49, 256: 50, 512: 51}[tile])
+    engine.lib.cogni_qmm_set_kernel_choice(53)
     try:
         w, x, y, ref = run_case(cuda, oracle, qtype, m, n, k, seed=19)
         engine.lib.cogni_qmm_set_kernel_choice(56)
         _, _, y_direct, _ = run_case(cuda, oracle, qtype, m, n, k, seed=19)
     finally:
         engine.lib.cogni_qmm_set_kernel_choice(55)
+        engine.lib.cogni_qmm_set_kernel_choice(52)
         engine.lib.cogni_qmm_set_kernel_choice(48)
     assert not np.isnan(y).any()
     assert np.abs(y - ref).max() <= 1e-4 * np.abs(ref).max()
@@ -125,13 +128,17 @@ def test_gemm_last_row_tile_is_reproducible(cuda, engine, qtype, m, n, k):
     w = synth.make_weight(qtype, n, k, seed=23, tensor_id=qtype)
     dw = DeviceQuantWeight.upload(QuantWeight(w, qtype, n, k), cuda)
     xd = torch.from_numpy(bf16_round(synth.make_activation(m, k, seed=23))).to(cuda).bfloat16()
-    engine.lib.cogni_qmm_set_kernel_choice(56)
+    engine.lib.cogni_qmm_set_kernel_choice(53)  # whole K per CTA: staged and direct reads then agree bit for bit
     try:
-        direct = dw.gemm(xd).clone()
+        engine.lib.cogni_qmm_set_kernel_choice(56)
+        try:
+            direct = dw.gemm(xd).clone()
+        finally:
+            engine.lib.cogni_qmm_set_kernel_choice(55)
+        for _ in range(100):
+            assert torch.equal(dw.gemm(xd), direct)
     finally:
-        engine.lib.cogni_qmm_set_kernel_choice(55)
-    for _ in range(100):
-        assert torch.equal(dw.gemm(xd), direct)
+        engine.lib.cogni_qmm_set_kernel_choice(52)
     assert engine.lib.cogni_qmm_wait_timeouts() == 0
 
 
@@ -153,6 +160,37 @@ def test_gemm_split_along_k(cuda, oracle, engine, tile, qtype, m, n, k):
     assert np.abs(y - ref).max() <= 1e-4 * np.abs(ref).max()
     assert np.array_equal(y, y2), "two addends commute: the split result must be reproducible"
     assert engine.lib.cogni_qmm_wait_timeouts() == 0
+
+
+@pytest.mark.parametrize("qtype,m,n,k", [(Q6_K, 513, 128, 4096), (Q4_K, 300, 260, 4352),
+                                         (Q8_0, 530, 300, 4096), (Q5_K, 1000, 384, 8192),
+                                         (Q6_K, 512, 1024, 12288), (IQ4_NL, 77, 200, 6144)])
+def test_gemm_four_ordered_splits(cuda, oracle, engine, qtype, m, n, k):
+    """Four CTAs per tile, a quarter of K each.  Four float addends do not commute, so the kernel
+    fixes the order: the tile's columns form four groups, split z adds its part of group
+    (z + t) mod 4 at step t, and a turn counter per (tile, group) admits the steps in order.  Every
+    launch must therefore give the same bits; y is not zeroed (the first part of a group is
+    stored), so the output buffer starts as NaN here.  k = 4352 gives unequal quarters."""
+    w = synth.make_weight(qtype, n, k, seed=31, tensor_id=qtype)
+    dw = DeviceQuantWeight.upload(QuantWeight(w, qtype, n, k), cuda)
+    x = bf16_round(synth.make_activation(m, k, seed=31))
+    xd = torch.from_numpy(x).to(cuda).bfloat16()
+    lib = engine.lib
+    lib.cogni_qmm_set_kernel_choice(59)
+    try:
+        first = dw.gemm(xd).clone()
+        for _ in range(20):
+            out = torch.full((m, n), float("nan"), dtype=torch.float32, device=cuda)
+            assert torch.equal(dw.gemm(xd, out=out), first), "the order of the additions is fixed"
+    finally:
+        lib.cogni_qmm_set_kernel_choice(52)
+    rb = len(w) // n
+    wq = np.stack([bf16_round(oracle.dequantize(qtype, w[c * rb:(c + 1) * rb], k)) for c in range(n)])
+    ref = x.astype(np.float64) @ wq.astype(np.float64).T
+    y = first.cpu().numpy()
+    assert not np.isnan(y).any()
+    assert np.abs(y - ref).max() <= 1e-4 * np.abs(ref).max()
+    assert lib.cogni_qmm_wait_timeouts() == 0
 
 
 @pytest.mark.parametrize("qtype,n,k", [(Q4_K, 1024, 4096), (Q6_K, 512, 12288), (Q8_0, 512, 4096),
