@@ -1944,12 +1944,13 @@ bool make_plan_pair(int in_dim, int nb, int pair, Params &p, size_t &smem, bool 
   const size_t off_xq = off;     off = al(off + (dense || v2 ? (size_t)in_dim * 2 * nb : (size_t)(in_dim / 64) * (4 * nb) * 64));
   const size_t off_stage = off;
   const size_t stage_bytes = al((size_t)kR * C::RS);
-  // Three stages, or for the 4- and 8-row instances two that still keep 80 KB in flight (Q5_K
-  // at 8 rows: one launch over two 45 KB stages beat two column ranges, 30 against 37 us; two
-  // 27 KB Q6_K stages did not: 340 against 279 us).  `thin`: two stages of any size, for the
-  // fused top-1, which cannot use column ranges.
+  // Three stages, or for the 4- and 8-row instances two that still keep 64 KB in flight (Q5_K
+  // at 8 rows: one launch over two 45 KB stages beat two column ranges, 30 against 37 us; Q4_K
+  // 17408 x 5120 at 8 rows: two 37 KB stages 29.7 us against two column ranges 31.7 and two K
+  // slabs 45.9; two 27 KB Q6_K stages did not: 340 against 279 us).  `thin`: two stages of any
+  // size, for the fused top-1, which cannot use column ranges.
   const size_t room = kDynSmemMax > off_stage ? kDynSmemMax - off_stage : 0;
-  const bool two_ok = nb > 2 && room >= 2 * stage_bytes && (thin || 2 * stage_bytes >= 80 * 1024);
+  const bool two_ok = nb > 2 && room >= 2 * stage_bytes && (thin || 2 * stage_bytes >= 64 * 1024);
   if (room < 3 * stage_bytes && !two_ok) return false;
   int stages = (int)((kDynSmemMax - off_stage) / stage_bytes);
   if (stages > 8) stages = 8;  // 2*stages mbarriers in the first 128 bytes of shared memory
@@ -2171,8 +2172,24 @@ int run_pass(int nj, const void *const *d_w, const float *d_x, const float *cons
   // shared memory and not divisible into equal slabs) one launch per column range.
   SlabRegion region{nullptr, nullptr};
   const bool have_ws = slab_region(s, region);
-  const int nslabs = choose_slabs<TYPE>(in_dim, nbk, tiles, thin, have_ws);
-  const int nsplit = nslabs > 0 ? 1 : column_splits<TYPE>(in_dim, nbk, thin);
+  int nslabs = choose_slabs<TYPE>(in_dim, nbk, tiles, thin, have_ws);
+  int nsplit = nslabs > 0 && (nslabs == 1 || top1 || ex || g_imma_force_slabs > 0) ? 1
+                                                                                 : column_splits<TYPE>(in_dim, nbk, thin);
+  if (nslabs > 1 && nsplit > 1) {
+    // Slabs or one launch per column range?  Every tile part of a slab launch pays a workspace
+    // round trip, a fence and a ticket in the folding warp's path (about 1.4 us); a column range
+    // pays a launch ramp and its activation pass.  With many tiles per SM the ranges are several
+    // full waves each and win, with few the slabs do.  Measured at batch 8, ranges / slabs in us:
+    // Q4_K 17408 x 5120 (1088 tiles) 31.7 / 45.9, Q4_K 12288 x 7168 (768) 30.9 / 57.7, Q4_K
+    // 12288 x 8192 37.4 / 51.1; Q6_K 4096 x 12288 (256) 41.4 / 30.5, Q6_K 5120 x 17408 (320)
+    // 84.6 / 54.8, Q4_K 4096 x 16384 (256) 42.8 / 33.7.  (On 256 tiles and two ranges the
+    // picture is mixed: Q5_K / Q8_0 4096 x 8192 21.6 / 25.2, Q6_K 4096 x 12288 at batch 4
+    // 26.2 / 21.3.)
+    if (tiles >= 3 * sm_count()) nslabs = 0;
+    else nsplit = 1;
+  } else if (nslabs > 0) {
+    nsplit = 1;
+  }
   if (nsplit == 0 || (top1 && nsplit > 1)) return COGNI_QMM_ERR_LIMIT;
   if (ex && nsplit > 1) return COGNI_QMM_ERR_LIMIT;  // the fused exchange needs the rows complete in one launch
   const int per = (nblk + nsplit - 1) / nsplit;
