@@ -50,7 +50,7 @@ sys.path.insert(0, str(ROOT))
 
 HIDDEN, FFN = 4096, 12288
 Q8_0, Q4_K, Q5_K, Q6_K = 8, 12, 13, 14
-TYPE_NAME = {8: "Q8_0", 12: "Q4_K", 13: "Q5_K", 14: "Q6_K"}
+TYPE_NAME = {8: "Q8_0", 12: "Q4_K", 13: "Q5_K", 14: "Q6_K", 20: "IQ4_NL"}
 Q4K_BYTES = FFN * (HIDDEN // 256) * 144      # 28,311,552
 Q6K_BYTES = HIDDEN * (FFN // 256) * 210      # 41,287,680
 DTYPE = "f32 io / bfp15 x, s32 group sums, f32 accumulate"

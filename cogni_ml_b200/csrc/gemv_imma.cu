@@ -57,9 +57,14 @@ namespace {
 
 // Consumer warps per CTA.  Every warp holds the stage bytes of its item until it is done, so
 // more warps leave fewer stages for the copies in flight; 16 (20 for single-superblock items of
-// the 210-byte Q6_K blocks) measured best.
+// the 210-byte Q6_K blocks) measured best for batches 1-2.  The 4- and 8-row instances of Q4_K,
+// Q8_0 and IQ4_NL are bound by their consumer warps' latencies and take 20 (Q4_K 65536 x 4096 at
+// batch 8: 55.4 -> 51.5 us, 4096 x 16384: 32.6 -> 27.2; 24 warps: 53.2); Q5_K and Q6_K, whose
+// warps hold more registers and whose slab launches need the stages, stay at 16 (Q6_K 4096 x 12288
+// at batch 8 with 20: 29.3 -> 31.4 us).
 __host__ __device__ constexpr int consumer_warps(int type, int pair, int nb = 1) {
-  return type == kQ6_K && pair == 1 && nb <= 2 ? 20 : 16;
+  if (nb > 2) return type == kQ4_K || type == kQ8_0 || type == kIQ4_NL ? 20 : 16;
+  return type == kQ6_K && pair == 1 ? 20 : 16;
 }
 // tiles whose partial sums can be pending (power of 2)
 __host__ __device__ constexpr int fold_bufs(int nb) { return nb > 2 ? 2 : 4; }
