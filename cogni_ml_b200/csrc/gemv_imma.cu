@@ -57,13 +57,13 @@ namespace {
 
 // Consumer warps per CTA.  Every warp holds the stage bytes of its item until it is done, so
 // more warps leave fewer stages for the copies in flight; 16 (20 for single-superblock items of
-// the 210-byte Q6_K blocks) measured best for batches 1-2.  The 4- and 8-row instances of Q4_K,
-// Q8_0 and IQ4_NL are bound by their consumer warps' latencies and take 20 (Q4_K 65536 x 4096 at
-// batch 8: 55.4 -> 51.5 us, 4096 x 16384: 32.6 -> 27.2; 24 warps: 53.2); Q5_K and Q6_K, whose
-// warps hold more registers and whose slab launches need the stages, stay at 16 (Q6_K 4096 x 12288
-// at batch 8 with 20: 29.3 -> 31.4 us).
+// the 210-byte Q6_K blocks) measured best for batches 1-2.  The 4- and 8-row instances are bound
+// by their consumer warps' latencies and take 20 (batch 8: Q4_K 65536 x 4096 55.4 -> 51.5 us,
+// 4096 x 16384 32.6 -> 27.2, Q5_K 65536 x 4096 69.6 -> 60.5; 24 warps: Q4_K 53.2), except Q6_K,
+// whose slab launches need the stages (4096 x 12288 with 20: 29.3 -> 31.4 us, the 151936 x 5120
+// head 262 -> 278).
 __host__ __device__ constexpr int consumer_warps(int type, int pair, int nb = 1) {
-  if (nb > 2) return type == kQ4_K || type == kQ8_0 || type == kIQ4_NL ? 20 : 16;
+  if (nb > 2) return type == kQ6_K ? 16 : 20;
   return type == kQ6_K && pair == 1 ? 20 : 16;
 }
 // tiles whose partial sums can be pending (power of 2)
