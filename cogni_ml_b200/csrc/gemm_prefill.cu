@@ -943,7 +943,8 @@ __global__ void __launch_bounds__(threads_for(TYPE, STAGED, BN), 1)
               }
             }
           }
-          __threadfence();  // this split's additions are performed before the next split's turn
+          // the additions of all threads happen before the leader's release below (barrier, then a
+          // cumulative gpu-scope release), and the next split's after its leader's acquire
           asm volatile("bar.sync 2, %0;" ::"n"(kEpiThreads) : "memory");
           if (leader)
             asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(turn + g), "r"(t == 3 ? 0u : (unsigned)(t + 1))
